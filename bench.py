@@ -1,0 +1,285 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE feed-forward hot path (one JSON line on stdout).
+
+Workload at every N: the configuration the headline metric is quoted on -- one
+MoE FFN layer call, Q4_0 experts, batch-1 decode (H=2048, E=128, top-8, I=768),
+issued over `--layers` DISTINCT layer blobs per step so that every call streams
+its 22 MB of routed expert weights from HBM (48 layers x 21 MB of active weights
+is ~8x the L2). One step = one token through all the layer blobs; the metric is
+layer calls x tokens per second. Batch-1 decode does not shard: with N > 1 ranks
+run as independent replicas ("weak" scaling, no collective in the data path).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--quant q4_0|q8_0|bf16]
+    python bench.py --impl reference ...   # the CPU reference path on the host cores
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+H, I, E, K = 2048, 768, 128, 8
+QUANTS = {"q8_0": 0, "q4_0": 1, "bf16": 2}
+BLK = {0: 34, 1: 18, 2: 64}
+
+
+def algorithmic_bytes(T: int, U: int, quant: int) -> int:
+    """Compulsory traffic of one layer call: router weight, the three matrices of
+    every distinct expert hit, activations in / residual in / output out."""
+    return E * H * 4 + U * 3 * (I * H // 32) * BLK[quant] + 3 * T * H * 4
+
+
+def gate_up_bytes(T: int, U: int, quant: int) -> int:
+    """Compulsory traffic of the gate/up + SwiGLU kernel alone."""
+    return U * 2 * (I * H // 32) * BLK[quant] + T * H * 4 + T * K * I * 4
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback (no MEASURED_PEAKS.json)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons during the timed region (read-only)."""
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons}
+
+
+def cpu_reference_leg(quant: int, T: int, budget_s: float, blob_np=None):
+    """Times the CPU reference path (oracle restatement, all host threads) on a
+    bounded sample of the same workload: single layer calls on one layer blob."""
+    import numpy as np
+    from oracle import oracle
+    from lumen_b200.synth import LayerLayout, make_layer_blob_numpy
+    lay = LayerLayout(H, I, E, quant)
+    if blob_np is None:
+        # 128 experts of seeded N(0,0.02) weights quantised by the oracle's quantiser
+        blob_np = make_layer_blob_numpy(lay, 0, oracle.quantize)
+    meta = lay.meta()
+    threads = oracle.hardware_threads()
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((T, H)).astype(np.float32)
+    calls, t0 = 0, time.perf_counter()
+    while True:
+        oracle.moe_layer(blob_np, 0, meta.expert_gate_offs, meta.expert_up_offs, meta.expert_down_offs, quant, H, I, E,
+                         K, x, x, threads=threads)
+        calls += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or calls >= 2000:
+            break
+    return {"value": calls * T / dt, "unit": "layer_tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{calls} single-layer calls of {T} token(s) on one layer blob, {dt:.1f} s"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    quant = QUANTS[args.quant]
+    from oracle import oracle
+    from lumen_b200.synth import LayerLayout, make_layer_blob_numpy
+    blob = make_layer_blob_numpy(LayerLayout(H, I, E, quant), 0, oracle.quantize)
+    per_step = max(0.5, min(20.0, 60.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_reference_leg(quant, args.tokens, 0.2, blob)
+    t0 = time.perf_counter()
+    vals = [cpu_reference_leg(quant, args.tokens, per_step, blob) for _ in range(args.steps)]
+    dt = time.perf_counter() - t0
+    v = statistics.mean(r["value"] for r in vals)
+    base = vals[-1]
+    base["value"] = v
+    base["sample"] = f"{args.steps} steps, each " + base["sample"]
+    line = {"impl": "reference", "metric": "moe_layer_decode_tokens_per_s", "value": v, "unit": "layer_tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000 * dt / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args), "cpu_baseline": base,
+            "e2e": {"value": v, "unit": "layer_tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args):
+    return {"workload": f"moe_ffn_decode_{args.quant}_T{args.tokens}", "hidden": H, "experts": E, "top_k": K,
+            "inter": I, "tokens_per_call": args.tokens, "distinct_layer_blobs": args.layers,
+            "l2_policy": "inputs larger than L2: every call reads a different layer's experts",
+            "parallelism": "replicas only (batch-1 decode does not shard)"}
+
+
+def run_gpu(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from lumen_b200 import build, moe, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    build.build()
+    quant, T, L = QUANTS[args.quant], args.tokens, args.layers
+    lay = synth.LayerLayout(H, I, E, quant)
+    scratch = moe.allocate_moe_scratch(H, I, E, K, 16, device=local)
+    layers, blob0 = [], None
+    for l in range(L):
+        blob = synth.make_layer_blob(lay, 1000 * rank + l, device=f"cuda:{local}")
+        layers.append(scratch.prepare_layer(blob, lay.meta()))
+        if l == 0 and rank == 0:
+            blob0 = blob.cpu().numpy()
+    g = torch.Generator(device=f"cuda:{local}")
+    g.manual_seed(1)
+    x = torch.randn((T, H), generator=g, device=f"cuda:{local}")
+    outs = torch.empty((L, T, H), device=f"cuda:{local}")
+    host_x = torch.randn((T, H)).pin_memory()
+    host_out = torch.empty((T, H)).pin_memory()
+
+    def step():
+        for l in range(L):
+            scratch.decode(layers[l], x, x, outs[l])
+
+    def step_e2e():
+        x.copy_(host_x, non_blocking=True)
+        step()
+        host_out.copy_(outs[L - 1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        ev0.record()
+        for _ in range(n):
+            fn()
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([ms], device=f"cuda:{local}")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    # distinct experts per call (for the algorithmic byte count)
+    U = []
+    for l in range(L):
+        scratch.decode(layers[l], x, x, outs[l])
+        U.append(len(np.unique(scratch.get_routing(T)["ids"])))
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    moe.launch_count(reset=True)
+    ms = timed(step, args.steps)
+    launches = moe.launch_count(reset=True)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = timed(step_e2e, args.steps)
+    units = args.steps * L * T * world
+    value = units / (ms / 1e3)
+    e2e = units / (ms_e2e / 1e3)
+
+    line = None
+    if rank == 0:
+        peak, peak_src = peaks()
+        # dominant kernel (gate/up + SwiGLU) alone, one launch per layer blob, CUDA events on the launch stream
+        for l in range(L):
+            scratch.debug_decode_phase(layers[l], 1)
+        torch.cuda.synchronize()
+        reps = 5
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(reps):
+            for l in range(L):
+                scratch.debug_decode_phase(layers[l], 1)
+        ev1.record()
+        torch.cuda.synchronize()
+        k_ms = ev0.elapsed_time(ev1) / (reps * L)
+        # routing tables in the context belong to the last layer called: same count of experts for every launch
+        k_bytes = gate_up_bytes(T, U[-1], quant)
+        achieved = k_bytes / (k_ms / 1e3) / 1e9
+        layer_bytes = sum(algorithmic_bytes(T, u, quant) for u in U) / L
+        layer_gbs = layer_bytes / ((ms / 1e3) / (args.steps * L)) / 1e9
+        cpu = cpu_reference_leg(quant, T, 12.0, blob0)
+        line = {"metric": "moe_layer_decode_tokens_per_s", "value": value, "unit": "layer_tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "config": workload_config(args),
+                "e2e": {"value": e2e, "unit": "layer_tokens/s", "h2d_bytes_per_step": T * H * 4,
+                        "d2h_bytes_per_step": T * H * 4},
+                "gpu_launches": int(launches),
+                "roofline": {"bound": "hbm", "kernel": "gate_up_kernel", "achieved": achieved, "peak": peak,
+                             "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                             "algorithmic_bytes_per_launch": k_bytes, "us_per_launch": k_ms * 1e3},
+                "layer_roofline": {"algorithmic_bytes_per_call": layer_bytes, "us_per_call": ms * 1e3 / (args.steps * L),
+                                   "achieved_gbs": layer_gbs, "frac_of_measured_peak": layer_gbs / peak,
+                                   "frac_of_8tbs": layer_gbs / 8000.0},
+                "cpu_baseline": cpu, "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--tokens", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--quant", default="q4_0", choices=sorted(QUANTS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,185 @@
+/*
+ * lumen_moe.h -- C ABI of the B200 (sm_100a) MoE feed-forward operator.
+ *
+ * This is the boundary a lumen-runtime CUDA backend binds instead of launching
+ * its NVRTC MoE kernels. Every entry point names the reference function it
+ * replaces (paths relative to the reference project's root). All pointers named
+ * d_* are device pointers; `stream` is a cudaStream_t passed as void*. Calls are
+ * asynchronous on that stream and never synchronise it, except where stated.
+ * No exceptions cross this boundary; every function returns a status code and
+ * lumen_moe_last_error() gives the text of the last failure on the calling thread.
+ *
+ * There is no CPU fallback: if the CUDA library cannot run a request it returns
+ * an error.
+ */
+#ifndef LUMEN_MOE_H
+#define LUMEN_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define LUMEN_MOE_API __attribute__((visibility("default")))
+#else
+#define LUMEN_MOE_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Result<(), RuntimeError> of crates/lumen-runtime/src/error.rs:6-31:
+ * INVALID_ARG / CUDA_ERROR ~ RuntimeError::Compute, UNSUPPORTED ~ RuntimeError::Unsupported. */
+typedef enum {
+    LUMEN_MOE_OK = 0,
+    LUMEN_MOE_INVALID_ARG = 1,
+    LUMEN_MOE_UNSUPPORTED = 2,
+    LUMEN_MOE_CUDA_ERROR = 3,
+    LUMEN_MOE_TIMEOUT = 4,
+    LUMEN_MOE_NCCL_ERROR = 5
+} lumen_moe_status_t;
+
+/* lumen_format::quantization::QuantScheme tags accepted on this path
+ * (cuda/moe.rs:1185-1191: gate and down must share one of these). */
+typedef enum { LUMEN_MOE_Q8_0 = 0, LUMEN_MOE_Q4_0 = 1, LUMEN_MOE_BF16 = 2 } lumen_moe_quant_t;
+
+/* SOFTMAX_RENORM: cuda/moe.rs:6464-6504 (CPU reference) and cuda/shaders/moe_router.cu:85-128.
+ * SIGMOID_RENORM: cuda/shaders/topk_moe_fused.cu:118-129 (the CUDA backend's default). */
+typedef enum { LUMEN_MOE_SOFTMAX_RENORM = 0, LUMEN_MOE_SIGMOID_RENORM = 1 } lumen_moe_gating_t;
+
+/* Activation element types of lumen_moe_prefill. */
+typedef enum { LUMEN_MOE_ACT_F32 = 0, LUMEN_MOE_ACT_BF16 = 1 } lumen_moe_act_t;
+
+typedef struct {
+    int32_t hidden_dim;   /* H, multiple of 32 */
+    int32_t inter_dim;    /* I, multiple of 32 */
+    int32_t num_experts;  /* E <= 256 (cuda/shaders/moe_router.cu:33) */
+    int32_t top_k;        /* K <= 16  (cuda/shaders/moe_router.cu:34) */
+    int32_t max_tokens;   /* initial prefill capacity; grows on demand */
+    int32_t gating_mode;  /* lumen_moe_gating_t */
+    int32_t device;       /* CUDA ordinal */
+    int32_t reserved;
+} lumen_moe_config;
+
+typedef struct lumen_moe_ctx lumen_moe_ctx;     /* ~ CudaMoeScratch, cuda/moe.rs:101-170 */
+typedef struct lumen_moe_layer lumen_moe_layer; /* ~ CudaMoeMeta + CudaMoeBatchedOffsets + CudaMoeRepacked */
+
+/* Replaces allocate_moe_scratch (cuda/moe.rs:968). Synchronous (allocates). */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_create(const lumen_moe_config* cfg, lumen_moe_ctx** out_ctx);
+LUMEN_MOE_API void lumen_moe_destroy(lumen_moe_ctx* ctx);
+
+/* Replaces ensure_prefill_grouped (cuda/moe.rs:1015): grow-only capacity for
+ * `tokens` tokens. Synchronous when it has to reallocate. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_ensure_prefill(lumen_moe_ctx* ctx, int32_t tokens);
+
+/* Replaces build_moe_meta (cuda/moe.rs:223) + build_batched_offsets (:272) +
+ * build_repacked_down (:337). d_layer_blob is the layer's weight blob as uploaded
+ * by the backend (router f32 [E,H] at router_off; expert e: gate [I,H] at
+ * gate_offs[e], up [I,H] at up_offs[e], down [H,I] at down_offs[e]; raw GGML
+ * Q8_0 / Q4_0 blocks or BF16, rows contiguous along the input dimension). The
+ * offset arrays are HOST arrays of num_experts entries. The blob is left
+ * untouched and must outlive the layer (the router weight is read in place); the
+ * expert weights are repacked once into aligned planes owned by the layer.
+ * Work is enqueued on `stream`; the function synchronises it before returning. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_layer_prepare(lumen_moe_ctx* ctx, const void* d_layer_blob,
+                                           size_t blob_bytes, uint64_t router_off,
+                                           const uint64_t* gate_offs, const uint64_t* up_offs,
+                                           const uint64_t* down_offs, int32_t quant, void* stream,
+                                           lumen_moe_layer** out_layer);
+LUMEN_MOE_API void lumen_moe_layer_destroy(lumen_moe_layer* layer);
+
+/* Replaces encode_moe_ffn_decode (cuda/moe.rs:1119): out[t] = residual[t] +
+ * sum_k w[t,k] * Down_e(silu(Gate_e x[t]) * Up_e x[t]), f32 [T,H] in and out,
+ * 1 <= T <= 16. d_out may alias d_residual (the backend passes the same buffer,
+ * cuda/backend_impl.rs:3570-3573) but not d_normed. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_decode(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                    const float* d_normed, const float* d_residual, float* d_out,
+                                    int32_t tokens, void* stream);
+
+/* Replaces encode_moe_ffn_decode_fused_norm (cuda/moe.rs:3184): normed =
+ * rmsnorm(x; gamma, eps) (cuda/shaders/norm.cu:28-76), then as lumen_moe_decode
+ * with residual = x. d_normed_out receives normed [T,H] (may be NULL). */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_decode_fused_norm(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                               const float* d_x, const float* d_gamma,
+                                               float* d_normed_out, float* d_out, float eps,
+                                               int32_t tokens, void* stream);
+
+/* Replaces encode_moe_ffn_prefill_grouped (cuda/moe.rs:1900) without its host
+ * round trip: routing, the stable counting sort (:2115-2147), the grouped expert
+ * products and the scatter-accumulate all run on the device. d_normed is
+ * [T,H] of act_dtype; d_residual and d_out are f32 [T,H]. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_prefill(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                     const void* d_normed, const float* d_residual, float* d_out,
+                                     int32_t tokens, int32_t act_dtype, void* stream);
+
+/* Router only (moe_router_logits_v2 + finalize, cuda/shaders/moe_batched.cu:708,755;
+ * batched: cuda/shaders/moe_grouped.cu:79 + topk_moe_fused.cu:172-296).
+ * d_ids u32 [T,K] in selection (descending weight) order, row stride K;
+ * d_weights f32 [T,K], each row sums to 1. d_logits_out [T,E] may be NULL. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_route_only(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                        const float* d_normed, int32_t tokens, uint32_t* d_ids,
+                                        float* d_weights, float* d_logits_out, void* stream);
+
+/* Gating + top-k + renormalisation on caller-supplied logits f32 [T,E]: the
+ * arithmetic of cpu_router_softmax phases 2-3 (cuda/moe.rs:6464-6504), bit for
+ * bit (ids and weights) for finite logits. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_topk_from_logits(lumen_moe_ctx* ctx, const float* d_logits,
+                                              int32_t tokens, uint32_t* d_ids, float* d_weights,
+                                              void* stream);
+
+/* Parity hook: while set (non-NULL), lumen_moe_decode / _prefill take the router
+ * logits f32 [T,E] from this device buffer instead of computing them, so that
+ * both sides of a parity test route on identical logits. NULL switches it off. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_set_logits_override(lumen_moe_ctx* ctx, const float* d_logits);
+
+/* Readback of the routing tables of the most recent call (debug / parity; the
+ * counterpart of the MOE_EXPERT_DUMP lines, cuda/moe.rs:1484-1492). Host output
+ * arrays, any may be NULL: ids [T,K], weights [T,K], dst_to_col [T*K],
+ * col_src_tok [T*K], expert_bounds [E+1] (cuda/moe.rs:2115-2147). Synchronises `stream`. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_get_routing(lumen_moe_ctx* ctx, int32_t tokens, uint32_t* ids,
+                                         float* weights, int32_t* dst_to_col, int32_t* col_src_tok,
+                                         int32_t* expert_bounds, void* stream);
+
+/* Device restatement of quantize_f32_to_q4_0 / _q8_0
+ * (crates/lumen-convert/src/dequant.rs:791-906) and of round-to-nearest-even BF16,
+ * used to synthesise weights in HBM. n_elements multiple of 32. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_quantize(const float* d_src, int64_t n_elements, int32_t quant,
+                                      void* d_dst, void* stream);
+
+/* rmsnorm of cuda/shaders/norm.cu:28-76 over [T,H] rows (FFN norm before the MoE call). */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_rmsnorm(const float* d_x, const float* d_gamma, float* d_out,
+                                     int32_t tokens, int32_t hidden_dim, float eps, void* stream);
+
+/* Stack of n_layers MoE FFN layers with identity mixers:
+ * x <- x + MoE_l(rmsnorm(x; gamma_l, eps)), in place on d_x f32 [T,H], T <= 16.
+ * The decode loop of cuda/backend_impl.rs:2184 (compute_layer_gpu) restricted to
+ * its FFN half (:3528-3580). */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_stack_decode(lumen_moe_ctx* ctx, const lumen_moe_layer* const* layers,
+                                          const float* const* d_gammas, int32_t n_layers,
+                                          float* d_x, float eps, int32_t tokens, void* stream);
+
+/* Device check of the library's exp used by the router (see exact_expf.h). */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_debug_expf(const float* d_in, float* d_out, int64_t n, void* stream);
+
+/* Instrumentation: re-launch ONE kernel of the most recent lumen_moe_decode call
+ * on `layer` with the routing tables that call left in the context (phase 0 =
+ * router, 1 = gate/up + SwiGLU, 2 = down + combine), so that a benchmark can time
+ * a single kernel with CUDA events. No counterpart in the reference (its
+ * profiler brackets whole stages, cuda/profiler.rs:1-80). */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_debug_decode_phase(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                              int32_t phase, void* stream);
+
+/* Bytes of device memory held by a prepared layer (repacked planes + tables). */
+LUMEN_MOE_API size_t lumen_moe_layer_bytes(const lumen_moe_layer* layer);
+
+/* Number of kernel launches issued by this library since the counter was last
+ * read with reset != 0 (benchmark bookkeeping). */
+LUMEN_MOE_API int64_t lumen_moe_launch_count(int32_t reset);
+
+LUMEN_MOE_API const char* lumen_moe_last_error(void);
+LUMEN_MOE_API const char* lumen_moe_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LUMEN_MOE_H */

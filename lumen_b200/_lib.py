@@ -1,0 +1,81 @@
+"""Loader of the CUDA library. There is no fallback: if the shared object is
+missing or cannot be loaded, importing an operator raises."""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "liblumen_moe_b200.so"
+
+OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, TIMEOUT, NCCL_ERROR = range(6)
+Q8_0, Q4_0, BF16 = 0, 1, 2
+SOFTMAX_RENORM, SIGMOID_RENORM = 0, 1
+ACT_F32, ACT_BF16 = 0, 1
+
+
+class MoeConfig(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in
+                ("hidden_dim", "inter_dim", "num_experts", "top_k", "max_tokens", "gating_mode", "device", "reserved")]
+
+
+class LumenMoeError(RuntimeError):
+    """Mirror of RuntimeError::Compute / ::Unsupported (crates/lumen-runtime/src/error.rs:6-31)."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[{['OK','INVALID_ARG','UNSUPPORTED','CUDA_ERROR','TIMEOUT','NCCL_ERROR'][code]}] {msg}")
+        self.code = code
+
+
+_lib = None
+vp, i32, i64, u64, f32, sz = (ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_uint64, ctypes.c_float,
+                              ctypes.c_size_t)
+
+# name -> argtypes; every entry point include/lumen_moe.h declares
+SIGNATURES = {
+    "lumen_moe_create": [ctypes.POINTER(MoeConfig), ctypes.POINTER(vp)],
+    "lumen_moe_destroy": [vp],
+    "lumen_moe_ensure_prefill": [vp, i32],
+    "lumen_moe_layer_prepare": [vp, vp, sz, u64, vp, vp, vp, i32, vp, ctypes.POINTER(vp)],
+    "lumen_moe_layer_destroy": [vp],
+    "lumen_moe_decode": [vp, vp, vp, vp, vp, i32, vp],
+    "lumen_moe_decode_fused_norm": [vp, vp, vp, vp, vp, vp, f32, i32, vp],
+    "lumen_moe_prefill": [vp, vp, vp, vp, vp, i32, i32, vp],
+    "lumen_moe_route_only": [vp, vp, vp, i32, vp, vp, vp, vp],
+    "lumen_moe_topk_from_logits": [vp, vp, i32, vp, vp, vp],
+    "lumen_moe_set_logits_override": [vp, vp],
+    "lumen_moe_get_routing": [vp, i32, vp, vp, vp, vp, vp, vp],
+    "lumen_moe_quantize": [vp, i64, i32, vp, vp],
+    "lumen_moe_rmsnorm": [vp, vp, vp, i32, i32, f32, vp],
+    "lumen_moe_stack_decode": [vp, vp, vp, i32, vp, f32, i32, vp],
+    "lumen_moe_debug_expf": [vp, vp, i64, vp],
+    "lumen_moe_debug_decode_phase": [vp, vp, i32, vp],
+    "lumen_moe_layer_bytes": [vp],
+    "lumen_moe_launch_count": [i32],
+    "lumen_moe_last_error": [],
+    "lumen_moe_version": [],
+}
+_RESTYPE = {"lumen_moe_destroy": None, "lumen_moe_layer_destroy": None, "lumen_moe_layer_bytes": sz,
+            "lumen_moe_launch_count": i64, "lumen_moe_last_error": ctypes.c_char_p,
+            "lumen_moe_version": ctypes.c_char_p}
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m lumen_b200.build` (nvcc, sm_100a). "
+                "lumen_b200 has no CPU or PyTorch fallback.")
+        l = ctypes.CDLL(str(LIB_PATH))
+        for name, args in SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.argtypes = args
+            fn.restype = _RESTYPE.get(name, i32)
+        _lib = l
+    return _lib
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise LumenMoeError(code, lib().lumen_moe_last_error().decode())

@@ -1,0 +1,244 @@
+// extern "C" boundary (include/lumen_moe.h): argument checks, handle
+// management and error text; all work is delegated to the host layer.
+#include "../../include/lumen_moe.h"
+#include "host_moe.hpp"
+#include <new>
+
+namespace lumen {
+long long read_launch_count(bool reset);
+}
+
+struct lumen_moe_ctx {
+    lumen::CudaMoeScratch scratch;
+};
+struct lumen_moe_layer {
+    lumen::MoeLayer layer;
+};
+
+static thread_local std::string g_last_error;
+
+static lumen_moe_status_t fail(int code, const std::string& msg) {
+    g_last_error = msg;
+    return static_cast<lumen_moe_status_t>(code);
+}
+static lumen_moe_status_t done(const lumen::Status& s) {
+    if (s.ok()) return LUMEN_MOE_OK;
+    return fail(s.code, s.msg);
+}
+
+extern "C" {
+
+const char* lumen_moe_last_error(void) { return g_last_error.c_str(); }
+const char* lumen_moe_version(void) { return "lumen-moe-b200 0.1 (sm_100a)"; }
+
+lumen_moe_status_t lumen_moe_create(const lumen_moe_config* cfg, lumen_moe_ctx** out_ctx) {
+    if (!cfg || !out_ctx) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+        return fail(LUMEN_MOE_CUDA_ERROR, "no CUDA device available; this library has no CPU path");
+    if (cfg->device < 0 || cfg->device >= ndev) return fail(LUMEN_MOE_INVALID_ARG, "device ordinal out of range");
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, cfg->device) != cudaSuccess)
+        return fail(LUMEN_MOE_CUDA_ERROR, "cudaGetDeviceProperties failed");
+    if (prop.major != 10)
+        return fail(LUMEN_MOE_UNSUPPORTED, "this build contains sm_100a code only (Blackwell B200 required)");
+    lumen_moe_ctx* ctx = new (std::nothrow) lumen_moe_ctx();
+    if (!ctx) return fail(LUMEN_MOE_CUDA_ERROR, "out of host memory");
+    lumen::Status s = lumen::allocate_moe_scratch(cfg->device, cfg->hidden_dim, cfg->inter_dim, cfg->num_experts,
+                                                  cfg->top_k, cfg->gating_mode, cfg->max_tokens, &ctx->scratch);
+    if (!s.ok()) {
+        delete ctx;
+        return done(s);
+    }
+    *out_ctx = ctx;
+    return LUMEN_MOE_OK;
+}
+
+void lumen_moe_destroy(lumen_moe_ctx* ctx) {
+    if (!ctx) return;
+    lumen::free_moe_scratch(&ctx->scratch);
+    delete ctx;
+}
+
+lumen_moe_status_t lumen_moe_ensure_prefill(lumen_moe_ctx* ctx, int32_t tokens) {
+    if (!ctx) return fail(LUMEN_MOE_INVALID_ARG, "null context");
+    return done(lumen::ensure_prefill_grouped(&ctx->scratch, tokens));
+}
+
+lumen_moe_status_t lumen_moe_layer_prepare(lumen_moe_ctx* ctx, const void* d_layer_blob, size_t blob_bytes,
+                                           uint64_t router_off, const uint64_t* gate_offs, const uint64_t* up_offs,
+                                           const uint64_t* down_offs, int32_t quant, void* stream,
+                                           lumen_moe_layer** out_layer) {
+    if (!ctx || !d_layer_blob || !gate_offs || !up_offs || !down_offs || !out_layer)
+        return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    if (quant < 0 || quant > 2) return fail(LUMEN_MOE_UNSUPPORTED, "unsupported quant scheme");
+    const lumen::CudaMoeScratch& sc = ctx->scratch;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    lumen::SubtensorOffsets sub;
+    sub.has_router = true;
+    sub.router_weight.offset = router_off;
+    sub.router_weight.length = (uint64_t)sc.E * sc.H * 4;
+    sub.experts.resize(sc.E);
+    for (int e = 0; e < sc.E; ++e) {
+        sub.experts[e].gate.offset = gate_offs[e];
+        sub.experts[e].up.offset = up_offs[e];
+        sub.experts[e].down.offset = down_offs[e];
+        sub.experts[e].gate.quant = sub.experts[e].up.quant = sub.experts[e].down.quant = quant;
+    }
+    lumen_moe_layer* l = new (std::nothrow) lumen_moe_layer();
+    if (!l) return fail(LUMEN_MOE_CUDA_ERROR, "out of host memory");
+    bool is_moe = false;
+    lumen::Status s = lumen::build_moe_meta(sub, &l->layer.meta, &is_moe);
+    if (s.ok() && !is_moe) s = lumen::Status::Err(LUMEN_MOE_INVALID_ARG, "layer has no experts");
+    if (s.ok()) s = lumen::build_batched_offsets(l->layer.meta, st, &l->layer.offsets);
+    if (s.ok())
+        s = lumen::build_repacked(sc, d_layer_blob, blob_bytes, l->layer.meta, l->layer.offsets, sc.H, sc.I, sc.E, st,
+                                  &l->layer.repacked, &l->layer.dev);
+    if (s.ok()) {
+        cudaError_t e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) s = lumen::Status::Err(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    }
+    if (!s.ok()) {
+        lumen::free_moe_layer(&l->layer);
+        delete l;
+        return done(s);
+    }
+    l->layer.blob_bytes = blob_bytes;
+    *out_layer = l;
+    return LUMEN_MOE_OK;
+}
+
+void lumen_moe_layer_destroy(lumen_moe_layer* layer) {
+    if (!layer) return;
+    lumen::free_moe_layer(&layer->layer);
+    delete layer;
+}
+
+size_t lumen_moe_layer_bytes(const lumen_moe_layer* layer) {
+    if (!layer) return 0;
+    return layer->layer.repacked.q_bytes + layer->layer.repacked.s_bytes + 5 * sizeof(uint64_t) * layer->layer.dev.E;
+}
+
+lumen_moe_status_t lumen_moe_decode(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const float* d_normed,
+                                    const float* d_residual, float* d_out, int32_t tokens, void* stream) {
+    if (!ctx || !layer) return fail(LUMEN_MOE_INVALID_ARG, "null handle");
+    return done(lumen::encode_moe_ffn_decode(&ctx->scratch, layer->layer, d_normed, d_residual, d_out, tokens,
+                                             static_cast<cudaStream_t>(stream)));
+}
+
+lumen_moe_status_t lumen_moe_decode_fused_norm(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const float* d_x,
+                                               const float* d_gamma, float* d_normed_out, float* d_out, float eps,
+                                               int32_t tokens, void* stream) {
+    if (!ctx || !layer) return fail(LUMEN_MOE_INVALID_ARG, "null handle");
+    return done(lumen::encode_moe_ffn_decode_fused_norm(&ctx->scratch, layer->layer, d_x, d_gamma, d_normed_out, d_out,
+                                                        eps, tokens, static_cast<cudaStream_t>(stream)));
+}
+
+lumen_moe_status_t lumen_moe_prefill(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const void* d_normed,
+                                     const float* d_residual, float* d_out, int32_t tokens, int32_t act_dtype,
+                                     void* stream) {
+    if (!ctx || !layer) return fail(LUMEN_MOE_INVALID_ARG, "null handle");
+    return done(lumen::encode_moe_ffn_prefill_grouped(&ctx->scratch, layer->layer, d_normed, act_dtype, d_residual,
+                                                      d_out, tokens, static_cast<cudaStream_t>(stream)));
+}
+
+lumen_moe_status_t lumen_moe_route_only(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const float* d_normed,
+                                        int32_t tokens, uint32_t* d_ids, float* d_weights, float* d_logits_out,
+                                        void* stream) {
+    if (!ctx || !layer || !d_normed) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    return done(lumen::encode_route_only(&ctx->scratch, &layer->layer, d_normed, nullptr, tokens, d_ids, d_weights,
+                                         d_logits_out, static_cast<cudaStream_t>(stream)));
+}
+
+lumen_moe_status_t lumen_moe_topk_from_logits(lumen_moe_ctx* ctx, const float* d_logits, int32_t tokens,
+                                              uint32_t* d_ids, float* d_weights, void* stream) {
+    if (!ctx || !d_logits) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    return done(lumen::encode_route_only(&ctx->scratch, nullptr, nullptr, d_logits, tokens, d_ids, d_weights, nullptr,
+                                         static_cast<cudaStream_t>(stream)));
+}
+
+lumen_moe_status_t lumen_moe_set_logits_override(lumen_moe_ctx* ctx, const float* d_logits) {
+    if (!ctx) return fail(LUMEN_MOE_INVALID_ARG, "null context");
+    ctx->scratch.logits_override = d_logits;
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_get_routing(lumen_moe_ctx* ctx, int32_t tokens, uint32_t* ids, float* weights,
+                                         int32_t* dst_to_col, int32_t* col_src_tok, int32_t* expert_bounds,
+                                         void* stream) {
+    if (!ctx) return fail(LUMEN_MOE_INVALID_ARG, "null context");
+    const lumen::CudaMoeScratch& s = ctx->scratch;
+    if (tokens < 1 || tokens > s.cap_tokens) return fail(LUMEN_MOE_INVALID_ARG, "tokens exceeds the last call's capacity");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t C = (size_t)tokens * s.K;
+    cudaError_t e = cudaStreamSynchronize(st);
+    if (e == cudaSuccess && ids) e = cudaMemcpy(ids, s.R.ids, C * 4, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && weights) e = cudaMemcpy(weights, s.R.weights, C * 4, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && dst_to_col) e = cudaMemcpy(dst_to_col, s.R.dst_to_col, C * 4, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && col_src_tok) e = cudaMemcpy(col_src_tok, s.R.col_src_tok, C * 4, cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && expert_bounds)
+        e = cudaMemcpy(expert_bounds, s.R.expert_bounds, (size_t)(s.E + 1) * 4, cudaMemcpyDeviceToHost);
+    int32_t dev_status = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&dev_status, s.status, 4, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    if (dev_status != 0) {
+        cudaMemset(s.status, 0, 4);
+        return fail(dev_status, "a device-side bounded wait expired in the grouped GEMM");
+    }
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_quantize(const float* d_src, int64_t n_elements, int32_t quant, void* d_dst,
+                                      void* stream) {
+    if (!d_src || !d_dst) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    if (n_elements <= 0 || n_elements % 32) return fail(LUMEN_MOE_INVALID_ARG, "n_elements must be a positive multiple of 32");
+    if (quant < 0 || quant > 2) return fail(LUMEN_MOE_UNSUPPORTED, "unsupported quant scheme");
+    cudaError_t e = lumen::launch_quantize(d_src, n_elements, quant, d_dst, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_rmsnorm(const float* d_x, const float* d_gamma, float* d_out, int32_t tokens,
+                                     int32_t hidden_dim, float eps, void* stream) {
+    if (!d_x || !d_gamma || !d_out || tokens < 1 || hidden_dim < 1) return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    cudaError_t e = lumen::launch_rmsnorm(d_x, d_gamma, d_out, tokens, hidden_dim, eps, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_stack_decode(lumen_moe_ctx* ctx, const lumen_moe_layer* const* layers,
+                                          const float* const* d_gammas, int32_t n_layers, float* d_x, float eps,
+                                          int32_t tokens, void* stream) {
+    if (!ctx || !layers || !d_gammas || !d_x || n_layers < 1) return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int l = 0; l < n_layers; ++l) {
+        if (!layers[l] || !d_gammas[l]) return fail(LUMEN_MOE_INVALID_ARG, "null layer or gamma");
+        // x <- x + MoE(rmsnorm(x)); residual and output are the same buffer (cuda/backend_impl.rs:3570-3573)
+        lumen::Status s = lumen::encode_moe_ffn_decode_fused_norm(&ctx->scratch, layers[l]->layer, d_x, d_gammas[l],
+                                                                  nullptr, d_x, eps, tokens, st);
+        if (!s.ok()) return done(s);
+    }
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_debug_expf(const float* d_in, float* d_out, int64_t n, void* stream) {
+    if (!d_in || !d_out || n <= 0) return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    cudaError_t e = lumen::launch_debug_expf(d_in, d_out, n, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_debug_decode_phase(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, int32_t phase,
+                                                void* stream) {
+    if (!ctx || !layer || phase < 0 || phase > 2) return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    if (!ctx->scratch.has_last_decode) return fail(LUMEN_MOE_INVALID_ARG, "no decode call has been made yet");
+    lumen::DecodeArgs a = ctx->scratch.last_decode;
+    a.L = layer->layer.dev;
+    cudaError_t e = lumen::launch_decode_phase(a, phase, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
+}
+
+int64_t lumen_moe_launch_count(int32_t reset) { return lumen::read_launch_count(reset != 0); }
+
+}  // extern "C"

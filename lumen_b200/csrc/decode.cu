@@ -1,0 +1,626 @@
+// Decode path (1..16 tokens) of the MoE FFN: three kernels chained with
+// programmatic dependent launch.
+//
+//   router_small_kernel   one CTA per expert: router logit(s) W_r[e]·x[t]
+//                         (moe_router_logits_v2, cuda/shaders/moe_batched.cu:708),
+//                         optional fused FFN RMSNorm (cuda/shaders/norm.cu:28-76),
+//                         activation fragments; the last CTA to finish (fence +
+//                         ticket, no spinning) does gating/top-k/renorm
+//                         (cuda/moe.rs:6464-6504) and the stable counting sort
+//                         (cuda/moe.rs:2115-2147).
+//   gate_up_kernel        per (distinct expert, 16 rows of I): gate and up rows
+//                         times the tokens routed to the expert, SwiGLU
+//                         (cuda/shaders/moe_expert_q4_0.cu:58-108, moe_expert.cu:62-97).
+//   down_combine_kernel   per 16 rows of H: down rows of every selected expert
+//                         (moe_expert_q4_0.cu:118-151) and the weighted combine
+//                         out = residual + sum_k w_k d_k in slot order
+//                         (cuda/shaders/moe_accum.cu:22-46, cuda/moe.rs:6508-6524).
+//
+// All three are HBM-bound: each weight byte is read exactly once with 128-bit
+// streaming loads, every load of a warp's share is in flight before the first
+// use, and the arithmetic runs on the tensor cores (mma_frag.cuh).
+#include "mma_frag.cuh"
+#include "router.cuh"
+
+namespace lumen {
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+constexpr int RS_THREADS = 256;
+constexpr int RS_WARPS = RS_THREADS / 32;
+
+__global__ void __launch_bounds__(RS_THREADS)
+router_small_kernel(const __grid_constant__ DecodeArgs a) {
+    __shared__ float red_s[RS_WARPS][DECODE_MAX_TOKENS];
+    __shared__ float scale_s[DECODE_MAX_TOKENS];
+    __shared__ float p_s[RS_WARPS][MAX_EXPERTS];
+    __shared__ float lg_s[RS_WARPS][MAX_EXPERTS];
+    __shared__ float sel_s[RS_WARPS][MAX_TOP_K];
+    __shared__ int ids_s[DECODE_MAX_TOKENS * MAX_TOP_K];
+    __shared__ int cnt_s[MAX_EXPERTS];
+    __shared__ int bounds_s[MAX_EXPERTS + 1];
+    __shared__ int is_last_s;
+
+    pdl_trigger();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int e = blockIdx.x;
+    const int H = a.L.H, E = a.L.E, T = a.T, K = a.K;
+    const int H4 = H >> 2;
+    const bool want_logits = (a.logits_override == nullptr);
+
+    // Router row in registers before waiting on the previous kernel (weights are static).
+    constexpr int MAXV = 4;  // covers H <= 4096 without re-reading
+    float4 wv[MAXV];
+    const float4* wrow = reinterpret_cast<const float4*>(a.L.router_w + (size_t)e * H);
+#pragma unroll
+    for (int j = 0; j < MAXV; ++j) {
+        const int i4 = tid + j * RS_THREADS;
+        wv[j] = (want_logits && i4 < H4) ? __ldg(wrow + i4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();
+
+    // fused FFN RMSNorm scale per token
+    if (a.gamma != nullptr) {
+        for (int t = 0; t < T; ++t) {
+            const float4* xr = reinterpret_cast<const float4*>(a.x + (size_t)t * H);
+            float ss = 0.0f;
+            for (int i4 = tid; i4 < H4; i4 += RS_THREADS) {
+                const float4 v = xr[i4];
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red_s[warp][t] = ss;
+        }
+        __syncthreads();
+        if (tid < T) {
+            float ss = 0.0f;
+            for (int w = 0; w < RS_WARPS; ++w) ss += red_s[w][tid];
+            scale_s[tid] = 1.0f / sqrtf(ss / (float)H + a.eps);
+        }
+        __syncthreads();
+    }
+    auto load_x4 = [&](int t, int i4) -> float4 {
+        float4 v = reinterpret_cast<const float4*>(a.x + (size_t)t * H)[i4];
+        if (a.gamma != nullptr) {
+            const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + i4);
+            const float sc = scale_s[t];
+            v.x = v.x * sc * g.x;
+            v.y = v.y * sc * g.y;
+            v.z = v.z * sc * g.z;
+            v.w = v.w * sc * g.w;
+        }
+        return v;
+    };
+
+    // logits for this expert row, all tokens
+    if (want_logits) {
+        float acc[DECODE_MAX_TOKENS];
+#pragma unroll
+        for (int t = 0; t < DECODE_MAX_TOKENS; ++t) acc[t] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            const int i4 = tid + j * RS_THREADS;
+            if (i4 < H4) {
+#pragma unroll
+                for (int t = 0; t < DECODE_MAX_TOKENS; ++t) {
+                    if (t < T) {
+                        const float4 xv = load_x4(t, i4);
+                        acc[t] += wv[j].x * xv.x + wv[j].y * xv.y + wv[j].z * xv.z + wv[j].w * xv.w;
+                    }
+                }
+            }
+        }
+        for (int i4 = tid + MAXV * RS_THREADS; i4 < H4; i4 += RS_THREADS) {  // H > 4096
+            const float4 w4 = __ldg(wrow + i4);
+#pragma unroll
+            for (int t = 0; t < DECODE_MAX_TOKENS; ++t) {
+                if (t < T) {
+                    const float4 xv = load_x4(t, i4);
+                    acc[t] += w4.x * xv.x + w4.y * xv.y + w4.z * xv.z + w4.w * xv.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < DECODE_MAX_TOKENS; ++t) {
+            if (t < T) {
+                float v = acc[t];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (lane == 0) red_s[warp][t] = v;
+            }
+        }
+        __syncthreads();
+        if (tid < T) {
+            float v = 0.0f;
+            for (int w = 0; w < RS_WARPS; ++w) v += red_s[w][tid];
+            a.R.logits[(size_t)tid * E + e] = v;
+        }
+    }
+
+    // activation fragments (and the normed output of the fused-norm entry point)
+    if (a.xf != nullptr) {
+        const int nblk = H >> 5, nblk_pad = a.L.kg_h * 4;
+        const bool bf16_mode = (a.L.quant == BF16);
+        const int sub = tid & 7, hl = sub >> 2, t4 = sub & 3;
+        for (int item = blockIdx.x * (RS_THREADS / 8) + (tid >> 3); item < T * nblk;
+             item += gridDim.x * (RS_THREADS / 8)) {
+            const int t = item / nblk, b = item - t * nblk;
+            const float4 lo4 = load_x4(t, b * 8 + t4);
+            const float4 hi4 = load_x4(t, b * 8 + 4 + t4);
+            a.xf[((size_t)(t * 2 + hl) * nblk_pad + b) * 4 + t4] = make_act_frag(lo4, hi4, hl, bf16_mode);
+            if (a.gamma != nullptr && a.normed_out != nullptr) {
+                float4* o = reinterpret_cast<float4*>(a.normed_out + (size_t)t * H);
+                o[b * 8 + (hl ? 4 : 0) + t4] = hl ? hi4 : lo4;
+            }
+        }
+    }
+
+    // last-CTA election: every writer fences, then one ticket per CTA
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned int ticket = atomicAdd(a.R.ticket, 1u);
+        is_last_s = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!is_last_s) return;
+    __threadfence();
+
+    const float* lg = want_logits ? a.R.logits : a.logits_override;
+    for (int t = warp; t < T; t += RS_WARPS) {
+        for (int i = lane; i < E; i += 32) lg_s[warp][i] = __ldcg(lg + (size_t)t * E + i);
+        __syncwarp();
+        warp_topk(lg_s[warp], E, K, a.gating, p_s[warp], sel_s[warp], a.R.ids + (size_t)t * K,
+                  a.R.weights + (size_t)t * K);
+        if (lane < K) ids_s[t * K + lane] = (int)a.R.ids[(size_t)t * K + lane];
+    }
+    __syncthreads();
+    const int C = T * K;
+    if (tid < E) {
+        int c = 0;
+        for (int p = 0; p < C; ++p) c += (ids_s[p] == tid);
+        cnt_s[tid] = c;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // exclusive scan over experts, 8 per lane (E <= 256), and the ascending
+        // list of experts that received at least one token
+        int local[8], lsum = 0, lnz = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int ee = lane * 8 + j;
+            local[j] = (ee < E) ? cnt_s[ee] : 0;
+            lsum += local[j];
+            lnz += (local[j] > 0);
+        }
+        int isum = lsum, inz = lnz;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v1 = __shfl_up_sync(0xffffffffu, isum, o);
+            const int v2 = __shfl_up_sync(0xffffffffu, inz, o);
+            if (lane >= o) {
+                isum += v1;
+                inz += v2;
+            }
+        }
+        int run = isum - lsum, unz = inz - lnz;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int ee = lane * 8 + j;
+            if (ee < E) {
+                bounds_s[ee] = run;
+                a.R.expert_bounds[ee] = run;
+                if (local[j] > 0) a.R.uexp[unz++] = ee;
+                run += local[j];
+            }
+        }
+        if (lane == 31) {
+            bounds_s[E] = isum;
+            a.R.expert_bounds[E] = isum;
+            *a.R.n_uexp = inz;
+        }
+    }
+    __syncthreads();
+    if (tid < E) {
+        int cur = bounds_s[tid];
+        for (int p = 0; p < C; ++p) {
+            if (ids_s[p] == tid) {
+                a.R.col_expert[cur] = tid;
+                a.R.col_src_tok[cur] = p / K;
+                a.R.dst_to_col[p] = cur;
+                ++cur;
+            }
+        }
+    }
+    if (tid == 0) *a.R.ticket = 0u;
+}
+
+// ---------------------------------------------------------------------------
+// gate/up + SwiGLU
+// ---------------------------------------------------------------------------
+constexpr int GU_THREADS = 256;
+constexpr int GU_WARPS = GU_THREADS / 32;
+
+template <int Q>
+__device__ __forceinline__ void tile_mma_pair(const WTile<Q>& wg, const WTile<Q>& wu,
+                                              const uint4* (&bptr)[4], int ngroups,
+                                              float (&acc_g)[4][4], float (&acc_u)[4][4]) {
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+        uint32_t g_lo[4], g_hi[4], u_lo[4], u_hi[4];
+        unpack_block<Q>(wg, b, g_lo, g_hi);
+        unpack_block<Q>(wu, b, u_lo, u_hi);
+        const float2 sg = block_scales<Q>(wg, b);
+        const float2 su = block_scales<Q>(wu, b);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            if (g < ngroups) {
+                uint4 bf = make_uint4(0u, 0u, 0u, 0u);
+                if (bptr[g] != nullptr) bf = ldg_cached(bptr[g] + b * 4);
+                float cg[4] = {0.f, 0.f, 0.f, 0.f}, cu[4] = {0.f, 0.f, 0.f, 0.f};
+                if (Q == BF16) {
+                    mma_bf16(cg, g_lo, bf.x, bf.y);
+                    mma_bf16(cg, g_hi, bf.z, bf.w);
+                    mma_bf16(cu, u_lo, bf.x, bf.y);
+                    mma_bf16(cu, u_hi, bf.z, bf.w);
+                } else {
+                    mma_f16(cg, g_lo, bf.x, bf.y);
+                    mma_f16(cg, g_hi, bf.z, bf.w);
+                    mma_f16(cu, u_lo, bf.x, bf.y);
+                    mma_f16(cu, u_hi, bf.z, bf.w);
+                }
+                acc_g[g][0] = fmaf(sg.x, cg[0], acc_g[g][0]);
+                acc_g[g][1] = fmaf(sg.x, cg[1], acc_g[g][1]);
+                acc_g[g][2] = fmaf(sg.y, cg[2], acc_g[g][2]);
+                acc_g[g][3] = fmaf(sg.y, cg[3], acc_g[g][3]);
+                acc_u[g][0] = fmaf(su.x, cu[0], acc_u[g][0]);
+                acc_u[g][1] = fmaf(su.x, cu[1], acc_u[g][1]);
+                acc_u[g][2] = fmaf(su.y, cu[2], acc_u[g][2]);
+                acc_u[g][3] = fmaf(su.y, cu[3], acc_u[g][3]);
+            }
+        }
+    }
+}
+
+// Position of element r (0..15 within a half block) inside the 8-half fragment
+// vector: quad t = r/4, order within the quad (v0, v2, v1, v3).
+__device__ __forceinline__ int frag_pos(int r) {
+    const int m = r & 3;
+    return (m == 0) ? 0 : (m == 2) ? 1 : (m == 1) ? 2 : 3;
+}
+
+template <int Q>
+__global__ void __launch_bounds__(GU_THREADS)
+gate_up_kernel(const __grid_constant__ DecodeArgs a) {
+    __shared__ float red[GU_WARPS][4][16][4][2];  // [warp][group][row][token in group][gate,up]
+    pdl_trigger();
+    pdl_wait();
+    const int u = blockIdx.y;
+    if (u >= *a.R.n_uexp) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, t4 = lane & 3;
+    const int rt = blockIdx.x;
+    const int e = a.R.uexp[u];
+    const int c0 = a.R.expert_bounds[e], c1 = a.R.expert_bounds[e + 1];
+    const int kg_h = a.L.kg_h, I = a.L.I;
+    const int nblk_pad = kg_h * 4, nblk_i_pad = a.L.kg_i * 4;
+    const uint4* gq_base = a.L.gate_q(e);
+    const uint4* uq_base = a.L.up_q(e);
+    const uint4* gs_base = a.L.gate_s(e);
+    const uint4* us_base = a.L.up_s(e);
+
+    for (int chunk = c0; chunk < c1; chunk += 16) {
+        const int ncol = min(16, c1 - chunk);
+        const int ng = (ncol + 3) >> 2;
+        const uint4* bbase[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const int col = chunk + 4 * g + (gq >> 1);
+            bbase[g] = nullptr;
+            if (g < ng && col < c1) {
+                const int tok = a.R.col_src_tok[col];
+                bbase[g] = a.xf + ((size_t)(tok * 2 + (gq & 1)) * nblk_pad) * 4 + t4;
+            }
+        }
+        float acc_g[4][4], acc_u[4][4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc_g[g][i] = acc_u[g][i] = 0.0f;
+
+        WTile<Q> wg, wu, ng_t, nu_t;
+        int kg = warp;
+        if (kg < kg_h) {
+            load_wtile<Q>(wg, gq_base, gs_base, rt * kg_h + kg, lane);
+            load_wtile<Q>(wu, uq_base, us_base, rt * kg_h + kg, lane);
+        }
+        for (; kg < kg_h; kg += GU_WARPS) {
+            const bool more = (kg + GU_WARPS) < kg_h;
+            if (more) {
+                load_wtile<Q>(ng_t, gq_base, gs_base, rt * kg_h + kg + GU_WARPS, lane);
+                load_wtile<Q>(nu_t, uq_base, us_base, rt * kg_h + kg + GU_WARPS, lane);
+            }
+            const uint4* bp[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) bp[g] = bbase[g] ? bbase[g] + (size_t)kg * 16 : nullptr;
+            tile_mma_pair<Q>(wg, wu, bp, ng, acc_g, acc_u);
+            if (more) {
+                wg = ng_t;
+                wu = nu_t;
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            red[warp][g][gq][t4][0] = acc_g[g][0] + acc_g[g][1];
+            red[warp][g][gq][t4][1] = acc_u[g][0] + acc_u[g][1];
+            red[warp][g][gq + 8][t4][0] = acc_g[g][2] + acc_g[g][3];
+            red[warp][g][gq + 8][t4][1] = acc_u[g][2] + acc_u[g][3];
+        }
+        __syncthreads();
+        {
+            const int row = tid & 15, tokc = tid >> 4;
+            if (tokc < ncol) {
+                float gate = 0.0f, up = 0.0f;
+#pragma unroll
+                for (int w = 0; w < GU_WARPS; ++w) {
+                    gate += red[w][tokc >> 2][row][tokc & 3][0];
+                    up += red[w][tokc >> 2][row][tokc & 3][1];
+                }
+                const float sv = (gate / (1.0f + expf(-gate))) * up;
+                const int col = chunk + tokc;
+                const int irow = rt * 16 + row;
+                if (a.s_f32 != nullptr) a.s_f32[(size_t)col * I + irow] = sv;
+                const bool bf16_mode = (Q == BF16);
+                const int blk = irow >> 5, within = irow & 31, j = within >> 4, r16 = within & 15;
+                unsigned short hi_bits, lo_bits;
+                if (!bf16_mode) {
+                    const __half h = __float2half_rn(sv);
+                    const __half l = __float2half_rn(sv - __half2float(h));
+                    hi_bits = __half_as_ushort(h);
+                    lo_bits = __half_as_ushort(l);
+                } else {
+                    const __nv_bfloat16 h = __float2bfloat16_rn(sv);
+                    const __nv_bfloat16 l = __float2bfloat16_rn(sv - __bfloat162float(h));
+                    hi_bits = __bfloat16_as_ushort(h);
+                    lo_bits = __bfloat16_as_ushort(l);
+                }
+                unsigned short* sf16 = reinterpret_cast<unsigned short*>(a.sf);
+                const size_t in_vec = (size_t)j * 4 + frag_pos(r16);
+                const size_t v_hi = (((size_t)(col * 2 + 0) * nblk_i_pad + blk) * 4 + (r16 >> 2)) * 8 + in_vec;
+                const size_t v_lo = (((size_t)(col * 2 + 1) * nblk_i_pad + blk) * 4 + (r16 >> 2)) * 8 + in_vec;
+                sf16[v_hi] = hi_bits;
+                sf16[v_lo] = lo_bits;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// down + weighted combine (decode: every expert has at most 16 columns)
+// ---------------------------------------------------------------------------
+constexpr int DC_THREADS = 256;
+constexpr int DC_WARPS = DC_THREADS / 32;
+constexpr int DC_MAX_COLS = DECODE_MAX_TOKENS * MAX_TOP_K;
+
+template <int Q>
+__global__ void __launch_bounds__(DC_THREADS)
+down_combine_kernel(const __grid_constant__ DecodeArgs a) {
+    __shared__ float dsm[DC_MAX_COLS][16];
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, t4 = lane & 3;
+    const int rt = blockIdx.x;
+    const int U = *a.R.n_uexp;
+    const int kg_i = a.L.kg_i, H = a.L.H, K = a.K, T = a.T;
+    const int nblk_i_pad = kg_i * 4;
+
+    // flattened (expert, k-group) items of this warp, one tile prefetched ahead
+    const int n_exp_w = (U > warp) ? (U - warp + DC_WARPS - 1) / DC_WARPS : 0;
+    const int nitems = n_exp_w * kg_i;
+    auto item_tile = [&](int n, const uint4*& qb, const uint4*& sb) -> int {
+        const int uu = warp + DC_WARPS * (n / kg_i), kg = n % kg_i;
+        const int ee = a.R.uexp[uu];
+        qb = a.L.down_q(ee);
+        sb = a.L.down_s(ee);
+        return rt * kg_i + kg;
+    };
+    WTile<Q> cur, nxt;
+    if (nitems > 0) {
+        const uint4 *qb, *sb;
+        const int tile = item_tile(0, qb, sb);
+        load_wtile<Q>(cur, qb, sb, tile, lane);
+    }
+    float acc[4][4];
+    const uint4* bbase[4] = {nullptr, nullptr, nullptr, nullptr};
+    int c0 = 0, ncol = 0, ng = 0;
+    for (int n = 0; n < nitems; ++n) {
+        if (n + 1 < nitems) {
+            const uint4 *qb, *sb;
+            const int tile = item_tile(n + 1, qb, sb);
+            load_wtile<Q>(nxt, qb, sb, tile, lane);
+        }
+        const int kg = n % kg_i;
+        if (kg == 0) {
+            const int uu = warp + DC_WARPS * (n / kg_i);
+            const int ee = a.R.uexp[uu];
+            c0 = a.R.expert_bounds[ee];
+            ncol = min(16, a.R.expert_bounds[ee + 1] - c0);
+            ng = (ncol + 3) >> 2;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int colr = 4 * g + (gq >> 1);
+                bbase[g] = (colr < ncol)
+                               ? a.sf + ((size_t)((c0 + colr) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4
+                               : nullptr;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[g][i] = 0.0f;
+            }
+        }
+        const uint4* bp[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) bp[g] = bbase[g] ? bbase[g] + (size_t)kg * 16 : nullptr;
+        tile_mma<Q, 4>(cur, bp, ng, acc);
+        if (kg == kg_i - 1) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const int tokc = 4 * g + t4;
+                if (tokc < ncol) {
+                    dsm[c0 + tokc][gq] = acc[g][0] + acc[g][1];
+                    dsm[c0 + tokc][gq + 8] = acc[g][2] + acc[g][3];
+                }
+            }
+        }
+        if (n + 1 < nitems) cur = nxt;
+    }
+    __syncthreads();
+    {
+        const int row = tid & 15, t = tid >> 4;
+        if (t < T) {
+            const size_t o = (size_t)t * H + rt * 16 + row;
+            float accv = a.residual[o];
+            for (int slot = 0; slot < K; ++slot) {
+                const int col = a.R.dst_to_col[t * K + slot];
+                const float w = a.R.weights[t * K + slot];
+                accv = __fadd_rn(accv, __fmul_rn(w, dsm[col][row]));
+            }
+            a.out[o] = accv;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// down projection for any number of columns per expert (mma.sync grouped path of
+// the prefill entry point): one CTA per (16 rows of H, expert), k-groups split
+// across warps, output f16 by compact column for the scatter-accumulate.
+// ---------------------------------------------------------------------------
+template <int Q>
+__global__ void __launch_bounds__(GU_THREADS)
+down_general_kernel(const __grid_constant__ DecodeArgs a, __half* __restrict__ d16) {
+    __shared__ float red[GU_WARPS][4][16][4];
+    const int u = blockIdx.y;
+    if (u >= *a.R.n_uexp) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, t4 = lane & 3;
+    const int rt = blockIdx.x;
+    const int e = a.R.uexp[u];
+    const int c0 = a.R.expert_bounds[e], c1 = a.R.expert_bounds[e + 1];
+    const int kg_i = a.L.kg_i, H = a.L.H;
+    const int nblk_i_pad = kg_i * 4;
+    const uint4* q_base = a.L.down_q(e);
+    const uint4* s_base = a.L.down_s(e);
+    for (int chunk = c0; chunk < c1; chunk += 16) {
+        const int ncol = min(16, c1 - chunk);
+        const int ng = (ncol + 3) >> 2;
+        const uint4* bbase[4];
+        float acc[4][4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const int colr = 4 * g + (gq >> 1);
+            bbase[g] = (colr < ncol)
+                           ? a.sf + ((size_t)((chunk + colr) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4
+                           : nullptr;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[g][i] = 0.0f;
+        }
+        for (int kg = warp; kg < kg_i; kg += GU_WARPS) {
+            WTile<Q> w;
+            load_wtile<Q>(w, q_base, s_base, rt * kg_i + kg, lane);
+            const uint4* bp[4];
+#pragma unroll
+            for (int g = 0; g < 4; ++g) bp[g] = bbase[g] ? bbase[g] + (size_t)kg * 16 : nullptr;
+            tile_mma<Q, 4>(w, bp, ng, acc);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            red[warp][g][gq][t4] = acc[g][0] + acc[g][1];
+            red[warp][g][gq + 8][t4] = acc[g][2] + acc[g][3];
+        }
+        __syncthreads();
+        {
+            const int row = tid & 15, tokc = tid >> 4;
+            if (tokc < ncol) {
+                float v = 0.0f;
+#pragma unroll
+                for (int w = 0; w < GU_WARPS; ++w) v += red[w][tokc >> 2][row][tokc & 3];
+                d16[(size_t)(chunk + tokc) * H + rt * 16 + row] = __float2half_rn(v);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+cudaError_t launch_grouped_mma(const DecodeArgs& a, __half* d16, cudaStream_t st) {
+    const dim3 g_gu(a.L.rt_i, a.L.E), g_dn(a.L.rt_h, a.L.E);
+    count_launch(2);
+    switch (a.L.quant) {
+        case Q4_0:
+            gate_up_kernel<Q4_0><<<g_gu, GU_THREADS, 0, st>>>(a);
+            down_general_kernel<Q4_0><<<g_dn, GU_THREADS, 0, st>>>(a, d16);
+            break;
+        case Q8_0:
+            gate_up_kernel<Q8_0><<<g_gu, GU_THREADS, 0, st>>>(a);
+            down_general_kernel<Q8_0><<<g_dn, GU_THREADS, 0, st>>>(a, d16);
+            break;
+        default:
+            gate_up_kernel<BF16><<<g_gu, GU_THREADS, 0, st>>>(a);
+            down_general_kernel<BF16><<<g_dn, GU_THREADS, 0, st>>>(a, d16);
+            break;
+    }
+    return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// launch
+// ---------------------------------------------------------------------------
+template <typename Kern>
+static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, cudaStream_t st, const DecodeArgs& a) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    count_launch();
+    return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
+cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st) {
+    return launch_pdl(router_small_kernel, dim3(a.L.E), dim3(RS_THREADS), st, a);
+}
+
+cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st) {
+    if (phase == 0) return launch_route_small(a, st);
+    const int C = a.T * a.K;
+    const int nu = C < a.L.E ? C : a.L.E;
+    const dim3 g_gu(a.L.rt_i, nu), g_dc(a.L.rt_h);
+    if (phase == 1) {
+        switch (a.L.quant) {
+            case Q4_0: return launch_pdl(gate_up_kernel<Q4_0>, g_gu, dim3(GU_THREADS), st, a);
+            case Q8_0: return launch_pdl(gate_up_kernel<Q8_0>, g_gu, dim3(GU_THREADS), st, a);
+            default: return launch_pdl(gate_up_kernel<BF16>, g_gu, dim3(GU_THREADS), st, a);
+        }
+    }
+    switch (a.L.quant) {
+        case Q4_0: return launch_pdl(down_combine_kernel<Q4_0>, g_dc, dim3(DC_THREADS), st, a);
+        case Q8_0: return launch_pdl(down_combine_kernel<Q8_0>, g_dc, dim3(DC_THREADS), st, a);
+        default: return launch_pdl(down_combine_kernel<BF16>, g_dc, dim3(DC_THREADS), st, a);
+    }
+}
+
+cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t st) {
+    for (int phase = 0; phase < 3; ++phase) {
+        const cudaError_t err = launch_decode_phase(a, phase, st);
+        if (err != cudaSuccess) return err;
+    }
+    return cudaSuccess;
+}
+
+}  // namespace lumen

@@ -1,0 +1,129 @@
+// Internal declarations shared by the kernels and the host layer of the MoE
+// operator: device-side layouts, scratch buffers and launch prototypes.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stddef.h>
+
+namespace lumen {
+
+enum Quant : int { Q8_0 = 0, Q4_0 = 1, BF16 = 2 };
+
+constexpr int MAX_EXPERTS = 256;  // cuda/shaders/moe_router.cu:33
+constexpr int MAX_TOP_K = 16;     // cuda/shaders/moe_router.cu:34
+constexpr int DECODE_MAX_TOKENS = 16;
+
+// ---------------------------------------------------------------------------
+// Repacked expert weights ("fragment planes").
+//
+// A matrix [R rows, Kdim] (rows = outputs, Kdim = inputs, 32-element blocks along
+// Kdim) is cut into tiles of 16 rows x 4 blocks (128 inputs). Tile (rt, kg) is
+// stored as NQ consecutive 512-byte vectors (one uint4 per lane of a warp), laid
+// out so that lane (g = lane/4, t = lane%4) finds in its own uint4s exactly the
+// words the m16n8k16 A fragment of rows {16rt+g, 16rt+g+8} needs:
+//   Q4_0 (NQ=2): vector j holds blocks 2j, 2j+1 of the group:
+//        {w(g,2j,t), w(g+8,2j,t), w(g,2j+1,t), w(g+8,2j+1,t)}, w(r,b,t) = 32-bit
+//        word t of the block's 16 nibble bytes (elements 4t..4t+3 low nibbles,
+//        16+4t..16+4t+3 high nibbles).
+//   Q8_0 (NQ=4): vector b holds block b: {w(g,b,t), w(g,b,4+t), w(g+8,b,t), w(g+8,b,4+t)},
+//        w(r,b,i) = 32-bit word i of the block's 32 int8 (elements 4i..4i+3).
+//   BF16 (NQ=8): vector 2b+r holds, for row g+8r, the 8 bf16 elements
+//        {4t..4t+3, 16+4t..16+4t+3} of block b.
+// Scales (Q4_0/Q8_0): per tile 8 uint4, one per g: f16 {row g: blocks 0..3, row g+8: blocks 0..3}.
+// Blocks past Kdim inside the last group are zero (scale 0).
+// ---------------------------------------------------------------------------
+struct LayerDev {
+    const uint8_t* blob;
+    const float* router_w;  // blob + router_off, [E,H] f32
+    const uint4* q;         // all experts' quant planes
+    const uint4* s;         // all experts' scale planes (unused for BF16)
+    int quant, H, I, E;
+    int kg_h, kg_i;  // 128-input groups along H (gate/up) and I (down)
+    int rt_i, rt_h;  // 16-row tiles of gate/up (I rows) and down (H rows)
+    int nq;          // uint4 per lane per tile
+    size_t q_gu, q_dn, q_exp;  // uint4 counts: one gate (or up) matrix, one down matrix, one expert
+    size_t s_gu, s_dn, s_exp;
+
+    __host__ __device__ const uint4* gate_q(int e) const { return q + (size_t)e * q_exp; }
+    __host__ __device__ const uint4* up_q(int e) const { return q + (size_t)e * q_exp + q_gu; }
+    __host__ __device__ const uint4* down_q(int e) const { return q + (size_t)e * q_exp + 2 * q_gu; }
+    __host__ __device__ const uint4* gate_s(int e) const { return s + (size_t)e * s_exp; }
+    __host__ __device__ const uint4* up_s(int e) const { return s + (size_t)e * s_exp + s_gu; }
+    __host__ __device__ const uint4* down_s(int e) const { return s + (size_t)e * s_exp + 2 * s_gu; }
+};
+
+// Routing tables of one call (device pointers into the context's scratch).
+struct RouteDev {
+    float* logits;         // [T,E]
+    uint32_t* ids;         // [T,K] selection order
+    float* weights;        // [T,K]
+    int32_t* expert_bounds;  // [E+1]
+    int32_t* col_expert;   // [C]
+    int32_t* col_src_tok;  // [C]
+    int32_t* dst_to_col;   // [C] indexed t*K+slot
+    int32_t* uexp;         // [E] distinct experts, ascending
+    int32_t* n_uexp;       // [1]
+    unsigned int* ticket;  // [1] last-block election counter (zero between launches)
+};
+
+// Activation fragments: for token (or compact column) c, half hl (0 = high part,
+// 1 = low part of the f32 value split into two f16), block b, t in 0..3: one uint4
+//   {pack(v[4t],v[4t+2]), pack(v[4t+1],v[4t+3]), pack(v[16+4t],v[16+4t+2]), pack(v[16+4t+1],v[16+4t+3])}
+// i.e. the m16n8k16 B fragments (b0,b1) of the low-nibble MMA then of the
+// high-nibble MMA of that block. Index: ((c*2 + hl)*nblk_pad + b)*4 + t.
+struct DecodeArgs {
+    LayerDev L;
+    RouteDev R;
+    const float* x;         // normed [T,H] (or raw x when gamma != null)
+    const float* gamma;     // fused FFN norm weight or null
+    float* normed_out;      // optional normed output when gamma != null
+    float eps;
+    const float* residual;  // [T,H]
+    float* out;             // [T,H]
+    const float* logits_override;  // [T,E] or null
+    uint4* xf;              // activation fragments [T][2][kg_h*4][4]
+    uint4* sf;              // SwiGLU fragments     [C][2][kg_i*4][4]
+    float* s_f32;           // optional [C,I] f32 copy of the SwiGLU output (null = skip)
+    int T, K, gating;
+};
+
+// launchers (kernels.cu files)
+cudaError_t launch_repack(const uint8_t* blob, const uint64_t* d_gate_offs, const uint64_t* d_up_offs,
+                          const uint64_t* d_down_offs, const LayerDev& L, uint4* q, uint4* s,
+                          cudaStream_t st);
+cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t st);
+cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st);
+cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st);  // router + tables only (T<=16)
+cudaError_t launch_quantize(const float* src, int64_t n, int quant, void* dst, cudaStream_t st);
+cudaError_t launch_rmsnorm(const float* x, const float* gamma, float* out, int T, int H, float eps,
+                           cudaStream_t st);
+cudaError_t launch_debug_expf(const float* in, float* out, int64_t n, cudaStream_t st);
+
+// prefill path
+struct PrefillArgs {
+    LayerDev L;
+    RouteDev R;
+    const void* x;          // normed [T,H], f32 or bf16
+    int act_dtype;          // 0 f32, 1 bf16
+    const float* residual;
+    float* out;
+    const float* logits_override;
+    int T, K, gating;
+    // scratch
+    int32_t* blk_hist;      // [nchunks, E]
+    __half* s16;            // [C, I] f16 SwiGLU output, row-major by compact column
+    __half* d16;            // [C, H] f16 down output by compact column
+    int4* tiles;            // tile list for the grouped GEMMs
+    int32_t* n_tiles;       // [2]: gate/up tiles, down tiles
+    unsigned int* tile_counter;  // [2] dynamic tile scheduler counters
+    int32_t* status;        // [1] device-side error flag (bounded waits)
+    int impl;               // 0 = tcgen05 path, 1 = mma.sync grouped fallback
+};
+cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st);
+cudaError_t launch_prefill(const PrefillArgs& a, cudaStream_t st);
+
+void count_launch(int n = 1);
+
+}  // namespace lumen

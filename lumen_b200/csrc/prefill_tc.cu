@@ -1,0 +1,472 @@
+// Prefill grouped expert products on the 5th-generation tensor cores (tcgen05,
+// accumulators in TMEM). Replaces the reference's tiled prefill kernels
+// (moe_grouped_gate_up_swiglu_q4_0_tiled_f32act / moe_grouped_down_q4_0_tiled_f32act,
+// cuda/shaders/moe_grouped.cu:1202-1510; the Q8_0 dp4a / mma.sync variants :566-1170,
+// :2183-2598; the BF16 variants :1523-1760).
+//
+// Formulation ("weights are the M operand"): for a tile of up to 128 compact
+// columns of one expert,  D[128 weight rows, N columns] += W[128, k] * X[N, k]^T,
+// one tcgen05.mma of shape M=128 x N(16..128) x K=16 per 16 inputs. N follows
+// the ragged per-expert column counts (Zipf-skewed loads) without padding M.
+//
+// One CTA per SM, persistent over a device-built tile list, warp-specialised:
+//   warps 0-3   epilogue: tcgen05.ld of the accumulators, SwiGLU (gate/up mode),
+//               f16 store by compact column
+//   warps 4-11  weight producers: 128-bit loads of the repacked quant tiles,
+//               dequantise to f16 (scale folded in) in registers, store into the
+//               128-byte-swizzled K-major operand tile in shared memory
+//   warps 12-15 activation producers: cp.async rows (gathered through
+//               col_src_tok) into the swizzled operand tile
+//   warp 16     one elected thread issues tcgen05.mma / tcgen05.commit
+// Stages are handed over with mbarriers; every wait is bounded (on expiry the
+// kernel raises a status word, drains and frees its TMEM instead of hanging).
+//
+// Inputs are 16-bit: activations pre-converted to f16 (bf16 for BF16 weights)
+// and pre-permuted within each 32-block to the order the dequantiser emits
+// (permute_x16_kernel); the SwiGLU output is written in the same order so the
+// down product reads it back without any shuffle.
+#include "mma_frag.cuh"
+
+namespace lumen {
+
+namespace tc {
+
+constexpr int EPI_WARPS = 4, A_WARPS = 8, B_WARPS = 4;
+constexpr int A_WARP0 = EPI_WARPS, B_WARP0 = A_WARP0 + A_WARPS, MMA_WARP = B_WARP0 + B_WARPS;
+constexpr int THREADS = (MMA_WARP + 1) * 32;
+constexpr int SUB_BYTES = 128 * 128;  // [128 rows x 64 k] f16, 128-byte rows, SWIZZLE_128B
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait. Returns false when another role aborted or the limit expired
+// (in which case it raises the abort flag itself).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+    if (mbar_try(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t i = 0;; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 63u) == 63u) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1u;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+    // K-major, SWIZZLE_128B: 8-row groups 1024 B apart (SBO), LBO unused (1), descriptor version 1
+    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ uint32_t make_idesc(int n, bool bf16) {
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// Position of element e (0..31) of a block in the permuted 16-bit layout:
+// chunk t = (e mod 16) / 4, slot order (4t, 4t+2, 16+4t, 16+4t+2, 4t+1, 4t+3, 16+4t+1, 16+4t+3).
+__host__ __device__ __forceinline__ int perm_pos(int e) {
+    const int hi = e >> 4, r = e & 15, t = r >> 2, m = r & 3;
+    const int slot = ((m & 1) ? 4 : 0) + (hi ? 2 : 0) + ((m >> 1) & 1);
+    return t * 8 + slot;
+}
+
+struct Args {
+    LayerDev L;
+    const int32_t* col_src_tok;  // gather table (gate/up mode) or nullptr (rows = columns)
+    const int4* tiles;
+    const int32_t* n_tiles;
+    const void* b_src;      // 16-bit activations [rows, kdim], permuted order
+    __half* out16;          // gate/up: S16 [C, I] permuted order; down: D16 [C, H] natural order
+    int32_t* status;
+    int kdim;               // H (gate/up) or I (down)
+    int out_ld;             // I or H
+};
+
+// Dequantise one lane's share of half a weight tile (16 rows x 64 k: blocks
+// 2*sub and 2*sub+1) into the operand tile: 4 chunks of 16 bytes (rows g, g+8).
+template <int Q>
+__device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32_t a_base, int rtl, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int bb = 0; bb < 2; ++bb) {
+        const int b = sub * 2 + bb;
+        uint32_t lo[4], hi[4];
+        unpack_block<Q>(w, b, lo, hi);
+        if (Q != BF16) {
+            const uint32_t s_g = (b < 2) ? w.s.x : w.s.y;
+            const uint32_t s_g8 = (b < 2) ? w.s.z : w.s.w;
+            const uint32_t sg2 = prmt(s_g, s_g, (b & 1) ? 0x3232u : 0x1010u);
+            const uint32_t sg82 = prmt(s_g8, s_g8, (b & 1) ? 0x3232u : 0x1010u);
+            lo[0] = hmul2_u32(lo[0], sg2);
+            hi[0] = hmul2_u32(hi[0], sg2);
+            lo[2] = hmul2_u32(lo[2], sg2);
+            hi[2] = hmul2_u32(hi[2], sg2);
+            lo[1] = hmul2_u32(lo[1], sg82);
+            hi[1] = hmul2_u32(hi[1], sg82);
+            lo[3] = hmul2_u32(lo[3], sg82);
+            hi[3] = hmul2_u32(hi[3], sg82);
+        }
+        const int c = bb * 4 + t;
+        const int r0 = rtl * 16 + g, r1 = r0 + 8;
+        sts128(a_base + r0 * 128 + ((c ^ (r0 & 7)) << 4), lo[0], hi[0], lo[2], hi[2]);
+        sts128(a_base + r1 * 128 + ((c ^ (r1 & 7)) << 4), lo[1], hi[1], lo[3], hi[3]);
+    }
+}
+
+template <int Q, int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
+    constexpr int NA = (MODE == 0) ? 2 : 1;
+    constexpr int STAGES = (MODE == 0) ? 4 : 6;       // one stage = 64 inputs (one swizzle atom in K)
+    constexpr int STAGE_BYTES = (NA + 1) * SUB_BYTES;  // A operand(s) then B
+    constexpr int ACC_COLS = NA * 128;
+    constexpr int TMEM_COLS = 2 * ACC_COLS;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ uint32_t abort_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    volatile uint32_t* abort_flag = &abort_s;
+
+    if (tid == 0) {
+        abort_s = 0u;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), A_WARPS * 32 + B_WARPS * 32);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&acc_full_bar[i]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[i]), EPI_WARPS * 32);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
+                     "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    const int ntiles = a.n_tiles[MODE];
+    const int kgs = a.kdim >> 7;   // 128-input groups (weight tile granularity)
+    const int khs = kgs * 2;       // 64-input pipeline stages per tile
+    const bool bf16_mode = (Q == BF16);
+
+    if (warp < EPI_WARPS) {
+        // ------------------------------ epilogue ------------------------------
+        const int row = warp * 32 + lane;
+        int tl = 0;
+        bool ok = true;
+        for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
+            const int4 tile = a.tiles[ti];
+            const int ncols = tile.z, ab = tl & 1, aph = (tl >> 1) & 1;
+            ok = mbar_wait(smem_u32(&acc_full_bar[ab]), aph, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + ab * ACC_COLS;
+            const int orow = tile.w * 128 + row;  // output row (I index or H index)
+            size_t ocol_off;
+            if (MODE == 0) ocol_off = (size_t)(orow & ~31) + perm_pos(orow & 31);
+            else ocol_off = (size_t)orow;
+            for (int n0 = 0; n0 < ncols; n0 += 16) {
+                uint32_t g[16], u[16];
+                tmem_ld16(taddr + n0, g);
+                if (MODE == 0) tmem_ld16(taddr + 128 + n0, u);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (n0 + j < ncols) {
+                        float v = __uint_as_float(g[j]);
+                        if (MODE == 0) {
+                            const float up = __uint_as_float(u[j]);
+                            v = (v / (1.0f + __expf(-v))) * up;
+                        }
+                        __half* dst = a.out16 + (size_t)(tile.y + n0 + j) * a.out_ld + ocol_off;
+                        if (MODE == 0 && bf16_mode)
+                            *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(v);
+                        else
+                            *dst = __float2half_rn(v);
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&acc_empty_bar[ab]));
+        }
+    } else if (warp < B_WARP0) {
+        // --------------------------- weight producers --------------------------
+        const int rtl = warp - A_WARP0;  // 16-row tile within the 128-row M tile
+        const int my_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const int ngroups = my_tiles * kgs;
+        WTile<Q> cur[NA], nxt[NA];
+        auto load_group = [&](int n, WTile<Q>(&dst)[NA]) {
+            const int4 tile = a.tiles[blockIdx.x + (n / kgs) * gridDim.x];
+            const int kg = n % kgs;
+            const int e = tile.x;
+            const int rt = tile.w * 8 + rtl;
+            if (MODE == 0) {
+                load_wtile<Q>(dst[0], a.L.gate_q(e), a.L.gate_s(e), rt * kgs + kg, lane);
+                load_wtile<Q>(dst[NA - 1], a.L.up_q(e), a.L.up_s(e), rt * kgs + kg, lane);
+            } else {
+                load_wtile<Q>(dst[0], a.L.down_q(e), a.L.down_s(e), rt * kgs + kg, lane);
+            }
+        };
+        if (ngroups > 0) load_group(0, cur);
+        bool ok = true;
+        int it = 0;
+        for (int n = 0; ok && n < ngroups; ++n) {
+            if (n + 1 < ngroups) load_group(n + 1, nxt);
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub, ++it) {
+                const int s = it % STAGES, ph = (it / STAGES) & 1;
+                ok = ok && mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
+                if (ok) {
+                    const uint32_t sbase = stage0 + s * STAGE_BYTES;
+#pragma unroll
+                    for (int op = 0; op < NA; ++op) dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
+                    fence_proxy_async();
+                    mbar_arrive(smem_u32(&full_bar[s]));
+                }
+            }
+            if (n + 1 < ngroups) {
+#pragma unroll
+                for (int op = 0; op < NA; ++op) cur[op] = nxt[op];
+            }
+        }
+    } else if (warp < MMA_WARP) {
+        // ------------------------- activation producers ------------------------
+        const int r = tid - B_WARP0 * 32;  // column within the tile = row of the B operand
+        const int my_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const int nitems = my_tiles * khs;
+        const uint8_t* src_row = nullptr;
+        bool valid = false;
+        bool ok = true;
+        int pending = -1;  // stage whose copies were issued but not yet published
+        for (int n = 0; ok && n < nitems; ++n) {
+            const int kh = n % khs;
+            if (kh == 0) {
+                const int4 tile = a.tiles[blockIdx.x + (n / khs) * gridDim.x];
+                valid = r < tile.z;
+                int srow = 0;
+                if (valid) srow = a.col_src_tok ? a.col_src_tok[tile.y + r] : (tile.y + r);
+                src_row = reinterpret_cast<const uint8_t*>(a.b_src) + (size_t)srow * a.kdim * 2;
+            }
+            // publish the previous stage once its copies have landed, then refill
+            if (pending >= 0) {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                fence_proxy_async();
+                mbar_arrive(smem_u32(&full_bar[pending]));
+                pending = -1;
+            }
+            const int s = n % STAGES, ph = (n / STAGES) & 1;
+            ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
+            if (!ok) break;
+            const uint32_t bbase = stage0 + s * STAGE_BYTES + NA * SUB_BYTES;
+            const uint8_t* src = src_row + (size_t)kh * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                cp_async16(bbase + r * 128 + ((c ^ (r & 7)) << 4), src + c * 16, valid ? 16u : 0u);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            pending = s;
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        if (ok && pending >= 0) {
+            fence_proxy_async();
+            mbar_arrive(smem_u32(&full_bar[pending]));
+        }
+    } else {
+        // -------------------------------- MMA ---------------------------------
+        if (lane == 0) {
+            int it = 0, tl = 0;
+            bool ok = true;
+            for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
+                const int4 tile = a.tiles[ti];
+                const int n16 = (tile.z + 15) & ~15;
+                const uint32_t idesc = make_idesc(n16, bf16_mode);
+                const int ab = tl & 1, aph = (tl >> 1) & 1;
+                ok = mbar_wait(smem_u32(&acc_empty_bar[ab]), aph ^ 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                for (int kh = 0; kh < khs; ++kh, ++it) {
+                    const int s = it % STAGES, ph = (it / STAGES) & 1;
+                    ok = mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sbase = stage0 + s * STAGE_BYTES;
+                    const uint32_t bbase = sbase + NA * SUB_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t bdesc = make_desc(bbase + j * 32);
+                        const uint32_t acc = (kh > 0 || j > 0) ? 1u : 0u;
+#pragma unroll
+                        for (int op = 0; op < NA; ++op) {
+                            const uint64_t adesc = make_desc(sbase + op * SUB_BYTES + j * 32);
+                            umma(tmem_base + ab * ACC_COLS + op * 128, adesc, bdesc, idesc, acc);
+                        }
+                    }
+                    umma_commit(smem_u32(&empty_bar[s]));
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&acc_full_bar[ab]));
+            }
+        }
+        __syncwarp();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
+                     : "memory");
+    }
+    if (tid == 0 && abort_s) atomicExch(a.status, 4);  // LUMEN_MOE_TIMEOUT
+}
+
+// activations -> 16-bit, permuted within each 32-block
+template <typename XT>
+__global__ void __launch_bounds__(256)
+permute_x16_kernel(const XT* __restrict__ x, size_t n, bool bf16_mode, uint16_t* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float v;
+    if (sizeof(XT) == 4) v = reinterpret_cast<const float*>(x)[i];
+    else v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]);
+    const size_t o = (i & ~(size_t)31) + perm_pos((int)(i & 31));
+    out[o] = bf16_mode ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+}
+
+}  // namespace tc
+
+cudaError_t launch_permute_x16(const void* x, int act_dtype, size_t n, bool bf16_mode, void* out, cudaStream_t st) {
+    count_launch();
+    if (act_dtype == 0)
+        tc::permute_x16_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const float*)x, n, bf16_mode,
+                                                                                   (uint16_t*)out);
+    else
+        tc::permute_x16_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+            (const __nv_bfloat16*)x, n, bf16_mode, (uint16_t*)out);
+    return cudaGetLastError();
+}
+
+template <int Q, int MODE>
+static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
+    constexpr int NA = (MODE == 0) ? 2 : 1;
+    constexpr int STAGES = (MODE == 0) ? 4 : 6;
+    const int smem = STAGES * (NA + 1) * tc::SUB_BYTES + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(tc::grouped_gemm_tc_kernel<Q, MODE>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    count_launch();
+    tc::grouped_gemm_tc_kernel<Q, MODE><<<grid, tc::THREADS, smem, st>>>(a);
+    return cudaGetLastError();
+}
+
+// gate/up + SwiGLU then down, both on tcgen05. x16: permuted 16-bit activations [T,H].
+cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st) {
+    const int C = p.T * p.K;
+    const int max_ct = C / 128 + p.L.E;
+    const int mt_gu = p.L.I / 128;
+    tc::Args gu{};
+    gu.L = p.L;
+    gu.col_src_tok = p.R.col_src_tok;
+    gu.tiles = p.tiles;
+    gu.n_tiles = p.n_tiles;
+    gu.b_src = x16;
+    gu.out16 = p.s16;
+    gu.status = p.status;
+    gu.kdim = p.L.H;
+    gu.out_ld = p.L.I;
+    tc::Args dn = gu;
+    dn.col_src_tok = nullptr;
+    dn.tiles = p.tiles + (size_t)max_ct * mt_gu;
+    dn.b_src = p.s16;
+    dn.out16 = p.d16;
+    dn.kdim = p.L.I;
+    dn.out_ld = p.L.H;
+    cudaError_t e;
+    switch (p.L.quant) {
+        case Q4_0:
+            e = launch_tc_one<Q4_0, 0>(gu, grid, st);
+            if (e != cudaSuccess) return e;
+            return launch_tc_one<Q4_0, 1>(dn, grid, st);
+        case Q8_0:
+            e = launch_tc_one<Q8_0, 0>(gu, grid, st);
+            if (e != cudaSuccess) return e;
+            return launch_tc_one<Q8_0, 1>(dn, grid, st);
+        default:
+            e = launch_tc_one<BF16, 0>(gu, grid, st);
+            if (e != cudaSuccess) return e;
+            return launch_tc_one<BF16, 1>(dn, grid, st);
+    }
+}
+
+}  // namespace lumen

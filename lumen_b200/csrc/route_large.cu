@@ -1,0 +1,328 @@
+// Routing and dispatch tables for multi-token batches (prefill), entirely on the
+// device: the reference does this part of encode_moe_ffn_prefill_grouped with a
+// blocking device-to-host copy, a host loop and four to six uploads per layer
+// (crates/lumen-runtime/src/cuda/moe.rs:2105-2207).
+//
+//   router_logits_large_kernel  logits[T,E] = X[T,H] W_r[E,H]^T, f32 accumulate
+//                               (moe_router_logits_batched, cuda/shaders/moe_grouped.cu:79)
+//   topk_large_kernel           one warp per token (router.cuh)
+//   sort_hist / sort_scan / sort_place
+//                               stable counting sort of (token, slot) pairs by
+//                               expert, tokens ascending then slots ascending:
+//                               expert_bounds, col_expert, col_src_tok, dst_to_col
+//                               exactly as cuda/moe.rs:2115-2147; sort_scan also
+//                               emits the list of experts with work and the tile
+//                               lists of the grouped GEMMs (cuda/moe.rs:2188-2207).
+//   scatter_accum_kernel        out[t] = residual[t] + sum_slot w[t,slot] * D[dst_to_col[t,slot]]
+//                               in slot order (moe_grouped_scatter_accum_q8_0,
+//                               cuda/shaders/moe_grouped.cu:493-517).
+#include "moe_internal.cuh"
+#include "router.cuh"
+#include "mma_frag.cuh"
+
+namespace lumen {
+
+// ---------------------------------------------------------------------------
+// logits: 64 tokens x 64 experts per CTA, BK = 32, 256 threads, 4x4 per thread
+// ---------------------------------------------------------------------------
+template <typename XT>
+__device__ __forceinline__ float x_to_f32(XT v);
+template <>
+__device__ __forceinline__ float x_to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float x_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename XT>
+__global__ void __launch_bounds__(256)
+router_logits_large_kernel(const XT* __restrict__ x, const float* __restrict__ w, float* __restrict__ logits,
+                           int T, int H, int E) {
+    constexpr int BM = 64, BN = 64, BK = 32;
+    __shared__ float xs[BK][BM + 1];
+    __shared__ float ws[BK][BN + 1];
+    const int tid = threadIdx.x;
+    const int t0 = blockIdx.x * BM, e0 = blockIdx.y * BN;
+    const int tx = tid & 15, ty = tid >> 4;  // tx: experts, ty: tokens
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    for (int k0 = 0; k0 < H; k0 += BK) {
+        for (int i = tid; i < BM * BK; i += 256) {
+            const int r = i / BK, c = i % BK;
+            const int t = t0 + r;
+            xs[c][r] = (t < T) ? x_to_f32<XT>(x[(size_t)t * H + k0 + c]) : 0.0f;
+        }
+        for (int i = tid; i < BN * BK; i += 256) {
+            const int r = i / BK, c = i % BK;
+            const int e = e0 + r;
+            ws[c][r] = (e < E) ? w[(size_t)e * H + k0 + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float xv[4], wv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) xv[i] = xs[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) wv[j] = ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = t0 + ty * 4 + i;
+        if (t >= T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = e0 + tx * 4 + j;
+            if (e < E) logits[(size_t)t * E + e] = acc[i][j];
+        }
+    }
+}
+
+constexpr int TK_WARPS = 4;
+__global__ void __launch_bounds__(TK_WARPS * 32)
+topk_large_kernel(const float* __restrict__ logits, int T, int E, int K, int gating,
+                  uint32_t* __restrict__ ids, float* __restrict__ weights) {
+    __shared__ float p_s[TK_WARPS][MAX_EXPERTS];
+    __shared__ float lg_s[TK_WARPS][MAX_EXPERTS];
+    __shared__ float sel_s[TK_WARPS][MAX_TOP_K];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * TK_WARPS + warp;
+    if (t >= T) return;
+    for (int i = lane; i < E; i += 32) lg_s[warp][i] = logits[(size_t)t * E + i];
+    __syncwarp();
+    warp_topk(lg_s[warp], E, K, gating, p_s[warp], sel_s[warp], ids + (size_t)t * K, weights + (size_t)t * K);
+}
+
+// ---------------------------------------------------------------------------
+// stable counting sort
+// ---------------------------------------------------------------------------
+constexpr int SORT_TOK = 32;  // tokens per chunk
+
+__global__ void __launch_bounds__(256)
+sort_hist_kernel(const uint32_t* __restrict__ ids, int T, int K, int E, int32_t* __restrict__ blk_hist) {
+    __shared__ int h[MAX_EXPERTS];
+    const int tid = threadIdx.x;
+    for (int e = tid; e < E; e += 256) h[e] = 0;
+    __syncthreads();
+    const int t0 = blockIdx.x * SORT_TOK;
+    const int n = min(SORT_TOK, T - t0) * K;
+    for (int p = tid; p < n; p += 256) atomicAdd(&h[ids[(size_t)t0 * K + p]], 1);
+    __syncthreads();
+    for (int e = tid; e < E; e += 256) blk_hist[(size_t)blockIdx.x * E + e] = h[e];
+}
+
+// One CTA of 256 threads (E <= 256). tile entry: {expert, col_start, ncols, m_tile}.
+__global__ void __launch_bounds__(256)
+sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R, int tile_cols,
+                 int mt_gu, int mt_dn, int4* __restrict__ tiles_gu, int4* __restrict__ tiles_dn,
+                 int32_t* __restrict__ n_tiles, int max_tiles_gu, int max_tiles_dn) {
+    __shared__ int cnt_s[MAX_EXPERTS];
+    __shared__ int bounds_s[MAX_EXPERTS + 1];
+    __shared__ int tile_off_s[MAX_EXPERTS + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid < E) {
+        int run = 0;
+        for (int b = 0; b < nchunks; ++b) {
+            const int v = blk_hist[(size_t)b * E + tid];
+            blk_hist[(size_t)b * E + tid] = run;
+            run += v;
+        }
+        cnt_s[tid] = run;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int local[8], ltiles[8], lsum = 0, lnz = 0, ltl = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int ee = lane * 8 + j;
+            local[j] = (ee < E) ? cnt_s[ee] : 0;
+            ltiles[j] = (local[j] + tile_cols - 1) / tile_cols;
+            lsum += local[j];
+            lnz += (local[j] > 0);
+            ltl += ltiles[j];
+        }
+        int isum = lsum, inz = lnz, itl = ltl;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v1 = __shfl_up_sync(0xffffffffu, isum, o);
+            const int v2 = __shfl_up_sync(0xffffffffu, inz, o);
+            const int v3 = __shfl_up_sync(0xffffffffu, itl, o);
+            if (lane >= o) {
+                isum += v1;
+                inz += v2;
+                itl += v3;
+            }
+        }
+        int run = isum - lsum, unz = inz - lnz, trun = itl - ltl;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int ee = lane * 8 + j;
+            if (ee < E) {
+                bounds_s[ee] = run;
+                tile_off_s[ee] = trun;
+                R.expert_bounds[ee] = run;
+                if (local[j] > 0) R.uexp[unz++] = ee;
+                run += local[j];
+                trun += ltiles[j];
+            }
+        }
+        if (lane == 31) {
+            bounds_s[E] = isum;
+            tile_off_s[E] = itl;
+            R.expert_bounds[E] = isum;
+            *R.n_uexp = inz;
+            n_tiles[0] = min(itl * mt_gu, max_tiles_gu);
+            n_tiles[1] = min(itl * mt_dn, max_tiles_dn);
+        }
+    }
+    __syncthreads();
+    if (tiles_gu != nullptr && tid < E) {
+        // column tiles of this expert; m-tile is the fastest index so that CTAs
+        // running side by side share the same activation tile
+        const int c0 = bounds_s[tid], n = cnt_s[tid];
+        const int ct0 = tile_off_s[tid], nct = tile_off_s[tid + 1] - ct0;
+        for (int ct = 0; ct < nct; ++ct) {
+            const int cs = c0 + ct * tile_cols;
+            const int nc = min(tile_cols, n - ct * tile_cols);
+            for (int mt = 0; mt < mt_gu; ++mt) {
+                const int idx = (ct0 + ct) * mt_gu + mt;
+                if (idx < max_tiles_gu) tiles_gu[idx] = make_int4(tid, cs, nc, mt);
+            }
+            for (int mt = 0; mt < mt_dn; ++mt) {
+                const int idx = (ct0 + ct) * mt_dn + mt;
+                if (idx < max_tiles_dn) tiles_dn[idx] = make_int4(tid, cs, nc, mt);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256)
+sort_place_kernel(const uint32_t* __restrict__ ids, int T, int K, int E, const int32_t* __restrict__ blk_hist,
+                  RouteDev R) {
+    __shared__ int ids_s[SORT_TOK * MAX_TOP_K];
+    const int tid = threadIdx.x;
+    const int t0 = blockIdx.x * SORT_TOK;
+    const int n = min(SORT_TOK, T - t0) * K;
+    for (int p = tid; p < n; p += 256) ids_s[p] = (int)ids[(size_t)t0 * K + p];
+    __syncthreads();
+    if (tid < E) {
+        int cur = R.expert_bounds[tid] + blk_hist[(size_t)blockIdx.x * E + tid];
+        for (int p = 0; p < n; ++p) {
+            if (ids_s[p] == tid) {
+                R.col_expert[cur] = tid;
+                R.col_src_tok[cur] = t0 + p / K;
+                R.dst_to_col[(size_t)t0 * K + p] = cur;
+                ++cur;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// activation fragments for the mma.sync grouped path (any T)
+// ---------------------------------------------------------------------------
+template <typename XT>
+__global__ void __launch_bounds__(256)
+build_xf_kernel(const XT* __restrict__ x, int T, int H, int nblk_pad, bool bf16_mode, uint4* __restrict__ xf) {
+    const int nblk = H >> 5;
+    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    const size_t total = (size_t)T * nblk * 8;
+    if (idx >= total) return;
+    const int sub = (int)(idx & 7), hl = sub >> 2, t4 = sub & 3;
+    const size_t item = idx >> 3;
+    const int t = (int)(item / nblk), b = (int)(item % nblk);
+    const XT* xr = x + (size_t)t * H + b * 32;
+    float4 lo4, hi4;
+    lo4.x = x_to_f32<XT>(xr[4 * t4]);
+    lo4.y = x_to_f32<XT>(xr[4 * t4 + 1]);
+    lo4.z = x_to_f32<XT>(xr[4 * t4 + 2]);
+    lo4.w = x_to_f32<XT>(xr[4 * t4 + 3]);
+    hi4.x = x_to_f32<XT>(xr[16 + 4 * t4]);
+    hi4.y = x_to_f32<XT>(xr[16 + 4 * t4 + 1]);
+    hi4.z = x_to_f32<XT>(xr[16 + 4 * t4 + 2]);
+    hi4.w = x_to_f32<XT>(xr[16 + 4 * t4 + 3]);
+    xf[((size_t)(t * 2 + hl) * nblk_pad + b) * 4 + t4] = make_act_frag(lo4, hi4, hl, bf16_mode);
+}
+
+// ---------------------------------------------------------------------------
+// scatter-accumulate
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+scatter_accum_kernel(const __half* __restrict__ d16, const float* __restrict__ residual,
+                     const float* __restrict__ weights, const int32_t* __restrict__ dst_to_col,
+                     float* __restrict__ out, int T, int H, int K) {
+    const int t = blockIdx.y;
+    const int h2 = blockIdx.x * 256 + threadIdx.x;  // pair index
+    if (h2 * 2 >= H) return;
+    const size_t o = (size_t)t * H + h2 * 2;
+    float2 acc = *reinterpret_cast<const float2*>(residual + o);
+    for (int slot = 0; slot < K; ++slot) {
+        const int col = dst_to_col[(size_t)t * K + slot];
+        const float w = weights[(size_t)t * K + slot];
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(d16 + (size_t)col * H + h2 * 2));
+        acc.x = __fadd_rn(acc.x, __fmul_rn(w, d.x));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(w, d.y));
+    }
+    *reinterpret_cast<float2*>(out + o) = acc;
+}
+
+cudaError_t launch_scatter_accum(const __half* d16, const float* residual, const RouteDev& R, float* out,
+                                 int T, int H, int K, cudaStream_t st) {
+    count_launch();
+    scatter_accum_kernel<<<dim3((H / 2 + 255) / 256, T), 256, 0, st>>>(d16, residual, R.weights, R.dst_to_col,
+                                                                       out, T, H, K);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_build_xf(const void* x, int act_dtype, int T, int H, int nblk_pad, bool bf16_mode,
+                            uint4* xf, cudaStream_t st) {
+    const size_t total = (size_t)T * (H / 32) * 8;
+    count_launch();
+    if (act_dtype == 0)
+        build_xf_kernel<float><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const float*)x, T, H, nblk_pad,
+                                                                               bf16_mode, xf);
+    else
+        build_xf_kernel<__nv_bfloat16><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+            (const __nv_bfloat16*)x, T, H, nblk_pad, bf16_mode, xf);
+    return cudaGetLastError();
+}
+
+// Router + tables for any T. tile lists are optional (tiles == nullptr skips them).
+cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
+    const int T = a.T, E = a.L.E, H = a.L.H, K = a.K;
+    const float* lg = a.logits_override;
+    if (lg == nullptr) {
+        const dim3 grid((T + 63) / 64, (E + 63) / 64);
+        count_launch();
+        if (a.act_dtype == 0)
+            router_logits_large_kernel<float><<<grid, 256, 0, st>>>((const float*)a.x, a.L.router_w, a.R.logits, T, H, E);
+        else
+            router_logits_large_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a.x, a.L.router_w,
+                                                                           a.R.logits, T, H, E);
+        lg = a.R.logits;
+    }
+    count_launch(4);
+    topk_large_kernel<<<(T + TK_WARPS - 1) / TK_WARPS, TK_WARPS * 32, 0, st>>>(lg, T, E, K, a.gating, a.R.ids,
+                                                                               a.R.weights);
+    const int nchunks = (T + SORT_TOK - 1) / SORT_TOK;
+    sort_hist_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist);
+    const int C = T * K;
+    const int tile_cols = 128;
+    const int max_ct = C / tile_cols + E;
+    const int mt_gu = a.L.I / 128, mt_dn = a.L.H / 128;
+    int4* tiles_gu = a.tiles;
+    int4* tiles_dn = a.tiles ? a.tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1) : nullptr;
+    sort_scan_kernel<<<1, 256, 0, st>>>(a.blk_hist, nchunks, E, a.R, tile_cols, mt_gu, mt_dn, tiles_gu, tiles_dn,
+                                        a.n_tiles, max_ct * mt_gu, max_ct * mt_dn);
+    sort_place_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist, a.R);
+    return cudaGetLastError();
+}
+
+}  // namespace lumen

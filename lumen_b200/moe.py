@@ -1,0 +1,280 @@
+"""Host-side mirror of the reference's MoE operator interface
+(crates/lumen-runtime/src/cuda/moe.rs) on top of the C ABI (include/lumen_moe.h).
+
+PyTorch is used for device memory and streams only; every computation is a call
+into liblumen_moe_b200.so. Names follow the reference:
+
+    allocate_moe_scratch(...)            -> MoeScratch      (cuda/moe.rs:968)
+    build_moe_meta(...)                  -> MoeMeta         (cuda/moe.rs:223)
+    MoeScratch.prepare_layer(...)        -> MoeLayer        (build_batched_offsets :272 + build_repacked_down :337)
+    encode_moe_ffn_decode(...)                              (cuda/moe.rs:1119)
+    encode_moe_ffn_decode_fused_norm(...)                   (cuda/moe.rs:3184)
+    encode_moe_ffn_prefill_grouped(...)                     (cuda/moe.rs:1900)
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import (ACT_BF16, ACT_F32, BF16, Q4_0, Q8_0, SIGMOID_RENORM, SOFTMAX_RENORM, LumenMoeError, MoeConfig,
+                   check)
+
+__all__ = ["MoeMeta", "MoeScratch", "MoeLayer", "allocate_moe_scratch", "build_moe_meta", "encode_moe_ffn_decode",
+           "encode_moe_ffn_decode_fused_norm", "encode_moe_ffn_prefill_grouped", "LumenMoeError", "Q8_0", "Q4_0",
+           "BF16", "SOFTMAX_RENORM", "SIGMOID_RENORM"]
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise LumenMoeError(_lib.INVALID_ARG, f"{name} must be a CUDA tensor (no CPU path)")
+    if t.dtype != dtype or not t.is_contiguous():
+        raise LumenMoeError(_lib.INVALID_ARG, f"{name} must be contiguous {dtype}")
+    return t
+
+
+@dataclass
+class MoeMeta:
+    """CudaMoeMeta (cuda/moe.rs:39-59): byte offsets inside the layer blob."""
+    router_weight_off: int
+    expert_gate_offs: np.ndarray
+    expert_up_offs: np.ndarray
+    expert_down_offs: np.ndarray
+    expert_gate_quant: int
+    expert_down_quant: int
+
+
+def build_moe_meta(router_weight_off: Optional[int], experts: Optional[Sequence[dict]]) -> Optional[MoeMeta]:
+    """build_moe_meta (cuda/moe.rs:223-260). `experts` is a list of
+    {"gate": (offset, quant), "up": (...), "down": (...)}; returns None when the
+    layer has no router or no experts (not an MoE layer), like the reference."""
+    if router_weight_off is None or not experts:
+        return None
+    return MoeMeta(int(router_weight_off),
+                   np.array([e["gate"][0] for e in experts], dtype=np.uint64),
+                   np.array([e["up"][0] for e in experts], dtype=np.uint64),
+                   np.array([e["down"][0] for e in experts], dtype=np.uint64),
+                   int(experts[0]["gate"][1]), int(experts[0]["down"][1]))
+
+
+class MoeLayer:
+    """Prepared layer: device offset tables + repacked expert planes."""
+
+    def __init__(self, handle: int, blob: torch.Tensor, meta: MoeMeta):
+        self._h = handle
+        self.blob = blob  # keeps the caller's blob alive: the router weight is read in place
+        self.meta = meta
+
+    @property
+    def device_bytes(self) -> int:
+        return int(_lib.lib().lumen_moe_layer_bytes(self._h))
+
+    def close(self) -> None:
+        if self._h:
+            _lib.lib().lumen_moe_layer_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class MoeScratch:
+    """CudaMoeScratch (cuda/moe.rs:101-210) behind lumen_moe_ctx."""
+
+    def __init__(self, hidden_dim: int, inter_dim: int, num_experts: int, top_k: int, max_tokens: int = 16,
+                 gating_mode: int = SOFTMAX_RENORM, device: int = 0):
+        self.H, self.I, self.E, self.K = hidden_dim, inter_dim, num_experts, top_k
+        self.device = device
+        cfg = MoeConfig(hidden_dim, inter_dim, num_experts, top_k, max_tokens, gating_mode, device, 0)
+        h = ctypes.c_void_p()
+        check(_lib.lib().lumen_moe_create(ctypes.byref(cfg), ctypes.byref(h)))
+        self._h = h.value
+        self._override = None
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            _lib.lib().lumen_moe_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- preload ----------------------------------------------------------
+    def prepare_layer(self, blob: torch.Tensor, meta: MoeMeta) -> MoeLayer:
+        _need(blob, torch.uint8, "layer blob")
+        if meta.expert_gate_quant != meta.expert_down_quant:
+            raise LumenMoeError(_lib.UNSUPPORTED, "gate and down quant schemes differ")
+        go = np.ascontiguousarray(meta.expert_gate_offs, dtype=np.uint64)
+        uo = np.ascontiguousarray(meta.expert_up_offs, dtype=np.uint64)
+        do = np.ascontiguousarray(meta.expert_down_offs, dtype=np.uint64)
+        if not (len(go) == len(uo) == len(do) == self.E):
+            raise LumenMoeError(_lib.INVALID_ARG, "offset tables must have num_experts entries")
+        h = ctypes.c_void_p()
+        check(_lib.lib().lumen_moe_layer_prepare(self._h, blob.data_ptr(), blob.numel(), meta.router_weight_off,
+                                                 go.ctypes.data, uo.ctypes.data, do.ctypes.data,
+                                                 meta.expert_gate_quant, _stream(), ctypes.byref(h)))
+        return MoeLayer(h.value, blob, meta)
+
+    def ensure_prefill_grouped(self, batch: int) -> None:
+        check(_lib.lib().lumen_moe_ensure_prefill(self._h, batch))
+
+    # -- operators --------------------------------------------------------
+    def decode(self, layer: MoeLayer, normed_x: torch.Tensor, residual: torch.Tensor,
+               output_x: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _need(normed_x, torch.float32, "normed_x")
+        _need(residual, torch.float32, "residual")
+        T = normed_x.numel() // self.H
+        if output_x is None:
+            output_x = torch.empty_like(residual)
+        _need(output_x, torch.float32, "output_x")
+        check(_lib.lib().lumen_moe_decode(self._h, layer._h, normed_x.data_ptr(), residual.data_ptr(),
+                                          output_x.data_ptr(), T, _stream()))
+        return output_x
+
+    def decode_fused_norm(self, layer: MoeLayer, attn_proj: torch.Tensor, ffn_norm: torch.Tensor, eps: float,
+                          normed_x: Optional[torch.Tensor] = None,
+                          output_x: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _need(attn_proj, torch.float32, "attn_proj")
+        _need(ffn_norm, torch.float32, "ffn_norm")
+        T = attn_proj.numel() // self.H
+        if output_x is None:
+            output_x = torch.empty_like(attn_proj)
+        check(_lib.lib().lumen_moe_decode_fused_norm(self._h, layer._h, attn_proj.data_ptr(), ffn_norm.data_ptr(),
+                                                     _ptr(normed_x), output_x.data_ptr(), eps, T, _stream()))
+        return output_x
+
+    def prefill(self, layer: MoeLayer, normed: torch.Tensor, residual: torch.Tensor,
+                output: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if normed.dtype == torch.float32:
+            act = ACT_F32
+        elif normed.dtype == torch.bfloat16:
+            act = ACT_BF16
+        else:
+            raise LumenMoeError(_lib.UNSUPPORTED, "activations must be float32 or bfloat16")
+        _need(normed, normed.dtype, "normed")
+        _need(residual, torch.float32, "residual")
+        T = normed.numel() // self.H
+        if output is None:
+            output = torch.empty_like(residual)
+        check(_lib.lib().lumen_moe_prefill(self._h, layer._h, normed.data_ptr(), residual.data_ptr(),
+                                           output.data_ptr(), T, act, _stream()))
+        return output
+
+    def route_only(self, layer: MoeLayer, normed_x: torch.Tensor, want_logits: bool = False):
+        _need(normed_x, torch.float32, "normed_x")
+        T = normed_x.numel() // self.H
+        ids = torch.empty((T, self.K), dtype=torch.int32, device=normed_x.device)
+        w = torch.empty((T, self.K), dtype=torch.float32, device=normed_x.device)
+        lg = torch.empty((T, self.E), dtype=torch.float32, device=normed_x.device) if want_logits else None
+        check(_lib.lib().lumen_moe_route_only(self._h, layer._h, normed_x.data_ptr(), T, ids.data_ptr(),
+                                              w.data_ptr(), _ptr(lg), _stream()))
+        return (ids, w, lg) if want_logits else (ids, w)
+
+    def topk_from_logits(self, logits: torch.Tensor):
+        _need(logits, torch.float32, "logits")
+        T = logits.numel() // self.E
+        ids = torch.empty((T, self.K), dtype=torch.int32, device=logits.device)
+        w = torch.empty((T, self.K), dtype=torch.float32, device=logits.device)
+        check(_lib.lib().lumen_moe_topk_from_logits(self._h, logits.data_ptr(), T, ids.data_ptr(), w.data_ptr(),
+                                                    _stream()))
+        return ids, w
+
+    def set_logits_override(self, logits: Optional[torch.Tensor]) -> None:
+        if logits is not None:
+            _need(logits, torch.float32, "logits")
+        self._override = logits
+        check(_lib.lib().lumen_moe_set_logits_override(self._h, _ptr(logits)))
+
+    def get_routing(self, tokens: int):
+        C = tokens * self.K
+        ids = np.zeros((tokens, self.K), np.uint32)
+        w = np.zeros((tokens, self.K), np.float32)
+        d2c = np.zeros(C, np.int32)
+        cst = np.zeros(C, np.int32)
+        bounds = np.zeros(self.E + 1, np.int32)
+        check(_lib.lib().lumen_moe_get_routing(self._h, tokens, ids.ctypes.data, w.ctypes.data, d2c.ctypes.data,
+                                               cst.ctypes.data, bounds.ctypes.data, _stream()))
+        return {"ids": ids, "weights": w, "dst_to_col": d2c, "col_src_tok": cst, "expert_bounds": bounds}
+
+    def debug_decode_phase(self, layer: MoeLayer, phase: int) -> None:
+        check(_lib.lib().lumen_moe_debug_decode_phase(self._h, layer._h, phase, _stream()))
+
+    def stack_decode(self, layers: Sequence[MoeLayer], gammas: Sequence[torch.Tensor], x: torch.Tensor,
+                     eps: float) -> torch.Tensor:
+        _need(x, torch.float32, "x")
+        n = len(layers)
+        lh = (ctypes.c_void_p * n)(*[l._h for l in layers])
+        gp = (ctypes.c_void_p * n)(*[g.data_ptr() for g in gammas])
+        T = x.numel() // self.H
+        check(_lib.lib().lumen_moe_stack_decode(self._h, lh, gp, n, x.data_ptr(), eps, T, _stream()))
+        return x
+
+
+def allocate_moe_scratch(hidden_dim: int, expert_inter_dim: int, num_experts: int, top_k: int,
+                         max_tokens: int = 16, gating_mode: int = SOFTMAX_RENORM, device: int = 0) -> MoeScratch:
+    """allocate_moe_scratch (cuda/moe.rs:968)."""
+    return MoeScratch(hidden_dim, expert_inter_dim, num_experts, top_k, max_tokens, gating_mode, device)
+
+
+def encode_moe_ffn_decode(scratch: MoeScratch, layer: MoeLayer, normed_x, residual, output_x):
+    """encode_moe_ffn_decode (cuda/moe.rs:1119): output_x = residual + MoE(normed_x)."""
+    return scratch.decode(layer, normed_x, residual, output_x)
+
+
+def encode_moe_ffn_decode_fused_norm(scratch: MoeScratch, layer: MoeLayer, attn_proj, ffn_norm, normed_x, output_x,
+                                     eps: float):
+    """encode_moe_ffn_decode_fused_norm (cuda/moe.rs:3184)."""
+    return scratch.decode_fused_norm(layer, attn_proj, ffn_norm, eps, normed_x, output_x)
+
+
+def encode_moe_ffn_prefill_grouped(scratch: MoeScratch, layer: MoeLayer, normed, residual, output):
+    """encode_moe_ffn_prefill_grouped (cuda/moe.rs:1900)."""
+    return scratch.prefill(layer, normed, residual, output)
+
+
+def quantize(src: torch.Tensor, quant: int) -> torch.Tensor:
+    """Device quantiser (crates/lumen-convert/src/dequant.rs:791-906); returns raw bytes."""
+    _need(src, torch.float32, "src")
+    n = src.numel()
+    nbytes = {Q8_0: n // 32 * 34, Q4_0: n // 32 * 18, BF16: n * 2}[quant]
+    dst = torch.empty(nbytes, dtype=torch.uint8, device=src.device)
+    check(_lib.lib().lumen_moe_quantize(src.data_ptr(), n, quant, dst.data_ptr(), _stream()))
+    return dst
+
+
+def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
+    _need(x, torch.float32, "x")
+    out = torch.empty_like(x)
+    H = gamma.numel()
+    check(_lib.lib().lumen_moe_rmsnorm(x.data_ptr(), gamma.data_ptr(), out.data_ptr(), x.numel() // H, H, eps,
+                                       _stream()))
+    return out
+
+
+def debug_expf(x: torch.Tensor) -> torch.Tensor:
+    _need(x, torch.float32, "x")
+    out = torch.empty_like(x)
+    check(_lib.lib().lumen_moe_debug_expf(x.data_ptr(), out.data_ptr(), x.numel(), _stream()))
+    return out
+
+
+def launch_count(reset: bool = False) -> int:
+    return int(_lib.lib().lumen_moe_launch_count(1 if reset else 0))

@@ -206,17 +206,35 @@ def run_gpu(args):
 
     for _ in range(max(3, args.warmup)):
         step()
+    # The 3*L launches of a step are replayed from one CUDA graph (the reference's
+    # backend enqueues them from Rust; a Python loop would time the interpreter).
+    launches_per_step = 3 * L
+    step_eager = step
+    if not args.no_graph:
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        moe.launch_count(reset=True)
+        with torch.cuda.graph(graph):
+            step()
+        launches_per_step = moe.launch_count(reset=True)
+        step = graph.replay
+        for _ in range(3):
+            step()
     # distinct experts per call (for the algorithmic byte count)
     U = []
+    torch.cuda.synchronize()
     for l in range(L):
         scratch.decode(layers[l], x, x, outs[l])
         U.append(len(np.unique(scratch.get_routing(T)["ids"])))
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    moe.launch_count(reset=True)
     ms = timed(step, args.steps)
-    launches = moe.launch_count(reset=True)
+    launches = launches_per_step * args.steps
     clocks = sampler.stop() if rank == 0 else None
     ms_e2e = timed(step_e2e, args.steps)
     units = args.steps * L * T * world
@@ -274,6 +292,7 @@ def main():
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--quant", default="q4_0", choices=sorted(QUANTS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

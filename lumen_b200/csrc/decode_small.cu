@@ -1,0 +1,317 @@
+// Latency-optimised expert kernels for decode batches of 1..4 tokens (every
+// expert then has at most 4 columns = one MMA column group).
+//
+// The general kernels in decode.cu stream a few weight tiles per warp; at batch 1
+// the whole layer is only 22 MB, so what counts is to have EVERY byte of a
+// kernel's weights requested before the first one is consumed, in a single wave
+// of CTAs. Here each warp issues all of its 128-bit weight loads up front
+// (registers are the staging buffer), the activation fragments of the expert's
+// tokens are staged once per CTA in shared memory, and only then does the
+// tensor-core loop start.
+//
+//   gate_up_small_kernel   CTA = (16 rows of I, distinct expert); WARPS warps split
+//                          the H/128 input groups, ITERS groups each, all loaded first
+//                          (cuda/shaders/moe_expert_q4_0.cu:58-108; moe_expert.cu:62-97)
+//   down_small_kernel      CTA = 16 rows of H; warp w walks experts w, w+8, ... with a
+//                          ring of RB weight tiles in flight; weighted combine in slot
+//                          order at the end (moe_expert_q4_0.cu:118-151;
+//                          cuda/shaders/moe_accum.cu:22-46)
+#include "mma_frag.cuh"
+
+namespace lumen {
+
+namespace {
+
+__device__ __forceinline__ void pdl_wait_() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger_() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ int frag_pos_(int r) {
+    const int m = r & 3;
+    return (m == 0) ? 0 : (m == 2) ? 1 : (m == 1) ? 2 : 3;
+}
+
+__device__ __forceinline__ uint4 lds128(const uint4* p) { return *p; }
+
+template <int Q>
+struct SmallCfg;
+template <>
+struct SmallCfg<Q4_0> {
+    static constexpr int GU_WARPS = 4, GU_ITERS = 4, DN_RING = 6;
+};
+template <>
+struct SmallCfg<Q8_0> {
+    static constexpr int GU_WARPS = 8, GU_ITERS = 2, DN_RING = 3;
+};
+template <>
+struct SmallCfg<BF16> {
+    static constexpr int GU_WARPS = 16, GU_ITERS = 1, DN_RING = 2;
+};
+
+// One block (two MMAs) of one column group with the B fragment taken from shared memory.
+template <int Q>
+__device__ __forceinline__ void block_mma_smem(const WTile<Q>& w, int b, const uint4* bsm, bool bvalid,
+                                               float (&acc)[4]) {
+    uint32_t a_lo[4], a_hi[4];
+    unpack_block<Q>(w, b, a_lo, a_hi);
+    const float2 sc = block_scales<Q>(w, b);
+    uint4 bf = make_uint4(0u, 0u, 0u, 0u);
+    if (bvalid) bf = lds128(bsm + b * 4);
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    if (Q == BF16) {
+        mma_bf16(c, a_lo, bf.x, bf.y);
+        mma_bf16(c, a_hi, bf.z, bf.w);
+    } else {
+        mma_f16(c, a_lo, bf.x, bf.y);
+        mma_f16(c, a_hi, bf.z, bf.w);
+    }
+    acc[0] = fmaf(sc.x, c[0], acc[0]);
+    acc[1] = fmaf(sc.x, c[1], acc[1]);
+    acc[2] = fmaf(sc.y, c[2], acc[2]);
+    acc[3] = fmaf(sc.y, c[3], acc[3]);
+}
+
+}  // namespace
+
+template <int Q>
+__global__ void __launch_bounds__(SmallCfg<Q>::GU_WARPS * 32)
+gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
+    constexpr int WARPS = SmallCfg<Q>::GU_WARPS, ITERS = SmallCfg<Q>::GU_ITERS;
+    extern __shared__ uint4 xs[];  // [4 columns][2][nblk_pad][4]
+    __shared__ float red[WARPS][16][4][2];
+    pdl_trigger_();
+    pdl_wait_();
+    const int u = blockIdx.y;
+    if (u >= *a.R.n_uexp) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, t4 = lane & 3;
+    const int rt = blockIdx.x;
+    const int e = a.R.uexp[u];
+    const int c0 = a.R.expert_bounds[e];
+    const int ncol = min(4, a.R.expert_bounds[e + 1] - c0);
+    const int kg_h = a.L.kg_h, I = a.L.I;
+    const int nblk_pad = kg_h * 4, nblk_i_pad = a.L.kg_i * 4;
+
+    // every weight byte of this warp is requested now
+    WTile<Q> wg[ITERS], wu[ITERS];
+    {
+        const uint4* gq_base = a.L.gate_q(e);
+        const uint4* uq_base = a.L.up_q(e);
+        const uint4* gs_base = a.L.gate_s(e);
+        const uint4* us_base = a.L.up_s(e);
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+            const int kg = warp + it * WARPS;
+            if (kg < kg_h) {
+                load_wtile<Q>(wg[it], gq_base, gs_base, rt * kg_h + kg, lane);
+                load_wtile<Q>(wu[it], uq_base, us_base, rt * kg_h + kg, lane);
+            }
+        }
+    }
+    // stage the activation fragments of this expert's tokens
+    const int per_col = 2 * nblk_pad * 4;
+    for (int j = 0; j < ncol; ++j) {
+        const int tok = a.R.col_src_tok[c0 + j];
+        const uint4* src = a.xf + (size_t)tok * per_col;
+        for (int i = tid; i < per_col; i += WARPS * 32) xs[j * per_col + i] = __ldg(src + i);
+    }
+    __syncthreads();
+
+    const int jcol = gq >> 1;
+    const bool bvalid = jcol < ncol;
+    const uint4* bbase = xs + ((size_t)(jcol * 2 + (gq & 1)) * nblk_pad) * 4 + t4;
+    float acc_g[4] = {0.f, 0.f, 0.f, 0.f}, acc_u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int kg = warp + it * WARPS;
+        if (kg < kg_h) {
+            const uint4* bp = bbase + (size_t)kg * 16;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                block_mma_smem<Q>(wg[it], b, bp, bvalid, acc_g);
+                block_mma_smem<Q>(wu[it], b, bp, bvalid, acc_u);
+            }
+        }
+    }
+    red[warp][gq][t4][0] = acc_g[0] + acc_g[1];
+    red[warp][gq][t4][1] = acc_u[0] + acc_u[1];
+    red[warp][gq + 8][t4][0] = acc_g[2] + acc_g[3];
+    red[warp][gq + 8][t4][1] = acc_u[2] + acc_u[3];
+    __syncthreads();
+    if (tid < 64) {
+        const int row = tid & 15, tokc = tid >> 4;
+        if (tokc < ncol) {
+            float gate = 0.0f, up = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                gate += red[w][row][tokc][0];
+                up += red[w][row][tokc][1];
+            }
+            const float sv = (gate / (1.0f + expf(-gate))) * up;
+            const int col = c0 + tokc;
+            const int irow = rt * 16 + row;
+            if (a.s_f32 != nullptr) a.s_f32[(size_t)col * I + irow] = sv;
+            unsigned short hi_bits, lo_bits;
+            if (Q != BF16) {
+                const __half h = __float2half_rn(sv);
+                const __half l = __float2half_rn(sv - __half2float(h));
+                hi_bits = __half_as_ushort(h);
+                lo_bits = __half_as_ushort(l);
+            } else {
+                const __nv_bfloat16 h = __float2bfloat16_rn(sv);
+                const __nv_bfloat16 l = __float2bfloat16_rn(sv - __bfloat162float(h));
+                hi_bits = __bfloat16_as_ushort(h);
+                lo_bits = __bfloat16_as_ushort(l);
+            }
+            const int blk = irow >> 5, within = irow & 31, j = within >> 4, r16 = within & 15;
+            unsigned short* sf16 = reinterpret_cast<unsigned short*>(a.sf);
+            const size_t in_vec = (size_t)j * 4 + frag_pos_(r16);
+            sf16[(((size_t)(col * 2 + 0) * nblk_i_pad + blk) * 4 + (r16 >> 2)) * 8 + in_vec] = hi_bits;
+            sf16[(((size_t)(col * 2 + 1) * nblk_i_pad + blk) * 4 + (r16 >> 2)) * 8 + in_vec] = lo_bits;
+        }
+    }
+}
+
+constexpr int DS_WARPS = 8;
+
+template <int Q>
+__global__ void __launch_bounds__(DS_WARPS * 32)
+down_small_kernel(const __grid_constant__ DecodeArgs a) {
+    constexpr int RB = SmallCfg<Q>::DN_RING;
+    extern __shared__ uint4 ss[];  // [C columns][2][nblk_i_pad][4], then float dsm[C][16]
+    pdl_trigger_();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, t4 = lane & 3;
+    const int rt = blockIdx.x;
+    const int kg_i = a.L.kg_i, H = a.L.H, K = a.K, T = a.T;
+    const int nblk_i_pad = kg_i * 4;
+    const int C = T * K;
+    const int per_col = 2 * nblk_i_pad * 4;
+    float* dsm = reinterpret_cast<float*>(ss + (size_t)C * per_col);
+    pdl_wait_();
+    const int U = *a.R.n_uexp;
+
+    const int n_exp_w = (U > warp) ? (U - warp + DS_WARPS - 1) / DS_WARPS : 0;
+    const int nitems = n_exp_w * kg_i;
+    auto load_item = [&](int n, WTile<Q>& dst) {
+        const int uu = warp + DS_WARPS * (n / kg_i), kg = n % kg_i;
+        const int ee = a.R.uexp[uu];
+        load_wtile<Q>(dst, a.L.down_q(ee), a.L.down_s(ee), rt * kg_i + kg, lane);
+    };
+    WTile<Q> ring[RB];
+#pragma unroll
+    for (int i = 0; i < RB; ++i)
+        if (i < nitems) load_item(i, ring[i]);
+
+    // stage all SwiGLU fragments (written by the previous kernel)
+    for (int i = tid; i < C * per_col; i += DS_WARPS * 32) ss[i] = a.sf[i];
+    __syncthreads();
+
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int c0 = 0, ncol = 0;
+    const uint4* bbase = ss;
+    bool bvalid = false;
+    for (int n0 = 0; n0 < nitems; n0 += RB) {
+#pragma unroll
+        for (int i = 0; i < RB; ++i) {
+            const int n = n0 + i;
+            if (n < nitems) {
+                const int kg = n % kg_i;
+                if (kg == 0) {
+                    const int uu = warp + DS_WARPS * (n / kg_i);
+                    const int ee = a.R.uexp[uu];
+                    c0 = a.R.expert_bounds[ee];
+                    ncol = min(4, a.R.expert_bounds[ee + 1] - c0);
+                    const int jcol = gq >> 1;
+                    bvalid = jcol < ncol;
+                    bbase = ss + ((size_t)((c0 + jcol) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4;
+                    acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+                }
+                const uint4* bp = bbase + (size_t)kg * 16;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) block_mma_smem<Q>(ring[i], b, bp, bvalid, acc);
+                if (n + RB < nitems) load_item(n + RB, ring[i]);
+                if (kg == kg_i - 1 && t4 < ncol) {
+                    dsm[(c0 + t4) * 16 + gq] = acc[0] + acc[1];
+                    dsm[(c0 + t4) * 16 + gq + 8] = acc[2] + acc[3];
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < 16 * T) {
+        const int row = tid & 15, t = tid >> 4;
+        const size_t o = (size_t)t * H + rt * 16 + row;
+        float accv = a.residual[o];
+        for (int slot = 0; slot < K; ++slot) {
+            const int col = a.R.dst_to_col[t * K + slot];
+            const float w = a.R.weights[t * K + slot];
+            accv = __fadd_rn(accv, __fmul_rn(w, dsm[col * 16 + row]));
+        }
+        a.out[o] = accv;
+    }
+}
+
+template <typename Kern>
+static cudaError_t launch_pdl_smem(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                   const DecodeArgs& a) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    count_launch();
+    return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
+// Whether the small-batch kernels apply (shape limits of the register staging
+// and of shared memory); otherwise the caller uses the general kernels.
+bool decode_small_applicable(const DecodeArgs& a) {
+    if (a.T > 4) return false;
+    const int q = a.L.quant;
+    const int warps = (q == Q4_0) ? 4 : (q == Q8_0) ? 8 : 16;
+    const int iters = (q == Q4_0) ? 4 : (q == Q8_0) ? 2 : 1;
+    if (a.L.kg_h > warps * iters) return false;
+    const size_t gu_smem = (size_t)4 * 2 * a.L.kg_h * 4 * 4 * 16;
+    const size_t dn_smem = (size_t)a.T * a.K * (2 * a.L.kg_i * 4 * 4 * 16 + 64);
+    return gu_smem <= 160 * 1024 && dn_smem <= 200 * 1024;
+}
+
+template <int Q>
+static cudaError_t launch_small_t(const DecodeArgs& a, int phase, cudaStream_t st) {
+    const int C = a.T * a.K;
+    const int nu = C < a.L.E ? C : a.L.E;
+    if (phase == 1) {
+        const size_t smem = (size_t)min(a.T, 4) * 2 * a.L.kg_h * 4 * 4 * 16;
+        static size_t attr_smem = 0;
+        if (smem > 48 * 1024 && smem > attr_smem) {
+            cudaError_t e = cudaFuncSetAttribute(gate_up_small_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem);
+            if (e != cudaSuccess) return e;
+            attr_smem = smem;
+        }
+        return launch_pdl_smem(gate_up_small_kernel<Q>, dim3(a.L.rt_i, nu), dim3(SmallCfg<Q>::GU_WARPS * 32), smem, st, a);
+    }
+    const size_t smem = (size_t)C * (2 * a.L.kg_i * 4 * 4 * 16 + 64);
+    static size_t attr_smem_dn = 0;
+    if (smem > 48 * 1024 && smem > attr_smem_dn) {
+        cudaError_t e = cudaFuncSetAttribute(down_small_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_smem_dn = smem;
+    }
+    return launch_pdl_smem(down_small_kernel<Q>, dim3(a.L.rt_h), dim3(DS_WARPS * 32), smem, st, a);
+}
+
+cudaError_t launch_decode_small_phase(const DecodeArgs& a, int phase, cudaStream_t st) {
+    switch (a.L.quant) {
+        case Q4_0: return launch_small_t<Q4_0>(a, phase, st);
+        case Q8_0: return launch_small_t<Q8_0>(a, phase, st);
+        default: return launch_small_t<BF16>(a, phase, st);
+    }
+}
+
+}  // namespace lumen

@@ -368,7 +368,7 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     CUDA_TRY(launch_route_large(p, st));
     const bool bf16_mode = (layer.dev.quant == BF16);
     if (p.impl == 0) {
-        CUDA_TRY(launch_permute_x16(normed, act_dtype, (size_t)batch * s->H, bf16_mode, s->x16, st));
+        CUDA_TRY(launch_permute_x16(normed, act_dtype, (size_t)batch * s->H, false, s->x16, st));
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

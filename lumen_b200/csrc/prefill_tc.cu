@@ -140,6 +140,11 @@ struct Args {
     int out_ld;             // I or H
 };
 
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+    const __half2 h = __floats2half2_rn(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 // Dequantise one lane's share of half a weight tile (16 rows x 64 k: blocks
 // 2*sub and 2*sub+1) into the operand tile: 4 chunks of 16 bytes (rows g, g+8).
 template <int Q>
@@ -150,7 +155,16 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
         const int b = sub * 2 + bb;
         uint32_t lo[4], hi[4];
         unpack_block<Q>(w, b, lo, hi);
-        if (Q != BF16) {
+        if (Q == BF16) {
+            // bf16 -> f16 is exact for 2^-14 <= |w| < 65504 (8 significand bits fit in 11);
+            // smaller magnitudes lose bits only below 2^-24 absolute. The host keeps layers
+            // with |w| >= 65504 off this path.
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                lo[i] = bf16x2_to_f16x2(lo[i]);
+                hi[i] = bf16x2_to_f16x2(hi[i]);
+            }
+        } else {
             const uint32_t s_g = (b < 2) ? w.s.x : w.s.y;
             const uint32_t s_g8 = (b < 2) ? w.s.z : w.s.w;
             const uint32_t sg2 = prmt(s_g, s_g, (b & 1) ? 0x3232u : 0x1010u);
@@ -215,7 +229,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     const int ntiles = a.n_tiles[MODE];
     const int kgs = a.kdim >> 7;   // 128-input groups (weight tile granularity)
     const int khs = kgs * 2;       // 64-input pipeline stages per tile
-    const bool bf16_mode = (Q == BF16);
+    // every operand is f16 here: BF16 weights are converted exactly (see dequant_store)
+    const bool bf16_mode = false;
 
     if (warp < EPI_WARPS) {
         // ------------------------------ epilogue ------------------------------

@@ -244,19 +244,22 @@ def run_gpu(args):
     line = None
     if rank == 0:
         peak, peak_src = peaks()
-        # dominant kernel (gate/up + SwiGLU) alone, one launch per layer blob, CUDA events on the launch stream
-        for l in range(L):
-            scratch.debug_decode_phase(layers[l], 1)
-        torch.cuda.synchronize()
-        reps = 5
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
-        for _ in range(reps):
+        # each kernel of the chain alone, one launch per layer blob, CUDA events on the launch stream
+        # (phase 1 = gate/up + SwiGLU is the dominant kernel)
+        def time_phase(phase, reps=5):
             for l in range(L):
-                scratch.debug_decode_phase(layers[l], 1)
-        ev1.record()
-        torch.cuda.synchronize()
-        k_ms = ev0.elapsed_time(ev1) / (reps * L)
+                scratch.debug_decode_phase(layers[l], phase)
+            torch.cuda.synchronize()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for _ in range(reps):
+                for l in range(L):
+                    scratch.debug_decode_phase(layers[l], phase)
+            ev1.record()
+            torch.cuda.synchronize()
+            return ev0.elapsed_time(ev1) / (reps * L)
+        phase_ms = [time_phase(ph) for ph in (0, 1, 2)]
+        k_ms = phase_ms[1]
         # routing tables in the context belong to the last layer called: same count of experts for every launch
         k_bytes = gate_up_bytes(T, U[-1], quant)
         achieved = k_bytes / (k_ms / 1e3) / 1e9
@@ -273,6 +276,8 @@ def run_gpu(args):
                 "roofline": {"bound": "hbm", "kernel": "gate_up_kernel", "achieved": achieved, "peak": peak,
                              "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
                              "algorithmic_bytes_per_launch": k_bytes, "us_per_launch": k_ms * 1e3},
+                "kernel_us": {"router_small_kernel": phase_ms[0] * 1e3, "gate_up_kernel": phase_ms[1] * 1e3,
+                              "down_combine_kernel": phase_ms[2] * 1e3},
                 "layer_roofline": {"algorithmic_bytes_per_call": layer_bytes, "us_per_call": ms * 1e3 / (args.steps * L),
                                    "achieved_gbs": layer_gbs, "frac_of_measured_peak": layer_gbs / peak,
                                    "frac_of_8tbs": layer_gbs / 8000.0},

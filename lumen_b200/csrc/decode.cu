@@ -157,16 +157,17 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
         }
     }
 
-    // last-CTA election: every writer fences, then one ticket per CTA
-    __threadfence();
+    // last-CTA election: the CTA barrier orders every thread's stores before
+    // thread 0's device-scope fence and ticket (fences are cumulative)
     __syncthreads();
     if (tid == 0) {
+        __threadfence();
         const unsigned int ticket = atomicAdd(a.R.ticket, 1u);
         is_last_s = (ticket == gridDim.x - 1);
+        if (is_last_s) __threadfence();
     }
     __syncthreads();
     if (!is_last_s) return;
-    __threadfence();
 
     const float* lg = want_logits ? a.R.logits : a.logits_override;
     for (int t = warp; t < T; t += RS_WARPS) {

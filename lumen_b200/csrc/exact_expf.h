@@ -34,19 +34,29 @@
 
 namespace lumen_exact {
 
+// 2^(i/32) as IEEE double bits, minus (i << 47) so that adding (k << 47) with
+// k = 32*q + i yields the bits of 2^(q + i/32).
+#define LUMEN_EXP2_TAB_INIT                                                                             \
+    {0x3ff0000000000000ULL, 0x3fefd9b0d3158574ULL, 0x3fefb5586cf9890fULL, 0x3fef9301d0125b51ULL,        \
+     0x3fef72b83c7d517bULL, 0x3fef54873168b9aaULL, 0x3fef387a6e756238ULL, 0x3fef1e9df51fdee1ULL,        \
+     0x3fef06fe0a31b715ULL, 0x3feef1a7373aa9cbULL, 0x3feedea64c123422ULL, 0x3feece086061892dULL,        \
+     0x3feebfdad5362a27ULL, 0x3feeb42b569d4f82ULL, 0x3feeab07dd485429ULL, 0x3feea47eb03a5585ULL,        \
+     0x3feea09e667f3bcdULL, 0x3fee9f75e8ec5f74ULL, 0x3feea11473eb0187ULL, 0x3feea589994cce13ULL,        \
+     0x3feeace5422aa0dbULL, 0x3feeb737b0cdc5e5ULL, 0x3feec49182a3f090ULL, 0x3feed503b23e255dULL,        \
+     0x3feee89f995ad3adULL, 0x3feeff76f2fb5e47ULL, 0x3fef199bdd85529cULL, 0x3fef3720dcef9069ULL,        \
+     0x3fef5818dcfba487ULL, 0x3fef7c97337b9b5fULL, 0x3fefa4afa2a490daULL, 0x3fefd0765b6e4540ULL}
+
+#if defined(__CUDACC__)
+static __device__ __constant__ uint64_t exp2_tab_dev[32] = LUMEN_EXP2_TAB_INIT;
+#endif
+static const uint64_t exp2_tab_host[32] = LUMEN_EXP2_TAB_INIT;
+
 LUMEN_HD uint64_t exp2_tab(int i) {
-    // 2^(i/32) as IEEE double bits, minus (i << 47) so that adding (k << 47) with
-    // k = 32*q + i yields the bits of 2^(q + i/32).
-    const uint64_t tab[32] = {
-        0x3ff0000000000000ULL, 0x3fefd9b0d3158574ULL, 0x3fefb5586cf9890fULL, 0x3fef9301d0125b51ULL,
-        0x3fef72b83c7d517bULL, 0x3fef54873168b9aaULL, 0x3fef387a6e756238ULL, 0x3fef1e9df51fdee1ULL,
-        0x3fef06fe0a31b715ULL, 0x3feef1a7373aa9cbULL, 0x3feedea64c123422ULL, 0x3feece086061892dULL,
-        0x3feebfdad5362a27ULL, 0x3feeb42b569d4f82ULL, 0x3feeab07dd485429ULL, 0x3feea47eb03a5585ULL,
-        0x3feea09e667f3bcdULL, 0x3fee9f75e8ec5f74ULL, 0x3feea11473eb0187ULL, 0x3feea589994cce13ULL,
-        0x3feeace5422aa0dbULL, 0x3feeb737b0cdc5e5ULL, 0x3feec49182a3f090ULL, 0x3feed503b23e255dULL,
-        0x3feee89f995ad3adULL, 0x3feeff76f2fb5e47ULL, 0x3fef199bdd85529cULL, 0x3fef3720dcef9069ULL,
-        0x3fef5818dcfba487ULL, 0x3fef7c97337b9b5fULL, 0x3fefa4afa2a490daULL, 0x3fefd0765b6e4540ULL};
-    return tab[i];
+#if defined(__CUDA_ARCH__)
+    return exp2_tab_dev[i];
+#else
+    return exp2_tab_host[i];
+#endif
 }
 
 LUMEN_HD float expf_libm(float x) {

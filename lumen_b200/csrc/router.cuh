@@ -47,16 +47,32 @@ __device__ __forceinline__ void warp_topk(const float* __restrict__ logits, int 
         smem_sel[lane] = -1.0f;
     }
     __syncwarp();
-    for (int e = lane; e < E; e += 32) {
-        const float pe = smem_p[e];
-        int rank = 0;
+    {
+        // rank of every expert under (p descending, index ascending); each lane
+        // ranks up to 8 experts (E <= 256) in one pass over the probabilities
+        float pe[8];
+        int rank[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = lane + 32 * i;
+            pe[i] = (e < E) ? smem_p[e] : 0.0f;
+            rank[i] = 0;
+        }
         for (int j = 0; j < E; ++j) {
             const float pj = smem_p[j];
-            rank += (pj > pe) || (pj == pe && j < e);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int e = lane + 32 * i;
+                rank[i] += (pj > pe[i]) || (pj == pe[i] && j < e);
+            }
         }
-        if (rank < K && pe > -1.0f) {
-            out_ids[rank] = (uint32_t)e;
-            smem_sel[rank] = pe;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && rank[i] < K && pe[i] > -1.0f) {
+                out_ids[rank[i]] = (uint32_t)e;
+                smem_sel[rank[i]] = pe[i];
+            }
         }
     }
     __syncwarp();

@@ -127,6 +127,28 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_topk_from_logits(lumen_moe_ctx* ctx, 
                                               int32_t tokens, uint32_t* d_ids, float* d_weights,
                                               void* stream);
 
+/* Routing for callers that cannot allocate device memory. No counterpart in the
+ * reference (its router always works out of the CudaMoeScratch that
+ * allocate_moe_scratch cudaMallocs). Same arithmetic and same results as
+ * lumen_moe_topk_from_logits for 1..16 tokens, but it takes no context: its
+ * working tables live in an 8 KiB array that is part of the library image on every
+ * GPU that loads it, so the call performs no cudaMalloc / cudaFree at all. Meant
+ * for hosts that pre-claim all device memory for their own pool, or that must not
+ * enter the driver allocator from their decode loop (it synchronises the device).
+ * Limits, fixed by that array and checked (LUMEN_MOE_INVALID_ARG otherwise):
+ * tokens <= 16, num_experts <= 256, top_k <= 16.
+ * d_logits f32 [T,E]; outputs d_ids u32 [T,K], d_weights f32 [T,K]; optional
+ * d_dst_to_col i32 [T*K] and d_expert_bounds i32 [E+1] (NULL to skip).
+ * The first call on a device looks up the array's device address; make that call
+ * at start-up, before any stream capture begins. All calls on a GPU share the
+ * array (it keeps the previous call's contents; the call clears what must start
+ * at zero), so calls that could overlap on the GPU must be serialised by the caller. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_route_small_static(const float* d_logits, int32_t tokens,
+                                                              int32_t num_experts, int32_t top_k,
+                                                              int32_t gating_mode, uint32_t* d_ids,
+                                                              float* d_weights, int32_t* d_dst_to_col,
+                                                              int32_t* d_expert_bounds, void* stream);
+
 /* Parity hook: while set (non-NULL), lumen_moe_decode / _prefill take the router
  * logits f32 [T,E] from this device buffer instead of computing them, so that
  * both sides of a parity test route on identical logits. NULL switches it off. */

@@ -43,6 +43,7 @@ SIGNATURES = {
     "lumen_moe_prefill": [vp, vp, vp, vp, vp, i32, i32, vp],
     "lumen_moe_route_only": [vp, vp, vp, i32, vp, vp, vp, vp],
     "lumen_moe_topk_from_logits": [vp, vp, i32, vp, vp, vp],
+    "lumen_moe_route_small_static": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp],
     "lumen_moe_set_logits_override": [vp, vp],
     "lumen_moe_get_routing": [vp, i32, vp, vp, vp, vp, vp, vp],
     "lumen_moe_quantize": [vp, i64, i32, vp, vp],

@@ -17,6 +17,11 @@ struct lumen_moe_layer {
 
 static thread_local std::string g_last_error;
 
+namespace lumen {
+// lets other translation units of the library report through lumen_moe_last_error()
+void set_last_error(const std::string& msg) { g_last_error = msg; }
+}  // namespace lumen
+
 static lumen_moe_status_t fail(int code, const std::string& msg) {
     g_last_error = msg;
     return static_cast<lumen_moe_status_t>(code);

@@ -278,3 +278,18 @@ def debug_expf(x: torch.Tensor) -> torch.Tensor:
 
 def launch_count(reset: bool = False) -> int:
     return int(_lib.lib().lumen_moe_launch_count(1 if reset else 0))
+
+
+def route_small_static(logits: torch.Tensor, top_k: int, gating_mode: int = SOFTMAX_RENORM, want_tables: bool = False):
+    """lumen_moe_route_small_static: context-free routing of 1..16 tokens for callers
+    that may not allocate device memory (the outputs created here are the CALLER's
+    buffers; the library itself allocates nothing)."""
+    _need(logits, torch.float32, "logits")
+    T, E = logits.shape
+    ids = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+    d2c = torch.empty(T * top_k, dtype=torch.int32, device=logits.device) if want_tables else None
+    bounds = torch.empty(E + 1, dtype=torch.int32, device=logits.device) if want_tables else None
+    check(_lib.lib().lumen_moe_route_small_static(logits.data_ptr(), T, E, top_k, gating_mode, ids.data_ptr(),
+                                                  w.data_ptr(), _ptr(d2c), _ptr(bounds), _stream()))
+    return (ids, w, d2c, bounds) if want_tables else (ids, w)

@@ -34,12 +34,13 @@ __global__ void __launch_bounds__(RS_THREADS)
 router_small_kernel(const __grid_constant__ DecodeArgs a) {
     __shared__ float red_s[RS_WARPS][DECODE_MAX_TOKENS];
     __shared__ float scale_s[DECODE_MAX_TOKENS];
-    __shared__ float p_s[RS_WARPS][MAX_EXPERTS];
-    __shared__ float lg_s[RS_WARPS][MAX_EXPERTS];
+    __shared__ __align__(16) float p_s[RS_WARPS][MAX_EXPERTS];
+    __shared__ __align__(16) float lg_s[RS_WARPS][MAX_EXPERTS];
     __shared__ float sel_s[RS_WARPS][MAX_TOP_K];
     __shared__ int ids_s[DECODE_MAX_TOKENS * MAX_TOP_K];
     __shared__ int cnt_s[MAX_EXPERTS];
     __shared__ int bounds_s[MAX_EXPERTS + 1];
+    __shared__ int uidx_s[MAX_EXPERTS];
     __shared__ int is_last_s;
 
     pdl_trigger();
@@ -213,10 +214,20 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
             if (ee < E) {
                 bounds_s[ee] = run;
                 a.R.expert_bounds[ee] = run;
-                if (local[j] > 0) a.R.uexp[unz++] = ee;
+                uidx_s[ee] = -1;
+                if (local[j] > 0) {
+                    // work descriptor of the unz-th expert with work: one 32-byte record that a
+                    // consumer CTA reads in a single round trip {expert, first column, columns}
+                    a.R.work[2 * unz] = make_int4(ee, run, local[j], 0);
+                    uidx_s[ee] = unz;
+                    a.R.uexp[unz++] = ee;
+                }
                 run += local[j];
             }
         }
+        const int total_u = __shfl_sync(0xffffffffu, inz, 31);
+        const int nu_max = (C < E) ? C : E;
+        for (int uu = total_u + lane; uu < nu_max; uu += 32) a.R.work[2 * uu] = make_int4(-1, 0, 0, 0);
         if (lane == 31) {
             bounds_s[E] = isum;
             a.R.expert_bounds[E] = isum;
@@ -226,11 +237,14 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
     __syncthreads();
     if (tid < E) {
         int cur = bounds_s[tid];
+        const int first = cur;
+        int* wtok = reinterpret_cast<int*>(a.R.work) + 8 * max(uidx_s[tid], 0) + 4;
         for (int p = 0; p < C; ++p) {
             if (ids_s[p] == tid) {
                 a.R.col_expert[cur] = tid;
                 a.R.col_src_tok[cur] = p / K;
                 a.R.dst_to_col[p] = cur;
+                if (cur - first < 4) wtok[cur - first] = p / K;  // source tokens of the first four columns
                 ++cur;
             }
         }

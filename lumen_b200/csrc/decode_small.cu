@@ -4,18 +4,23 @@
 // The general kernels in decode.cu stream a few weight tiles per warp; at batch 1
 // the whole layer is only 22 MB, so what counts is to have EVERY byte of a
 // kernel's weights requested before the first one is consumed, in a single wave
-// of CTAs. Here each warp issues all of its 128-bit weight loads up front
-// (registers are the staging buffer), the activation fragments of the expert's
-// tokens are staged once per CTA in shared memory, and only then does the
-// tensor-core loop start.
+// of CTAs, and to keep the chain of dependent loads in front of that as short as
+// possible. Each CTA reads ONE 32-byte work descriptor written by the router
+// (expert, first column, column count, source tokens), each warp then issues all
+// of its 128-bit weight loads (registers are the staging buffer), the activation
+// fragments of the expert's tokens are staged in shared memory with cp.async
+// while the weights are in flight, and only then does the tensor-core loop start.
 //
 //   gate_up_small_kernel   CTA = (16 rows of I, distinct expert); WARPS warps split
-//                          the H/128 input groups, ITERS groups each, all loaded first
+//                          the H/128 input groups, ITERS groups each
 //                          (cuda/shaders/moe_expert_q4_0.cu:58-108; moe_expert.cu:62-97)
 //   down_small_kernel      CTA = 16 rows of H; warp w walks experts w, w+8, ... with a
-//                          ring of RB weight tiles in flight; weighted combine in slot
-//                          order at the end (moe_expert_q4_0.cu:118-151;
-//                          cuda/shaders/moe_accum.cu:22-46)
+//                          ring of RB weight tiles in flight. Its weight loads depend
+//                          only on the routing, so they are issued BEFORE the kernel
+//                          waits for the gate/up kernel (programmatic dependent launch):
+//                          the down weights stream while gate/up is still computing.
+//                          Weighted combine in slot order at the end
+//                          (moe_expert_q4_0.cu:118-151; cuda/shaders/moe_accum.cu:22-46)
 #include "mma_frag.cuh"
 
 namespace lumen {
@@ -30,13 +35,17 @@ __device__ __forceinline__ int frag_pos_(int r) {
     return (m == 0) ? 0 : (m == 2) ? 1 : (m == 1) ? 2 : 3;
 }
 
-__device__ __forceinline__ uint4 lds128(const uint4* p) { return *p; }
+__device__ __forceinline__ void cp_async16_(void* smem_dst, const void* gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all_() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 template <int Q>
 struct SmallCfg;
 template <>
 struct SmallCfg<Q4_0> {
-    static constexpr int GU_WARPS = 4, GU_ITERS = 4, DN_RING = 6;
+    static constexpr int GU_WARPS = 8, GU_ITERS = 2, DN_RING = 6;
 };
 template <>
 struct SmallCfg<Q8_0> {
@@ -55,7 +64,7 @@ __device__ __forceinline__ void block_mma_smem(const WTile<Q>& w, int b, const u
     unpack_block<Q>(w, b, a_lo, a_hi);
     const float2 sc = block_scales<Q>(w, b);
     uint4 bf = make_uint4(0u, 0u, 0u, 0u);
-    if (bvalid) bf = lds128(bsm + b * 4);
+    if (bvalid) bf = bsm[b * 4];
     float c[4] = {0.f, 0.f, 0.f, 0.f};
     if (Q == BF16) {
         mma_bf16(c, a_lo, bf.x, bf.y);
@@ -78,16 +87,18 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
     constexpr int WARPS = SmallCfg<Q>::GU_WARPS, ITERS = SmallCfg<Q>::GU_ITERS;
     extern __shared__ uint4 xs[];  // [4 columns][2][nblk_pad][4]
     __shared__ float red[WARPS][16][4][2];
-    pdl_trigger_();
     pdl_wait_();
+    // the router has completed: everything the next kernel reads before ITS wait is final
+    pdl_trigger_();
     const int u = blockIdx.y;
-    if (u >= *a.R.n_uexp) return;
+    const int4 wd = a.R.work[2 * u];
+    if (wd.x < 0) return;
+    const int4 wt = a.R.work[2 * u + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, t4 = lane & 3;
     const int rt = blockIdx.x;
-    const int e = a.R.uexp[u];
-    const int c0 = a.R.expert_bounds[e];
-    const int ncol = min(4, a.R.expert_bounds[e + 1] - c0);
+    const int e = wd.x, c0 = wd.y;
+    const int ncol = min(4, wd.z);
     const int kg_h = a.L.kg_h, I = a.L.I;
     const int nblk_pad = kg_h * 4, nblk_i_pad = a.L.kg_i * 4;
 
@@ -107,13 +118,17 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
             }
         }
     }
-    // stage the activation fragments of this expert's tokens
+    // stage the activation fragments of this expert's tokens while the weights are in flight
     const int per_col = 2 * nblk_pad * 4;
-    for (int j = 0; j < ncol; ++j) {
-        const int tok = a.R.col_src_tok[c0 + j];
-        const uint4* src = a.xf + (size_t)tok * per_col;
-        for (int i = tid; i < per_col; i += WARPS * 32) xs[j * per_col + i] = __ldg(src + i);
+    const int toks[4] = {wt.x, wt.y, wt.z, wt.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (j < ncol) {
+            const uint4* src = a.xf + (size_t)toks[j] * per_col;
+            for (int i = tid; i < per_col; i += WARPS * 32) cp_async16_(&xs[j * per_col + i], src + i);
+        }
     }
+    cp_async_wait_all_();
     __syncthreads();
 
     const int jcol = gq >> 1;
@@ -178,7 +193,6 @@ __global__ void __launch_bounds__(DS_WARPS * 32)
 down_small_kernel(const __grid_constant__ DecodeArgs a) {
     constexpr int RB = SmallCfg<Q>::DN_RING;
     extern __shared__ uint4 ss[];  // [C columns][2][nblk_i_pad][4], then float dsm[C][16]
-    pdl_trigger_();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, t4 = lane & 3;
     const int rt = blockIdx.x;
@@ -187,14 +201,16 @@ down_small_kernel(const __grid_constant__ DecodeArgs a) {
     const int C = T * K;
     const int per_col = 2 * nblk_i_pad * 4;
     float* dsm = reinterpret_cast<float*>(ss + (size_t)C * per_col);
-    pdl_wait_();
-    const int U = *a.R.n_uexp;
 
+    // Routing tables come from the router kernel, which had completed before the
+    // gate/up kernel (the immediate predecessor) released this launch; they are
+    // read, and the weight loads they determine issued, before waiting for gate/up.
+    const int U = *a.R.n_uexp;
     const int n_exp_w = (U > warp) ? (U - warp + DS_WARPS - 1) / DS_WARPS : 0;
     const int nitems = n_exp_w * kg_i;
     auto load_item = [&](int n, WTile<Q>& dst) {
         const int uu = warp + DS_WARPS * (n / kg_i), kg = n % kg_i;
-        const int ee = a.R.uexp[uu];
+        const int ee = a.R.work[2 * uu].x;
         load_wtile<Q>(dst, a.L.down_q(ee), a.L.down_s(ee), rt * kg_i + kg, lane);
     };
     WTile<Q> ring[RB];
@@ -202,8 +218,11 @@ down_small_kernel(const __grid_constant__ DecodeArgs a) {
     for (int i = 0; i < RB; ++i)
         if (i < nitems) load_item(i, ring[i]);
 
-    // stage all SwiGLU fragments (written by the previous kernel)
-    for (int i = tid; i < C * per_col; i += DS_WARPS * 32) ss[i] = a.sf[i];
+    pdl_wait_();
+    pdl_trigger_();
+    // stage all SwiGLU fragments (written by the gate/up kernel)
+    for (int i = tid; i < C * per_col; i += DS_WARPS * 32) cp_async16_(&ss[i], a.sf + i);
+    cp_async_wait_all_();
     __syncthreads();
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -218,9 +237,9 @@ down_small_kernel(const __grid_constant__ DecodeArgs a) {
                 const int kg = n % kg_i;
                 if (kg == 0) {
                     const int uu = warp + DS_WARPS * (n / kg_i);
-                    const int ee = a.R.uexp[uu];
-                    c0 = a.R.expert_bounds[ee];
-                    ncol = min(4, a.R.expert_bounds[ee + 1] - c0);
+                    const int4 wd = a.R.work[2 * uu];
+                    c0 = wd.y;
+                    ncol = min(4, wd.z);
                     const int jcol = gq >> 1;
                     bvalid = jcol < ncol;
                     bbase = ss + ((size_t)((c0 + jcol) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4;
@@ -273,8 +292,8 @@ static cudaError_t launch_pdl_smem(Kern kern, dim3 grid, dim3 block, size_t smem
 bool decode_small_applicable(const DecodeArgs& a) {
     if (a.T > 4) return false;
     const int q = a.L.quant;
-    const int warps = (q == Q4_0) ? 4 : (q == Q8_0) ? 8 : 16;
-    const int iters = (q == Q4_0) ? 4 : (q == Q8_0) ? 2 : 1;
+    const int warps = (q == BF16) ? 16 : 8;
+    const int iters = (q == BF16) ? 1 : 2;
     if (a.L.kg_h > warps * iters) return false;
     const size_t gu_smem = (size_t)4 * 2 * a.L.kg_h * 4 * 4 * 16;
     const size_t dn_smem = (size_t)a.T * a.K * (2 * a.L.kg_i * 4 * 4 * 16 + 64);

@@ -191,7 +191,8 @@ Status allocate_moe_scratch(int device, int H, int I, int E, int K, int gating, 
     s.E = E;
     s.K = K;
     s.gating = gating;
-    const size_t fixed = align_up((size_t)(E + 1) * 4, 256) + align_up((size_t)E * 4, 256) + 256 * 4;
+    const size_t fixed = align_up((size_t)(E + 1) * 4, 256) + align_up((size_t)E * 4, 256) + 256 * 4 +
+                         (size_t)MAX_EXPERTS * 2 * sizeof(int4);
     CUDA_TRY(cudaMalloc(&s.arena, fixed));
     CUDA_TRY(cudaMemset(s.arena, 0, fixed));
     uint8_t* b = static_cast<uint8_t*>(s.arena);
@@ -203,6 +204,7 @@ Status allocate_moe_scratch(int device, int H, int I, int E, int K, int gating, 
     s.R.ticket = reinterpret_cast<unsigned int*>(b + 256);
     s.n_tiles = reinterpret_cast<int32_t*>(b + 512);
     s.status = reinterpret_cast<int32_t*>(b + 768);
+    s.R.work = reinterpret_cast<int4*>(b + 1024);
     const char* impl = std::getenv("LUMEN_MOE_PREFILL_IMPL");
     s.prefill_impl = (impl && std::strcmp(impl, "mma") == 0) ? 1 : 0;
     const int cap = max_tokens > DECODE_MAX_TOKENS ? max_tokens : DECODE_MAX_TOKENS;

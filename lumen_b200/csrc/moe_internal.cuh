@@ -66,6 +66,7 @@ struct RouteDev {
     int32_t* uexp;         // [E] distinct experts, ascending
     int32_t* n_uexp;       // [1]
     unsigned int* ticket;  // [1] last-block election counter (zero between launches)
+    int4* work;            // [2*E] decode work descriptors: {expert | -1, first column, columns, 0}, {tok0..tok3}
 };
 
 // Activation fragments: for token (or compact column) c, half hl (0 = high part,

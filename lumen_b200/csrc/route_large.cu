@@ -89,8 +89,8 @@ constexpr int TK_WARPS = 4;
 __global__ void __launch_bounds__(TK_WARPS * 32)
 topk_large_kernel(const float* __restrict__ logits, int T, int E, int K, int gating,
                   uint32_t* __restrict__ ids, float* __restrict__ weights) {
-    __shared__ float p_s[TK_WARPS][MAX_EXPERTS];
-    __shared__ float lg_s[TK_WARPS][MAX_EXPERTS];
+    __shared__ __align__(16) float p_s[TK_WARPS][MAX_EXPERTS];
+    __shared__ __align__(16) float lg_s[TK_WARPS][MAX_EXPERTS];
     __shared__ float sel_s[TK_WARPS][MAX_TOP_K];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * TK_WARPS + warp;

@@ -61,8 +61,8 @@ __global__ void __launch_bounds__(256)
 route_small_static_kernel(const float* __restrict__ logits, int T, int E, int K, int gating,
                           uint32_t* __restrict__ ids_out, float* __restrict__ w_out,
                           int32_t* __restrict__ scratch) {
-    __shared__ float p_s[8][MAX_EXPERTS];
-    __shared__ float lg_s[8][MAX_EXPERTS];
+    __shared__ __align__(16) float p_s[8][MAX_EXPERTS];
+    __shared__ __align__(16) float lg_s[8][MAX_EXPERTS];
     __shared__ float sel_s[8][MAX_TOP_K];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int32_t* counts = scratch + RS_OFF_COUNTS;

@@ -247,14 +247,23 @@ def run_gpu(args):
         # each kernel of the chain alone, one launch per layer blob, CUDA events on the launch stream
         # (phase 1 = gate/up + SwiGLU is the dominant kernel)
         def time_phase(phase, reps=5):
-            for l in range(L):
-                scratch.debug_decode_phase(layers[l], phase)
+            def run():
+                for l in range(L):
+                    scratch.debug_decode_phase(layers[l], phase)
+            run()
+            torch.cuda.synchronize()
+            fn = run
+            if not args.no_graph:
+                gph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gph):
+                    run()
+                fn = gph.replay
+                fn()
             torch.cuda.synchronize()
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
             for _ in range(reps):
-                for l in range(L):
-                    scratch.debug_decode_phase(layers[l], phase)
+                fn()
             ev1.record()
             torch.cuda.synchronize()
             return ev0.elapsed_time(ev1) / (reps * L)
@@ -288,8 +297,55 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_prefill(args):
+    """Secondary workload (not the headline line): one prefill call of `--tokens`
+    tokens on one layer, Zipf(1.1)-skewed expert loads, bf16 activations; reports
+    tokens/s and the tensor roofline of the grouped GEMMs."""
+    import torch
+    from lumen_b200 import build, moe, synth
+    build.build()
+    quant, T = QUANTS[args.quant], args.tokens
+    lay = synth.LayerLayout(H, I, E, quant)
+    sc = moe.allocate_moe_scratch(H, I, E, K, T)
+    layers = [sc.prepare_layer(synth.make_layer_blob(lay, l), lay.meta()) for l in range(min(args.layers, 4))]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1)
+    x = torch.randn((T, H), generator=g, device="cuda").to(torch.bfloat16)
+    res = torch.zeros((T, H), device="cuda")
+    out = torch.empty_like(res)
+    lg = synth.zipf_logits(T, E, 2) if args.routing == "zipf" else synth.uniform_logits(T, E, 2)
+    if args.routing != "router":
+        sc.set_logits_override(lg)
+
+    def step():
+        for l in layers:
+            sc.prefill(l, x, res, out)
+    for _ in range(max(3, args.warmup)):
+        step()
+    sc.get_routing(T)  # raises if a device-side wait expired
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / (args.steps * len(layers))
+    flops = T * (2 * E * H + K * 6 * I * H)
+    peaks_d = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak = float(peaks_d.get("bf16_tflops", 1590.0))
+    tf = flops / (ms / 1e3) / 1e12
+    print(json.dumps({"metric": "moe_layer_prefill_tokens_per_s", "value": T / (ms / 1e3), "unit": "tokens/s",
+                      "n_gpus": 1, "steps": args.steps, "ms_per_call": ms, "dtype": "f16 operands, f32 accumulate",
+                      "config": {"workload": f"moe_ffn_prefill_{args.quant}_T{T}_{args.routing}", "layers_rotated": len(layers)},
+                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s",
+                                   "frac": tf / peak, "flops_per_call": flops}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
+    ap.add_argument("--routing", default="zipf", choices=["zipf", "uniform", "router"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -301,6 +357,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_gpu(args)
 

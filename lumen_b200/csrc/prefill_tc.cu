@@ -150,6 +150,7 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
 template <int Q>
 __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32_t a_base, int rtl, int lane) {
     const int g = lane >> 2, t = lane & 3;
+    uint32_t d[2][2][4];  // [block of the pair][row g | row g+8][four f16x2 words of one 16-byte chunk]
 #pragma unroll
     for (int bb = 0; bb < 2; ++bb) {
         const int b = sub * 2 + bb;
@@ -178,20 +179,36 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
             lo[3] = hmul2_u32(lo[3], sg82);
             hi[3] = hmul2_u32(hi[3], sg82);
         }
-        const int c = bb * 4 + t;
-        const int r0 = rtl * 16 + g, r1 = r0 + 8;
-        sts128(a_base + r0 * 128 + ((c ^ (r0 & 7)) << 4), lo[0], hi[0], lo[2], hi[2]);
-        sts128(a_base + r1 * 128 + ((c ^ (r1 & 7)) << 4), lo[1], hi[1], lo[3], hi[3]);
+        d[bb][0][0] = lo[0]; d[bb][0][1] = hi[0]; d[bb][0][2] = lo[2]; d[bb][0][3] = hi[2];
+        d[bb][1][0] = lo[1]; d[bb][1][1] = hi[1]; d[bb][1][2] = lo[3]; d[bb][1][3] = hi[3];
+    }
+    // Lanes with odd g store the second block first: the eight lanes of a quarter
+    // warp then hit eight different 16-byte chunk positions (rows are 128 bytes
+    // apart, i.e. a whole bank cycle) and the 128-bit stores are conflict-free.
+    const bool odd = (g & 1) != 0;
+    const int r0 = rtl * 16 + g, r1 = r0 + 8;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+        const bool second = (pass == 1) != odd;  // which block of the pair this lane stores in this pass
+        uint32_t x[2][4];
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) x[rr][i] = second ? d[1][rr][i] : d[0][rr][i];
+        const int c = (second ? 4 : 0) + t;
+        sts128(a_base + r0 * 128 + ((c ^ (r0 & 7)) << 4), x[0][0], x[0][1], x[0][2], x[0][3]);
+        sts128(a_base + r1 * 128 + ((c ^ (r1 & 7)) << 4), x[1][0], x[1][1], x[1][2], x[1][3]);
     }
 }
 
 template <int Q, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
-    constexpr int NA = (MODE == 0) ? 2 : 1;
-    constexpr int STAGES = (MODE == 0) ? 4 : 6;       // one stage = 64 inputs (one swizzle atom in K)
-    constexpr int STAGE_BYTES = (NA + 1) * SUB_BYTES;  // A operand(s) then B
-    constexpr int ACC_COLS = NA * 128;
+    constexpr int NA = (MODE == 0) ? 2 : 1;            // weight operands per stage (gate+up | down)
+    constexpr int BN = (MODE == 0) ? 128 : 256;        // columns per tile; NA * BN accumulator columns
+    constexpr int STAGES = 4;                          // one stage = 64 inputs (one swizzle atom in K)
+    constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operand(s) then B
+    constexpr int ACC_COLS = NA * BN;
     constexpr int TMEM_COLS = 2 * ACC_COLS;
 
     extern __shared__ uint8_t smem_raw[];
@@ -251,7 +268,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             for (int n0 = 0; n0 < ncols; n0 += 16) {
                 uint32_t g[16], u[16];
                 tmem_ld16(taddr + n0, g);
-                if (MODE == 0) tmem_ld16(taddr + 128 + n0, u);
+                if (MODE == 0) tmem_ld16(taddr + BN + n0, u);
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
@@ -278,9 +295,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         const int my_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const int ngroups = my_tiles * kgs;
         WTile<Q> cur[NA], nxt[NA];
-        auto load_group = [&](int n, WTile<Q>(&dst)[NA]) {
-            const int4 tile = a.tiles[blockIdx.x + (n / kgs) * gridDim.x];
-            const int kg = n % kgs;
+        auto issue = [&](const int4& tile, int kg, WTile<Q>(&dst)[NA]) {
             const int e = tile.x;
             const int rt = tile.w * 8 + rtl;
             if (MODE == 0) {
@@ -290,11 +305,18 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 load_wtile<Q>(dst[0], a.L.down_q(e), a.L.down_s(e), rt * kgs + kg, lane);
             }
         };
-        if (ngroups > 0) load_group(0, cur);
+        // tile descriptors are fetched one tile ahead so that no weight load waits on one
+        int4 tile_c = (my_tiles > 0) ? a.tiles[blockIdx.x] : make_int4(0, 0, 0, 0);
+        int4 tile_n = tile_c;
+        if (ngroups > 0) issue(tile_c, 0, cur);
         bool ok = true;
-        int it = 0;
+        int it = 0, kg = 0, tl = 0;
         for (int n = 0; ok && n < ngroups; ++n) {
-            if (n + 1 < ngroups) load_group(n + 1, nxt);
+            if (kg == 0 && tl + 1 < my_tiles) tile_n = a.tiles[blockIdx.x + (tl + 1) * gridDim.x];
+            if (n + 1 < ngroups) {
+                if (kg + 1 < kgs) issue(tile_c, kg + 1, nxt);
+                else issue(tile_n, 0, nxt);
+            }
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub, ++it) {
                 const int s = it % STAGES, ph = (it / STAGES) & 1;
@@ -311,47 +333,64 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 #pragma unroll
                 for (int op = 0; op < NA; ++op) cur[op] = nxt[op];
             }
+            if (++kg == kgs) {
+                kg = 0;
+                ++tl;
+                tile_c = tile_n;
+            }
         }
     } else if (warp < MMA_WARP) {
         // ------------------------- activation producers ------------------------
-        const int r = tid - B_WARP0 * 32;  // column within the tile = row of the B operand
+        constexpr int RPT = BN / 128;              // B-operand rows (tile columns) per thread
+        const int r = tid - B_WARP0 * 32;
         const int my_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const int nitems = my_tiles * khs;
-        const uint8_t* src_row = nullptr;
-        bool valid = false;
+        const uint8_t* src_row[RPT];
+        uint32_t nbytes[RPT];
         bool ok = true;
-        int pending = -1;  // stage whose copies were issued but not yet published
+        // Copies of up to three stages are in flight: stage n is issued as soon as its
+        // slot is free, stage n-2 is published once its own copy group has landed.
+        constexpr int LAG = 2;
+        int issued = 0;
         for (int n = 0; ok && n < nitems; ++n) {
             const int kh = n % khs;
             if (kh == 0) {
                 const int4 tile = a.tiles[blockIdx.x + (n / khs) * gridDim.x];
-                valid = r < tile.z;
-                int srow = 0;
-                if (valid) srow = a.col_src_tok ? a.col_src_tok[tile.y + r] : (tile.y + r);
-                src_row = reinterpret_cast<const uint8_t*>(a.b_src) + (size_t)srow * a.kdim * 2;
-            }
-            // publish the previous stage once its copies have landed, then refill
-            if (pending >= 0) {
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-                fence_proxy_async();
-                mbar_arrive(smem_u32(&full_bar[pending]));
-                pending = -1;
+#pragma unroll
+                for (int q = 0; q < RPT; ++q) {
+                    const int rr = r + q * 128;
+                    const bool valid = rr < tile.z;
+                    int srow = 0;
+                    if (valid) srow = a.col_src_tok ? a.col_src_tok[tile.y + rr] : (tile.y + rr);
+                    src_row[q] = reinterpret_cast<const uint8_t*>(a.b_src) + (size_t)srow * a.kdim * 2;
+                    nbytes[q] = valid ? 16u : 0u;
+                }
             }
             const int s = n % STAGES, ph = (n / STAGES) & 1;
             ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
             if (!ok) break;
             const uint32_t bbase = stage0 + s * STAGE_BYTES + NA * SUB_BYTES;
-            const uint8_t* src = src_row + (size_t)kh * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                cp_async16(bbase + r * 128 + ((c ^ (r & 7)) << 4), src + c * 16, valid ? 16u : 0u);
+            for (int q = 0; q < RPT; ++q) {
+                const int rr = r + q * 128;
+                const uint8_t* src = src_row[q] + (size_t)kh * 128;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    cp_async16(bbase + rr * 128 + ((c ^ (rr & 7)) << 4), src + c * 16, nbytes[q]);
+            }
             asm volatile("cp.async.commit_group;" ::: "memory");
-            pending = s;
+            issued = n + 1;
+            if (n >= LAG) {
+                asm volatile("cp.async.wait_group 2;" ::: "memory");
+                fence_proxy_async();
+                mbar_arrive(smem_u32(&full_bar[(n - LAG) % STAGES]));
+            }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        if (ok && pending >= 0) {
+        if (ok) {
             fence_proxy_async();
-            mbar_arrive(smem_u32(&full_bar[pending]));
+            for (int m = (issued > LAG ? issued - LAG : 0); m < issued; ++m)
+                mbar_arrive(smem_u32(&full_bar[m % STAGES]));
         }
     } else {
         // -------------------------------- MMA ---------------------------------
@@ -380,7 +419,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 #pragma unroll
                         for (int op = 0; op < NA; ++op) {
                             const uint64_t adesc = make_desc(sbase + op * SUB_BYTES + j * 32);
-                            umma(tmem_base + ab * ACC_COLS + op * 128, adesc, bdesc, idesc, acc);
+                            umma(tmem_base + ab * ACC_COLS + op * BN, adesc, bdesc, idesc, acc);
                         }
                     }
                     umma_commit(smem_u32(&empty_bar[s]));
@@ -431,8 +470,8 @@ cudaError_t launch_permute_x16(const void* x, int act_dtype, size_t n, bool bf16
 template <int Q, int MODE>
 static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
     constexpr int NA = (MODE == 0) ? 2 : 1;
-    constexpr int STAGES = (MODE == 0) ? 4 : 6;
-    const int smem = STAGES * (NA + 1) * tc::SUB_BYTES + 1024;
+    constexpr int BN = (MODE == 0) ? 128 : 256;
+    const int smem = 4 * (NA * tc::SUB_BYTES + BN * 128) + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(tc::grouped_gemm_tc_kernel<Q, MODE>,

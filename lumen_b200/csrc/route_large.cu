@@ -126,6 +126,7 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
     __shared__ int cnt_s[MAX_EXPERTS];
     __shared__ int bounds_s[MAX_EXPERTS + 1];
     __shared__ int tile_off_s[MAX_EXPERTS + 1];
+    __shared__ int tile_off_dn_s[MAX_EXPERTS + 1];  // down tiles are two gate/up tiles wide
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid < E) {
         int run = 0;
@@ -138,7 +139,7 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
     }
     __syncthreads();
     if (warp == 0) {
-        int local[8], ltiles[8], lsum = 0, lnz = 0, ltl = 0;
+        int local[8], ltiles[8], lsum = 0, lnz = 0, ltl = 0, ltd = 0;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int ee = lane * 8 + j;
@@ -147,39 +148,45 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
             lsum += local[j];
             lnz += (local[j] > 0);
             ltl += ltiles[j];
+            ltd += (ltiles[j] + 1) >> 1;
         }
-        int isum = lsum, inz = lnz, itl = ltl;
+        int isum = lsum, inz = lnz, itl = ltl, itd = ltd;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const int v1 = __shfl_up_sync(0xffffffffu, isum, o);
             const int v2 = __shfl_up_sync(0xffffffffu, inz, o);
             const int v3 = __shfl_up_sync(0xffffffffu, itl, o);
+            const int v4 = __shfl_up_sync(0xffffffffu, itd, o);
             if (lane >= o) {
                 isum += v1;
                 inz += v2;
                 itl += v3;
+                itd += v4;
             }
         }
-        int run = isum - lsum, unz = inz - lnz, trun = itl - ltl;
+        int run = isum - lsum, unz = inz - lnz, trun = itl - ltl, drun = itd - ltd;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int ee = lane * 8 + j;
             if (ee < E) {
                 bounds_s[ee] = run;
                 tile_off_s[ee] = trun;
+                tile_off_dn_s[ee] = drun;
                 R.expert_bounds[ee] = run;
                 if (local[j] > 0) R.uexp[unz++] = ee;
                 run += local[j];
                 trun += ltiles[j];
+                drun += (ltiles[j] + 1) >> 1;
             }
         }
         if (lane == 31) {
             bounds_s[E] = isum;
             tile_off_s[E] = itl;
+            tile_off_dn_s[E] = itd;
             R.expert_bounds[E] = isum;
             *R.n_uexp = inz;
             n_tiles[0] = min(itl * mt_gu, max_tiles_gu);
-            n_tiles[1] = min(itl * mt_dn, max_tiles_dn);
+            n_tiles[1] = min(itd * mt_dn, max_tiles_dn);
         }
     }
     __syncthreads();
@@ -195,8 +202,13 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
                 const int idx = (ct0 + ct) * mt_gu + mt;
                 if (idx < max_tiles_gu) tiles_gu[idx] = make_int4(tid, cs, nc, mt);
             }
+        }
+        const int dt0 = tile_off_dn_s[tid], ndt = tile_off_dn_s[tid + 1] - dt0;
+        for (int ct = 0; ct < ndt; ++ct) {
+            const int cs = c0 + ct * 2 * tile_cols;
+            const int nc = min(2 * tile_cols, n - ct * 2 * tile_cols);
             for (int mt = 0; mt < mt_dn; ++mt) {
-                const int idx = (ct0 + ct) * mt_dn + mt;
+                const int idx = (dt0 + ct) * mt_dn + mt;
                 if (idx < max_tiles_dn) tiles_dn[idx] = make_int4(tid, cs, nc, mt);
             }
         }

@@ -133,8 +133,8 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
     // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf
     const size_t C = (size_t)cap * s.K;
     const size_t nblk_h_pad = (size_t)((s.H / 32 + 3) / 4) * 4, nblk_i_pad = (size_t)((s.I / 32 + 3) / 4) * 4;
-    const size_t max_ct = C / 128 + s.E;
-    const size_t mt = (size_t)s.I / 128 + (size_t)s.H / 128;
+    const size_t max_ct = C / 256 + s.E;
+    const size_t mt = (size_t)s.I / 64 + (size_t)s.H / 128;
     size_t sizes[13] = {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,
         (size_t)((cap + 31) / 32) * s.E * 4,

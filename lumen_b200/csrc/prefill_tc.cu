@@ -204,8 +204,11 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
 template <int Q, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
-    constexpr int NA = (MODE == 0) ? 2 : 1;            // weight operands per stage (gate+up | down)
-    constexpr int BN = (MODE == 0) ? 128 : 256;        // columns per tile; NA * BN accumulator columns
+    // One weight operand per stage in both modes. Gate/up mode packs 64 gate rows
+    // (TMEM lanes 0-63) and the 64 matching up rows (lanes 64-127) into one M=128
+    // tile, so one 256-column accumulator holds both and can be double-buffered.
+    constexpr int NA = 1;
+    constexpr int BN = 256;                            // columns per tile
     constexpr int STAGES = 4;                          // one stage = 64 inputs (one swizzle atom in K)
     constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operand(s) then B
     constexpr int ACC_COLS = NA * BN;
@@ -215,6 +218,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ uint32_t abort_s;
+    __shared__ float xch[2][64][17];  // gate/up epilogue exchange (up half -> gate half)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -261,28 +265,43 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + ab * ACC_COLS;
-            const int orow = tile.w * 128 + row;  // output row (I index or H index)
-            size_t ocol_off;
-            if (MODE == 0) ocol_off = (size_t)(orow & ~31) + perm_pos(orow & 31);
-            else ocol_off = (size_t)orow;
-            for (int n0 = 0; n0 < ncols; n0 += 16) {
-                uint32_t g[16], u[16];
-                tmem_ld16(taddr + n0, g);
-                if (MODE == 0) tmem_ld16(taddr + BN + n0, u);
-                tmem_ld_wait();
+            if (MODE == 0) {
+                // lanes 0-63 hold gate rows, lanes 64-127 the matching up rows: the up half
+                // hands its values over through shared memory, 16 columns at a time
+                const int irow = tile.w * 64 + (row & 63);
+                const size_t ocol_off = (size_t)(irow & ~31) + perm_pos(irow & 31);
+                int buf = 0;
+                for (int n0 = 0; n0 < ncols; n0 += 16, buf ^= 1) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + n0, v);
+                    tmem_ld_wait();
+                    if (warp >= 2) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (n0 + j < ncols) {
-                        float v = __uint_as_float(g[j]);
-                        if (MODE == 0) {
-                            const float up = __uint_as_float(u[j]);
-                            v = (v / (1.0f + __expf(-v))) * up;
+                        for (int j = 0; j < 16; ++j) xch[buf][row - 64][j] = __uint_as_float(v[j]);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (warp < 2) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            if (n0 + j < ncols) {
+                                const float gt = __uint_as_float(v[j]);
+                                const float sv = (gt / (1.0f + __expf(-gt))) * xch[buf][row][j];
+                                a.out16[(size_t)(tile.y + n0 + j) * a.out_ld + ocol_off] = __float2half_rn(sv);
+                            }
                         }
-                        __half* dst = a.out16 + (size_t)(tile.y + n0 + j) * a.out_ld + ocol_off;
-                        if (MODE == 0 && bf16_mode)
-                            *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(v);
-                        else
-                            *dst = __float2half_rn(v);
+                    }
+                }
+            } else {
+                const size_t ocol_off = (size_t)(tile.w * 128 + row);
+                for (int n0 = 0; n0 < ncols; n0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(taddr + n0, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (n0 + j < ncols)
+                            a.out16[(size_t)(tile.y + n0 + j) * a.out_ld + ocol_off] =
+                                __float2half_rn(__uint_as_float(v[j]));
                     }
                 }
             }
@@ -297,11 +316,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         WTile<Q> cur[NA], nxt[NA];
         auto issue = [&](const int4& tile, int kg, WTile<Q>(&dst)[NA]) {
             const int e = tile.x;
-            const int rt = tile.w * 8 + rtl;
             if (MODE == 0) {
-                load_wtile<Q>(dst[0], a.L.gate_q(e), a.L.gate_s(e), rt * kgs + kg, lane);
-                load_wtile<Q>(dst[NA - 1], a.L.up_q(e), a.L.up_s(e), rt * kgs + kg, lane);
+                const int rt = tile.w * 4 + (rtl & 3);  // m-tile = 64 rows of I: warps 0-3 gate, 4-7 up
+                if (rtl < 4) load_wtile<Q>(dst[0], a.L.gate_q(e), a.L.gate_s(e), rt * kgs + kg, lane);
+                else load_wtile<Q>(dst[0], a.L.up_q(e), a.L.up_s(e), rt * kgs + kg, lane);
             } else {
+                const int rt = tile.w * 8 + rtl;
                 load_wtile<Q>(dst[0], a.L.down_q(e), a.L.down_s(e), rt * kgs + kg, lane);
             }
         };
@@ -469,8 +489,8 @@ cudaError_t launch_permute_x16(const void* x, int act_dtype, size_t n, bool bf16
 
 template <int Q, int MODE>
 static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
-    constexpr int NA = (MODE == 0) ? 2 : 1;
-    constexpr int BN = (MODE == 0) ? 128 : 256;
+    constexpr int NA = 1;
+    constexpr int BN = 256;
     const int smem = 4 * (NA * tc::SUB_BYTES + BN * 128) + 1024;
     static bool attr_set = false;
     if (!attr_set) {
@@ -487,8 +507,8 @@ static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
 // gate/up + SwiGLU then down, both on tcgen05. x16: permuted 16-bit activations [T,H].
 cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st) {
     const int C = p.T * p.K;
-    const int max_ct = C / 128 + p.L.E;
-    const int mt_gu = p.L.I / 128;
+    const int max_ct = C / 256 + p.L.E;
+    const int mt_gu = p.L.I / 64;
     tc::Args gu{};
     gu.L = p.L;
     gu.col_src_tok = p.R.col_src_tok;

@@ -126,7 +126,7 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
     __shared__ int cnt_s[MAX_EXPERTS];
     __shared__ int bounds_s[MAX_EXPERTS + 1];
     __shared__ int tile_off_s[MAX_EXPERTS + 1];
-    __shared__ int tile_off_dn_s[MAX_EXPERTS + 1];  // down tiles are two gate/up tiles wide
+    __shared__ int tile_off_dn_s[MAX_EXPERTS + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid < E) {
         int run = 0;
@@ -148,7 +148,7 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
             lsum += local[j];
             lnz += (local[j] > 0);
             ltl += ltiles[j];
-            ltd += (ltiles[j] + 1) >> 1;
+            ltd += ltiles[j];
         }
         int isum = lsum, inz = lnz, itl = ltl, itd = ltd;
 #pragma unroll
@@ -176,7 +176,7 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
                 if (local[j] > 0) R.uexp[unz++] = ee;
                 run += local[j];
                 trun += ltiles[j];
-                drun += (ltiles[j] + 1) >> 1;
+                drun += ltiles[j];
             }
         }
         if (lane == 31) {
@@ -205,8 +205,8 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
         }
         const int dt0 = tile_off_dn_s[tid], ndt = tile_off_dn_s[tid + 1] - dt0;
         for (int ct = 0; ct < ndt; ++ct) {
-            const int cs = c0 + ct * 2 * tile_cols;
-            const int nc = min(2 * tile_cols, n - ct * 2 * tile_cols);
+            const int cs = c0 + ct * tile_cols;
+            const int nc = min(tile_cols, n - ct * tile_cols);
             for (int mt = 0; mt < mt_dn; ++mt) {
                 const int idx = (dt0 + ct) * mt_dn + mt;
                 if (idx < max_tiles_dn) tiles_dn[idx] = make_int4(tid, cs, nc, mt);
@@ -326,9 +326,9 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const int nchunks = (T + SORT_TOK - 1) / SORT_TOK;
     sort_hist_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist);
     const int C = T * K;
-    const int tile_cols = 128;
+    const int tile_cols = 256;  // columns per grouped-GEMM tile (both products)
     const int max_ct = C / tile_cols + E;
-    const int mt_gu = a.L.I / 128, mt_dn = a.L.H / 128;
+    const int mt_gu = a.L.I / 64, mt_dn = a.L.H / 128;  // gate/up m-tiles pair 64 gate rows with 64 up rows
     int4* tiles_gu = a.tiles;
     int4* tiles_dn = a.tiles ? a.tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1) : nullptr;
     sort_scan_kernel<<<1, 256, 0, st>>>(a.blk_hist, nchunks, E, a.R, tile_cols, mt_gu, mt_dn, tiles_gu, tiles_dn,

@@ -80,6 +80,9 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_ensure_prefill(lumen_moe_ctx* ctx, in
  * offset arrays are HOST arrays of num_experts entries. The blob is left
  * untouched and must outlive the layer (the router weight is read in place); the
  * expert weights are repacked once into aligned planes owned by the layer.
+ * Passing NULL for all three offset tables prepares a router-only layer (nothing
+ * repacked; valid for lumen_moe_route_only only), which is what an expert-parallel
+ * rank uses for the replicated router.
  * Work is enqueued on `stream`; the function synchronises it before returning. */
 LUMEN_MOE_API lumen_moe_status_t lumen_moe_layer_prepare(lumen_moe_ctx* ctx, const void* d_layer_blob,
                                            size_t blob_bytes, uint64_t router_off,
@@ -111,6 +114,17 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_decode_fused_norm(lumen_moe_ctx* ctx,
 LUMEN_MOE_API lumen_moe_status_t lumen_moe_prefill(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
                                      const void* d_normed, const float* d_residual, float* d_out,
                                      int32_t tokens, int32_t act_dtype, void* stream);
+
+/* As lumen_moe_prefill, with the routing supplied by the caller instead of being
+ * computed: d_ids u32 [T,K] (expert ids valid for THIS context, i.e. local ids on
+ * an expert-parallel rank), d_weights f32 [T,K] or NULL (all 1). No counterpart in
+ * the reference (it has no expert parallelism, cuda/ffi.rs:61-87): this is what a
+ * rank runs on the rows it received in the dispatch all-to-all. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_prefill_routed(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                          const void* d_normed, const uint32_t* d_ids,
+                                                          const float* d_weights, const float* d_residual,
+                                                          float* d_out, int32_t tokens, int32_t act_dtype,
+                                                          void* stream);
 
 /* Router only (moe_router_logits_v2 + finalize, cuda/shaders/moe_batched.cu:708,755;
  * batched: cuda/shaders/moe_grouped.cu:79 + topk_moe_fused.cu:172-296).

@@ -74,11 +74,28 @@ lumen_moe_status_t lumen_moe_layer_prepare(lumen_moe_ctx* ctx, const void* d_lay
                                            uint64_t router_off, const uint64_t* gate_offs, const uint64_t* up_offs,
                                            const uint64_t* down_offs, int32_t quant, void* stream,
                                            lumen_moe_layer** out_layer) {
-    if (!ctx || !d_layer_blob || !gate_offs || !up_offs || !down_offs || !out_layer)
-        return fail(LUMEN_MOE_INVALID_ARG, "null argument");
-    if (quant < 0 || quant > 2) return fail(LUMEN_MOE_UNSUPPORTED, "unsupported quant scheme");
+    if (!ctx || !d_layer_blob || !out_layer) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
     const lumen::CudaMoeScratch& sc = ctx->scratch;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (!gate_offs && !up_offs && !down_offs) {
+        // router-only layer: nothing is repacked; usable with lumen_moe_route_only
+        if (router_off % 4 != 0 || router_off + (uint64_t)sc.E * sc.H * 4 > blob_bytes ||
+            (reinterpret_cast<uintptr_t>(d_layer_blob) + router_off) % 16 != 0)
+            return fail(LUMEN_MOE_INVALID_ARG, "router weight misaligned or outside the layer blob");
+        lumen_moe_layer* r = new (std::nothrow) lumen_moe_layer();
+        if (!r) return fail(LUMEN_MOE_CUDA_ERROR, "out of host memory");
+        r->layer.dev.blob = static_cast<const uint8_t*>(d_layer_blob);
+        r->layer.dev.router_w = reinterpret_cast<const float*>(r->layer.dev.blob + router_off);
+        r->layer.dev.H = sc.H;
+        r->layer.dev.I = sc.I;
+        r->layer.dev.E = sc.E;
+        r->layer.dev.quant = -1;
+        r->layer.blob_bytes = blob_bytes;
+        *out_layer = r;
+        return LUMEN_MOE_OK;
+    }
+    if (!gate_offs || !up_offs || !down_offs) return fail(LUMEN_MOE_INVALID_ARG, "null offset table");
+    if (quant < 0 || quant > 2) return fail(LUMEN_MOE_UNSUPPORTED, "unsupported quant scheme");
     lumen::SubtensorOffsets sub;
     sub.has_router = true;
     sub.router_weight.offset = router_off;
@@ -145,6 +162,15 @@ lumen_moe_status_t lumen_moe_prefill(lumen_moe_ctx* ctx, const lumen_moe_layer* 
     if (!ctx || !layer) return fail(LUMEN_MOE_INVALID_ARG, "null handle");
     return done(lumen::encode_moe_ffn_prefill_grouped(&ctx->scratch, layer->layer, d_normed, act_dtype, d_residual,
                                                       d_out, tokens, static_cast<cudaStream_t>(stream)));
+}
+
+lumen_moe_status_t lumen_moe_prefill_routed(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const void* d_normed,
+                                            const uint32_t* d_ids, const float* d_weights, const float* d_residual,
+                                            float* d_out, int32_t tokens, int32_t act_dtype, void* stream) {
+    if (!ctx || !layer || !d_ids) return fail(LUMEN_MOE_INVALID_ARG, "null handle or ids");
+    return done(lumen::encode_moe_ffn_prefill_grouped(&ctx->scratch, layer->layer, d_normed, act_dtype, d_residual,
+                                                      d_out, tokens, static_cast<cudaStream_t>(stream), d_ids,
+                                                      d_weights));
 }
 
 lumen_moe_status_t lumen_moe_route_only(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const float* d_normed,

@@ -239,6 +239,7 @@ void free_moe_layer(MoeLayer* l) {
 static Status check_layer(const CudaMoeScratch* s, const MoeLayer& layer) {
     if (layer.dev.H != s->H || layer.dev.I != s->I || layer.dev.E != s->E)
         return Status::Err(1, "layer shape does not match the context");
+    if (layer.dev.quant < 0) return Status::Err(1, "router-only layer: expert weights were not prepared");
     return Status::Ok();
 }
 
@@ -340,7 +341,8 @@ Status encode_route_only(CudaMoeScratch* s, const MoeLayer* layer, const float* 
 
 // cuda/moe.rs:1900-2760
 Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, const void* normed, int act_dtype,
-                                      const float* residual, float* output, int batch, cudaStream_t st) {
+                                      const float* residual, float* output, int batch, cudaStream_t st,
+                                      const uint32_t* ids_in, const float* weights_in) {
     if (batch < 1) return Status::Err(1, "batch must be positive");
     if (!normed || !residual || !output) return Status::Err(1, "null activation pointer");
     if (act_dtype != 0 && act_dtype != 1) return Status::Err(2, "activation dtype must be f32 or bf16");
@@ -356,6 +358,8 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     p.residual = residual;
     p.out = output;
     p.logits_override = s->logits_override;
+    p.ids_in = ids_in;
+    p.weights_in = weights_in;
     p.T = batch;
     p.K = s->K;
     p.gating = s->gating;

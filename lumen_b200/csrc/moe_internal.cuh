@@ -121,6 +121,8 @@ struct PrefillArgs {
     unsigned int* tile_counter;  // [2] dynamic tile scheduler counters
     int32_t* status;        // [1] device-side error flag (bounded waits)
     int impl;               // 0 = tcgen05 path, 1 = mma.sync grouped fallback
+    const uint32_t* ids_in;  // caller-supplied routing [T,K] (null = route here)
+    const float* weights_in; // [T,K] or null (= 1)
 };
 cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st);
 cudaError_t launch_prefill(const PrefillArgs& a, cudaStream_t st);

@@ -306,11 +306,25 @@ cudaError_t launch_build_xf(const void* x, int act_dtype, int T, int H, int nblk
     return cudaGetLastError();
 }
 
+// Caller-supplied routing (expert-parallel ranks receive rows that were routed
+// elsewhere): copy the ids, weights default to 1.
+__global__ void set_routing_kernel(const uint32_t* __restrict__ ids_in, const float* __restrict__ w_in, int n,
+                                   uint32_t* __restrict__ ids, float* __restrict__ w) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i < n) {
+        ids[i] = ids_in[i];
+        w[i] = w_in ? w_in[i] : 1.0f;
+    }
+}
+
 // Router + tables for any T. tile lists are optional (tiles == nullptr skips them).
 cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const int T = a.T, E = a.L.E, H = a.L.H, K = a.K;
     const float* lg = a.logits_override;
-    if (lg == nullptr) {
+    if (a.ids_in != nullptr) {
+        count_launch();
+        set_routing_kernel<<<(T * K + 255) / 256, 256, 0, st>>>(a.ids_in, a.weights_in, T * K, a.R.ids, a.R.weights);
+    } else if (lg == nullptr) {
         const dim3 grid((T + 63) / 64, (E + 63) / 64);
         count_launch();
         if (a.act_dtype == 0)
@@ -321,8 +335,9 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
         lg = a.R.logits;
     }
     count_launch(4);
-    topk_large_kernel<<<(T + TK_WARPS - 1) / TK_WARPS, TK_WARPS * 32, 0, st>>>(lg, T, E, K, a.gating, a.R.ids,
-                                                                               a.R.weights);
+    if (a.ids_in == nullptr)
+        topk_large_kernel<<<(T + TK_WARPS - 1) / TK_WARPS, TK_WARPS * 32, 0, st>>>(lg, T, E, K, a.gating, a.R.ids,
+                                                                                   a.R.weights);
     const int nchunks = (T + SORT_TOK - 1) / SORT_TOK;
     sort_hist_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist);
     const int C = T * K;

@@ -1,0 +1,135 @@
+"""Expert-parallel MoE layer over G ranks (one process per GPU, torch.distributed).
+
+The reference is single-GPU (one context, one stream, cuda/ffi.rs:61-87); this is the
+additive multi-GPU form of the same layer for multi-token batches:
+
+  tokens are sharded over ranks (each rank routes its own tokens with the replicated
+  router weight), experts are sharded E/G per rank. Per layer call:
+    1. route locally                               (lumen_moe_route_only)
+    2. all-to-all of per-destination row counts    (G x G integers)
+    3. dispatch all-to-all-v: activation rows + local expert ids to the owning rank
+    4. grouped expert products on the received rows (lumen_moe_prefill_routed, K = 1)
+    5. combine all-to-all-v: expert outputs back to the token's home rank
+    6. out[t] = residual[t] + sum_slot w[t,slot] * d[t,slot]   in slot order
+
+The stable counting sort by expert (cuda/moe.rs:2115-2147) already groups the
+(token, slot) pairs by destination rank, because experts are contiguous per rank.
+Batch-1 decode does not use this path (replicas only).
+
+The collective plumbing is backend-agnostic (NCCL on GPUs, gloo on CPU for the
+host-logic tests): `route_fn` and `expert_fn` are injectable, the defaults call
+the CUDA library.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def dispatch_plan(ids: torch.Tensor, experts_per_rank: int, world: int):
+    """ids [T,K] (global expert ids) -> (order, send_counts, local_ids).
+
+    order: permutation of the T*K (token, slot) pairs, stable by destination rank
+    then by expert (tokens ascending, slots ascending inside an expert -- the
+    reference's compact-column order); send_counts[r]: pairs going to rank r;
+    local_ids: expert id relative to the owning rank, in `order`.
+    """
+    flat = ids.reshape(-1).to(torch.int64)
+    order = torch.argsort(flat, stable=True)
+    sorted_ids = flat[order]
+    dest = torch.div(sorted_ids, experts_per_rank, rounding_mode="floor")
+    send_counts = torch.bincount(dest, minlength=world)[:world]
+    local_ids = (sorted_ids - dest * experts_per_rank).to(torch.int32)
+    return order, send_counts, local_ids
+
+
+def all_to_all_v(t: torch.Tensor, send_counts, recv_counts, group=None) -> torch.Tensor:
+    out = t.new_empty((int(sum(recv_counts)),) + tuple(t.shape[1:]))
+    dist.all_to_all_single(out, t.contiguous(), output_split_sizes=list(recv_counts),
+                           input_split_sizes=list(send_counts), group=group)
+    return out
+
+
+class ExpertParallelMoe:
+    """One MoE layer, experts [rank*E/G, (rank+1)*E/G) resident on this rank.
+
+    route_fn(x [T,H]) -> (ids int32 [T,K], weights f32 [T,K])
+    expert_fn(rows [R,H], local_ids int32 [R]) -> d [R,H] (f32): the expert FFN of
+        each row's local expert, unweighted.
+    """
+
+    def __init__(self, num_experts: int, top_k: int, route_fn: Callable, expert_fn: Callable, group=None,
+                 wire_dtype: torch.dtype = torch.bfloat16):
+        self.E, self.K = num_experts, top_k
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if num_experts % self.world:
+            raise ValueError("num_experts must be divisible by the number of ranks")
+        self.epr = num_experts // self.world
+        self.route_fn, self.expert_fn = route_fn, expert_fn
+        self.wire_dtype = wire_dtype
+        self.last = {}
+
+    def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        T, H = normed.shape
+        ids, w = self.route_fn(normed)
+        order, send_counts, local_ids = dispatch_plan(ids, self.epr, self.world)
+        # (2) counts
+        sc = send_counts.to(torch.int64)
+        rc = torch.empty_like(sc)
+        dist.all_to_all_single(rc, sc, group=self.group)
+        send_l, recv_l = sc.tolist(), rc.tolist()  # the one host sync of the call (NCCL sizes are host arguments)
+        # (3) dispatch rows and local expert ids
+        tok = torch.div(order, self.K, rounding_mode="floor")
+        rows = normed[tok].to(self.wire_dtype)
+        recv_rows = all_to_all_v(rows, send_l, recv_l, self.group)
+        recv_ids = all_to_all_v(local_ids, send_l, recv_l, self.group)
+        # (4) local experts
+        d = self.expert_fn(recv_rows, recv_ids)
+        # (5) combine
+        back = all_to_all_v(d.to(self.wire_dtype), recv_l, send_l, self.group)
+        # (6) weighted sum in slot order
+        dpair = torch.empty((T * self.K, H), dtype=torch.float32, device=normed.device)
+        dpair[order] = back.to(torch.float32)
+        dpair = dpair.view(T, self.K, H)
+        out = residual.clone()
+        for slot in range(self.K):
+            out += w[:, slot, None] * dpair[:, slot]
+        self.last = {"ids": ids, "weights": w, "send_counts": send_l, "recv_counts": recv_l}
+        return out
+
+
+def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.Tensor, rank: int, world: int,
+                   max_tokens: int, gating_mode: int = 0) -> Tuple[Callable, Callable, dict]:
+    """Builds route_fn / expert_fn on the CUDA library for this rank.
+
+    `full_blob` is the complete layer blob (router + all experts) in the reference
+    layout; only this rank's expert slice is repacked and kept by the expert
+    context (K = 1, E/G experts); a second, router-only context routes."""
+    from . import moe, synth
+    epr = E // world
+    lay = synth.LayerLayout(H, I, E, quant)
+    meta = lay.meta()
+    route_sc = moe.allocate_moe_scratch(H, I, E, K, max_tokens, gating_mode)
+    route_layer = route_sc.prepare_router_only(full_blob, meta.router_weight_off)
+    exp_sc = moe.allocate_moe_scratch(H, I, epr, 1, max_tokens * K, gating_mode)
+    sl = slice(rank * epr, (rank + 1) * epr)
+    local_meta = moe.MoeMeta(0, meta.expert_gate_offs[sl].copy(), meta.expert_up_offs[sl].copy(),
+                             meta.expert_down_offs[sl].copy(), quant, quant)
+    exp_layer = exp_sc.prepare_layer(full_blob, local_meta)
+
+    def route_fn(x):
+        ids, w = route_sc.route_only(route_layer, x.float().contiguous())
+        return ids, w
+
+    def expert_fn(rows, local_ids):
+        R = rows.shape[0]
+        if R == 0:
+            return torch.zeros((0, H), dtype=torch.float32, device=rows.device)
+        zero = torch.zeros((R, H), dtype=torch.float32, device=rows.device)
+        return exp_sc.prefill_routed(exp_layer, rows.contiguous(), local_ids.contiguous(), None, zero)
+
+    return route_fn, expert_fn, {"route": route_sc, "experts": exp_sc, "layers": (route_layer, exp_layer)}

@@ -133,6 +133,15 @@ class MoeScratch:
                                                  meta.expert_gate_quant, _stream(), ctypes.byref(h)))
         return MoeLayer(h.value, blob, meta)
 
+    def prepare_router_only(self, blob: torch.Tensor, router_weight_off: int = 0) -> MoeLayer:
+        """Layer usable for route_only only (no expert planes): the replicated router of
+        an expert-parallel rank."""
+        _need(blob, torch.uint8, "layer blob")
+        h = ctypes.c_void_p()
+        check(_lib.lib().lumen_moe_layer_prepare(self._h, blob.data_ptr(), blob.numel(), router_weight_off, None,
+                                                 None, None, 0, _stream(), ctypes.byref(h)))
+        return MoeLayer(h.value, blob, None)
+
     def ensure_prefill_grouped(self, batch: int) -> None:
         check(_lib.lib().lumen_moe_ensure_prefill(self._h, batch))
 
@@ -176,6 +185,21 @@ class MoeScratch:
             output = torch.empty_like(residual)
         check(_lib.lib().lumen_moe_prefill(self._h, layer._h, normed.data_ptr(), residual.data_ptr(),
                                            output.data_ptr(), T, act, _stream()))
+        return output
+
+    def prefill_routed(self, layer: MoeLayer, normed: torch.Tensor, ids: torch.Tensor,
+                       weights: Optional[torch.Tensor], residual: torch.Tensor,
+                       output: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """lumen_moe_prefill_routed: expert products + combine for caller-supplied routing."""
+        act = ACT_F32 if normed.dtype == torch.float32 else ACT_BF16
+        _need(normed, normed.dtype, "normed")
+        _need(ids, torch.int32, "ids")
+        _need(residual, torch.float32, "residual")
+        T = normed.numel() // self.H
+        if output is None:
+            output = torch.empty_like(residual)
+        check(_lib.lib().lumen_moe_prefill_routed(self._h, layer._h, normed.data_ptr(), ids.data_ptr(), _ptr(weights),
+                                                  residual.data_ptr(), output.data_ptr(), T, act, _stream()))
         return output
 
     def route_only(self, layer: MoeLayer, normed_x: torch.Tensor, want_logits: bool = False):

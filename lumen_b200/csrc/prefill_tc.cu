@@ -218,7 +218,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ uint32_t abort_s;
-    __shared__ float xch[2][64][17];  // gate/up epilogue exchange (up half -> gate half)
+    __shared__ float xch[2][2][64][17];  // gate/up epilogue exchange: [buffer][up->gate | gate->up][row][column]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -257,6 +257,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         // ------------------------------ epilogue ------------------------------
         const int row = warp * 32 + lane;
         int tl = 0;
+        int xbuf = 0;  // exchange buffer parity: alternates over ALL chunks of all tiles
         bool ok = true;
         for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
             const int4 tile = a.tiles[ti];
@@ -270,24 +271,28 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 // hands its values over through shared memory, 16 columns at a time
                 const int irow = tile.w * 64 + (row & 63);
                 const size_t ocol_off = (size_t)(irow & ~31) + perm_pos(irow & 31);
-                int buf = 0;
-                for (int n0 = 0; n0 < ncols; n0 += 16, buf ^= 1) {
-                    uint32_t v[16];
-                    tmem_ld16(taddr + n0, v);
+                // Per 32 columns: the gate half computes the first 16 (it receives the up
+                // values), the up half computes the last 16 (it receives the gate values),
+                // so all four warps share the SwiGLU and store work.
+                const int r64 = row & 63;
+                for (int n0 = 0; n0 < ncols; n0 += 32, xbuf ^= 1) {
+                    uint32_t v0[16], v1[16];
+                    tmem_ld16(taddr + n0, v0);
+                    tmem_ld16(taddr + n0 + 16, v1);
                     tmem_ld_wait();
-                    if (warp >= 2) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) xch[buf][row - 64][j] = __uint_as_float(v[j]);
-                    }
+                    for (int j = 0; j < 16; ++j)
+                        xch[xbuf][warp >= 2 ? 0 : 1][r64][j] = __uint_as_float(warp >= 2 ? v0[j] : v1[j]);
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (warp < 2) {
+                    const int cbase = n0 + (warp >= 2 ? 16 : 0);
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            if (n0 + j < ncols) {
-                                const float gt = __uint_as_float(v[j]);
-                                const float sv = (gt / (1.0f + __expf(-gt))) * xch[buf][row][j];
-                                a.out16[(size_t)(tile.y + n0 + j) * a.out_ld + ocol_off] = __float2half_rn(sv);
-                            }
+                    for (int j = 0; j < 16; ++j) {
+                        if (cbase + j < ncols) {
+                            const float other = xch[xbuf][warp >= 2 ? 1 : 0][r64][j];
+                            const float gt = (warp >= 2) ? other : __uint_as_float(v0[j]);
+                            const float up = (warp >= 2) ? __uint_as_float(v1[j]) : other;
+                            const float sv = (gt / (1.0f + __expf(-gt))) * up;
+                            a.out16[(size_t)(tile.y + cbase + j) * a.out_ld + ocol_off] = __float2half_rn(sv);
                         }
                     }
                 }

@@ -134,7 +134,7 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
     const size_t C = (size_t)cap * s.K;
     const size_t nblk_h_pad = (size_t)((s.H / 32 + 3) / 4) * 4, nblk_i_pad = (size_t)((s.I / 32 + 3) / 4) * 4;
     const size_t max_ct = C / 256 + s.E;
-    const size_t mt = (size_t)s.I / 64 + (size_t)s.H / 128;
+    const size_t mt = (size_t)s.I / 128 + (size_t)s.H / 256 + 1;
     size_t sizes[13] = {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,
         (size_t)((cap + 31) / 32) * s.E * 4,
@@ -369,7 +369,7 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     p.tiles = s->tiles;
     p.n_tiles = s->n_tiles;
     p.status = s->status;
-    const bool tc_ok = (s->H % 128 == 0) && (s->I % 128 == 0);
+    const bool tc_ok = (s->H % 256 == 0) && (s->I % 128 == 0);
     p.impl = (s->prefill_impl == 1 || !tc_ok) ? 1 : 0;
     CUDA_TRY(launch_route_large(p, st));
     const bool bf16_mode = (layer.dev.quant == BF16);

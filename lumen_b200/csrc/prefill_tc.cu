@@ -31,7 +31,7 @@ namespace lumen {
 
 namespace tc {
 
-constexpr int EPI_WARPS = 4, A_WARPS = 8, B_WARPS = 4;
+constexpr int EPI_WARPS = 8, A_WARPS = 8, B_WARPS = 4;
 constexpr int A_WARP0 = EPI_WARPS, B_WARP0 = A_WARP0 + A_WARPS, MMA_WARP = B_WARP0 + B_WARPS;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int SUB_BYTES = 128 * 128;  // [128 rows x 64 k] f16, 128-byte rows, SWIZZLE_128B
@@ -204,21 +204,22 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
 template <int Q, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
-    // One weight operand per stage in both modes. Gate/up mode packs 64 gate rows
-    // (TMEM lanes 0-63) and the 64 matching up rows (lanes 64-127) into one M=128
-    // tile, so one 256-column accumulator holds both and can be double-buffered.
-    constexpr int NA = 1;
+    // Two 128-row weight operands share every 256-column activation stage (gate and
+    // up rows of the same I range; two adjacent row tiles of the down matrix): the
+    // activation operand, which comes from L2 at 2 bytes per element, is then read
+    // at 32 B/clk/SM instead of 64. The two 256-column f32 accumulators fill TMEM
+    // (512 columns), so there is one accumulator set and the epilogue of a tile is
+    // not overlapped with the next tile's MMAs (its producers do run ahead).
+    constexpr int NA = 2;
     constexpr int BN = 256;                            // columns per tile
-    constexpr int STAGES = 4;                          // one stage = 64 inputs (one swizzle atom in K)
-    constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operand(s) then B
-    constexpr int ACC_COLS = NA * BN;
-    constexpr int TMEM_COLS = 2 * ACC_COLS;
+    constexpr int STAGES = 3;                          // one stage = 64 inputs (one swizzle atom in K)
+    constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operands then B
+    constexpr int TMEM_COLS = NA * BN;
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[2], acc_empty_bar[2];
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar, acc_empty_bar;
     __shared__ uint32_t tmem_base_s;
     __shared__ uint32_t abort_s;
-    __shared__ float xch[2][2][64][17];  // gate/up epilogue exchange: [buffer][up->gate | gate->up][row][column]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -230,10 +231,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             mbar_init(smem_u32(&full_bar[s]), A_WARPS * 32 + B_WARPS * 32);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&acc_full_bar[i]), 1);
-            mbar_init(smem_u32(&acc_empty_bar[i]), EPI_WARPS * 32);
-        }
+        mbar_init(smem_u32(&acc_full_bar), 1);
+        mbar_init(smem_u32(&acc_empty_bar), EPI_WARPS * 32);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == MMA_WARP) {
@@ -255,63 +254,48 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 
     if (warp < EPI_WARPS) {
         // ------------------------------ epilogue ------------------------------
-        const int row = warp * 32 + lane;
+        // warp w reads TMEM lanes 32*(w%4).. (hardware rule); warps 0-3 take columns
+        // 0-127 of the tile, warps 4-7 columns 128-255
+        const int row = (warp & 3) * 32 + lane;
+        const int chalf = (warp >> 2) * 128;
         int tl = 0;
-        int xbuf = 0;  // exchange buffer parity: alternates over ALL chunks of all tiles
         bool ok = true;
         for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
             const int4 tile = a.tiles[ti];
-            const int ncols = tile.z, ab = tl & 1, aph = (tl >> 1) & 1;
-            ok = mbar_wait(smem_u32(&acc_full_bar[ab]), aph, abort_flag);
+            const int ncols = tile.z;
+            ok = mbar_wait(smem_u32(&acc_full_bar), tl & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + ab * ACC_COLS;
+            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            size_t off0, off1 = 0;
             if (MODE == 0) {
-                // lanes 0-63 hold gate rows, lanes 64-127 the matching up rows: the up half
-                // hands its values over through shared memory, 16 columns at a time
-                const int irow = tile.w * 64 + (row & 63);
-                const size_t ocol_off = (size_t)(irow & ~31) + perm_pos(irow & 31);
-                // Per 32 columns: the gate half computes the first 16 (it receives the up
-                // values), the up half computes the last 16 (it receives the gate values),
-                // so all four warps share the SwiGLU and store work.
-                const int r64 = row & 63;
-                for (int n0 = 0; n0 < ncols; n0 += 32, xbuf ^= 1) {
-                    uint32_t v0[16], v1[16];
-                    tmem_ld16(taddr + n0, v0);
-                    tmem_ld16(taddr + n0 + 16, v1);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        xch[xbuf][warp >= 2 ? 0 : 1][r64][j] = __uint_as_float(warp >= 2 ? v0[j] : v1[j]);
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    const int cbase = n0 + (warp >= 2 ? 16 : 0);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (cbase + j < ncols) {
-                            const float other = xch[xbuf][warp >= 2 ? 1 : 0][r64][j];
-                            const float gt = (warp >= 2) ? other : __uint_as_float(v0[j]);
-                            const float up = (warp >= 2) ? __uint_as_float(v1[j]) : other;
-                            const float sv = (gt / (1.0f + __expf(-gt))) * up;
-                            a.out16[(size_t)(tile.y + cbase + j) * a.out_ld + ocol_off] = __float2half_rn(sv);
-                        }
-                    }
-                }
+                const int irow = tile.w * 128 + row;  // SwiGLU output is stored in the permuted order
+                off0 = (size_t)(irow & ~31) + perm_pos(irow & 31);
             } else {
-                const size_t ocol_off = (size_t)(tile.w * 128 + row);
-                for (int n0 = 0; n0 < ncols; n0 += 16) {
-                    uint32_t v[16];
-                    tmem_ld16(taddr + n0, v);
-                    tmem_ld_wait();
+                off0 = (size_t)(tile.w * 256 + row);
+                off1 = off0 + 128;
+            }
+            for (int n0 = chalf; n0 < ncols && n0 < chalf + 128; n0 += 16) {
+                uint32_t v0[16], v1[16];
+                tmem_ld16(taddr + n0, v0);
+                tmem_ld16(taddr + BN + n0, v1);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        if (n0 + j < ncols)
-                            a.out16[(size_t)(tile.y + n0 + j) * a.out_ld + ocol_off] =
-                                __float2half_rn(__uint_as_float(v[j]));
+                for (int j = 0; j < 16; ++j) {
+                    if (n0 + j < ncols) {
+                        __half* dst = a.out16 + (size_t)(tile.y + n0 + j) * a.out_ld;
+                        if (MODE == 0) {
+                            const float gt = __uint_as_float(v0[j]);
+                            dst[off0] = __float2half_rn((gt / (1.0f + __expf(-gt))) * __uint_as_float(v1[j]));
+                        } else {
+                            dst[off0] = __float2half_rn(__uint_as_float(v0[j]));
+                            dst[off1] = __float2half_rn(__uint_as_float(v1[j]));
+                        }
                     }
                 }
             }
             tc_fence_before();
-            mbar_arrive(smem_u32(&acc_empty_bar[ab]));
+            mbar_arrive(smem_u32(&acc_empty_bar));
         }
     } else if (warp < B_WARP0) {
         // --------------------------- weight producers --------------------------
@@ -322,12 +306,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         auto issue = [&](const int4& tile, int kg, WTile<Q>(&dst)[NA]) {
             const int e = tile.x;
             if (MODE == 0) {
-                const int rt = tile.w * 4 + (rtl & 3);  // m-tile = 64 rows of I: warps 0-3 gate, 4-7 up
-                if (rtl < 4) load_wtile<Q>(dst[0], a.L.gate_q(e), a.L.gate_s(e), rt * kgs + kg, lane);
-                else load_wtile<Q>(dst[0], a.L.up_q(e), a.L.up_s(e), rt * kgs + kg, lane);
+                const int rt = tile.w * 8 + rtl;  // m-tile = 128 rows of I: operand 0 gate, operand 1 up
+                load_wtile<Q>(dst[0], a.L.gate_q(e), a.L.gate_s(e), rt * kgs + kg, lane);
+                load_wtile<Q>(dst[1], a.L.up_q(e), a.L.up_s(e), rt * kgs + kg, lane);
             } else {
-                const int rt = tile.w * 8 + rtl;
+                const int rt = tile.w * 16 + rtl;  // m-tile = 256 rows of H: two adjacent 128-row tiles
                 load_wtile<Q>(dst[0], a.L.down_q(e), a.L.down_s(e), rt * kgs + kg, lane);
+                load_wtile<Q>(dst[1], a.L.down_q(e), a.L.down_s(e), (rt + 8) * kgs + kg, lane);
             }
         };
         // tile descriptors are fetched one tile ahead so that no weight load waits on one
@@ -426,8 +411,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 const int4 tile = a.tiles[ti];
                 const int n16 = (tile.z + 15) & ~15;
                 const uint32_t idesc = make_idesc(n16, bf16_mode);
-                const int ab = tl & 1, aph = (tl >> 1) & 1;
-                ok = mbar_wait(smem_u32(&acc_empty_bar[ab]), aph ^ 1, abort_flag);
+                ok = mbar_wait(smem_u32(&acc_empty_bar), (tl & 1) ^ 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 for (int kh = 0; kh < khs; ++kh, ++it) {
@@ -444,13 +428,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 #pragma unroll
                         for (int op = 0; op < NA; ++op) {
                             const uint64_t adesc = make_desc(sbase + op * SUB_BYTES + j * 32);
-                            umma(tmem_base + ab * ACC_COLS + op * BN, adesc, bdesc, idesc, acc);
+                            umma(tmem_base + op * BN, adesc, bdesc, idesc, acc);
                         }
                     }
                     umma_commit(smem_u32(&empty_bar[s]));
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&acc_full_bar[ab]));
+                umma_commit(smem_u32(&acc_full_bar));
             }
         }
         __syncwarp();
@@ -494,9 +478,9 @@ cudaError_t launch_permute_x16(const void* x, int act_dtype, size_t n, bool bf16
 
 template <int Q, int MODE>
 static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
-    constexpr int NA = 1;
+    constexpr int NA = 2;
     constexpr int BN = 256;
-    const int smem = 4 * (NA * tc::SUB_BYTES + BN * 128) + 1024;
+    const int smem = 3 * (NA * tc::SUB_BYTES + BN * 128) + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(tc::grouped_gemm_tc_kernel<Q, MODE>,
@@ -513,7 +497,7 @@ static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
 cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st) {
     const int C = p.T * p.K;
     const int max_ct = C / 256 + p.L.E;
-    const int mt_gu = p.L.I / 64;
+    const int mt_gu = p.L.I / 128;
     tc::Args gu{};
     gu.L = p.L;
     gu.col_src_tok = p.R.col_src_tok;

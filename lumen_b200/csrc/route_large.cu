@@ -343,7 +343,7 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const int C = T * K;
     const int tile_cols = 256;  // columns per grouped-GEMM tile (both products)
     const int max_ct = C / tile_cols + E;
-    const int mt_gu = a.L.I / 64, mt_dn = a.L.H / 128;  // gate/up m-tiles pair 64 gate rows with 64 up rows
+    const int mt_gu = a.L.I / 128, mt_dn = a.L.H / 256;  // m-tiles: 128 gate + 128 up rows | 256 down rows
     int4* tiles_gu = a.tiles;
     int4* tiles_dn = a.tiles ? a.tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1) : nullptr;
     sort_scan_kernel<<<1, 256, 0, st>>>(a.blk_hist, nchunks, E, a.R, tile_cols, mt_gu, mt_dn, tiles_gu, tiles_dn,

@@ -376,6 +376,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                     nbytes[q] = valid ? 16u : 0u;
                 }
             }
+            // publish stage n-2 first (its copies were issued two iterations ago), so that
+            // handing a stage to the MMA never waits for a free slot
+            if (n >= LAG) {
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+                fence_proxy_async();
+                mbar_arrive(smem_u32(&full_bar[(n - LAG) % STAGES]));
+            }
             const int s = n % STAGES, ph = (n / STAGES) & 1;
             ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
             if (!ok) break;
@@ -390,11 +397,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             }
             asm volatile("cp.async.commit_group;" ::: "memory");
             issued = n + 1;
-            if (n >= LAG) {
-                asm volatile("cp.async.wait_group 2;" ::: "memory");
-                fence_proxy_async();
-                mbar_arrive(smem_u32(&full_bar[(n - LAG) % STAGES]));
-            }
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         if (ok) {

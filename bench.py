@@ -342,9 +342,75 @@ def run_prefill(args):
                                    "frac": tf / peak, "flops_per_call": flops}}), flush=True)
 
 
+def run_ep_prefill(args):
+    """Secondary workload: expert-parallel prefill (BASELINE config 4). `--tokens` tokens
+    in total, sharded over the ranks; 128 experts split evenly; NCCL all-to-all dispatch
+    and combine. Strong scaling: total work fixed as N grows. At N = 1 the same tokens go
+    through the single-GPU prefill entry point."""
+    import torch
+    import torch.distributed as dist
+    from lumen_b200 import build, ep, moe, synth
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if rank == 0:
+        build.build()
+    if world > 1:
+        dist.barrier()
+    quant, T = QUANTS[args.quant], args.tokens
+    Tl = T // world
+    lay = synth.LayerLayout(H, I, E, quant)
+    blob = synth.make_layer_blob(lay, 0, device=dev)        # identical on every rank
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    x_all = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16)
+    x = x_all[rank * Tl:(rank + 1) * Tl].contiguous()
+    res = torch.zeros((Tl, H), device=dev)
+    if world == 1:
+        sc = moe.allocate_moe_scratch(H, I, E, K, T, device=local)
+        layer = sc.prepare_layer(blob, lay.meta())
+        fwd = lambda: sc.prefill(layer, x, res)
+    else:
+        route_fn, expert_fn, keep = ep.cuda_layer_fns(H, I, E, K, quant, blob, rank, world, Tl)
+        epl = ep.ExpertParallelMoe(E, K, route_fn, expert_fn)
+        fwd = lambda: epl.forward(x, res)
+    for _ in range(max(3, args.warmup)):
+        out = fwd()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        out = fwd()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    checksum = float(out.float().abs().sum())
+    if world > 1:
+        t = torch.tensor([ms, checksum], device=dev, dtype=torch.float64)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, checksum = float(tmax[0]), float(t[1])
+    if rank == 0:
+        print(json.dumps({"metric": "moe_layer_ep_prefill_tokens_per_s", "value": T / (ms / 1e3), "unit": "tokens/s",
+                          "n_gpus": world, "steps": args.steps, "ms_per_call": ms, "scaling": "strong",
+                          "config": {"workload": f"moe_ffn_ep_prefill_{args.quant}_T{T}", "experts_per_gpu": E // world,
+                                     "tokens_per_gpu": Tl, "wire_dtype": "bf16", "collective": "nccl all_to_all_single"},
+                          "abs_sum_of_output": checksum}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_prefill"])
     ap.add_argument("--routing", default="zipf", choices=["zipf", "uniform", "router"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -359,6 +425,8 @@ def main():
         run_reference(args)
     elif args.workload == "prefill":
         run_prefill(args)
+    elif args.workload == "ep_prefill":
+        run_ep_prefill(args)
     else:
         run_gpu(args)
 

@@ -1,0 +1,64 @@
+"""Expert-parallel layer on 2 GPUs (NCCL) against the single-GPU result. Needs two
+devices; skipped otherwise (the host logic is covered on CPU by test_ep_gloo.py)."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from lumen_b200 import ep, moe, synth
+        H, I, E, K, T = 512, 256, 32, 4, 600
+        dev = f"cuda:{rank}"
+        lay = synth.LayerLayout(H, I, E, 1)
+        blob = synth.make_layer_blob(lay, 3, device=dev)
+        g = torch.Generator(device=dev)
+        g.manual_seed(4)
+        x_all = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16)
+        res_all = torch.randn((T, H), generator=g, device=dev)
+        Tl = T // world
+        sl = slice(rank * Tl, (rank + 1) * Tl)
+        route_fn, expert_fn, keep = ep.cuda_layer_fns(H, I, E, K, 1, blob, rank, world, Tl)
+        layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn)
+        out = layer.forward(x_all[sl].contiguous(), res_all[sl].contiguous())
+        sc = moe.allocate_moe_scratch(H, I, E, K, T, device=rank)
+        full = sc.prepare_layer(blob, lay.meta())
+        ref = sc.prefill(full, x_all, res_all)[sl]
+        rel = float(((out - ref) - 0).norm() / (ref - res_all[sl]).norm())
+        r = sc.get_routing(T)
+        ids_ok = bool((torch.from_numpy(r["ids"][sl].astype("int32")).to(dev) == layer.last["ids"]).all())
+        q.put((rank, rel, ids_ok))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_matches_single_gpu(cuda_lib):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, rel, ids_ok in results:
+        assert ids_ok
+        assert rel < 2e-3, (rank, rel)  # bf16 rows on the wire in both directions

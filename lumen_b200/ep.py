@@ -61,7 +61,7 @@ class ExpertParallelMoe:
     """
 
     def __init__(self, num_experts: int, top_k: int, route_fn: Callable, expert_fn: Callable, group=None,
-                 wire_dtype: torch.dtype = torch.bfloat16):
+                 wire_dtype: torch.dtype = torch.bfloat16, combine_dtype: torch.dtype = torch.float16):
         self.E, self.K = num_experts, top_k
         self.group = group
         self.world = dist.get_world_size(group)
@@ -70,7 +70,8 @@ class ExpertParallelMoe:
             raise ValueError("num_experts must be divisible by the number of ranks")
         self.epr = num_experts // self.world
         self.route_fn, self.expert_fn = route_fn, expert_fn
-        self.wire_dtype = wire_dtype
+        self.wire_dtype = wire_dtype        # activation rows on the wire (bf16 inputs travel exactly)
+        self.combine_dtype = combine_dtype  # expert outputs on the wire (f16, as the single-GPU path stores them)
         self.last = {}
 
     def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
@@ -90,7 +91,7 @@ class ExpertParallelMoe:
         # (4) local experts
         d = self.expert_fn(recv_rows, recv_ids)
         # (5) combine
-        back = all_to_all_v(d.to(self.wire_dtype), recv_l, send_l, self.group)
+        back = all_to_all_v(d.to(self.combine_dtype), recv_l, send_l, self.group)
         # (6) weighted sum in slot order
         dpair = torch.empty((T * self.K, H), dtype=torch.float32, device=normed.device)
         dpair[order] = back.to(torch.float32)

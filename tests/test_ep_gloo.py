@@ -56,7 +56,7 @@ def _worker(rank, world, port, tokens_per_rank, result_q):
                 out[i] = oracle.matvec(blob[int(meta.expert_down_offs[e]):], oracle.swiglu(g, u), H, I, QUANT)
             return torch.from_numpy(out)
 
-        layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, wire_dtype=torch.float32)
+        layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, wire_dtype=torch.float32, combine_dtype=torch.float32)
         out = layer.forward(torch.from_numpy(x), torch.from_numpy(x)).numpy()
         if T > 0:
             ref, ids, _ = oracle.moe_layer(blob, 0, meta.expert_gate_offs, meta.expert_up_offs, meta.expert_down_offs,

@@ -14,7 +14,8 @@ cudaError_t launch_scatter_accum(const __half* d16, const float* residual, const
                                  int T, int H, int K, cudaStream_t st);
 cudaError_t launch_build_xf(const void* x, int act_dtype, int T, int H, int nblk_pad, bool bf16_mode,
                             uint4* xf, cudaStream_t st);
-cudaError_t launch_permute_x16(const void* x, int act_dtype, size_t n, bool bf16_mode, void* out, cudaStream_t st);
+cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_t* col_src_tok, int C, int H, void* out,
+                                      cudaStream_t st);
 cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st);
 
 static std::atomic<long long> g_launches{0};
@@ -139,7 +140,7 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,
         (size_t)((cap + 31) / 32) * s.E * 4,
         max_ct * (mt ? mt : 1) * sizeof(int4),
-        C * s.I * 2, C * s.H * 2, (size_t)cap * s.H * 2,
+        C * s.I * 2, C * s.H * 2, C * s.H * 2,
         (size_t)cap * 2 * nblk_h_pad * 64, C * 2 * nblk_i_pad * 64};
     size_t off = 0;
     for (int i = 0; i < 13; ++i) {
@@ -374,7 +375,7 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     CUDA_TRY(launch_route_large(p, st));
     const bool bf16_mode = (layer.dev.quant == BF16);
     if (p.impl == 0) {
-        CUDA_TRY(launch_permute_x16(normed, act_dtype, (size_t)batch * s->H, false, s->x16, st));
+        CUDA_TRY(launch_gather_permute_x16(normed, act_dtype, s->R.col_src_tok, batch * s->K, s->H, s->x16, st));
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

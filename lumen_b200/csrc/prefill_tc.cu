@@ -26,12 +26,14 @@
 // (permute_x16_kernel); the SwiGLU output is written in the same order so the
 // down product reads it back without any shuffle.
 #include "mma_frag.cuh"
+#include <cuda.h>
+#include <cstdlib>
 
 namespace lumen {
 
 namespace tc {
 
-constexpr int EPI_WARPS = 8, A_WARPS = 8, B_WARPS = 4;
+constexpr int EPI_WARPS = 8, A_WARPS = 8, B_WARPS = 1;  // B: one thread drives the TMA
 constexpr int A_WARP0 = EPI_WARPS, B_WARP0 = A_WARP0 + A_WARPS, MMA_WARP = B_WARP0 + B_WARPS;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 constexpr int SUB_BYTES = 128 * 128;  // [128 rows x 64 k] f16, 128-byte rows, SWIZZLE_128B
@@ -129,8 +131,9 @@ __host__ __device__ __forceinline__ int perm_pos(int e) {
 }
 
 struct Args {
+    CUtensorMap tmap;            // activation operand [rows, kdim] f16, box 64 x 128, SWIZZLE_128B (first: 64-byte aligned)
     LayerDev L;
-    const int32_t* col_src_tok;  // gather table (gate/up mode) or nullptr (rows = columns)
+    const int32_t* col_src_tok;  // unused by the GEMM (rows are pre-gathered); kept for diagnostics
     const int4* tiles;
     const int32_t* n_tiles;
     const void* b_src;      // 16-bit activations [rows, kdim], permuted order
@@ -138,6 +141,7 @@ struct Args {
     int32_t* status;
     int kdim;               // H (gate/up) or I (down)
     int out_ld;             // I or H
+    int dbg;                // timing experiments only (LUMEN_TC_DBG): 1 skip dequant, 2 skip activation copies, 4 skip stores
 };
 
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
@@ -228,7 +232,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     if (tid == 0) {
         abort_s = 0u;
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), A_WARPS * 32 + B_WARPS * 32);
+            mbar_init(smem_u32(&full_bar[s]), A_WARPS * 32 + 1);  // weight producers + the TMA thread's expect_tx arrive
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         mbar_init(smem_u32(&acc_full_bar), 1);
@@ -282,7 +286,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    if (n0 + j < ncols) {
+                    if (n0 + j < ncols && !(a.dbg & 4)) {
                         __half* dst = a.out16 + (size_t)(tile.y + n0 + j) * a.out_ld;
                         if (MODE == 0) {
                             const float gt = __uint_as_float(v0[j]);
@@ -334,7 +338,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 if (ok) {
                     const uint32_t sbase = stage0 + s * STAGE_BYTES;
 #pragma unroll
-                    for (int op = 0; op < NA; ++op) dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
+                    for (int op = 0; op < NA; ++op)
+                        if (!(a.dbg & 1)) dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
                     fence_proxy_async();
                     mbar_arrive(smem_u32(&full_bar[s]));
                 }
@@ -351,59 +356,43 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         }
     } else if (warp < MMA_WARP) {
         // ------------------------- activation producers ------------------------
-        constexpr int RPT = BN / 128;              // B-operand rows (tile columns) per thread
-        const int r = tid - B_WARP0 * 32;
-        const int my_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        const int nitems = my_tiles * khs;
-        const uint8_t* src_row[RPT];
-        uint32_t nbytes[RPT];
-        bool ok = true;
-        // Copies of up to three stages are in flight: stage n is issued as soon as its
-        // slot is free, stage n-2 is published once its own copy group has landed.
-        constexpr int LAG = 2;
-        int issued = 0;
-        for (int n = 0; ok && n < nitems; ++n) {
-            const int kh = n % khs;
-            if (kh == 0) {
-                const int4 tile = a.tiles[blockIdx.x + (n / khs) * gridDim.x];
-#pragma unroll
-                for (int q = 0; q < RPT; ++q) {
-                    const int rr = r + q * 128;
-                    const bool valid = rr < tile.z;
-                    int srow = 0;
-                    if (valid) srow = a.col_src_tok ? a.col_src_tok[tile.y + rr] : (tile.y + rr);
-                    src_row[q] = reinterpret_cast<const uint8_t*>(a.b_src) + (size_t)srow * a.kdim * 2;
-                    nbytes[q] = valid ? 16u : 0u;
+        // One thread feeds the activation operand with TMA: per 64-input stage one or two
+        // 128-row boxes of the compact (pre-gathered, pre-permuted) f16 activations land
+        // in the SWIZZLE_128B layout the MMA descriptor expects; completion is counted in
+        // bytes on the stage's full barrier.
+        if (lane == 0) {
+            const int my_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            const int nitems = my_tiles * khs;
+            const uint64_t tmap_addr = reinterpret_cast<uint64_t>(&a.tmap);
+            int row0 = 0, nbox = 1;
+            bool ok = true;
+            for (int n = 0; ok && n < nitems; ++n) {
+                const int kh = n % khs;
+                if (kh == 0) {
+                    const int4 tile = a.tiles[blockIdx.x + (n / khs) * gridDim.x];
+                    row0 = tile.y;
+                    nbox = (tile.z > 128) ? 2 : 1;
                 }
+                const int s = n % STAGES, ph = (n / STAGES) & 1;
+                ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
+                if (!ok) break;
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                const uint32_t bbase = stage0 + s * STAGE_BYTES + NA * SUB_BYTES;
+                if (a.dbg & 2) {
+                    mbar_arrive(bar);
+                    continue;
+                }
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nbox * SUB_BYTES)
+                             : "memory");
+                for (int q = 0; q < nbox; ++q)
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                        "[%0], [%1, {%2, %3}], [%4];" ::"r"(bbase + q * SUB_BYTES),
+                        "l"(tmap_addr), "r"(kh * 64), "r"(row0 + q * 128), "r"(bar)
+                        : "memory");
             }
-            // publish stage n-2 first (its copies were issued two iterations ago), so that
-            // handing a stage to the MMA never waits for a free slot
-            if (n >= LAG) {
-                asm volatile("cp.async.wait_group 1;" ::: "memory");
-                fence_proxy_async();
-                mbar_arrive(smem_u32(&full_bar[(n - LAG) % STAGES]));
-            }
-            const int s = n % STAGES, ph = (n / STAGES) & 1;
-            ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
-            if (!ok) break;
-            const uint32_t bbase = stage0 + s * STAGE_BYTES + NA * SUB_BYTES;
-#pragma unroll
-            for (int q = 0; q < RPT; ++q) {
-                const int rr = r + q * 128;
-                const uint8_t* src = src_row[q] + (size_t)kh * 128;
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    cp_async16(bbase + rr * 128 + ((c ^ (rr & 7)) << 4), src + c * 16, nbytes[q]);
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            issued = n + 1;
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        if (ok) {
-            fence_proxy_async();
-            for (int m = (issued > LAG ? issued - LAG : 0); m < issued; ++m)
-                mbar_arrive(smem_u32(&full_bar[m % STAGES]));
-        }
+        __syncwarp();
     } else {
         // -------------------------------- MMA ---------------------------------
         if (lane == 0) {
@@ -452,30 +441,60 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     if (tid == 0 && abort_s) atomicExch(a.status, 4);  // LUMEN_MOE_TIMEOUT
 }
 
-// activations -> 16-bit, permuted within each 32-block
+// activations -> f16, gathered into compact-column order (row c = token
+// col_src_tok[c]) and permuted within each 32-block: the grouped GEMM then reads
+// plain 2-D boxes of it with TMA
 template <typename XT>
 __global__ void __launch_bounds__(256)
-permute_x16_kernel(const XT* __restrict__ x, size_t n, bool bf16_mode, uint16_t* __restrict__ out) {
-    const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
-    if (i >= n) return;
-    float v;
-    if (sizeof(XT) == 4) v = reinterpret_cast<const float*>(x)[i];
-    else v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]);
-    const size_t o = (i & ~(size_t)31) + perm_pos((int)(i & 31));
-    out[o] = bf16_mode ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ col_src_tok, int H,
+                          uint16_t* __restrict__ out) {
+    const int c = blockIdx.x;
+    const int tok = col_src_tok[c];
+    const XT* src = x + (size_t)tok * H;
+    uint16_t* dst = out + (size_t)c * H;
+    for (int i = threadIdx.x; i < H; i += 256) {
+        float v;
+        if (sizeof(XT) == 4) v = reinterpret_cast<const float*>(src)[i];
+        else v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[i]);
+        dst[(i & ~31) + perm_pos(i & 31)] = __half_as_ushort(__float2half_rn(v));
+    }
 }
 
 }  // namespace tc
 
-cudaError_t launch_permute_x16(const void* x, int act_dtype, size_t n, bool bf16_mode, void* out, cudaStream_t st) {
+cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_t* col_src_tok, int C, int H, void* out,
+                                      cudaStream_t st) {
     count_launch();
     if (act_dtype == 0)
-        tc::permute_x16_kernel<float><<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const float*)x, n, bf16_mode,
-                                                                                   (uint16_t*)out);
+        tc::gather_permute_x16_kernel<float><<<C, 256, 0, st>>>((const float*)x, col_src_tok, H, (uint16_t*)out);
     else
-        tc::permute_x16_kernel<__nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
-            (const __nv_bfloat16*)x, n, bf16_mode, (uint16_t*)out);
+        tc::gather_permute_x16_kernel<__nv_bfloat16><<<C, 256, 0, st>>>((const __nv_bfloat16*)x, col_src_tok, H,
+                                                                        (uint16_t*)out);
     return cudaGetLastError();
+}
+
+// [rows, cols] f16 row-major -> tensor map with a 64 x 128 box and the 128-byte swizzle
+static cudaError_t make_tmap(const void* base, uint64_t rows, uint64_t cols, CUtensorMap* out) {
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return e;
+        if (qres != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+        encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
 template <int Q, int MODE>
@@ -501,6 +520,8 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     const int max_ct = C / 256 + p.L.E;
     const int mt_gu = p.L.I / 128;
     tc::Args gu{};
+    cudaError_t te = make_tmap(x16, (uint64_t)C, (uint64_t)p.L.H, &gu.tmap);
+    if (te != cudaSuccess) return te;
     gu.L = p.L;
     gu.col_src_tok = p.R.col_src_tok;
     gu.tiles = p.tiles;
@@ -510,7 +531,13 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     gu.status = p.status;
     gu.kdim = p.L.H;
     gu.out_ld = p.L.I;
+    {
+        const char* d = std::getenv("LUMEN_TC_DBG");
+        gu.dbg = d ? std::atoi(d) : 0;
+    }
     tc::Args dn = gu;
+    te = make_tmap(p.s16, (uint64_t)C, (uint64_t)p.L.I, &dn.tmap);
+    if (te != cudaSuccess) return te;
     dn.col_src_tok = nullptr;
     dn.tiles = p.tiles + (size_t)max_ct * mt_gu;
     dn.b_src = p.s16;

@@ -77,6 +77,15 @@ lumen_moe_status_t lumen_moe_layer_prepare(lumen_moe_ctx* ctx, const void* d_lay
     if (!ctx || !d_layer_blob || !out_layer) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
     const lumen::CudaMoeScratch& sc = ctx->scratch;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    {
+        int cur = -1;
+        if (cudaGetDevice(&cur) != cudaSuccess || cur != sc.device)
+            return fail(LUMEN_MOE_INVALID_ARG, "the context belongs to another CUDA device than the current one");
+        cudaPointerAttributes pa;
+        if (cudaPointerGetAttributes(&pa, d_layer_blob) != cudaSuccess || pa.type != cudaMemoryTypeDevice ||
+            pa.device != sc.device)
+            return fail(LUMEN_MOE_INVALID_ARG, "the layer blob is not device memory of the context's GPU");
+    }
     if (!gate_offs && !up_offs && !down_offs) {
         // router-only layer: nothing is repacked; usable with lumen_moe_route_only
         if (router_off % 4 != 0 || router_off + (uint64_t)sc.E * sc.H * 4 > blob_bytes ||

@@ -237,7 +237,17 @@ void free_moe_layer(MoeLayer* l) {
     if (l->repacked.s) cudaFree(l->repacked.s);
 }
 
+static Status check_device(const CudaMoeScratch* s) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != s->device)
+        return Status::Err(1, "the context belongs to CUDA device " + std::to_string(s->device) +
+                                  " but the calling thread's current device is " + std::to_string(cur));
+    return Status::Ok();
+}
+
 static Status check_layer(const CudaMoeScratch* s, const MoeLayer& layer) {
+    Status d = check_device(s);
+    if (!d.ok()) return d;
     if (layer.dev.H != s->H || layer.dev.I != s->I || layer.dev.E != s->E)
         return Status::Err(1, "layer shape does not match the context");
     if (layer.dev.quant < 0) return Status::Err(1, "router-only layer: expert weights were not prepared");
@@ -299,6 +309,8 @@ Status encode_route_only(CudaMoeScratch* s, const MoeLayer* layer, const float* 
                          int tokens, uint32_t* d_ids, float* d_weights, float* d_logits_out, cudaStream_t st) {
     if (tokens < 1) return Status::Err(1, "tokens must be positive");
     if (!logits_in && (!layer || !normed)) return Status::Err(1, "route_only needs a layer and activations");
+    Status dv = check_device(s);
+    if (!dv.ok()) return dv;
     Status g = ensure_prefill_grouped(s, tokens);
     if (!g.ok()) return g;
     const size_t C = (size_t)tokens * s->K;

@@ -112,11 +112,12 @@ def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.
     context (K = 1, E/G experts); a second, router-only context routes."""
     from . import moe, synth
     epr = E // world
+    dev = full_blob.device.index
     lay = synth.LayerLayout(H, I, E, quant)
     meta = lay.meta()
-    route_sc = moe.allocate_moe_scratch(H, I, E, K, max_tokens, gating_mode)
+    route_sc = moe.allocate_moe_scratch(H, I, E, K, max_tokens, gating_mode, dev)
     route_layer = route_sc.prepare_router_only(full_blob, meta.router_weight_off)
-    exp_sc = moe.allocate_moe_scratch(H, I, epr, 1, max_tokens * K, gating_mode)
+    exp_sc = moe.allocate_moe_scratch(H, I, epr, 1, max_tokens * K, gating_mode, dev)
     sl = slice(rank * epr, (rank + 1) * epr)
     local_meta = moe.MoeMeta(0, meta.expert_gate_offs[sl].copy(), meta.expert_up_offs[sl].copy(),
                              meta.expert_down_offs[sl].copy(), quant, quant)

@@ -31,7 +31,7 @@ def _worker(rank, world, port, q):
         route_fn, expert_fn, keep = ep.cuda_layer_fns(H, I, E, K, 1, blob, rank, world, Tl)
         layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn)
         out = layer.forward(x_all[sl].contiguous(), res_all[sl].contiguous())
-        sc = moe.allocate_moe_scratch(H, I, E, K, T, device=rank)
+        sc = moe.allocate_moe_scratch(H, I, E, K, T, device=rank)  # contexts are per device
         full = sc.prepare_layer(blob, lay.meta())
         ref = sc.prefill(full, x_all, res_all)[sl]
         rel = float(((out - ref) - 0).norm() / (ref - res_all[sl]).norm())

@@ -270,8 +270,8 @@ __global__ void __launch_bounds__(256)
 scatter_accum_kernel(const __half* __restrict__ d16, const float* __restrict__ residual,
                      const float* __restrict__ weights, const int32_t* __restrict__ dst_to_col,
                      float* __restrict__ out, int T, int H, int K) {
-    const int t = blockIdx.y;
-    const int h2 = blockIdx.x * 256 + threadIdx.x;  // pair index
+    const int t = blockIdx.x;  // tokens on grid.x: the y dimension is limited to 65535
+    const int h2 = blockIdx.y * 256 + threadIdx.x;  // pair index
     if (h2 * 2 >= H) return;
     const size_t o = (size_t)t * H + h2 * 2;
     float2 acc = *reinterpret_cast<const float2*>(residual + o);
@@ -288,7 +288,7 @@ scatter_accum_kernel(const __half* __restrict__ d16, const float* __restrict__ r
 cudaError_t launch_scatter_accum(const __half* d16, const float* residual, const RouteDev& R, float* out,
                                  int T, int H, int K, cudaStream_t st) {
     count_launch();
-    scatter_accum_kernel<<<dim3((H / 2 + 255) / 256, T), 256, 0, st>>>(d16, residual, R.weights, R.dst_to_col,
+    scatter_accum_kernel<<<dim3(T, (H / 2 + 255) / 256), 256, 0, st>>>(d16, residual, R.weights, R.dst_to_col,
                                                                        out, T, H, K);
     return cudaGetLastError();
 }

@@ -376,7 +376,7 @@ def run_ep_prefill(args):
         fwd = lambda: sc.prefill(layer, x, res)
     else:
         route_fn, expert_fn, keep = ep.cuda_layer_fns(H, I, E, K, quant, blob, rank, world, Tl)
-        epl = ep.ExpertParallelMoe(E, K, route_fn, expert_fn)
+        epl = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, combine_fn=keep["combine_fn"])
         fwd = lambda: epl.forward(x, res)
     for _ in range(max(3, args.warmup)):
         out = fwd()

@@ -126,6 +126,22 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_prefill_routed(lumen_moe_ctx* ctx, co
                                                           float* d_out, int32_t tokens, int32_t act_dtype,
                                                           void* stream);
 
+/* Expert-parallel building blocks (no counterpart in the reference).
+ * lumen_moe_experts_routed_f16: on a context with top_k = 1, the expert FFN
+ * Down_e(silu(Gate_e x) * Up_e x) of every row with its caller-supplied local expert id
+ * d_ids[r]; output f16 [rows, H] in the caller's row order, unweighted.
+ * lumen_moe_combine_f16: out[t] = residual[t] + sum_slot w[t,slot] * D[dst_to_col[t*K+slot]]
+ * in slot order (moe_grouped_scatter_accum_q8_0, cuda/shaders/moe_grouped.cu:493-517) on
+ * f16 rows D, e.g. those returned by the combine all-to-all. Needs no context. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_experts_routed_f16(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                              const void* d_rows, const uint32_t* d_ids,
+                                                              void* d_out16, int32_t rows, int32_t act_dtype,
+                                                              void* stream);
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_combine_f16(const void* d_d16, const float* d_residual,
+                                                       const float* d_weights, const int32_t* d_dst_to_col,
+                                                       float* d_out, int32_t tokens, int32_t hidden_dim,
+                                                       int32_t top_k, void* stream);
+
 /* Router only (moe_router_logits_v2 + finalize, cuda/shaders/moe_batched.cu:708,755;
  * batched: cuda/shaders/moe_grouped.cu:79 + topk_moe_fused.cu:172-296).
  * d_ids u32 [T,K] in selection (descending weight) order, row stride K;

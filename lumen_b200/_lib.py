@@ -42,6 +42,8 @@ SIGNATURES = {
     "lumen_moe_decode_fused_norm": [vp, vp, vp, vp, vp, vp, f32, i32, vp],
     "lumen_moe_prefill": [vp, vp, vp, vp, vp, i32, i32, vp],
     "lumen_moe_prefill_routed": [vp, vp, vp, vp, vp, vp, vp, i32, i32, vp],
+    "lumen_moe_experts_routed_f16": [vp, vp, vp, vp, vp, i32, i32, vp],
+    "lumen_moe_combine_f16": [vp, vp, vp, vp, vp, i32, i32, i32, vp],
     "lumen_moe_route_only": [vp, vp, vp, i32, vp, vp, vp, vp],
     "lumen_moe_topk_from_logits": [vp, vp, i32, vp, vp, vp],
     "lumen_moe_route_small_static": [vp, i32, i32, i32, i32, vp, vp, vp, vp, vp],

@@ -6,6 +6,8 @@
 
 namespace lumen {
 long long read_launch_count(bool reset);
+cudaError_t launch_scatter_accum(const __half* d16, const float* residual, const RouteDev& R, float* out, int T, int H,
+                                 int K, cudaStream_t st);
 }
 
 struct lumen_moe_ctx {
@@ -180,6 +182,30 @@ lumen_moe_status_t lumen_moe_prefill_routed(lumen_moe_ctx* ctx, const lumen_moe_
     return done(lumen::encode_moe_ffn_prefill_grouped(&ctx->scratch, layer->layer, d_normed, act_dtype, d_residual,
                                                       d_out, tokens, static_cast<cudaStream_t>(stream), d_ids,
                                                       d_weights));
+}
+
+lumen_moe_status_t lumen_moe_experts_routed_f16(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const void* d_rows,
+                                                const uint32_t* d_ids, void* d_out16, int32_t rows, int32_t act_dtype,
+                                                void* stream) {
+    if (!ctx || !layer || !d_ids || !d_out16) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    return done(lumen::encode_moe_ffn_prefill_grouped(&ctx->scratch, layer->layer, d_rows, act_dtype, nullptr, nullptr,
+                                                      rows, static_cast<cudaStream_t>(stream), d_ids, nullptr,
+                                                      static_cast<__half*>(d_out16)));
+}
+
+lumen_moe_status_t lumen_moe_combine_f16(const void* d_d16, const float* d_residual, const float* d_weights,
+                                         const int32_t* d_dst_to_col, float* d_out, int32_t tokens, int32_t hidden_dim,
+                                         int32_t top_k, void* stream) {
+    if (!d_d16 || !d_residual || !d_weights || !d_dst_to_col || !d_out || tokens < 1 || hidden_dim < 2 || hidden_dim % 2 ||
+        top_k < 1)
+        return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    lumen::RouteDev R{};
+    R.weights = const_cast<float*>(d_weights);
+    R.dst_to_col = const_cast<int32_t*>(d_dst_to_col);
+    cudaError_t e = lumen::launch_scatter_accum(static_cast<const __half*>(d_d16), d_residual, R, d_out, tokens,
+                                                hidden_dim, top_k, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
 }
 
 lumen_moe_status_t lumen_moe_route_only(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const float* d_normed,

@@ -16,7 +16,8 @@ cudaError_t launch_build_xf(const void* x, int act_dtype, int T, int H, int nblk
                             uint4* xf, cudaStream_t st);
 cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_t* col_src_tok, int C, int H, void* out,
                                       cudaStream_t st);
-cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st);
+cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st, __half* out16_rows);
+cudaError_t launch_rows_from_cols(const __half* d16, const int32_t* dst_to_col, __half* out16, int T, int H, cudaStream_t st);
 
 static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches += n; }
@@ -355,9 +356,14 @@ Status encode_route_only(CudaMoeScratch* s, const MoeLayer* layer, const float* 
 // cuda/moe.rs:1900-2760
 Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, const void* normed, int act_dtype,
                                       const float* residual, float* output, int batch, cudaStream_t st,
-                                      const uint32_t* ids_in, const float* weights_in) {
+                                      const uint32_t* ids_in, const float* weights_in, __half* out16_rows) {
     if (batch < 1) return Status::Err(1, "batch must be positive");
-    if (!normed || !residual || !output) return Status::Err(1, "null activation pointer");
+    if (out16_rows) {
+        if (s->K != 1 || !ids_in) return Status::Err(1, "f16 row output needs top_k = 1 and caller-supplied ids");
+        if (!normed) return Status::Err(1, "null activation pointer");
+    } else if (!normed || !residual || !output) {
+        return Status::Err(1, "null activation pointer");
+    }
     if (act_dtype != 0 && act_dtype != 1) return Status::Err(2, "activation dtype must be f32 or bf16");
     Status c = check_layer(s, layer);
     if (!c.ok()) return c;
@@ -391,11 +397,15 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        CUDA_TRY(launch_grouped_tc(p, s->x16, sms, st));
+        CUDA_TRY(launch_grouped_tc(p, s->x16, sms, st, out16_rows));
     } else {
         CUDA_TRY(launch_build_xf(normed, act_dtype, batch, s->H, layer.dev.kg_h * 4, bf16_mode, s->xf, st));
         DecodeArgs a = make_decode_args(s, layer, batch);
         CUDA_TRY(launch_grouped_mma(a, s->d16, st));
+    }
+    if (out16_rows) {
+        if (p.impl != 0) CUDA_TRY(launch_rows_from_cols(s->d16, s->R.dst_to_col, out16_rows, batch, s->H, st));
+        return Status::Ok();
     }
     CUDA_TRY(launch_scatter_accum(s->d16, residual, s->R, output, batch, s->H, s->K, st));
     return Status::Ok();

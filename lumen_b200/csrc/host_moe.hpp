@@ -132,7 +132,7 @@ Status encode_moe_ffn_decode_fused_norm(CudaMoeScratch* scratch, const MoeLayer&
 Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* scratch, const MoeLayer& layer, const void* normed,
                                       int act_dtype, const float* residual, float* output, int batch,
                                       cudaStream_t st, const uint32_t* ids_in = nullptr,
-                                      const float* weights_in = nullptr);
+                                      const float* weights_in = nullptr, __half* out16_rows = nullptr);
 Status encode_route_only(CudaMoeScratch* scratch, const MoeLayer* layer, const float* normed,
                          const float* logits_in, int tokens, uint32_t* d_ids, float* d_weights,
                          float* d_logits_out, cudaStream_t st);

@@ -141,6 +141,7 @@ struct Args {
     int32_t* status;
     int kdim;               // H (gate/up) or I (down)
     int out_ld;             // I or H
+    const int32_t* out_row_map;  // down mode: output row of compact column c (null = c itself)
     int dbg;                // timing experiments only (LUMEN_TC_DBG): 1 skip dequant, 2 skip activation copies, 4 skip stores
 };
 
@@ -287,7 +288,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     if (n0 + j < ncols && !(a.dbg & 4)) {
-                        __half* dst = a.out16 + (size_t)(tile.y + n0 + j) * a.out_ld;
+                        int orow_idx = tile.y + n0 + j;
+                        if (MODE == 1 && a.out_row_map != nullptr) orow_idx = a.out_row_map[orow_idx];
+                        __half* dst = a.out16 + (size_t)orow_idx * a.out_ld;
                         if (MODE == 0) {
                             const float gt = __uint_as_float(v0[j]);
                             dst[off0] = __float2half_rn((gt / (1.0f + __expf(-gt))) * __uint_as_float(v1[j]));
@@ -515,7 +518,7 @@ static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
 }
 
 // gate/up + SwiGLU then down, both on tcgen05. x16: permuted 16-bit activations [T,H].
-cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st) {
+cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st, __half* out16_rows) {
     const int C = p.T * p.K;
     const int max_ct = C / 256 + p.L.E;
     const int mt_gu = p.L.I / 128;
@@ -541,7 +544,9 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     dn.col_src_tok = nullptr;
     dn.tiles = p.tiles + (size_t)max_ct * mt_gu;
     dn.b_src = p.s16;
-    dn.out16 = p.d16;
+    // out16_rows: write the down product straight into caller rows (row = col_src_tok[column])
+    dn.out16 = out16_rows ? out16_rows : p.d16;
+    dn.out_row_map = out16_rows ? p.R.col_src_tok : nullptr;
     dn.kdim = p.L.I;
     dn.out_ld = p.L.H;
     cudaError_t e;

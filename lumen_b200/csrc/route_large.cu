@@ -115,7 +115,8 @@ sort_hist_kernel(const uint32_t* __restrict__ ids, int T, int K, int E, int32_t*
     const int n = min(SORT_TOK, T - t0) * K;
     for (int p = tid; p < n; p += 256) atomicAdd(&h[ids[(size_t)t0 * K + p]], 1);
     __syncthreads();
-    for (int e = tid; e < E; e += 256) blk_hist[(size_t)blockIdx.x * E + e] = h[e];
+    // layout [expert][chunk]: a warp of sort_scan then scans one expert's row with coalesced loads
+    for (int e = tid; e < E; e += 256) blk_hist[(size_t)e * gridDim.x + blockIdx.x] = h[e];
 }
 
 // One CTA of 256 threads (E <= 256). tile entry: {expert, col_start, ncols, m_tile}.
@@ -128,14 +129,23 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
     __shared__ int tile_off_s[MAX_EXPERTS + 1];
     __shared__ int tile_off_dn_s[MAX_EXPERTS + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid < E) {
+    // exclusive scan over the chunks of every expert row, one warp per row, 32 chunks per step
+    for (int e = warp; e < E; e += 8) {
+        int32_t* rowp = blk_hist + (size_t)e * nchunks;
         int run = 0;
-        for (int b = 0; b < nchunks; ++b) {
-            const int v = blk_hist[(size_t)b * E + tid];
-            blk_hist[(size_t)b * E + tid] = run;
-            run += v;
+        for (int c0 = 0; c0 < nchunks; c0 += 32) {
+            const int c = c0 + lane;
+            const int v = (c < nchunks) ? rowp[c] : 0;
+            int inc = v;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += u;
+            }
+            if (c < nchunks) rowp[c] = run + inc - v;
+            run += __shfl_sync(0xffffffffu, inc, 31);
         }
-        cnt_s[tid] = run;
+        if (lane == 0) cnt_s[e] = run;
     }
     __syncthreads();
     if (warp == 0) {
@@ -215,25 +225,36 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
     }
 }
 
+// One warp per chunk of SORT_TOK tokens: the chunk's (token, slot) pairs are taken 32 at
+// a time in order; lanes holding the same expert find each other with match.any, the
+// position inside the expert's segment is the expert's running cursor plus the number
+// of lower lanes with the same expert, so the placement is stable.
 __global__ void __launch_bounds__(256)
 sort_place_kernel(const uint32_t* __restrict__ ids, int T, int K, int E, const int32_t* __restrict__ blk_hist,
-                  RouteDev R) {
-    __shared__ int ids_s[SORT_TOK * MAX_TOP_K];
-    const int tid = threadIdx.x;
-    const int t0 = blockIdx.x * SORT_TOK;
+                  int nchunks, RouteDev R) {
+    __shared__ int cursor[8][MAX_EXPERTS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int chunk = blockIdx.x * 8 + warp;
+    if (chunk >= nchunks) return;
+    for (int e = lane; e < E; e += 32) cursor[warp][e] = R.expert_bounds[e] + blk_hist[(size_t)e * nchunks + chunk];
+    __syncwarp();
+    const int t0 = chunk * SORT_TOK;
     const int n = min(SORT_TOK, T - t0) * K;
-    for (int p = tid; p < n; p += 256) ids_s[p] = (int)ids[(size_t)t0 * K + p];
-    __syncthreads();
-    if (tid < E) {
-        int cur = R.expert_bounds[tid] + blk_hist[(size_t)blockIdx.x * E + tid];
-        for (int p = 0; p < n; ++p) {
-            if (ids_s[p] == tid) {
-                R.col_expert[cur] = tid;
-                R.col_src_tok[cur] = t0 + p / K;
-                R.dst_to_col[(size_t)t0 * K + p] = cur;
-                ++cur;
-            }
+    for (int p0 = 0; p0 < n; p0 += 32) {
+        const int p = p0 + lane;
+        const bool valid = p < n;
+        const int e = valid ? (int)ids[(size_t)t0 * K + p] : -1 - lane;  // invalid lanes match nobody
+        const unsigned int same = __match_any_sync(0xffffffffu, e);
+        if (valid) {
+            const int rank = __popc(same & ((1u << lane) - 1u));
+            const int col = cursor[warp][e] + rank;
+            R.col_expert[col] = e;
+            R.col_src_tok[col] = t0 + p / K;
+            R.dst_to_col[(size_t)t0 * K + p] = col;
         }
+        __syncwarp();
+        if (valid && (same & ((1u << lane) - 1u)) == 0u) cursor[warp][e] += __popc(same);  // one leader per expert
+        __syncwarp();
     }
 }
 
@@ -293,6 +314,22 @@ cudaError_t launch_scatter_accum(const __half* d16, const float* residual, const
     return cudaGetLastError();
 }
 
+__global__ void __launch_bounds__(256)
+rows_from_cols_kernel(const __half* __restrict__ d16, const int32_t* __restrict__ dst_to_col, __half* __restrict__ out16,
+                      int H) {
+    const int t = blockIdx.x;
+    const uint4* src = reinterpret_cast<const uint4*>(d16 + (size_t)dst_to_col[t] * H);
+    uint4* dst = reinterpret_cast<uint4*>(out16 + (size_t)t * H);
+    for (int i = threadIdx.x; i < H / 8; i += 256) dst[i] = src[i];
+}
+
+cudaError_t launch_rows_from_cols(const __half* d16, const int32_t* dst_to_col, __half* out16, int T, int H,
+                                  cudaStream_t st) {
+    count_launch();
+    rows_from_cols_kernel<<<T, 256, 0, st>>>(d16, dst_to_col, out16, H);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_build_xf(const void* x, int act_dtype, int T, int H, int nblk_pad, bool bf16_mode,
                             uint4* xf, cudaStream_t st) {
     const size_t total = (size_t)T * (H / 32) * 8;
@@ -348,7 +385,7 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     int4* tiles_dn = a.tiles ? a.tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1) : nullptr;
     sort_scan_kernel<<<1, 256, 0, st>>>(a.blk_hist, nchunks, E, a.R, tile_cols, mt_gu, mt_dn, tiles_gu, tiles_dn,
                                         a.n_tiles, max_ct * mt_gu, max_ct * mt_dn);
-    sort_place_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist, a.R);
+    sort_place_kernel<<<(nchunks + 7) / 8, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist, nchunks, a.R);
     return cudaGetLastError();
 }
 

@@ -61,6 +61,7 @@ class ExpertParallelMoe:
     """
 
     def __init__(self, num_experts: int, top_k: int, route_fn: Callable, expert_fn: Callable, group=None,
+                 combine_fn: Optional[Callable] = None,
                  wire_dtype: torch.dtype = torch.bfloat16, combine_dtype: torch.dtype = torch.float16):
         self.E, self.K = num_experts, top_k
         self.group = group
@@ -70,6 +71,7 @@ class ExpertParallelMoe:
             raise ValueError("num_experts must be divisible by the number of ranks")
         self.epr = num_experts // self.world
         self.route_fn, self.expert_fn = route_fn, expert_fn
+        self.combine_fn = combine_fn  # (back [T*K,H] in send order, residual, w, inv_order) -> out; None = torch ops
         self.wire_dtype = wire_dtype        # activation rows on the wire (bf16 inputs travel exactly)
         self.combine_dtype = combine_dtype  # expert outputs on the wire (f16, as the single-GPU path stores them)
         self.last = {}
@@ -93,6 +95,11 @@ class ExpertParallelMoe:
         # (5) combine
         back = all_to_all_v(d.to(self.combine_dtype), recv_l, send_l, self.group)
         # (6) weighted sum in slot order
+        self.last = {"ids": ids, "weights": w, "send_counts": send_l, "recv_counts": recv_l}
+        if self.combine_fn is not None:
+            inv = torch.empty(T * self.K, dtype=torch.int32, device=normed.device)
+            inv[order] = torch.arange(T * self.K, dtype=torch.int32, device=normed.device)
+            return self.combine_fn(back, residual, w, inv)
         dpair = torch.empty((T * self.K, H), dtype=torch.float32, device=normed.device)
         dpair[order] = back.to(torch.float32)
         dpair = dpair.view(T, self.K, H)
@@ -128,10 +135,11 @@ def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.
         return ids, w
 
     def expert_fn(rows, local_ids):
-        R = rows.shape[0]
-        if R == 0:
-            return torch.zeros((0, H), dtype=torch.float32, device=rows.device)
-        zero = torch.zeros((R, H), dtype=torch.float32, device=rows.device)
-        return exp_sc.prefill_routed(exp_layer, rows.contiguous(), local_ids.contiguous(), None, zero)
+        if rows.shape[0] == 0:
+            return torch.zeros((0, H), dtype=torch.float16, device=rows.device)
+        return exp_sc.experts_routed_f16(exp_layer, rows.contiguous(), local_ids.contiguous())
 
-    return route_fn, expert_fn, {"route": route_sc, "experts": exp_sc, "layers": (route_layer, exp_layer)}
+    def combine_fn(back, residual, w, inv):
+        return moe.combine_f16(back.contiguous(), residual, w.contiguous(), inv)
+
+    return route_fn, expert_fn, {"combine_fn": combine_fn, "route": route_sc, "experts": exp_sc, "layers": (route_layer, exp_layer)}

@@ -202,6 +202,17 @@ class MoeScratch:
                                                   residual.data_ptr(), output.data_ptr(), T, act, _stream()))
         return output
 
+    def experts_routed_f16(self, layer: MoeLayer, rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+        """lumen_moe_experts_routed_f16 (context with top_k = 1): f16 [R,H] expert outputs in row order."""
+        act = ACT_F32 if rows.dtype == torch.float32 else ACT_BF16
+        _need(rows, rows.dtype, "rows")
+        _need(ids, torch.int32, "ids")
+        R = rows.numel() // self.H
+        out = torch.empty((R, self.H), dtype=torch.float16, device=rows.device)
+        check(_lib.lib().lumen_moe_experts_routed_f16(self._h, layer._h, rows.data_ptr(), ids.data_ptr(),
+                                                      out.data_ptr(), R, act, _stream()))
+        return out
+
     def route_only(self, layer: MoeLayer, normed_x: torch.Tensor, want_logits: bool = False):
         _need(normed_x, torch.float32, "normed_x")
         T = normed_x.numel() // self.H
@@ -317,3 +328,19 @@ def route_small_static(logits: torch.Tensor, top_k: int, gating_mode: int = SOFT
     check(_lib.lib().lumen_moe_route_small_static(logits.data_ptr(), T, E, top_k, gating_mode, ids.data_ptr(),
                                                   w.data_ptr(), _ptr(d2c), _ptr(bounds), _stream()))
     return (ids, w, d2c, bounds) if want_tables else (ids, w)
+
+
+def combine_f16(d16: torch.Tensor, residual: torch.Tensor, weights: torch.Tensor, dst_to_col: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """lumen_moe_combine_f16: out[t] = residual[t] + sum_slot w[t,slot] * d16[dst_to_col[t*K+slot]]."""
+    _need(d16, torch.float16, "d16")
+    _need(residual, torch.float32, "residual")
+    _need(weights, torch.float32, "weights")
+    _need(dst_to_col, torch.int32, "dst_to_col")
+    T, H = residual.shape
+    K = weights.numel() // T
+    if out is None:
+        out = torch.empty_like(residual)
+    check(_lib.lib().lumen_moe_combine_f16(d16.data_ptr(), residual.data_ptr(), weights.data_ptr(),
+                                           dst_to_col.data_ptr(), out.data_ptr(), T, H, K, _stream()))
+    return out

@@ -29,7 +29,7 @@ def _worker(rank, world, port, q):
         Tl = T // world
         sl = slice(rank * Tl, (rank + 1) * Tl)
         route_fn, expert_fn, keep = ep.cuda_layer_fns(H, I, E, K, 1, blob, rank, world, Tl)
-        layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn)
+        layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, combine_fn=keep["combine_fn"])
         out = layer.forward(x_all[sl].contiguous(), res_all[sl].contiguous())
         sc = moe.allocate_moe_scratch(H, I, E, K, T, device=rank)  # contexts are per device
         full = sc.prepare_layer(blob, lay.meta())

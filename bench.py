@@ -390,6 +390,12 @@ def run_ep_prefill(args):
     ev1.record()
     torch.cuda.synchronize()
     ms = ev0.elapsed_time(ev1) / args.steps
+    phases = None
+    if world > 1:
+        epl.profile = True
+        fwd()
+        phases = {k: round(v, 3) for k, v in epl.phase_times_ms()}
+        epl.profile = False
     checksum = float(out.float().abs().sum())
     if world > 1:
         t = torch.tensor([ms, checksum], device=dev, dtype=torch.float64)
@@ -402,7 +408,7 @@ def run_ep_prefill(args):
                           "n_gpus": world, "steps": args.steps, "ms_per_call": ms, "scaling": "strong",
                           "config": {"workload": f"moe_ffn_ep_prefill_{args.quant}_T{T}", "experts_per_gpu": E // world,
                                      "tokens_per_gpu": Tl, "wire_dtype": "bf16", "collective": "nccl all_to_all_single"},
-                          "abs_sum_of_output": checksum}), flush=True)
+                          "phase_ms_rank0": phases, "abs_sum_of_output": checksum}), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

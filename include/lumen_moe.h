@@ -192,6 +192,15 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_get_routing(lumen_moe_ctx* ctx, int32
                                          float* weights, int32_t* dst_to_col, int32_t* col_src_tok,
                                          int32_t* expert_bounds, void* stream);
 
+/* Device-to-device copy of the sort tables of the most recent routing call (no
+ * synchronisation): dst_to_col [T*K], col_src_tok [T*K], col_expert [T*K],
+ * expert_bounds [E+1] (cuda/moe.rs:2115-2147); any pointer may be NULL. The
+ * expert-parallel dispatch uses them as its send plan. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_get_routing_device(lumen_moe_ctx* ctx, int32_t tokens,
+                                                              int32_t* d_dst_to_col, int32_t* d_col_src_tok,
+                                                              int32_t* d_col_expert, int32_t* d_expert_bounds,
+                                                              void* stream);
+
 /* Device restatement of quantize_f32_to_q4_0 / _q8_0
  * (crates/lumen-convert/src/dequant.rs:791-906) and of round-to-nearest-even BF16,
  * used to synthesise weights in HBM. n_elements multiple of 32. */

@@ -254,6 +254,24 @@ lumen_moe_status_t lumen_moe_get_routing(lumen_moe_ctx* ctx, int32_t tokens, uin
     return LUMEN_MOE_OK;
 }
 
+lumen_moe_status_t lumen_moe_get_routing_device(lumen_moe_ctx* ctx, int32_t tokens, int32_t* d_dst_to_col,
+                                                int32_t* d_col_src_tok, int32_t* d_col_expert,
+                                                int32_t* d_expert_bounds, void* stream) {
+    if (!ctx) return fail(LUMEN_MOE_INVALID_ARG, "null context");
+    const lumen::CudaMoeScratch& s = ctx->scratch;
+    if (tokens < 1 || tokens > s.cap_tokens) return fail(LUMEN_MOE_INVALID_ARG, "tokens exceeds the last call's capacity");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t C = (size_t)tokens * s.K;
+    cudaError_t e = cudaSuccess;
+    if (d_dst_to_col) e = cudaMemcpyAsync(d_dst_to_col, s.R.dst_to_col, C * 4, cudaMemcpyDeviceToDevice, st);
+    if (e == cudaSuccess && d_col_src_tok) e = cudaMemcpyAsync(d_col_src_tok, s.R.col_src_tok, C * 4, cudaMemcpyDeviceToDevice, st);
+    if (e == cudaSuccess && d_col_expert) e = cudaMemcpyAsync(d_col_expert, s.R.col_expert, C * 4, cudaMemcpyDeviceToDevice, st);
+    if (e == cudaSuccess && d_expert_bounds)
+        e = cudaMemcpyAsync(d_expert_bounds, s.R.expert_bounds, (size_t)(s.E + 1) * 4, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
+}
+
 lumen_moe_status_t lumen_moe_quantize(const float* d_src, int64_t n_elements, int32_t quant, void* d_dst,
                                       void* stream) {
     if (!d_src || !d_dst) return fail(LUMEN_MOE_INVALID_ARG, "null argument");

@@ -132,19 +132,20 @@ Status build_repacked(const CudaMoeScratch& sc, const void* layer_buf, size_t bl
 }
 
 static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
-    // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf
+    // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf, w16
     const size_t C = (size_t)cap * s.K;
     const size_t nblk_h_pad = (size_t)((s.H / 32 + 3) / 4) * 4, nblk_i_pad = (size_t)((s.I / 32 + 3) / 4) * 4;
     const size_t max_ct = C / 256 + s.E;
     const size_t mt = (size_t)s.I / 128 + (size_t)s.H / 256 + 1;
-    size_t sizes[13] = {
+    size_t sizes[14] = {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,
         (size_t)((cap + 31) / 32) * s.E * 4,
         max_ct * (mt ? mt : 1) * sizeof(int4),
         C * s.I * 2, C * s.H * 2, C * s.H * 2,
-        (size_t)cap * 2 * nblk_h_pad * 64, C * 2 * nblk_i_pad * 64};
+        (size_t)cap * 2 * nblk_h_pad * 64, C * 2 * nblk_i_pad * 64,
+        (size_t)s.E * s.H * 4};
     size_t off = 0;
-    for (int i = 0; i < 13; ++i) {
+    for (int i = 0; i < 14; ++i) {
         offs[i] = off;
         off += align_up(sizes[i], 256);
     }
@@ -152,7 +153,7 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
 }
 
 static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
-    size_t offs[13];
+    size_t offs[14];
     const size_t bytes = tok_arena_bytes(*s, cap, offs);
     void* p = nullptr;
     CUDA_TRY(cudaMalloc(&p, bytes));
@@ -175,6 +176,7 @@ static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
     s->x16 = reinterpret_cast<__half*>(b + offs[10]);
     s->xf = reinterpret_cast<uint4*>(b + offs[11]);
     s->sf = reinterpret_cast<uint4*>(b + offs[12]);
+    s->w16 = reinterpret_cast<__half*>(b + offs[13]);
     return Status::Ok();
 }
 
@@ -342,6 +344,7 @@ Status encode_route_only(CudaMoeScratch* s, const MoeLayer* layer, const float* 
         p.gating = s->gating;
         p.logits_override = logits_in;
         p.blk_hist = s->blk_hist;
+    p.w16 = s->w16;
         p.tiles = nullptr;
         p.n_tiles = s->n_tiles;
         CUDA_TRY(launch_route_large(p, st));
@@ -383,6 +386,7 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     p.K = s->K;
     p.gating = s->gating;
     p.blk_hist = s->blk_hist;
+    p.w16 = s->w16;
     p.s16 = s->s16;
     p.d16 = s->d16;
     p.tiles = s->tiles;

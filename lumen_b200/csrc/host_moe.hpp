@@ -89,6 +89,7 @@ struct CudaMoeScratch {
     float* s_f32 = nullptr; // optional debug copy
     // prefill (grow-only)
     int32_t* blk_hist = nullptr;
+    __half* w16 = nullptr;
     __half* s16 = nullptr;
     __half* d16 = nullptr;
     __half* x16 = nullptr;  // permuted 16-bit activations for the tcgen05 path

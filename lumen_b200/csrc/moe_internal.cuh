@@ -114,6 +114,7 @@ struct PrefillArgs {
     int T, K, gating;
     // scratch
     int32_t* blk_hist;      // [nchunks, E]
+    __half* w16;            // [2, E, H] router weight split into f16 high and low planes (per call)
     __half* s16;            // [C, I] f16 SwiGLU output, row-major by compact column
     __half* d16;            // [C, H] f16 down output by compact column
     int4* tiles;            // tile list for the grouped GEMMs

@@ -85,6 +85,167 @@ router_logits_large_kernel(const XT* __restrict__ x, const float* __restrict__ w
     }
 }
 
+// ---------------------------------------------------------------------------
+// logits on the tensor cores with f32-grade accuracy: X and W_r are each split into
+// a high and a low f16 part and up to three m16n8k16 products (hi*hi + hi*lo + lo*hi)
+// are accumulated in f32; the dropped lo*lo term is ~2^-22 relative. W_r is split
+// once per call into two [E,H] f16 planes; X is split in registers (the lo*hi
+// product is skipped for a fragment whose low parts are all zero, which is the
+// usual case for bf16 activations).
+// CTA = 64 tokens x (up to) 128 experts, 4 warps of 16 tokens. Per 32-input slab
+// lane (g,t) owns inputs 8t..8t+7 of token rows g and g+8 (one 16-byte load each
+// for bf16) and of expert row 8n+g (one 16-byte shared load per plane): the same
+// input -> k-slot assignment on both operands, so the contraction is unchanged.
+// ---------------------------------------------------------------------------
+__global__ void split_router_w_kernel(const float* __restrict__ w, __half* __restrict__ w16, size_t n) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = w[i];
+    const __half hi = __float2half_rn(v);
+    w16[i] = hi;
+    w16[n + i] = __float2half_rn(v - __half2float(hi));
+}
+
+__device__ __forceinline__ void cp_async16_rl(void* smem_dst, const void* gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+
+template <typename XT>
+struct XSlab;  // 8 consecutive inputs of one token row
+template <>
+struct XSlab<__nv_bfloat16> {
+    uint4 v;
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void get(float* f) const {
+        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(u[i] << 16);
+            f[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+        }
+    }
+};
+template <>
+struct XSlab<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = *reinterpret_cast<const float4*>(p);
+        b = *reinterpret_cast<const float4*>(p + 4);
+    }
+    __device__ __forceinline__ void get(float* f) const {
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+        f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    }
+};
+
+__device__ __forceinline__ void split_pair(float v0, float v1, uint32_t& hi, uint32_t& lo) {
+    const __half2 h = __floats2half2_rn(v0, v1);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(v0 - hf.x, v1 - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(128)
+router_logits_mma_kernel(const XT* __restrict__ x, const __half* __restrict__ w16, float* __restrict__ logits,
+                         int T, int H, int E) {
+    constexpr int BM = 64, BK = 32;
+    // [buffer][plane][expert row][32 inputs]: 64-byte rows, 16-byte fragment loads are conflict-free
+    __shared__ __align__(16) __half ws[2][2][128][BK];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int t0 = blockIdx.x * BM, e0 = blockIdx.y * 128;
+    const int ne = min(128, E - e0);
+    const int ntile = (ne + 7) >> 3;
+    const size_t plane = (size_t)E * H;
+    float acc[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
+    const int ra = t0 + warp * 16 + g, rb = ra + 8;
+    const XT* xa = x + (size_t)min(ra, T - 1) * H + 8 * t4;
+    const XT* xb = x + (size_t)min(rb, T - 1) * H + 8 * t4;
+    auto stage_w = [&](int buf, int k0) {
+        // 128 rows x 4 chunks x 2 planes = 1024 16-byte copies, 8 per thread
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = tid + i * 128;
+            const int pl = c >> 9, row = (c >> 2) & 127, ch = c & 3;
+            const __half* src = w16 + pl * plane + (size_t)min(e0 + row, E - 1) * H + k0 + ch * 8;
+            cp_async16_rl(&ws[buf][pl][row][ch * 8], src);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int nslab = H / BK;
+    XSlab<XT> na, nb;
+    stage_w(0, 0);
+    na.load(xa);
+    nb.load(xb);
+    for (int sidx = 0; sidx < nslab; ++sidx) {
+        const int buf = sidx & 1;
+        XSlab<XT> ca = na, cb = nb;
+        if (sidx + 1 < nslab) {
+            stage_w(buf ^ 1, (sidx + 1) * BK);
+            na.load(xa + (sidx + 1) * BK);
+            nb.load(xb + (sidx + 1) * BK);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        float fa[8], fb[8];
+        ca.get(fa);
+        cb.get(fb);
+        uint32_t ah[2][4], al[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            split_pair(fa[4 * j], fa[4 * j + 1], ah[j][0], al[j][0]);
+            split_pair(fb[4 * j], fb[4 * j + 1], ah[j][1], al[j][1]);
+            split_pair(fa[4 * j + 2], fa[4 * j + 3], ah[j][2], al[j][2]);
+            split_pair(fb[4 * j + 2], fb[4 * j + 3], ah[j][3], al[j][3]);
+        }
+        uint32_t lo_or = 0;
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) lo_or |= al[j][i];
+        const bool use_lo = __any_sync(0xffffffffu, (lo_or & 0x7fff7fffu) != 0);
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+            if (n < ntile) {
+                const uint4 bh = *reinterpret_cast<const uint4*>(&ws[buf][0][n * 8 + g][8 * t4]);
+                const uint4 bl = *reinterpret_cast<const uint4*>(&ws[buf][1][n * 8 + g][8 * t4]);
+                if (use_lo) {
+                    mma_f16(acc[n], al[0], bh.x, bh.y);
+                    mma_f16(acc[n], al[1], bh.z, bh.w);
+                }
+                mma_f16(acc[n], ah[0], bl.x, bl.y);
+                mma_f16(acc[n], ah[1], bl.z, bl.w);
+                mma_f16(acc[n], ah[0], bh.x, bh.y);
+                mma_f16(acc[n], ah[1], bh.z, bh.w);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+        if (n < ntile) {
+            const int ec = e0 + n * 8 + 2 * t4;
+            if (ra < T) {
+                if (ec < E) logits[(size_t)ra * E + ec] = acc[n][0];
+                if (ec + 1 < E) logits[(size_t)ra * E + ec + 1] = acc[n][1];
+            }
+            if (rb < T) {
+                if (ec < E) logits[(size_t)rb * E + ec] = acc[n][2];
+                if (ec + 1 < E) logits[(size_t)rb * E + ec + 1] = acc[n][3];
+            }
+        }
+    }
+}
+
 constexpr int TK_WARPS = 4;
 __global__ void __launch_bounds__(TK_WARPS * 32)
 topk_large_kernel(const float* __restrict__ logits, int T, int E, int K, int gating,
@@ -119,9 +280,40 @@ sort_hist_kernel(const uint32_t* __restrict__ ids, int T, int K, int E, int32_t*
     for (int e = tid; e < E; e += 256) blk_hist[(size_t)e * gridDim.x + blockIdx.x] = h[e];
 }
 
-// One CTA of 256 threads (E <= 256). tile entry: {expert, col_start, ncols, m_tile}.
+// One warp per expert: exclusive scan over the chunk counts of the expert's row (in place);
+// the row total goes to expert_bounds[e] for sort_scan_kernel.
+__global__ void __launch_bounds__(32)
+sort_rowscan_kernel(int32_t* __restrict__ blk_hist, int nchunks, RouteDev R) {
+    const int e = blockIdx.x, lane = threadIdx.x;
+    int32_t* rowp = blk_hist + (size_t)e * nchunks;
+    int run = 0;
+    for (int c0 = 0; c0 < nchunks; c0 += 128) {
+        int v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u * 32 + lane;
+            v[u] = (c < nchunks) ? rowp[c] : 0;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = c0 + u * 32 + lane;
+            int inc = v[u];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int w = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += w;
+            }
+            if (c < nchunks) rowp[c] = run + inc - v[u];
+            run += __shfl_sync(0xffffffffu, inc, 31);
+        }
+    }
+    if (lane == 0) R.expert_bounds[e] = run;
+}
+
+// One CTA of 256 threads (E <= 256): expert segment bounds from the row totals and the
+// tile lists. tile entry: {expert, col_start, ncols, m_tile}.
 __global__ void __launch_bounds__(256)
-sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R, int tile_cols,
+sort_scan_kernel(int nchunks, int E, RouteDev R, int tile_cols,
                  int mt_gu, int mt_dn, int4* __restrict__ tiles_gu, int4* __restrict__ tiles_dn,
                  int32_t* __restrict__ n_tiles, int max_tiles_gu, int max_tiles_dn) {
     __shared__ int cnt_s[MAX_EXPERTS];
@@ -129,24 +321,7 @@ sort_scan_kernel(int32_t* __restrict__ blk_hist, int nchunks, int E, RouteDev R,
     __shared__ int tile_off_s[MAX_EXPERTS + 1];
     __shared__ int tile_off_dn_s[MAX_EXPERTS + 1];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    // exclusive scan over the chunks of every expert row, one warp per row, 32 chunks per step
-    for (int e = warp; e < E; e += 8) {
-        int32_t* rowp = blk_hist + (size_t)e * nchunks;
-        int run = 0;
-        for (int c0 = 0; c0 < nchunks; c0 += 32) {
-            const int c = c0 + lane;
-            const int v = (c < nchunks) ? rowp[c] : 0;
-            int inc = v;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int u = __shfl_up_sync(0xffffffffu, inc, o);
-                if (lane >= o) inc += u;
-            }
-            if (c < nchunks) rowp[c] = run + inc - v;
-            run += __shfl_sync(0xffffffffu, inc, 31);
-        }
-        if (lane == 0) cnt_s[e] = run;
-    }
+    if (tid < E) cnt_s[tid] = R.expert_bounds[tid];
     __syncthreads();
     if (warp == 0) {
         int local[8], ltiles[8], lsum = 0, lnz = 0, ltl = 0, ltd = 0;
@@ -362,16 +537,28 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
         count_launch();
         set_routing_kernel<<<(T * K + 255) / 256, 256, 0, st>>>(a.ids_in, a.weights_in, T * K, a.R.ids, a.R.weights);
     } else if (lg == nullptr) {
-        const dim3 grid((T + 63) / 64, (E + 63) / 64);
         count_launch();
-        if (a.act_dtype == 0)
-            router_logits_large_kernel<float><<<grid, 256, 0, st>>>((const float*)a.x, a.L.router_w, a.R.logits, T, H, E);
-        else
-            router_logits_large_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a.x, a.L.router_w,
-                                                                           a.R.logits, T, H, E);
+        if (H % 32 == 0 && a.w16 != nullptr && reinterpret_cast<uintptr_t>(a.x) % 16 == 0) {
+            const size_t n = (size_t)E * H;
+            split_router_w_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.L.router_w, a.w16, n);
+            count_launch(1);
+            const dim3 grid((T + 63) / 64, (E + 127) / 128);
+            if (a.act_dtype == 0)
+                router_logits_mma_kernel<float><<<grid, 128, 0, st>>>((const float*)a.x, a.w16, a.R.logits, T, H, E);
+            else
+                router_logits_mma_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)a.x, a.w16,
+                                                                             a.R.logits, T, H, E);
+        } else {
+            const dim3 grid((T + 63) / 64, (E + 63) / 64);
+            if (a.act_dtype == 0)
+                router_logits_large_kernel<float><<<grid, 256, 0, st>>>((const float*)a.x, a.L.router_w, a.R.logits, T, H, E);
+            else
+                router_logits_large_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a.x, a.L.router_w,
+                                                                               a.R.logits, T, H, E);
+        }
         lg = a.R.logits;
     }
-    count_launch(4);
+    count_launch(5);
     if (a.ids_in == nullptr)
         topk_large_kernel<<<(T + TK_WARPS - 1) / TK_WARPS, TK_WARPS * 32, 0, st>>>(lg, T, E, K, a.gating, a.R.ids,
                                                                                    a.R.weights);
@@ -383,7 +570,8 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const int mt_gu = a.L.I / 128, mt_dn = a.L.H / 256;  // m-tiles: 128 gate + 128 up rows | 256 down rows
     int4* tiles_gu = a.tiles;
     int4* tiles_dn = a.tiles ? a.tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1) : nullptr;
-    sort_scan_kernel<<<1, 256, 0, st>>>(a.blk_hist, nchunks, E, a.R, tile_cols, mt_gu, mt_dn, tiles_gu, tiles_dn,
+    sort_rowscan_kernel<<<E, 32, 0, st>>>(a.blk_hist, nchunks, a.R);
+    sort_scan_kernel<<<1, 256, 0, st>>>(nchunks, E, a.R, tile_cols, mt_gu, mt_dn, tiles_gu, tiles_dn,
                                         a.n_tiles, max_ct * mt_gu, max_ct * mt_dn);
     sort_place_kernel<<<(nchunks + 7) / 8, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist, nchunks, a.R);
     return cudaGetLastError();

@@ -75,31 +75,71 @@ class ExpertParallelMoe:
         self.wire_dtype = wire_dtype        # activation rows on the wire (bf16 inputs travel exactly)
         self.combine_dtype = combine_dtype  # expert outputs on the wire (f16, as the single-GPU path stores them)
         self.last = {}
+        self.profile = False
+        self._marks = []
+
+    def _mark(self, name):
+        if self.profile and torch.cuda.is_available():
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((name, ev))
+
+    def phase_times_ms(self):
+        """Per-phase device times of the last forward (profile=True): [(phase, ms), ...]."""
+        torch.cuda.synchronize()
+        return [(b[0], a[1].elapsed_time(b[1])) for a, b in zip(self._marks[:-1], self._marks[1:])]
 
     def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         T, H = normed.shape
-        ids, w = self.route_fn(normed)
-        order, send_counts, local_ids = dispatch_plan(ids, self.epr, self.world)
+        self._marks = []
+        self._mark("start")
+        routed = self.route_fn(normed)
+        ids, w = routed[0], routed[1]
+        self._mark("route")
+        if len(routed) > 2:
+            # the router's own counting sort is the send plan (compact-column order)
+            tables = routed[2]
+            tok = tables["col_src_tok"].to(torch.int64)
+            order = None
+            if self.combine_fn is None:
+                d2c = tables["dst_to_col"].to(torch.int64)
+                order = torch.empty_like(d2c)
+                order[d2c] = torch.arange(d2c.numel(), device=d2c.device)
+            b = tables["expert_bounds"].to(torch.int64)
+            edges = b[torch.arange(0, self.E + 1, self.epr, device=b.device)]
+            send_counts = edges[1:] - edges[:-1]
+            local_ids = (tables["col_expert"] % self.epr).to(torch.int32)
+        else:
+            order, send_counts, local_ids = dispatch_plan(ids, self.epr, self.world)
+            tok = torch.div(order, self.K, rounding_mode="floor")
         # (2) counts
         sc = send_counts.to(torch.int64)
         rc = torch.empty_like(sc)
         dist.all_to_all_single(rc, sc, group=self.group)
         send_l, recv_l = sc.tolist(), rc.tolist()  # the one host sync of the call (NCCL sizes are host arguments)
+        self._mark("plan+counts")
         # (3) dispatch rows and local expert ids
-        tok = torch.div(order, self.K, rounding_mode="floor")
         rows = normed[tok].to(self.wire_dtype)
         recv_rows = all_to_all_v(rows, send_l, recv_l, self.group)
         recv_ids = all_to_all_v(local_ids, send_l, recv_l, self.group)
+        self._mark("dispatch")
         # (4) local experts
         d = self.expert_fn(recv_rows, recv_ids)
+        self._mark("experts")
         # (5) combine
         back = all_to_all_v(d.to(self.combine_dtype), recv_l, send_l, self.group)
+        self._mark("combine_a2a")
         # (6) weighted sum in slot order
         self.last = {"ids": ids, "weights": w, "send_counts": send_l, "recv_counts": recv_l}
         if self.combine_fn is not None:
-            inv = torch.empty(T * self.K, dtype=torch.int32, device=normed.device)
-            inv[order] = torch.arange(T * self.K, dtype=torch.int32, device=normed.device)
-            return self.combine_fn(back, residual, w, inv)
+            if len(routed) > 2:
+                inv = routed[2]["dst_to_col"]
+            else:
+                inv = torch.empty(T * self.K, dtype=torch.int32, device=normed.device)
+                inv[order] = torch.arange(T * self.K, dtype=torch.int32, device=normed.device)
+            out = self.combine_fn(back, residual, w, inv)
+            self._mark("combine")
+            return out
         dpair = torch.empty((T * self.K, H), dtype=torch.float32, device=normed.device)
         dpair[order] = back.to(torch.float32)
         dpair = dpair.view(T, self.K, H)
@@ -132,7 +172,7 @@ def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.
 
     def route_fn(x):
         ids, w = route_sc.route_only(route_layer, x.float().contiguous())
-        return ids, w
+        return ids, w, route_sc.get_routing_device(x.shape[0], x.device)
 
     def expert_fn(rows, local_ids):
         if rows.shape[0] == 0:

@@ -238,6 +238,17 @@ class MoeScratch:
         self._override = logits
         check(_lib.lib().lumen_moe_set_logits_override(self._h, _ptr(logits)))
 
+    def get_routing_device(self, tokens: int, device):
+        """Sort tables of the last routing call as device tensors (no host sync)."""
+        C = tokens * self.K
+        d2c = torch.empty(C, dtype=torch.int32, device=device)
+        cst = torch.empty(C, dtype=torch.int32, device=device)
+        cex = torch.empty(C, dtype=torch.int32, device=device)
+        bounds = torch.empty(self.E + 1, dtype=torch.int32, device=device)
+        check(_lib.lib().lumen_moe_get_routing_device(self._h, tokens, d2c.data_ptr(), cst.data_ptr(), cex.data_ptr(),
+                                                      bounds.data_ptr(), _stream()))
+        return {"dst_to_col": d2c, "col_src_tok": cst, "col_expert": cex, "expert_bounds": bounds}
+
     def get_routing(self, tokens: int):
         C = tokens * self.K
         ids = np.zeros((tokens, self.K), np.uint32)

@@ -230,6 +230,16 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_debug_expf(const float* d_in, float* 
 LUMEN_MOE_API lumen_moe_status_t lumen_moe_debug_decode_phase(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
                                                               int32_t phase, void* stream);
 
+/* Re-runs the most recent decode call through the fused persistent kernel (batches
+ * of 1..4 tokens) and records, per CTA, globaltimer stamps (ns): 0 entry, 1 after the
+ * wait on the previous kernel, 2 logits done, 3 barrier 1 passed, 4 routing done,
+ * 5 gate/up done, 6 barrier 2 passed, 7 SwiGLU fragments staged, 8 down products
+ * done, 9 end (10, 11 unused). d_trace: [SM count][12] uint64 on the device, zeroed
+ * by the caller.
+ * LUMEN_MOE_UNSUPPORTED when the call's shape takes the three-kernel chain. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_debug_decode_trace(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                              uint64_t* d_trace, void* stream);
+
 /* Bytes of device memory held by a prepared layer (repacked planes + tables). */
 LUMEN_MOE_API size_t lumen_moe_layer_bytes(const lumen_moe_layer* layer);
 

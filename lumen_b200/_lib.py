@@ -54,6 +54,7 @@ SIGNATURES = {
     "lumen_moe_rmsnorm": [vp, vp, vp, i32, i32, f32, vp],
     "lumen_moe_stack_decode": [vp, vp, vp, i32, vp, f32, i32, vp],
     "lumen_moe_debug_expf": [vp, vp, i64, vp],
+    "lumen_moe_debug_decode_trace": [vp, vp, vp, vp],
     "lumen_moe_debug_decode_phase": [vp, vp, i32, vp],
     "lumen_moe_layer_bytes": [vp],
     "lumen_moe_launch_count": [i32],

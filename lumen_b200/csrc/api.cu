@@ -249,7 +249,8 @@ lumen_moe_status_t lumen_moe_get_routing(lumen_moe_ctx* ctx, int32_t tokens, uin
     if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
     if (dev_status != 0) {
         cudaMemset(s.status, 0, 4);
-        return fail(dev_status, "a device-side bounded wait expired in the grouped GEMM");
+        cudaMemset(s.bar, 0, 1024 * 4);
+        return fail(dev_status, "a device-side bounded wait expired (grouped GEMM pipeline or decode grid barrier)");
     }
     return LUMEN_MOE_OK;
 }
@@ -319,6 +320,19 @@ lumen_moe_status_t lumen_moe_debug_decode_phase(lumen_moe_ctx* ctx, const lumen_
     lumen::DecodeArgs a = ctx->scratch.last_decode;
     a.L = layer->layer.dev;
     cudaError_t e = lumen::launch_decode_phase(a, phase, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_debug_decode_trace(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                uint64_t* d_trace, void* stream) {
+    if (!ctx || !layer) return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    if (!ctx->scratch.has_last_decode) return fail(LUMEN_MOE_INVALID_ARG, "no decode call has been made yet");
+    lumen::DecodeArgs a = ctx->scratch.last_decode;
+    a.L = layer->layer.dev;
+    a.trace = reinterpret_cast<unsigned long long*>(d_trace);
+    if (!lumen::decode_fused_applicable(a)) return fail(LUMEN_MOE_UNSUPPORTED, "the fused decode kernel does not apply to this call");
+    cudaError_t e = lumen::launch_decode_fused(a, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
     return LUMEN_MOE_OK;
 }

@@ -36,7 +36,6 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
     __shared__ float scale_s[DECODE_MAX_TOKENS];
     __shared__ __align__(16) float p_s[RS_WARPS][MAX_EXPERTS];
     __shared__ __align__(16) float lg_s[RS_WARPS][MAX_EXPERTS];
-    __shared__ float sel_s[RS_WARPS][MAX_TOP_K];
     __shared__ int ids_s[DECODE_MAX_TOKENS * MAX_TOP_K];
     __shared__ int cnt_s[MAX_EXPERTS];
     __shared__ int bounds_s[MAX_EXPERTS + 1];
@@ -174,7 +173,7 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
     for (int t = warp; t < T; t += RS_WARPS) {
         for (int i = lane; i < E; i += 32) lg_s[warp][i] = __ldcg(lg + (size_t)t * E + i);
         __syncwarp();
-        warp_topk(lg_s[warp], E, K, a.gating, p_s[warp], sel_s[warp], a.R.ids + (size_t)t * K,
+        warp_topk(lg_s[warp], E, K, a.gating, p_s[warp], nullptr, a.R.ids + (size_t)t * K,
                   a.R.weights + (size_t)t * K);
         if (lane < K) ids_s[t * K + lane] = (int)a.R.ids[(size_t)t * K + lane];
     }
@@ -634,7 +633,11 @@ cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st)
     }
 }
 
+bool decode_fused_applicable(const DecodeArgs& a);
+cudaError_t launch_decode_fused(const DecodeArgs& a, cudaStream_t st);
+
 cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t st) {
+    if (decode_fused_applicable(a)) return launch_decode_fused(a, st);
     for (int phase = 0; phase < 3; ++phase) {
         const cudaError_t err = launch_decode_phase(a, phase, st);
         if (err != cudaSuccess) return err;

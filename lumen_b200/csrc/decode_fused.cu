@@ -1,0 +1,572 @@
+// One persistent kernel for a whole MoE layer call at decode batches of 1..4 tokens.
+//
+// The three-kernel chain (router -> gate/up -> down) pays a kernel boundary twice;
+// at batch 1 a layer is only ~22 MB of weights, so those boundaries cost more than
+// the streaming itself. Here one CTA per SM stays resident and the two boundaries
+// become grid barriers:
+//
+//   phase A  router logit of expert row(s) e = CTA, CTA + G, ... (cuda/moe.rs:1119-1140);
+//            every CTA also builds the activation fragments of all tokens in its own
+//            shared memory (and the fused FFN RMSNorm scale when asked)
+//   barrier 1
+//   phase B  every CTA redoes the (tiny) top-k and counting sort from the logits, so the
+//            routing never makes a second trip through memory; CTA 0 publishes the tables.
+//            gate/up + SwiGLU work items (expert with work, 16 inter rows), dealt
+//            round-robin from the last CTA downwards; each warp owns one 128-input
+//            group, next item's weights are requested before the current one is used.
+//            The down-projection weights of this CTA's 16 output rows are prefetched
+//            into shared memory with cp.async as soon as the routing is known.
+//            (cuda/shaders/moe_expert_q4_0.cu:58-108; moe_expert.cu:62-97)
+//   barrier 2
+//   phase C  down product for output rows 16*CTA.., all experts with work; weighted
+//            combine in slot order + residual
+//            (moe_expert_q4_0.cu:118-151; cuda/shaders/moe_accum.cu:22-46)
+//
+// The barrier is an arrive counter plus a generation word, both left ready for the
+// next launch; every wait is bounded (one second), after which the kernel raises the
+// context's status word and every CTA returns.
+#include "decode_common.cuh"
+#include "router.cuh"
+
+namespace lumen {
+
+namespace {
+
+using namespace dcommon;
+
+constexpr int FW = 16;        // warps per CTA
+constexpr int FT = FW * 32;   // threads per CTA
+constexpr int FMAX_T = 4;     // tokens
+constexpr int FMAX_C = 32;    // (token, slot) pairs
+
+template <int Q>
+struct TileU4 {  // uint4 words of one weight tile staged in shared memory: lane-major q words, then 8 scale words
+    static constexpr int value = QTraits<Q>::NQ * 32 + 8;
+};
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_add_u32(unsigned* p, unsigned v) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Grid barrier: one arrival counter that only grows (bar[0]); barrier number `epoch`
+// (counted per CTA in bar[1 + cta], written by that CTA alone) is passed when the
+// counter reaches epoch * G, compared modulo 2^32, so nothing is reset between
+// launches. One fire-and-forget reduction to arrive, one thread per CTA polls.
+// Returns false when the wait expired (one second) or another CTA already raised the
+// status word.
+__device__ __forceinline__ bool grid_barrier(unsigned* bar, int* status, int G, unsigned epoch, int* fail_s) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        red_release_add_u32(bar, 1u);
+        const unsigned target = epoch * (unsigned)G;
+        unsigned long long t0 = 0;
+        unsigned spins = 0;
+        bool ok = true;
+        while ((int)(ld_relaxed_u32(bar) - target) < 0) {
+            if ((++spins & 63u) == 0) {
+                if (t0 == 0) t0 = global_ns();
+                if (global_ns() - t0 > 1000000000ull || *reinterpret_cast<volatile int*>(status) != 0) {
+                    ok = false;
+                    break;
+                }
+            }
+        }
+        __threadfence();
+        if (!ok) {
+            atomicCAS(status, 0, 4);  // LUMEN_MOE_TIMEOUT
+            *fail_s = 1;
+        }
+    }
+    __syncthreads();
+    return *fail_s == 0;
+}
+
+template <int Q>
+__device__ __forceinline__ void read_staged_tile(WTile<Q>& w, const uint4* slot, int lane) {
+#pragma unroll
+    for (int j = 0; j < QTraits<Q>::NQ; ++j) w.q[j] = slot[j * 32 + lane];
+    if (Q != BF16) w.s = slot[QTraits<Q>::NQ * 32 + (lane >> 2)];
+}
+
+struct RouteSm {
+    int ids[FMAX_C];
+    float w[FMAX_C];
+    int d2c[FMAX_C];      // pair -> column
+    int col_u[FMAX_C];    // column -> index of its expert in the list of experts with work
+    int col_tok[FMAX_C];  // column -> source token
+    int ue[FMAX_C];       // experts with work, ascending
+    int uc0[FMAX_C];      // first column of the expert
+    int uncol[FMAX_C];    // columns of the expert
+    int U;
+};
+
+struct TopkSm {
+    float lg[FMAX_T][MAX_EXPERTS];
+    float p[FMAX_T][MAX_EXPERTS];
+    unsigned long long tab[32];  // copy of the exp table: lanes index it divergently
+};
+
+}  // namespace
+
+template <int Q>
+__global__ void __launch_bounds__(FT, 1)
+decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots) {
+    extern __shared__ uint4 dyn[];
+    __shared__ __align__(16) TopkSm ts;
+    __shared__ float red_a[FW][FMAX_T];
+    __shared__ float scale_s[FMAX_T];
+    __shared__ float red[FW][16][4][2];
+    __shared__ RouteSm rs;
+    __shared__ int fail_s;
+
+    pdl_trigger();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    auto stamp = [&](int i) {
+        if (a.trace != nullptr && tid == 0) a.trace[(size_t)blockIdx.x * 12 + i] = global_ns();
+    };
+    stamp(0);
+    if (tid < 32) ts.tab[tid] = lumen_exact::exp2_tab_entry(tid);
+    if (tid == 0) fail_s = 0;
+    const int gq = lane >> 2, t4 = lane & 3;
+    const int cta = blockIdx.x, G = gridDim.x;
+    const int H = a.L.H, I = a.L.I, E = a.L.E, T = a.T, K = a.K;
+    const int C = T * K;
+    const int H4 = H >> 2;
+    const int kg_h = a.L.kg_h, kg_i = a.L.kg_i;
+    const int nblk = H >> 5, nblk_pad = kg_h * 4, nblk_i_pad = kg_i * 4;
+    const int per_col = 2 * nblk_pad * 4, per_col_i = 2 * nblk_i_pad * 4;
+    const bool want_logits = (a.logits_override == nullptr);
+    constexpr int TU4 = TileU4<Q>::value;
+
+    // dynamic shared memory: activation fragments | SwiGLU fragments | down partial sums | staged down tiles
+    uint4* xs = dyn;                                  // [T][per_col]
+    uint4* ss = xs + (size_t)T * per_col;             // [C][per_col_i]
+    float* part = reinterpret_cast<float*>(ss + (size_t)C * per_col_i);  // [C * kg_i][4 cols][16 rows]
+    uint4* pf = reinterpret_cast<uint4*>(part + (size_t)C * kg_i * 64);  // [FW][pf_slots][TU4]
+
+    // ---------------- phase A ----------------
+    // first router row in registers before waiting on the previous kernel (weights are static)
+    float4 wv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (want_logits && cta < E && tid < H4)
+        wv = __ldg(reinterpret_cast<const float4*>(a.L.router_w + (size_t)cta * H) + tid);
+    pdl_wait();
+    stamp(1);
+    if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier launch gave up: do not touch the barrier
+    unsigned epoch = *reinterpret_cast<volatile unsigned*>(a.bar + 1 + cta);  // barriers this CTA has passed so far
+
+    // normalised activations of all tokens, f32, in shared memory (the region is reused for
+    // the SwiGLU fragments and partial sums, which are written only after the routing)
+    float4* xn4 = reinterpret_cast<float4*>(ss);
+    if (a.gamma != nullptr) {
+#pragma unroll 1
+        for (int t = 0; t < T; ++t) {
+            const float4* xr = reinterpret_cast<const float4*>(a.x + (size_t)t * H);
+            float sq = 0.0f;
+#pragma unroll 1
+            for (int i4 = tid; i4 < H4; i4 += FT) {
+                const float4 v = xr[i4];
+                sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) red_a[warp][t] = sq;
+        }
+        __syncthreads();
+        if (tid < T) {
+            float sq = 0.0f;
+#pragma unroll 1
+            for (int w = 0; w < FW; ++w) sq += red_a[w][tid];
+            scale_s[tid] = 1.0f / sqrtf(sq / (float)H + a.eps);
+        }
+        __syncthreads();
+    }
+#pragma unroll 1
+    for (int i = tid; i < T * H4; i += FT) {
+        float4 v = reinterpret_cast<const float4*>(a.x)[i];
+        if (a.gamma != nullptr) {
+            const int t = i / H4;
+            const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + (i - t * H4));
+            const float sc = scale_s[t];
+            v.x = v.x * sc * g.x;
+            v.y = v.y * sc * g.y;
+            v.z = v.z * sc * g.z;
+            v.w = v.w * sc * g.w;
+            if (a.normed_out != nullptr && (i % G) == cta) reinterpret_cast<float4*>(a.normed_out)[i] = v;
+        }
+        xn4[i] = v;
+    }
+    __syncthreads();
+
+    if (want_logits) {
+#pragma unroll 1
+        for (int e = cta; e < E; e += G) {
+            const float4* wrow = reinterpret_cast<const float4*>(a.L.router_w + (size_t)e * H);
+#pragma unroll 1
+            for (int t = 0; t < T; ++t) {
+                float acc = 0.0f;
+#pragma unroll 1
+                for (int i4 = tid; i4 < H4; i4 += FT) {
+                    const float4 w4 = (e == cta && i4 == tid) ? wv : __ldg(wrow + i4);
+                    const float4 xv = xn4[t * H4 + i4];
+                    acc += w4.x * xv.x + w4.y * xv.y + w4.z * xv.z + w4.w * xv.w;
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (lane == 0) red_a[warp][t] = acc;
+            }
+            __syncthreads();
+            if (tid < T) {
+                float v = 0.0f;
+#pragma unroll 1
+                for (int w = 0; w < FW; ++w) v += red_a[w][tid];
+                a.R.logits[(size_t)tid * E + e] = v;
+            }
+            __syncthreads();
+        }
+    }
+    // activation fragments of every token, private to this CTA
+    {
+        const bool bf16_mode = (Q == BF16);
+        const int sub = tid & 7, hl = sub >> 2, s4 = sub & 3;
+#pragma unroll 1
+        for (int item = tid >> 3; item < T * nblk; item += FT / 8) {
+            const int t = item / nblk, b = item - t * nblk;
+            const float4 lo4 = xn4[t * H4 + b * 8 + s4];
+            const float4 hi4 = xn4[t * H4 + b * 8 + 4 + s4];
+            xs[(size_t)t * per_col + ((size_t)hl * nblk_pad + b) * 4 + s4] = make_act_frag(lo4, hi4, hl, bf16_mode);
+        }
+        // padding blocks (kg_h * 4 > H / 32) must read as zero
+        const int per = (nblk_pad - nblk) * 4;
+#pragma unroll 1
+        for (int i = tid; i < T * 2 * per; i += FT) {
+            const int th = i / per, r = i - th * per;
+            xs[(size_t)(th >> 1) * per_col + ((size_t)(th & 1) * nblk_pad + nblk) * 4 + r] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    }
+    stamp(2);
+    if (want_logits) {
+        if (!grid_barrier(a.bar, a.status, G, ++epoch, &fail_s)) return;
+    } else {
+        __syncthreads();
+    }
+    stamp(3);
+
+    // ---------------- phase B: routing (redundantly per CTA) ----------------
+    {
+        // four warps per token share the exps, the first of them finishes the token
+        const float* lg = want_logits ? a.R.logits : a.logits_override;
+        const int tok = warp >> 2, sub = warp & 3;
+        if (tok < T) {
+#pragma unroll 1
+            for (int i = sub * 32 + lane; i < E; i += 128) ts.lg[tok][i] = __ldcg(lg + (size_t)tok * E + i);
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
+            warp_gate_probs(ts.lg[tok], E, a.gating, ts.p[tok], ts.tab, sub, 4);
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
+            if (sub == 0)
+                warp_select(ts.p[tok], E, K, a.gating, reinterpret_cast<uint32_t*>(rs.ids) + tok * K, rs.w + tok * K);
+        }
+        __syncthreads();
+        stamp(10);
+        if (warp == 0) {
+            // stable counting sort of the C <= 32 pairs by expert, one pair per lane
+            const int my = (lane < C) ? rs.ids[lane] : 0x7fffffff;
+            int less = 0, eqb = 0, cnt = 0;
+            for (int q = 0; q < C; ++q) {
+                const int eq = __shfl_sync(0xffffffffu, my, q);
+                less += (eq < my);
+                cnt += (eq == my);
+                eqb += (eq == my && q < lane);
+            }
+            const bool first = (lane < C) && (eqb == 0);
+            const unsigned fmask = __ballot_sync(0xffffffffu, first);
+            int u = 0;
+            for (int q = 0; q < C; ++q) {
+                const int eq = __shfl_sync(0xffffffffu, my, q);
+                u += (((fmask >> q) & 1u) && eq < my);
+            }
+            if (lane < C) {
+                const int col = less + eqb;
+                rs.d2c[lane] = col;
+                rs.col_u[col] = u;
+                rs.col_tok[col] = lane / K;
+                if (first) {
+                    rs.ue[u] = my;
+                    rs.uc0[u] = col;
+                    rs.uncol[u] = cnt;
+                }
+                if (cta == 0) {
+                    a.R.ids[lane] = (uint32_t)my;
+                    a.R.weights[lane] = rs.w[lane];
+                    a.R.dst_to_col[lane] = col;
+                    a.R.col_expert[col] = my;
+                    a.R.col_src_tok[col] = lane / K;
+                    if (first) a.R.uexp[u] = my;
+                }
+            }
+            if (lane == 0) {
+                rs.U = __popc(fmask);
+                if (cta == 0) *a.R.n_uexp = __popc(fmask);
+            }
+            if (cta == 0) {
+                for (int e = lane; e <= E; e += 32) {
+                    int below = 0;
+                    for (int q = 0; q < C; ++q) below += (rs.ids[q] < e);
+                    a.R.expert_bounds[e] = below;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    stamp(4);
+    const int U = rs.U;
+    const int rt_i = a.L.rt_i;
+    const int n_items = U * rt_i;
+    // work items of this CTA: G-1-cta, then every G-th (the CTAs without down rows take the odd ones out first)
+    const int it0 = G - 1 - cta;
+
+    auto load_gu = [&](int it, WTile<Q>& g, WTile<Q>& up) {
+        const int u = it / rt_i, rt = it - u * rt_i;
+        const int e = rs.ue[u];
+        if (warp < kg_h) {
+            load_wtile<Q>(g, a.L.gate_q(e), a.L.gate_s(e), rt * kg_h + warp, lane);
+            load_wtile<Q>(up, a.L.up_q(e), a.L.up_s(e), rt * kg_h + warp, lane);
+        }
+    };
+    WTile<Q> wg0, wu0, wg1, wu1;
+    if (it0 < n_items) load_gu(it0, wg0, wu0);
+
+    // down tiles of this CTA's output rows: request the first pf_slots items of every warp now
+    const bool has_down = cta < a.L.rt_h;
+    const int n_down = U * kg_i;
+    if (has_down) {
+        for (int i = 0; i < pf_slots; ++i) {
+            const int n = warp + FW * i;
+            if (n < n_down) {
+                const int uu = n / kg_i, kg = n - uu * kg_i;
+                const int ee = rs.ue[uu];
+                const int tile = cta * kg_i + kg;
+                uint4* slot = pf + ((size_t)warp * pf_slots + i) * TU4;
+                const uint4* qp = a.L.down_q(ee) + ((size_t)tile * QTraits<Q>::NQ) * 32 + lane;
+#pragma unroll
+                for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(slot + j * 32 + lane, qp + j * 32);
+                if (Q != BF16 && lane < 8)
+                    cp_async16(slot + QTraits<Q>::NQ * 32 + lane, a.L.down_s(ee) + (size_t)tile * 8 + lane);
+            }
+        }
+    }
+
+    // gate/up + SwiGLU
+    auto compute_gu = [&](int it, const WTile<Q>& g, const WTile<Q>& up) {
+        const int u = it / rt_i, rt = it - u * rt_i;
+        const int c0 = rs.uc0[u];
+        const int ncol = min(4, rs.uncol[u]);
+        const int jcol = gq >> 1;
+        const bool bvalid = jcol < ncol;
+        const int tok = bvalid ? rs.col_tok[c0 + jcol] : 0;
+        float acc_g[4] = {0.f, 0.f, 0.f, 0.f}, acc_u[4] = {0.f, 0.f, 0.f, 0.f};
+        if (warp < kg_h) {
+            const uint4* bp = xs + (size_t)tok * per_col + ((size_t)(gq & 1) * nblk_pad) * 4 + t4 + (size_t)warp * 16;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                block_mma_smem<Q>(g, b, bp, bvalid, acc_g);
+                block_mma_smem<Q>(up, b, bp, bvalid, acc_u);
+            }
+        }
+        red[warp][gq][t4][0] = acc_g[0] + acc_g[1];
+        red[warp][gq][t4][1] = acc_u[0] + acc_u[1];
+        red[warp][gq + 8][t4][0] = acc_g[2] + acc_g[3];
+        red[warp][gq + 8][t4][1] = acc_u[2] + acc_u[3];
+        __syncthreads();
+        if (tid < 64) {
+            const int row = tid & 15, tokc = tid >> 4;
+            if (tokc < ncol) {
+                float gate = 0.0f, upv = 0.0f;
+#pragma unroll
+                for (int w = 0; w < FW; ++w) {
+                    gate += red[w][row][tokc][0];
+                    upv += red[w][row][tokc][1];
+                }
+                const float sv = (gate / (1.0f + expf(-gate))) * upv;
+                const int col = c0 + tokc;
+                const int irow = rt * 16 + row;
+                if (a.s_f32 != nullptr) a.s_f32[(size_t)col * I + irow] = sv;
+                store_swiglu_frag<Q>(a.sf, col, irow, nblk_i_pad, sv);
+            }
+        }
+        __syncthreads();
+    };
+#pragma unroll 1
+    for (int it = it0; it < n_items; it += G) {
+        const bool more = it + G < n_items;
+        if (more) load_gu(it + G, wg1, wu1);
+        compute_gu(it, wg0, wu0);
+        if (more) {
+            wg0 = wg1;
+            wu0 = wu1;
+        }
+    }
+    // residual of this CTA's output rows, requested before the barrier
+    float resid = 0.0f;
+    if (has_down && tid < 16 * T) resid = a.residual[(size_t)(tid >> 4) * H + cta * 16 + (tid & 15)];
+    stamp(5);
+    if (!grid_barrier(a.bar, a.status, G, ++epoch, &fail_s)) {
+        cp_async_wait_all();
+        return;
+    }
+    if (tid == 0) a.bar[1 + cta] = epoch;
+    stamp(6);
+
+    // ---------------- phase C: down + combine ----------------
+    if (!has_down) {
+        cp_async_wait_all();
+        return;
+    }
+    for (int i = tid; i < C * per_col_i; i += FT) cp_async16(&ss[i], a.sf + i);
+    cp_async_wait_all();
+    __syncthreads();
+    stamp(7);
+    for (int rt = cta; rt < a.L.rt_h; rt += G) {
+        for (int i = 0; warp + FW * i < n_down; ++i) {
+            const int n = warp + FW * i;
+            const int uu = n / kg_i, kg = n - uu * kg_i;
+            WTile<Q> w;
+            if (rt == cta && i < pf_slots) {
+                read_staged_tile<Q>(w, pf + ((size_t)warp * pf_slots + i) * TU4, lane);
+            } else {
+                const int ee = rs.ue[uu];
+                load_wtile<Q>(w, a.L.down_q(ee), a.L.down_s(ee), rt * kg_i + kg, lane);
+            }
+            const int c0 = rs.uc0[uu];
+            const int ncol = min(4, rs.uncol[uu]);
+            const int jcol = gq >> 1;
+            const bool bvalid = jcol < ncol;
+            const uint4* bp = ss + ((size_t)((c0 + (bvalid ? jcol : 0)) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4 + (size_t)kg * 16;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int b = 0; b < 4; ++b) block_mma_smem<Q>(w, b, bp, bvalid, acc);
+            float* pp = part + (size_t)n * 64 + t4 * 16;
+            pp[gq] = acc[0] + acc[1];
+            pp[gq + 8] = acc[2] + acc[3];
+        }
+        __syncthreads();
+        stamp(8);
+        if (tid < 16 * T) {
+            const int row = tid & 15, t = tid >> 4;
+            const size_t o = (size_t)t * H + rt * 16 + row;
+            float accv = (rt == cta) ? resid : a.residual[o];
+            for (int slot = 0; slot < K; ++slot) {
+                const int col = rs.d2c[t * K + slot];
+                const int uu = rs.col_u[col];
+                const int j = min(col - rs.uc0[uu], 3);
+                float d = 0.0f;
+                for (int kg = 0; kg < kg_i; ++kg) d += part[(size_t)(uu * kg_i + kg) * 64 + j * 16 + row];
+                accv = __fadd_rn(accv, __fmul_rn(rs.w[t * K + slot], d));
+            }
+            a.out[o] = accv;
+        }
+        __syncthreads();
+    }
+    stamp(9);
+}
+
+// Shared memory the fused kernel needs besides its static arrays; pf_slots = staged down tiles per warp.
+static size_t fused_smem_bytes(const DecodeArgs& a, int tile_u4, int pf_slots) {
+    const size_t C = (size_t)a.T * a.K;
+    return (size_t)a.T * 2 * a.L.kg_h * 16 * 16 + C * 2 * a.L.kg_i * 16 * 16 + C * a.L.kg_i * 256 +
+           (size_t)FW * pf_slots * tile_u4 * 16;
+}
+
+static int tile_u4_of(int quant) {
+    return quant == Q4_0 ? TileU4<Q4_0>::value : quant == Q8_0 ? TileU4<Q8_0>::value : TileU4<BF16>::value;
+}
+
+struct FusedDeviceInfo {
+    int sms = 0;
+    int smem_optin = 0;
+};
+
+static const FusedDeviceInfo& fused_device_info(int device) {
+    static FusedDeviceInfo info[64];
+    FusedDeviceInfo& d = info[device & 63];
+    if (d.sms == 0) {
+        int sms = 0, smem = 0;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+        cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device);
+        d.smem_optin = smem;
+        d.sms = sms;
+    }
+    return d;
+}
+
+// Shape limits of the fused kernel: one 128-input group per warp, one pair per lane in
+// the sort, one CTA per 16 output rows, and the shared-memory budget.
+bool decode_fused_applicable(const DecodeArgs& a) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return false;
+    if (a.bar == nullptr || a.status == nullptr) return false;
+    if (a.T < 1 || a.T > FMAX_T || a.T * a.K > FMAX_C) return false;
+    if (a.L.kg_h > FW || a.L.H > FT * 4) return false;
+    const FusedDeviceInfo& d = fused_device_info(device);
+    if (d.sms <= 0 || d.sms > 1023 || a.L.rt_h > d.sms) return false;
+    const size_t static_smem = 20 * 1024;
+    return fused_smem_bytes(a, tile_u4_of(a.L.quant), 0) + static_smem <= (size_t)d.smem_optin;
+}
+
+template <int Q>
+static cudaError_t launch_fused_t(const DecodeArgs& a, int device, cudaStream_t st) {
+    const FusedDeviceInfo& d = fused_device_info(device);
+    const size_t static_smem = 20 * 1024;
+    const int C = a.T * a.K;
+    const int want = (C * a.L.kg_i + FW - 1) / FW;  // down tiles per warp when every pair has its own expert
+    int pf = want;
+    while (pf > 0 && fused_smem_bytes(a, TileU4<Q>::value, pf) + static_smem > (size_t)d.smem_optin) --pf;
+    const size_t smem = fused_smem_bytes(a, TileU4<Q>::value, pf);
+    static size_t attr_smem[64] = {};
+    if (smem > attr_smem[device & 63]) {
+        cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_smem[device & 63] = smem;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(d.sms);
+    cfg.blockDim = dim3(FT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    // All CTAs must be resident at once (grid barriers): a cooperative launch makes the
+    // driver check that; the programmatic attribute lets the prologue overlap the
+    // previous kernel's tail.
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    count_launch();
+    return cudaLaunchKernelEx(&cfg, decode_fused_kernel<Q>, a, pf);
+}
+
+cudaError_t launch_decode_fused(const DecodeArgs& a, cudaStream_t st) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    switch (a.L.quant) {
+        case Q4_0: return launch_fused_t<Q4_0>(a, device, st);
+        case Q8_0: return launch_fused_t<Q8_0>(a, device, st);
+        default: return launch_fused_t<BF16>(a, device, st);
+    }
+}
+
+}  // namespace lumen

@@ -21,25 +21,13 @@
 //                          the down weights stream while gate/up is still computing.
 //                          Weighted combine in slot order at the end
 //                          (moe_expert_q4_0.cu:118-151; cuda/shaders/moe_accum.cu:22-46)
-#include "mma_frag.cuh"
+#include "decode_common.cuh"
 
 namespace lumen {
 
 namespace {
 
-__device__ __forceinline__ void pdl_wait_() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_trigger_() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-__device__ __forceinline__ int frag_pos_(int r) {
-    const int m = r & 3;
-    return (m == 0) ? 0 : (m == 2) ? 1 : (m == 1) ? 2 : 3;
-}
-
-__device__ __forceinline__ void cp_async16_(void* smem_dst, const void* gsrc) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all_() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+using namespace dcommon;
 
 template <int Q>
 struct SmallCfg;
@@ -56,29 +44,6 @@ struct SmallCfg<BF16> {
     static constexpr int GU_WARPS = 16, GU_ITERS = 1, DN_RING = 2;
 };
 
-// One block (two MMAs) of one column group with the B fragment taken from shared memory.
-template <int Q>
-__device__ __forceinline__ void block_mma_smem(const WTile<Q>& w, int b, const uint4* bsm, bool bvalid,
-                                               float (&acc)[4]) {
-    uint32_t a_lo[4], a_hi[4];
-    unpack_block<Q>(w, b, a_lo, a_hi);
-    const float2 sc = block_scales<Q>(w, b);
-    uint4 bf = make_uint4(0u, 0u, 0u, 0u);
-    if (bvalid) bf = bsm[b * 4];
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
-    if (Q == BF16) {
-        mma_bf16(c, a_lo, bf.x, bf.y);
-        mma_bf16(c, a_hi, bf.z, bf.w);
-    } else {
-        mma_f16(c, a_lo, bf.x, bf.y);
-        mma_f16(c, a_hi, bf.z, bf.w);
-    }
-    acc[0] = fmaf(sc.x, c[0], acc[0]);
-    acc[1] = fmaf(sc.x, c[1], acc[1]);
-    acc[2] = fmaf(sc.y, c[2], acc[2]);
-    acc[3] = fmaf(sc.y, c[3], acc[3]);
-}
-
 }  // namespace
 
 template <int Q>
@@ -87,9 +52,9 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
     constexpr int WARPS = SmallCfg<Q>::GU_WARPS, ITERS = SmallCfg<Q>::GU_ITERS;
     extern __shared__ uint4 xs[];  // [4 columns][2][nblk_pad][4]
     __shared__ float red[WARPS][16][4][2];
-    pdl_wait_();
+    pdl_wait();
     // the router has completed: everything the next kernel reads before ITS wait is final
-    pdl_trigger_();
+    pdl_trigger();
     const int u = blockIdx.y;
     const int4 wd = a.R.work[2 * u];
     if (wd.x < 0) return;
@@ -125,10 +90,10 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
     for (int j = 0; j < 4; ++j) {
         if (j < ncol) {
             const uint4* src = a.xf + (size_t)toks[j] * per_col;
-            for (int i = tid; i < per_col; i += WARPS * 32) cp_async16_(&xs[j * per_col + i], src + i);
+            for (int i = tid; i < per_col; i += WARPS * 32) cp_async16(&xs[j * per_col + i], src + i);
         }
     }
-    cp_async_wait_all_();
+    cp_async_wait_all();
     __syncthreads();
 
     const int jcol = gq >> 1;
@@ -165,23 +130,7 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
             const int col = c0 + tokc;
             const int irow = rt * 16 + row;
             if (a.s_f32 != nullptr) a.s_f32[(size_t)col * I + irow] = sv;
-            unsigned short hi_bits, lo_bits;
-            if (Q != BF16) {
-                const __half h = __float2half_rn(sv);
-                const __half l = __float2half_rn(sv - __half2float(h));
-                hi_bits = __half_as_ushort(h);
-                lo_bits = __half_as_ushort(l);
-            } else {
-                const __nv_bfloat16 h = __float2bfloat16_rn(sv);
-                const __nv_bfloat16 l = __float2bfloat16_rn(sv - __bfloat162float(h));
-                hi_bits = __bfloat16_as_ushort(h);
-                lo_bits = __bfloat16_as_ushort(l);
-            }
-            const int blk = irow >> 5, within = irow & 31, j = within >> 4, r16 = within & 15;
-            unsigned short* sf16 = reinterpret_cast<unsigned short*>(a.sf);
-            const size_t in_vec = (size_t)j * 4 + frag_pos_(r16);
-            sf16[(((size_t)(col * 2 + 0) * nblk_i_pad + blk) * 4 + (r16 >> 2)) * 8 + in_vec] = hi_bits;
-            sf16[(((size_t)(col * 2 + 1) * nblk_i_pad + blk) * 4 + (r16 >> 2)) * 8 + in_vec] = lo_bits;
+            store_swiglu_frag<Q>(a.sf, col, irow, nblk_i_pad, sv);
         }
     }
 }
@@ -218,11 +167,11 @@ down_small_kernel(const __grid_constant__ DecodeArgs a) {
     for (int i = 0; i < RB; ++i)
         if (i < nitems) load_item(i, ring[i]);
 
-    pdl_wait_();
-    pdl_trigger_();
+    pdl_wait();
+    pdl_trigger();
     // stage all SwiGLU fragments (written by the gate/up kernel)
-    for (int i = tid; i < C * per_col; i += DS_WARPS * 32) cp_async16_(&ss[i], a.sf + i);
-    cp_async_wait_all_();
+    for (int i = tid; i < C * per_col; i += DS_WARPS * 32) cp_async16(&ss[i], a.sf + i);
+    cp_async_wait_all();
     __syncthreads();
 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};

@@ -31,6 +31,11 @@
 #else
 #define LUMEN_HD static inline
 #endif
+#if defined(__CUDACC__)
+#define LUMEN_HD_MEMBER __host__ __device__ __forceinline__
+#else
+#define LUMEN_HD_MEMBER inline
+#endif
 
 namespace lumen_exact {
 
@@ -59,7 +64,17 @@ LUMEN_HD uint64_t exp2_tab(int i) {
 #endif
 }
 
-LUMEN_HD float expf_libm(float x) {
+struct Exp2TabDefault {
+    LUMEN_HD_MEMBER uint64_t operator()(int i) const { return exp2_tab(i); }
+};
+// table held by the caller (a copy in shared memory: lanes index it divergently)
+struct Exp2TabPtr {
+    const uint64_t* p;
+    LUMEN_HD_MEMBER uint64_t operator()(int i) const { return p[i]; }
+};
+
+template <typename Tab>
+LUMEN_HD float expf_libm_tab(float x, Tab tab) {
     uint32_t xb;
     memcpy(&xb, &x, 4);
     const uint32_t ax = xb & 0x7fffffffu;
@@ -83,7 +98,7 @@ LUMEN_HD float expf_libm(float x) {
     memcpy(&ki, &kd, 8);
     kd -= shift;
     const double r = z - kd;
-    uint64_t t = exp2_tab((int)(ki & 31u));
+    uint64_t t = tab((int)(ki & 31u));
     t += ki << 47;
     double s;
     memcpy(&s, &t, 8);
@@ -94,5 +109,9 @@ LUMEN_HD float expf_libm(float x) {
     y = y * s;
     return (float)y;
 }
+
+LUMEN_HD float expf_libm(float x) { return expf_libm_tab(x, Exp2TabDefault()); }
+
+LUMEN_HD uint64_t exp2_tab_entry(int i) { return exp2_tab(i); }
 
 }  // namespace lumen_exact

@@ -196,7 +196,7 @@ Status allocate_moe_scratch(int device, int H, int I, int E, int K, int gating, 
     s.K = K;
     s.gating = gating;
     const size_t fixed = align_up((size_t)(E + 1) * 4, 256) + align_up((size_t)E * 4, 256) + 256 * 4 +
-                         (size_t)MAX_EXPERTS * 2 * sizeof(int4);
+                         (size_t)MAX_EXPERTS * 2 * sizeof(int4) + 1024 * 4;
     CUDA_TRY(cudaMalloc(&s.arena, fixed));
     CUDA_TRY(cudaMemset(s.arena, 0, fixed));
     uint8_t* b = static_cast<uint8_t*>(s.arena);
@@ -209,6 +209,9 @@ Status allocate_moe_scratch(int device, int H, int I, int E, int K, int gating, 
     s.n_tiles = reinterpret_cast<int32_t*>(b + 512);
     s.status = reinterpret_cast<int32_t*>(b + 768);
     s.R.work = reinterpret_cast<int4*>(b + 1024);
+    s.bar = reinterpret_cast<unsigned int*>(b + 1024 + (size_t)MAX_EXPERTS * 2 * sizeof(int4));  // 1024 per-CTA flags
+    const char* dimpl = std::getenv("LUMEN_MOE_DECODE_IMPL");
+    s.decode_impl = (dimpl && std::strcmp(dimpl, "split") == 0) ? 1 : 0;
     const char* impl = std::getenv("LUMEN_MOE_PREFILL_IMPL");
     s.prefill_impl = (impl && std::strcmp(impl, "mma") == 0) ? 1 : 0;
     const int cap = max_tokens > DECODE_MAX_TOKENS ? max_tokens : DECODE_MAX_TOKENS;
@@ -268,6 +271,9 @@ static DecodeArgs make_decode_args(CudaMoeScratch* s, const MoeLayer& layer, int
     a.K = s->K;
     a.gating = s->gating;
     a.logits_override = s->logits_override;
+    a.bar = (s->decode_impl == 0) ? s->bar : nullptr;
+    a.status = s->status;
+    a.trace = nullptr;
     return a;
 }
 

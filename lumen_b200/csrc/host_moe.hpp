@@ -101,6 +101,8 @@ struct CudaMoeScratch {
     DecodeArgs last_decode{};   // arguments of the most recent decode call (instrumentation)
     bool has_last_decode = false;
     int prefill_impl = 0;
+    int decode_impl = 0;            // 0 = fused persistent kernel where it applies, 1 = three-kernel chain
+    unsigned int* bar = nullptr;    // grid barrier words of the fused decode kernel
     void* arena = nullptr;       // one allocation for the fixed-size part
     void* arena_tok = nullptr;   // one allocation for the token-sized part
     size_t arena_tok_bytes = 0;

@@ -88,6 +88,9 @@ struct DecodeArgs {
     uint4* sf;              // SwiGLU fragments     [C][2][kg_i*4][4]
     float* s_f32;           // optional [C,I] f32 copy of the SwiGLU output (null = skip)
     int T, K, gating;
+    unsigned int* bar;      // grid barrier of the fused kernel: arrival counter + per-CTA barrier counts (1024 words); null = three-kernel chain
+    int32_t* status;        // context status word (non-zero after a bounded wait expired)
+    unsigned long long* trace;  // optional [grid][12] globaltimer stamps of the fused kernel's phases (null = off)
 };
 
 // launchers (kernels.cu files)
@@ -96,6 +99,8 @@ cudaError_t launch_repack(const uint8_t* blob, const uint64_t* d_gate_offs, cons
                           cudaStream_t st);
 cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t st);
 cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st);
+bool decode_fused_applicable(const DecodeArgs& a);
+cudaError_t launch_decode_fused(const DecodeArgs& a, cudaStream_t st);
 cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st);  // router + tables only (T<=16)
 cudaError_t launch_quantize(const float* src, int64_t n, int quant, void* dst, cudaStream_t st);
 cudaError_t launch_rmsnorm(const float* x, const float* gamma, float* out, int T, int H, float eps,

@@ -252,13 +252,12 @@ topk_large_kernel(const float* __restrict__ logits, int T, int E, int K, int gat
                   uint32_t* __restrict__ ids, float* __restrict__ weights) {
     __shared__ __align__(16) float p_s[TK_WARPS][MAX_EXPERTS];
     __shared__ __align__(16) float lg_s[TK_WARPS][MAX_EXPERTS];
-    __shared__ float sel_s[TK_WARPS][MAX_TOP_K];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * TK_WARPS + warp;
     if (t >= T) return;
     for (int i = lane; i < E; i += 32) lg_s[warp][i] = logits[(size_t)t * E + i];
     __syncwarp();
-    warp_topk(lg_s[warp], E, K, gating, p_s[warp], sel_s[warp], ids + (size_t)t * K, weights + (size_t)t * K);
+    warp_topk(lg_s[warp], E, K, gating, p_s[warp], nullptr, ids + (size_t)t * K, weights + (size_t)t * K);
 }
 
 // ---------------------------------------------------------------------------

@@ -7,8 +7,8 @@
 //   sum   = p[0] + p[1] + ...                 (sequential f32, e ascending)
 //   p[e] /= sum                               (IEEE division)
 //   K rounds of argmax with strict '>' (the lowest index wins a tie), the winner
-//          masked to -1: done here as a warp-shuffle argmax on (value, index) with
-//          the explicit lower-index tie-break of cuda/shaders/topk_moe_fused.cu:251
+//          masked: done here as two warp reductions per round (largest value, then the
+//          lowest index holding it: the tie-break of cuda/shaders/topk_moe_fused.cu:251)
 //   renorm = sel[0] + sel[1] + ...            (sequential f32, k ascending)
 //   w[k]  = sel[k] / renorm  if renorm > 0
 // SIGMOID_RENORM (cuda/shaders/topk_moe_fused.cu:118-129) replaces the first four
@@ -20,96 +20,139 @@
 
 namespace lumen {
 
-// smem_p: E floats (E <= 256), private to the calling warp. out_ids / out_w may
-// point to global or shared memory; lane k (< K) also returns ids[k] in *my_id.
-__device__ __forceinline__ void warp_topk(const float* __restrict__ logits, int E, int K, int gating,
-                                          float* smem_p, float* /*unused*/, uint32_t* out_ids,
-                                          float* out_w) {
+// smem_p: E floats (E <= 256), 16-byte aligned, private to the calling warp. `tab` is
+// a copy of the 32-entry exp table in shared memory, or null for the library's own
+// copy (lanes index the table divergently, which a generic load handles better than
+// the constant cache). out_ids / out_w may point to global or shared memory.
+//
+// The chain of dependent operations is what costs here, so: the sequential sum runs
+// on every lane redundantly from shared memory, sixteen values per step with the next
+// sixteen already loading; each selection round is two warp reductions (redux.sync):
+// the largest key, then the lowest index holding it. Keys are the probability's bit
+// pattern + 1 (probabilities are >= 0, so unsigned order is value order); 0 marks
+// padding and already selected experts.
+//
+// Double-precision instructions issue slowly on this part, and the exp is the only
+// place that needs them, so the exps of one token can be shared by `nsub` warps
+// (warp_gate_probs with sub = 0..nsub-1, the caller synchronises them) before one
+// warp finishes the token (warp_select). warp_topk is the one-warp form.
+
+// Unnormalised gate values into smem_p[e] for the experts of this warp's share:
+// 32-expert group (e >> 5) belongs to sub-warp (e >> 5) % nsub. Softmax: exp(logit - max);
+// sigmoid: the final 1 / (1 + exp(-logit)). `logits` may be shared or global memory.
+__device__ __forceinline__ void warp_gate_probs(const float* __restrict__ logits, int E, int gating, float* smem_p,
+                                                const unsigned long long* tab, int sub, int nsub) {
     const int lane = threadIdx.x & 31;
-    float pe[8];  // expert e = lane + 32*i
-    if (gating == 0) {
-        float m = -INFINITY;
+    const lumen_exact::Exp2TabPtr et{tab != nullptr ? reinterpret_cast<const uint64_t*>(tab)
+                                                    : lumen_exact::exp2_tab_dev};
+    float lg[8];  // expert e = lane + 32*i
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int e = lane + 32 * i;
-            pe[i] = (e < E) ? logits[e] : -INFINITY;
-            m = fmaxf(m, pe[i]);
-        }
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        lg[i] = (e < E) ? logits[e] : -INFINITY;
+    }
+    float m = 0.0f;
+    if (gating == 0) {
+        m = lg[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) m = fmaxf(m, lg[i]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int e = lane + 32 * i;
-            if (e < E) {
-                pe[i] = lumen_exact::expf_libm(pe[i] - m);
-                smem_p[e] = pe[i];
-            }
-        }
-        __syncwarp();
-        float sum = 0.0f;
-        if (lane == 0) {
-            int e = 0;
-            for (; e + 4 <= E; e += 4) {
-                const float4 v = *reinterpret_cast<const float4*>(smem_p + e);
-                sum = __fadd_rn(sum, v.x);
-                sum = __fadd_rn(sum, v.y);
-                sum = __fadd_rn(sum, v.z);
-                sum = __fadd_rn(sum, v.w);
-            }
-            for (; e < E; ++e) sum = __fadd_rn(sum, smem_p[e]);
-        }
-        sum = __shfl_sync(0xffffffffu, sum, 0);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) pe[i] = (lane + 32 * i < E) ? __fdiv_rn(pe[i], sum) : -2.0f;
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int e = lane + 32 * i;
-            pe[i] = (e < E) ? __fdiv_rn(1.0f, __fadd_rn(1.0f, lumen_exact::expf_libm(-logits[e]))) : -2.0f;
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        if (e < E && (i % nsub) == sub) {
+            const float ex = lumen_exact::expf_libm_tab((gating == 0) ? lg[i] - m : -lg[i], et);
+            smem_p[e] = (gating == 0) ? ex : __fdiv_rn(1.0f, __fadd_rn(1.0f, ex));
         }
     }
-    float my_sel = 0.0f;  // lane k keeps the k-th selected probability
+}
+
+// Normalisation (softmax), K selection rounds and renormalised weights from the gate
+// values in smem_p (all E of them visible to this warp).
+__device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, int gating, uint32_t* out_ids,
+                                            float* out_w) {
+    const int lane = threadIdx.x & 31;
+    float pe[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pe[i] = (lane + 32 * i < E) ? smem_p[lane + 32 * i] : 0.0f;
+    if (gating == 0) {
+        float sum = 0.0f;
+        const int E16 = E & ~15;
+        int e = 0;
+        if (E16 > 0) {
+            const float4* p4 = reinterpret_cast<const float4*>(smem_p);
+            float4 c0 = p4[0], c1 = p4[1], c2 = p4[2], c3 = p4[3];
+#pragma unroll 1
+            for (; e < E16; e += 16) {
+                float4 n0 = c0, n1 = c1, n2 = c2, n3 = c3;
+                if (e + 16 < E16) {
+                    const float4* q4 = p4 + ((e + 16) >> 2);
+                    n0 = q4[0];
+                    n1 = q4[1];
+                    n2 = q4[2];
+                    n3 = q4[3];
+                }
+                sum = __fadd_rn(sum, c0.x); sum = __fadd_rn(sum, c0.y); sum = __fadd_rn(sum, c0.z); sum = __fadd_rn(sum, c0.w);
+                sum = __fadd_rn(sum, c1.x); sum = __fadd_rn(sum, c1.y); sum = __fadd_rn(sum, c1.z); sum = __fadd_rn(sum, c1.w);
+                sum = __fadd_rn(sum, c2.x); sum = __fadd_rn(sum, c2.y); sum = __fadd_rn(sum, c2.z); sum = __fadd_rn(sum, c2.w);
+                sum = __fadd_rn(sum, c3.x); sum = __fadd_rn(sum, c3.y); sum = __fadd_rn(sum, c3.z); sum = __fadd_rn(sum, c3.w);
+                c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+            }
+        }
+#pragma unroll 1
+        for (; e < E; ++e) sum = __fadd_rn(sum, smem_p[e]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (lane + 32 * i < E) pe[i] = __fdiv_rn(pe[i], sum);
+    }
+    unsigned key[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) key[i] = (lane + 32 * i < E) ? __float_as_uint(pe[i]) + 1u : 0u;
+    float my_sel = 0.0f, renorm = 0.0f;
     int my_id = 0;
+#pragma unroll 1
     for (int k = 0; k < K; ++k) {
-        // local best: strict '>' in ascending index order keeps the lowest index among equals
-        float bv = -1.0f;
-        int bi = 0x7fffffff;
+        // own best: ascending scan with strict '>' keeps the lowest index among equals
+        unsigned hk = key[0];
+        int hi = 0;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (pe[i] > bv) {
-                bv = pe[i];
-                bi = lane + 32 * i;
+        for (int i = 1; i < 8; ++i) {
+            if (key[i] > hk) {
+                hk = key[i];
+                hi = i;
             }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) {
-                bv = ov;
-                bi = oi;
-            }
+        const unsigned mk = __reduce_max_sync(0xffffffffu, hk);
+        int win = __reduce_min_sync(0xffffffffu, (hk == mk) ? lane + 32 * hi : 0x7fffffff);
+        float sel = __uint_as_float(mk - 1u);
+        if (mk == 0u) {  // nothing left: the reference's fold starts at (index 0, -1.0)
+            win = 0;
+            sel = -1.0f;
         }
-        if (bi == 0x7fffffff) bi = 0;  // nothing above -1: the reference's fold starts at (0, -1.0)
+        renorm = __fadd_rn(renorm, sel);  // sel[0] + sel[1] + ... in order, on every lane
         if (lane == k) {
-            my_sel = bv;
-            my_id = bi;
+            my_sel = sel;
+            my_id = win;
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-            if (lane + 32 * i == bi) pe[i] = -1.0f;  // mask the winner
-    }
-    // renorm = sel[0] + sel[1] + ... in order, on lane 0
-    float renorm = 0.0f;
-    for (int k = 0; k < K; ++k) {
-        const float s = __shfl_sync(0xffffffffu, my_sel, k);
-        renorm = __fadd_rn(renorm, s);
+            if (lane + 32 * i == win) key[i] = 0u;
     }
     if (lane < K) {
         out_ids[lane] = (uint32_t)my_id;
         out_w[lane] = (renorm > 0.0f) ? __fdiv_rn(my_sel, renorm) : my_sel;
     }
     __syncwarp();
+}
+
+__device__ __forceinline__ void warp_topk(const float* __restrict__ logits, int E, int K, int gating,
+                                          float* smem_p, const unsigned long long* tab, uint32_t* out_ids,
+                                          float* out_w) {
+    warp_gate_probs(logits, E, gating, smem_p, tab, 0, 1);
+    __syncwarp();
+    warp_select(smem_p, E, K, gating, out_ids, out_w);
 }
 
 }  // namespace lumen

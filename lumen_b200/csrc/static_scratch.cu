@@ -63,7 +63,6 @@ route_small_static_kernel(const float* __restrict__ logits, int T, int E, int K,
                           int32_t* __restrict__ scratch) {
     __shared__ __align__(16) float p_s[8][MAX_EXPERTS];
     __shared__ __align__(16) float lg_s[8][MAX_EXPERTS];
-    __shared__ float sel_s[8][MAX_TOP_K];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int32_t* counts = scratch + RS_OFF_COUNTS;
     int32_t* bounds = scratch + RS_OFF_BOUNDS;
@@ -73,7 +72,7 @@ route_small_static_kernel(const float* __restrict__ logits, int T, int E, int K,
     for (int t = warp; t < T; t += 8) {
         for (int i = lane; i < E; i += 32) lg_s[warp][i] = logits[(size_t)t * E + i];
         __syncwarp();
-        warp_topk(lg_s[warp], E, K, gating, p_s[warp], sel_s[warp], ids_out + (size_t)t * K, w_out + (size_t)t * K);
+        warp_topk(lg_s[warp], E, K, gating, p_s[warp], nullptr, ids_out + (size_t)t * K, w_out + (size_t)t * K);
         if (lane < K) {
             const int e = (int)ids_out[(size_t)t * K + lane];
             ids_g[t * K + lane] = e;

@@ -260,6 +260,13 @@ class MoeScratch:
                                                cst.ctypes.data, bounds.ctypes.data, _stream()))
         return {"ids": ids, "weights": w, "dst_to_col": d2c, "col_src_tok": cst, "expert_bounds": bounds}
 
+    def debug_decode_trace(self, layer):
+        """Per-CTA phase stamps (ns) of the fused decode kernel for the last decode call: int64 [SMs, 12]."""
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        tr = torch.zeros((sms, 12), dtype=torch.int64, device=f"cuda:{self.device}")
+        check(_lib.lib().lumen_moe_debug_decode_trace(self._h, layer._h, tr.data_ptr(), _stream()))
+        return tr
+
     def debug_decode_phase(self, layer: MoeLayer, phase: int) -> None:
         check(_lib.lib().lumen_moe_debug_decode_phase(self._h, layer._h, phase, _stream()))
 

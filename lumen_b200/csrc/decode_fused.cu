@@ -22,8 +22,8 @@
 //            combine in slot order + residual
 //            (moe_expert_q4_0.cu:118-151; cuda/shaders/moe_accum.cu:22-46)
 //
-// The barrier is an arrive counter plus a generation word, both left ready for the
-// next launch; every wait is bounded (one second), after which the kernel raises the
+// The barrier is an arrival counter that only grows, so nothing is reset between
+// launches; every wait is bounded (one second), after which the kernel raises the
 // context's status word and every CTA returns.
 #include "decode_common.cuh"
 #include "router.cuh"
@@ -62,13 +62,16 @@ __device__ __forceinline__ void red_release_add_u32(unsigned* p, unsigned v) {
 // Grid barrier: one arrival counter that only grows (bar[0]); barrier number `epoch`
 // (counted per CTA in bar[1 + cta], written by that CTA alone) is passed when the
 // counter reaches epoch * G, compared modulo 2^32, so nothing is reset between
-// launches. One fire-and-forget reduction to arrive, one thread per CTA polls.
+// launches. Arriving is one fire-and-forget reduction by thread 0 (call it after a
+// __syncthreads that follows the CTA's last store); one thread per CTA polls.
+__device__ __forceinline__ void grid_arrive(unsigned* bar) {
+    if (threadIdx.x == 0) red_release_add_u32(bar, 1u);
+}
+
 // Returns false when the wait expired (one second) or another CTA already raised the
 // status word.
-__device__ __forceinline__ bool grid_barrier(unsigned* bar, int* status, int G, unsigned epoch, int* fail_s) {
-    __syncthreads();
+__device__ __forceinline__ bool grid_wait(unsigned* bar, int* status, int G, unsigned epoch, int* fail_s) {
     if (threadIdx.x == 0) {
-        red_release_add_u32(bar, 1u);
         const unsigned target = epoch * (unsigned)G;
         unsigned long long t0 = 0;
         unsigned spins = 0;
@@ -90,6 +93,20 @@ __device__ __forceinline__ bool grid_barrier(unsigned* bar, int* status, int G, 
     }
     __syncthreads();
     return *fail_s == 0;
+}
+
+// Waits until at most n of this thread's cp.async groups are still pending.
+__device__ __forceinline__ void cp_async_wait_pending(int n) {
+    switch (n) {
+        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
+        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
+        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
+        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
+        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
+        case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
+        case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
+        default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+    }
 }
 
 template <int Q>
@@ -121,7 +138,7 @@ struct TopkSm {
 
 template <int Q>
 __global__ void __launch_bounds__(FT, 1)
-decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots) {
+decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, const int gs_slots) {
     extern __shared__ uint4 dyn[];
     __shared__ __align__(16) TopkSm ts;
     __shared__ float red_a[FW][FMAX_T];
@@ -153,7 +170,11 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots) {
     uint4* xs = dyn;                                  // [T][per_col]
     uint4* ss = xs + (size_t)T * per_col;             // [C][per_col_i]
     float* part = reinterpret_cast<float*>(ss + (size_t)C * per_col_i);  // [C * kg_i][4 cols][16 rows]
-    uint4* pf = reinterpret_cast<uint4*>(part + (size_t)C * kg_i * 64);  // [FW][pf_slots][TU4]
+    float* wd = part + (size_t)C * kg_i * 64;         // [C][16] weighted expert outputs
+    // the f32 activations of phase A share the ss/part/wd region, whichever is larger
+    const size_t mid_bytes = max((size_t)C * per_col_i * 16 + (size_t)C * kg_i * 256 + (size_t)C * 64, (size_t)T * H * 4);
+    uint4* pf = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(ss) + mid_bytes);  // [FW][pf_slots][TU4]
+    uint4* gs = pf + (size_t)FW * pf_slots * TU4;     // [gs_slots][FW][gate, up][TU4] staged gate/up tiles
 
     // ---------------- phase A ----------------
     // first router row in registers before waiting on the previous kernel (weights are static)
@@ -162,79 +183,86 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots) {
         wv = __ldg(reinterpret_cast<const float4*>(a.L.router_w + (size_t)cta * H) + tid);
     pdl_wait();
     stamp(1);
-    if (*reinterpret_cast<volatile int*>(a.status) != 0) return;  // an earlier launch gave up: do not touch the barrier
+    // Thread i holds inputs 4i..4i+3 of every token (H <= 4 * FT): they feed the router
+    // dot products straight from registers; the status word and this CTA's barrier count
+    // are requested in the same round trip.
+    float4 xv[FMAX_T];
+#pragma unroll
+    for (int t = 0; t < FMAX_T; ++t)
+        xv[t] = (t < T && tid < H4) ? reinterpret_cast<const float4*>(a.x)[t * H4 + tid] : make_float4(0.f, 0.f, 0.f, 0.f);
+    const int status_now = *reinterpret_cast<volatile int*>(a.status);
     unsigned epoch = *reinterpret_cast<volatile unsigned*>(a.bar + 1 + cta);  // barriers this CTA has passed so far
+    if (status_now != 0) return;  // an earlier launch gave up: do not touch the barrier
 
-    // normalised activations of all tokens, f32, in shared memory (the region is reused for
-    // the SwiGLU fragments and partial sums, which are written only after the routing)
+    // normalised activations of all tokens, f32, in shared memory for the fragment build (the
+    // region is reused for the SwiGLU fragments and partial sums, written only after the routing)
     float4* xn4 = reinterpret_cast<float4*>(ss);
     if (a.gamma != nullptr) {
-#pragma unroll 1
-        for (int t = 0; t < T; ++t) {
-            const float4* xr = reinterpret_cast<const float4*>(a.x + (size_t)t * H);
-            float sq = 0.0f;
-#pragma unroll 1
-            for (int i4 = tid; i4 < H4; i4 += FT) {
-                const float4 v = xr[i4];
-                sq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-            }
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-            if (lane == 0) red_a[warp][t] = sq;
+        for (int t = 0; t < FMAX_T; ++t) {
+            if (t < T) {
+                float sq = xv[t].x * xv[t].x + xv[t].y * xv[t].y + xv[t].z * xv[t].z + xv[t].w * xv[t].w;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (lane == 0) red_a[warp][t] = sq;
+            }
         }
         __syncthreads();
         if (tid < T) {
             float sq = 0.0f;
-#pragma unroll 1
+#pragma unroll
             for (int w = 0; w < FW; ++w) sq += red_a[w][tid];
             scale_s[tid] = 1.0f / sqrtf(sq / (float)H + a.eps);
         }
         __syncthreads();
-    }
-#pragma unroll 1
-    for (int i = tid; i < T * H4; i += FT) {
-        float4 v = reinterpret_cast<const float4*>(a.x)[i];
-        if (a.gamma != nullptr) {
-            const int t = i / H4;
-            const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + (i - t * H4));
-            const float sc = scale_s[t];
-            v.x = v.x * sc * g.x;
-            v.y = v.y * sc * g.y;
-            v.z = v.z * sc * g.z;
-            v.w = v.w * sc * g.w;
-            if (a.normed_out != nullptr && (i % G) == cta) reinterpret_cast<float4*>(a.normed_out)[i] = v;
+        if (tid < H4) {
+            const float4 g = __ldg(reinterpret_cast<const float4*>(a.gamma) + tid);
+#pragma unroll
+            for (int t = 0; t < FMAX_T; ++t) {
+                if (t < T) {
+                    const float sc = scale_s[t];
+                    xv[t].x = xv[t].x * sc * g.x;
+                    xv[t].y = xv[t].y * sc * g.y;
+                    xv[t].z = xv[t].z * sc * g.z;
+                    xv[t].w = xv[t].w * sc * g.w;
+                    if (a.normed_out != nullptr && (tid % G) == cta)
+                        reinterpret_cast<float4*>(a.normed_out)[t * H4 + tid] = xv[t];
+                }
+            }
         }
-        xn4[i] = v;
     }
-    __syncthreads();
+#pragma unroll
+    for (int t = 0; t < FMAX_T; ++t)
+        if (t < T && tid < H4) xn4[t * H4 + tid] = xv[t];
 
     if (want_logits) {
 #pragma unroll 1
         for (int e = cta; e < E; e += G) {
-            const float4* wrow = reinterpret_cast<const float4*>(a.L.router_w + (size_t)e * H);
-#pragma unroll 1
-            for (int t = 0; t < T; ++t) {
-                float acc = 0.0f;
-#pragma unroll 1
-                for (int i4 = tid; i4 < H4; i4 += FT) {
-                    const float4 w4 = (e == cta && i4 == tid) ? wv : __ldg(wrow + i4);
-                    const float4 xv = xn4[t * H4 + i4];
-                    acc += w4.x * xv.x + w4.y * xv.y + w4.z * xv.z + w4.w * xv.w;
-                }
+            float4 w4 = wv;
+            if (e != cta && tid < H4) w4 = __ldg(reinterpret_cast<const float4*>(a.L.router_w + (size_t)e * H) + tid);
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (lane == 0) red_a[warp][t] = acc;
+            for (int t = 0; t < FMAX_T; ++t) {
+                if (t < T) {
+                    float acc = w4.x * xv[t].x + w4.y * xv[t].y + w4.z * xv[t].z + w4.w * xv[t].w;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    if (lane == 0) red_a[warp][t] = acc;
+                }
             }
             __syncthreads();
             if (tid < T) {
                 float v = 0.0f;
-#pragma unroll 1
+#pragma unroll
                 for (int w = 0; w < FW; ++w) v += red_a[w][tid];
                 a.R.logits[(size_t)tid * E + e] = v;
             }
             __syncthreads();
         }
     }
+    // logits are out (the loop above ends on a CTA barrier): arrive now, build the
+    // activation fragments while the other CTAs catch up
+    __syncthreads();
+    if (want_logits) grid_arrive(a.bar);
     // activation fragments of every token, private to this CTA
     {
         const bool bf16_mode = (Q == BF16);
@@ -256,7 +284,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots) {
     }
     stamp(2);
     if (want_logits) {
-        if (!grid_barrier(a.bar, a.status, G, ++epoch, &fail_s)) return;
+        if (!grid_wait(a.bar, a.status, G, ++epoch, &fail_s)) return;
     } else {
         __syncthreads();
     }
@@ -343,8 +371,31 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots) {
             load_wtile<Q>(up, a.L.up_q(e), a.L.up_s(e), rt * kg_h + warp, lane);
         }
     };
+    // Every byte this CTA will need is requested now: the tiles of its first gs_slots
+    // items go to shared memory with cp.async (one commit group per item), the first
+    // item beyond those (if any) to registers; then the down tiles (last group).
+    auto stage_tile = [&](uint4* slot, const uint4* qbase, const uint4* sbase, int tile) {
+        const uint4* qp = qbase + ((size_t)tile * QTraits<Q>::NQ) * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(slot + j * 32 + lane, qp + j * 32);
+        if (Q != BF16 && lane < 8) cp_async16(slot + QTraits<Q>::NQ * 32 + lane, sbase + (size_t)tile * 8 + lane);
+    };
+    const int n_my = (it0 < n_items) ? (n_items - it0 + G - 1) / G : 0;
+    const int n_st = min(n_my, gs_slots);
+#pragma unroll 1
+    for (int j = 0; j < n_st; ++j) {
+        const int it = it0 + j * G;
+        const int u = it / rt_i, rt = it - u * rt_i;
+        const int e = rs.ue[u];
+        if (warp < kg_h) {
+            uint4* slot = gs + ((size_t)(j * FW + warp) * 2) * TU4;
+            stage_tile(slot, a.L.gate_q(e), a.L.gate_s(e), rt * kg_h + warp);
+            stage_tile(slot + TU4, a.L.up_q(e), a.L.up_s(e), rt * kg_h + warp);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     WTile<Q> wg0, wu0, wg1, wu1;
-    if (it0 < n_items) load_gu(it0, wg0, wu0);
+    if (n_st < n_my) load_gu(it0 + n_st * G, wg1, wu1);
 
     // down tiles of this CTA's output rows: request the first pf_slots items of every warp now
     const bool has_down = cta < a.L.rt_h;
@@ -355,16 +406,11 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots) {
             if (n < n_down) {
                 const int uu = n / kg_i, kg = n - uu * kg_i;
                 const int ee = rs.ue[uu];
-                const int tile = cta * kg_i + kg;
-                uint4* slot = pf + ((size_t)warp * pf_slots + i) * TU4;
-                const uint4* qp = a.L.down_q(ee) + ((size_t)tile * QTraits<Q>::NQ) * 32 + lane;
-#pragma unroll
-                for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(slot + j * 32 + lane, qp + j * 32);
-                if (Q != BF16 && lane < 8)
-                    cp_async16(slot + QTraits<Q>::NQ * 32 + lane, a.L.down_s(ee) + (size_t)tile * 8 + lane);
+                stage_tile(pf + ((size_t)warp * pf_slots + i) * TU4, a.L.down_q(ee), a.L.down_s(ee), cta * kg_i + kg);
             }
         }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
 
     // gate/up + SwiGLU
     auto compute_gu = [&](int it, const WTile<Q>& g, const WTile<Q>& up) {
@@ -407,20 +453,31 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots) {
         __syncthreads();
     };
 #pragma unroll 1
-    for (int it = it0; it < n_items; it += G) {
-        const bool more = it + G < n_items;
-        if (more) load_gu(it + G, wg1, wu1);
-        compute_gu(it, wg0, wu0);
-        if (more) {
+    for (int j = 0; j < n_my; ++j) {
+        if (j < n_st) {
+            // item j's group is complete once at most (n_st - 1 - j) + 1 younger groups are pending;
+            // a warp only reads the tiles its own lanes copied
+            cp_async_wait_pending(n_st - j);
+            __syncwarp();
+            if (warp < kg_h) {
+                const uint4* slot = gs + ((size_t)(j * FW + warp) * 2) * TU4;
+                read_staged_tile<Q>(wg0, slot, lane);
+                read_staged_tile<Q>(wu0, slot + TU4, lane);
+            }
+        } else {
             wg0 = wg1;
             wu0 = wu1;
+            if (j + 1 < n_my) load_gu(it0 + (j + 1) * G, wg1, wu1);
         }
+        compute_gu(it0 + j * G, wg0, wu0);
     }
     // residual of this CTA's output rows, requested before the barrier
     float resid = 0.0f;
     if (has_down && tid < 16 * T) resid = a.residual[(size_t)(tid >> 4) * H + cta * 16 + (tid & 15)];
     stamp(5);
-    if (!grid_barrier(a.bar, a.status, G, ++epoch, &fail_s)) {
+    __syncthreads();
+    grid_arrive(a.bar);
+    if (!grid_wait(a.bar, a.status, G, ++epoch, &fail_s)) {
         cp_async_wait_all();
         return;
     }
@@ -436,55 +493,81 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots) {
     cp_async_wait_all();
     __syncthreads();
     stamp(7);
-    for (int rt = cta; rt < a.L.rt_h; rt += G) {
-        for (int i = 0; warp + FW * i < n_down; ++i) {
-            const int n = warp + FW * i;
-            const int uu = n / kg_i, kg = n - uu * kg_i;
-            WTile<Q> w;
-            if (rt == cta && i < pf_slots) {
-                read_staged_tile<Q>(w, pf + ((size_t)warp * pf_slots + i) * TU4, lane);
-            } else {
-                const int ee = rs.ue[uu];
-                load_wtile<Q>(w, a.L.down_q(ee), a.L.down_s(ee), rt * kg_i + kg, lane);
-            }
-            const int c0 = rs.uc0[uu];
-            const int ncol = min(4, rs.uncol[uu]);
-            const int jcol = gq >> 1;
-            const bool bvalid = jcol < ncol;
-            const uint4* bp = ss + ((size_t)((c0 + (bvalid ? jcol : 0)) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4 + (size_t)kg * 16;
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    {
+        // DG tiles of a warp are worked on together: their dependent chains (shared load ->
+        // unpack -> two MMAs -> scale) overlap instead of running one after the other
+        constexpr int DG = (Q == Q4_0) ? 3 : (Q == Q8_0) ? 2 : 1;
+        const int rt = cta;
+#pragma unroll 1
+        for (int i0 = 0; warp + FW * i0 < n_down; i0 += DG) {
+            WTile<Q> w[DG];
+            int nn[DG];
 #pragma unroll
-            for (int b = 0; b < 4; ++b) block_mma_smem<Q>(w, b, bp, bvalid, acc);
-            float* pp = part + (size_t)n * 64 + t4 * 16;
-            pp[gq] = acc[0] + acc[1];
-            pp[gq + 8] = acc[2] + acc[3];
+            for (int j = 0; j < DG; ++j) {
+                const int i = i0 + j;
+                nn[j] = min(warp + FW * i, n_down - 1);
+                if (i < pf_slots) {
+                    read_staged_tile<Q>(w[j], pf + ((size_t)warp * pf_slots + i) * TU4, lane);
+                } else {
+                    const int uu = nn[j] / kg_i, kg = nn[j] - uu * kg_i;
+                    const int ee = rs.ue[uu];
+                    load_wtile<Q>(w[j], a.L.down_q(ee), a.L.down_s(ee), rt * kg_i + kg, lane);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < DG; ++j) {
+                const int uu = nn[j] / kg_i, kg = nn[j] - uu * kg_i;
+                const int c0 = rs.uc0[uu];
+                const int ncol = min(4, rs.uncol[uu]);
+                const int jcol = gq >> 1;
+                const bool bvalid = jcol < ncol;
+                const uint4* bp = ss + ((size_t)((c0 + (bvalid ? jcol : 0)) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4 +
+                                  (size_t)kg * 16;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int b = 0; b < 4; ++b) block_mma_smem<Q>(w[j], b, bp, bvalid, acc);
+                if (warp + FW * (i0 + j) < n_down) {
+                    float* pp = part + (size_t)nn[j] * 64 + t4 * 16;
+                    pp[gq] = acc[0] + acc[1];
+                    pp[gq + 8] = acc[2] + acc[3];
+                }
+            }
         }
         __syncthreads();
         stamp(8);
-        if (tid < 16 * T) {
-            const int row = tid & 15, t = tid >> 4;
-            const size_t o = (size_t)t * H + rt * 16 + row;
-            float accv = (rt == cta) ? resid : a.residual[o];
-            for (int slot = 0; slot < K; ++slot) {
-                const int col = rs.d2c[t * K + slot];
-                const int uu = rs.col_u[col];
-                const int j = min(col - rs.uc0[uu], 3);
-                float d = 0.0f;
-                for (int kg = 0; kg < kg_i; ++kg) d += part[(size_t)(uu * kg_i + kg) * 64 + j * 16 + row];
-                accv = __fadd_rn(accv, __fmul_rn(rs.w[t * K + slot], d));
-            }
-            a.out[o] = accv;
+        // weighted expert outputs of every (token, slot) pair, one (pair, row) per thread ...
+#pragma unroll 1
+        for (int idx = tid; idx < C * 16; idx += FT) {
+            const int pair = idx >> 4, row = idx & 15;
+            const int col = rs.d2c[pair];
+            const int uu = rs.col_u[col];
+            const int j = min(col - rs.uc0[uu], 3);
+            const float* pp = part + (size_t)uu * kg_i * 64 + j * 16 + row;
+            float d = 0.0f;
+#pragma unroll 2
+            for (int kg = 0; kg < kg_i; ++kg) d += pp[kg * 64];
+            wd[idx] = __fmul_rn(rs.w[pair], d);
         }
         __syncthreads();
+        // ... then the sum in slot order on top of the residual (cuda/shaders/moe_accum.cu:22-46)
+        if (tid < 16 * T) {
+            const int row = tid & 15, t = tid >> 4;
+            float accv = resid;
+#pragma unroll 1
+            for (int slot = 0; slot < K; ++slot) accv = __fadd_rn(accv, wd[(t * K + slot) * 16 + row]);
+            a.out[(size_t)t * H + rt * 16 + row] = accv;
+        }
     }
     stamp(9);
 }
 
 // Shared memory the fused kernel needs besides its static arrays; pf_slots = staged down tiles per warp.
-static size_t fused_smem_bytes(const DecodeArgs& a, int tile_u4, int pf_slots) {
+static size_t fused_smem_bytes(const DecodeArgs& a, int tile_u4, int pf_slots, int gs_slots = 0) {
     const size_t C = (size_t)a.T * a.K;
-    return (size_t)a.T * 2 * a.L.kg_h * 16 * 16 + C * 2 * a.L.kg_i * 16 * 16 + C * a.L.kg_i * 256 +
-           (size_t)FW * pf_slots * tile_u4 * 16;
+    const size_t mid = C * 2 * a.L.kg_i * 16 * 16 + C * a.L.kg_i * 256 + C * 64;
+    const size_t xn = (size_t)a.T * a.L.H * 4;
+    return (size_t)a.T * 2 * a.L.kg_h * 16 * 16 + (mid > xn ? mid : xn) + (size_t)FW * pf_slots * tile_u4 * 16 +
+           (size_t)gs_slots * FW * 2 * tile_u4 * 16;
 }
 
 static int tile_u4_of(int quant) {
@@ -529,9 +612,14 @@ static cudaError_t launch_fused_t(const DecodeArgs& a, int device, cudaStream_t 
     const size_t static_smem = 20 * 1024;
     const int C = a.T * a.K;
     const int want = (C * a.L.kg_i + FW - 1) / FW;  // down tiles per warp when every pair has its own expert
+    // shared memory goes to the gate/up items of a CTA first (they are needed first), then to the down tiles
+    const int nu_max = C < a.L.E ? C : a.L.E;
+    int gs = (nu_max * a.L.rt_i + d.sms - 1) / d.sms;
+    if (gs > 7) gs = 7;
+    while (gs > 0 && fused_smem_bytes(a, TileU4<Q>::value, 0, gs) + static_smem > (size_t)d.smem_optin) --gs;
     int pf = want;
-    while (pf > 0 && fused_smem_bytes(a, TileU4<Q>::value, pf) + static_smem > (size_t)d.smem_optin) --pf;
-    const size_t smem = fused_smem_bytes(a, TileU4<Q>::value, pf);
+    while (pf > 0 && fused_smem_bytes(a, TileU4<Q>::value, pf, gs) + static_smem > (size_t)d.smem_optin) --pf;
+    const size_t smem = fused_smem_bytes(a, TileU4<Q>::value, pf, gs);
     static size_t attr_smem[64] = {};
     if (smem > attr_smem[device & 63]) {
         cudaError_t e = cudaFuncSetAttribute(decode_fused_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -555,7 +643,7 @@ static cudaError_t launch_fused_t(const DecodeArgs& a, int device, cudaStream_t 
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     count_launch();
-    return cudaLaunchKernelEx(&cfg, decode_fused_kernel<Q>, a, pf);
+    return cudaLaunchKernelEx(&cfg, decode_fused_kernel<Q>, a, pf, gs);
 }
 
 cudaError_t launch_decode_fused(const DecodeArgs& a, cudaStream_t st) {

@@ -32,6 +32,11 @@ QUANTS = {"q8_0": 0, "q4_0": 1, "bf16": 2}
 BLK = {0: 34, 1: 18, 2: 64}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# capture summarised under profiles/ (kernel, quant, tokens) -> bytes
+NCU_DRAM_BYTES_PER_LAUNCH = {("decode_fused_kernel", "q4_0", 1): 22_372_000}
+
+
 def algorithmic_bytes(T: int, U: int, quant: int) -> int:
     """Compulsory traffic of one layer call: router weight, the three matrices of
     every distinct expert hit, activations in / residual in / output out."""
@@ -208,7 +213,10 @@ def run_gpu(args):
         step()
     # The 3*L launches of a step are replayed from one CUDA graph (the reference's
     # backend enqueues them from Rust; a Python loop would time the interpreter).
-    launches_per_step = 3 * L
+    torch.cuda.synchronize()
+    moe.launch_count(reset=True)
+    step()
+    launches_per_step = moe.launch_count(reset=True)  # L with the fused kernel, 3 L with the three-kernel chain
     step_eager = step
     if not args.no_graph:
         torch.cuda.synchronize()
@@ -244,36 +252,59 @@ def run_gpu(args):
     line = None
     if rank == 0:
         peak, peak_src = peaks()
-        # each kernel of the chain alone, one launch per layer blob, CUDA events on the launch stream
-        # (phase 1 = gate/up + SwiGLU is the dominant kernel)
-        def time_phase(phase, reps=5):
-            def run():
-                for l in range(L):
-                    scratch.debug_decode_phase(layers[l], phase)
-            run()
-            torch.cuda.synchronize()
-            fn = run
-            if not args.no_graph:
-                gph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gph):
-                    run()
-                fn = gph.replay
-                fn()
-            torch.cuda.synchronize()
-            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            ev0.record()
-            for _ in range(reps):
-                fn()
-            ev1.record()
-            torch.cuda.synchronize()
-            return ev0.elapsed_time(ev1) / (reps * L)
-        phase_ms = [time_phase(ph) for ph in (0, 1, 2)]
-        k_ms = phase_ms[1]
-        # routing tables in the context belong to the last layer called: same count of experts for every launch
-        k_bytes = gate_up_bytes(T, U[-1], quant)
-        achieved = k_bytes / (k_ms / 1e3) / 1e9
         layer_bytes = sum(algorithmic_bytes(T, u, quant) for u in U) / L
         layer_gbs = layer_bytes / ((ms / 1e3) / (args.steps * L)) / 1e9
+        fused = launches_per_step == L  # one launch per layer call: the persistent fused kernel ran
+        if fused:
+            # the timed region IS this kernel, launch after launch: average launch duration from the same events
+            k_name = "decode_fused_kernel"
+            k_ms = ms / (args.steps * L)
+            k_bytes = layer_bytes
+            achieved = layer_gbs
+            tr = scratch.debug_decode_trace(layers[L - 1]).cpu().numpy().astype(np.int64)
+            t0 = tr[:, 0].min()
+            med = lambda i: float(np.median((tr[:, i][tr[:, i] > 0] - t0) / 1e3))
+            stamps = [med(i) for i in range(10)]
+            kernel_us = {"decode_fused_kernel": k_ms * 1e3,
+                         "phases_us_median_over_ctas": {
+                             "wait_previous_kernel": stamps[1], "router_logits": stamps[2] - stamps[1],
+                             "grid_barrier_1": stamps[3] - stamps[2], "topk_and_sort": stamps[4] - stamps[3],
+                             "gate_up_swiglu": stamps[5] - stamps[4], "grid_barrier_2": stamps[6] - stamps[5],
+                             "stage_swiglu": stamps[7] - stamps[6], "down": stamps[8] - stamps[7],
+                             "combine": stamps[9] - stamps[8]}}
+        else:
+            # each kernel of the chain alone, one launch per layer blob, CUDA events on the launch stream
+            # (phase 1 = gate/up + SwiGLU is the dominant kernel)
+            def time_phase(phase, reps=5):
+                def run():
+                    for l in range(L):
+                        scratch.debug_decode_phase(layers[l], phase)
+                run()
+                torch.cuda.synchronize()
+                fn = run
+                if not args.no_graph:
+                    gph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gph):
+                        run()
+                    fn = gph.replay
+                    fn()
+                torch.cuda.synchronize()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+                for _ in range(reps):
+                    fn()
+                ev1.record()
+                torch.cuda.synchronize()
+                return ev0.elapsed_time(ev1) / (reps * L)
+            phase_ms = [time_phase(ph) for ph in (0, 1, 2)]
+            k_name = "gate_up_kernel"
+            k_ms = phase_ms[1]
+            # routing tables in the context belong to the last layer called: same count of experts for every launch
+            k_bytes = gate_up_bytes(T, U[-1], quant)
+            achieved = k_bytes / (k_ms / 1e3) / 1e9
+            kernel_us = {"router_small_kernel": phase_ms[0] * 1e3, "gate_up_kernel": phase_ms[1] * 1e3,
+                         "down_combine_kernel": phase_ms[2] * 1e3}
+        traffic = NCU_DRAM_BYTES_PER_LAUNCH.get((k_name, args.quant, T))
         cpu = cpu_reference_leg(quant, T, 12.0, blob0)
         line = {"metric": "moe_layer_decode_tokens_per_s", "value": value, "unit": "layer_tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
@@ -282,11 +313,10 @@ def run_gpu(args):
                 "e2e": {"value": e2e, "unit": "layer_tokens/s", "h2d_bytes_per_step": T * H * 4,
                         "d2h_bytes_per_step": T * H * 4},
                 "gpu_launches": int(launches),
-                "roofline": {"bound": "hbm", "kernel": "gate_up_kernel", "achieved": achieved, "peak": peak,
-                             "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                "roofline": {"bound": "hbm", "kernel": k_name, "achieved": achieved, "peak": peak,
+                             "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                              "algorithmic_bytes_per_launch": k_bytes, "us_per_launch": k_ms * 1e3},
-                "kernel_us": {"router_small_kernel": phase_ms[0] * 1e3, "gate_up_kernel": phase_ms[1] * 1e3,
-                              "down_combine_kernel": phase_ms[2] * 1e3},
+                "kernel_us": kernel_us,
                 "layer_roofline": {"algorithmic_bytes_per_call": layer_bytes, "us_per_call": ms * 1e3 / (args.steps * L),
                                    "achieved_gbs": layer_gbs, "frac_of_measured_peak": layer_gbs / peak,
                                    "frac_of_8tbs": layer_gbs / 8000.0},

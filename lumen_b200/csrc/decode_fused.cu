@@ -126,6 +126,9 @@ struct RouteSm {
     int uc0[FMAX_C];      // first column of the expert
     int uncol[FMAX_C];    // columns of the expert
     int U;
+    int pr_ue[FMAX_C];    // experts with work as predicted from the raw logits, ascending
+    int pr_U;
+    unsigned pr_mask[MAX_EXPERTS / 32];
 };
 
 struct TopkSm {
@@ -291,18 +294,93 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     stamp(3);
 
     // ---------------- phase B: routing (redundantly per CTA) ----------------
+    // The exact gating below takes a few microseconds in which HBM would sit idle. The SET
+    // of selected experts almost always equals the top-K by raw logit (the exp and the
+    // division are monotonic; only probabilities that round to the same value with the
+    // higher logit at the higher index can differ), and the set is all the weight staging
+    // needs. So: rank the raw logits, request every tile for the predicted set, run the
+    // exact gating while the tiles stream, then check the prediction and, if it was wrong,
+    // drain and request again.
+    const int rt_i = a.L.rt_i;
+    const int it0 = G - 1 - cta;  // work items of this CTA: G-1-cta, then every G-th (CTAs without down rows first)
+    const bool has_down = cta < a.L.rt_h;
+    auto stage_tile = [&](uint4* slot, const uint4* qbase, const uint4* sbase, int tile) {
+        const uint4* qp = qbase + ((size_t)tile * QTraits<Q>::NQ) * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(slot + j * 32 + lane, qp + j * 32);
+        if (Q != BF16 && lane < 8) cp_async16(slot + QTraits<Q>::NQ * 32 + lane, sbase + (size_t)tile * 8 + lane);
+    };
+    // Requests every byte this CTA needs for the experts ue[0..nu): the tiles of its first
+    // gs_slots gate/up items (one commit group per item), then the down tiles of its 16
+    // output rows (last group).
+    auto stage_all = [&](const int* ue, int nu, int swarp, int n_swarps) {
+        const int n_items_ = nu * rt_i;
+        const int n_my_ = (it0 < n_items_) ? (n_items_ - it0 + G - 1) / G : 0;
+        const int n_st_ = min(n_my_, gs_slots);
+#pragma unroll 1
+        for (int j = 0; j < n_st_; ++j) {
+            const int it = it0 + j * G;
+            const int u = it / rt_i, rt = it - u * rt_i;
+            const int e = ue[u];
+#pragma unroll 1
+            for (int kg = swarp; kg < kg_h; kg += n_swarps) {
+                uint4* slot = gs + ((size_t)(j * FW + kg) * 2) * TU4;
+                stage_tile(slot, a.L.gate_q(e), a.L.gate_s(e), rt * kg_h + kg);
+                stage_tile(slot + TU4, a.L.up_q(e), a.L.up_s(e), rt * kg_h + kg);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        }
+        if (has_down) {
+            const int n_down_ = min(nu * kg_i, FW * pf_slots);
+#pragma unroll 1
+            for (int n = swarp; n < n_down_; n += n_swarps) {
+                const int uu = n / kg_i, kg = n - uu * kg_i;
+                stage_tile(pf + ((size_t)(n % FW) * pf_slots + n / FW) * TU4, a.L.down_q(ue[uu]), a.L.down_s(ue[uu]),
+                           cta * kg_i + kg);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
     {
-        // four warps per token share the exps, the first of them finishes the token
+        // Four warps per token share the exps; then warp 0 of the four finishes the token
+        // exactly while warp 1 ranks the raw logits. The warps that are not finishing a
+        // token (16 - T of them) then turn the predicted mask into a list and request the tiles.
         const float* lg = want_logits ? a.R.logits : a.logits_override;
         const int tok = warp >> 2, sub = warp & 3;
+        const bool selects = (tok < T) && (sub == 0);
+        const int n_swarps = FW - T;
+        const int swarp = warp - min(T, (warp + 3) >> 2);  // index among the staging warps
+        if (tid < MAX_EXPERTS / 32) rs.pr_mask[tid] = 0u;
+        __syncthreads();
         if (tok < T) {
 #pragma unroll 1
             for (int i = sub * 32 + lane; i < E; i += 128) ts.lg[tok][i] = __ldcg(lg + (size_t)tok * E + i);
             asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
-            warp_gate_probs(ts.lg[tok], E, a.gating, ts.p[tok], ts.tab, sub, 4);
-            asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
-            if (sub == 0)
-                warp_select(ts.p[tok], E, K, a.gating, reinterpret_cast<uint32_t*>(rs.ids) + tok * K, rs.w + tok * K);
+            if (sub == 1) warp_predict_mask(ts.lg[tok], E, K, rs.pr_mask);
+            else warp_gate_probs(ts.lg[tok], E, a.gating, ts.p[tok], ts.tab, sub == 0 ? 2 : sub - 2, 3);  // the finishing warp takes the smallest share
+            if (sub != 1) asm volatile("bar.sync %0, 96;" ::"r"(7 + tok) : "memory");
+        }
+        if (selects) {
+            warp_select(ts.p[tok], E, K, a.gating, reinterpret_cast<uint32_t*>(rs.ids) + tok * K, rs.w + tok * K);
+        } else {
+            const int n_sthreads = n_swarps * 32, stid = swarp * 32 + lane;
+            asm volatile("bar.sync 6, %0;" ::"r"(n_sthreads) : "memory");
+            for (int e = stid; e < E; e += n_sthreads) {
+                const unsigned word = rs.pr_mask[e >> 5];
+                if ((word >> (e & 31)) & 1u) {
+                    int pos = __popc(word & ((1u << (e & 31)) - 1u));
+                    for (int w = 0; w < (e >> 5); ++w) pos += __popc(rs.pr_mask[w]);
+                    rs.pr_ue[pos] = e;
+                }
+            }
+            if (stid == 0) {
+                int tot = 0;
+                for (int w = 0; w < MAX_EXPERTS / 32; ++w) tot += __popc(rs.pr_mask[w]);
+                rs.pr_U = tot;
+            }
+            asm volatile("bar.sync 6, %0;" ::"r"(n_sthreads) : "memory");
+            stage_all(rs.pr_ue, rs.pr_U, swarp, n_swarps);
+            stamp(11);
         }
         __syncthreads();
         stamp(10);
@@ -358,11 +436,17 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     }
     stamp(4);
     const int U = rs.U;
-    const int rt_i = a.L.rt_i;
     const int n_items = U * rt_i;
-    // work items of this CTA: G-1-cta, then every G-th (the CTAs without down rows take the odd ones out first)
-    const int it0 = G - 1 - cta;
-
+    const int n_down = U * kg_i;
+    {
+        bool same = (U == rs.pr_U);
+        if (same && tid < U) same = (rs.ue[tid] == rs.pr_ue[tid]);
+        if (__syncthreads_or(same ? 0 : 1)) {
+            cp_async_wait_all();  // the copies of the wrong prediction land in the same slots
+            __syncthreads();
+            stage_all(rs.ue, U, warp, FW);
+        }
+    }
     auto load_gu = [&](int it, WTile<Q>& g, WTile<Q>& up) {
         const int u = it / rt_i, rt = it - u * rt_i;
         const int e = rs.ue[u];
@@ -371,46 +455,10 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
             load_wtile<Q>(up, a.L.up_q(e), a.L.up_s(e), rt * kg_h + warp, lane);
         }
     };
-    // Every byte this CTA will need is requested now: the tiles of its first gs_slots
-    // items go to shared memory with cp.async (one commit group per item), the first
-    // item beyond those (if any) to registers; then the down tiles (last group).
-    auto stage_tile = [&](uint4* slot, const uint4* qbase, const uint4* sbase, int tile) {
-        const uint4* qp = qbase + ((size_t)tile * QTraits<Q>::NQ) * 32 + lane;
-#pragma unroll
-        for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(slot + j * 32 + lane, qp + j * 32);
-        if (Q != BF16 && lane < 8) cp_async16(slot + QTraits<Q>::NQ * 32 + lane, sbase + (size_t)tile * 8 + lane);
-    };
     const int n_my = (it0 < n_items) ? (n_items - it0 + G - 1) / G : 0;
     const int n_st = min(n_my, gs_slots);
-#pragma unroll 1
-    for (int j = 0; j < n_st; ++j) {
-        const int it = it0 + j * G;
-        const int u = it / rt_i, rt = it - u * rt_i;
-        const int e = rs.ue[u];
-        if (warp < kg_h) {
-            uint4* slot = gs + ((size_t)(j * FW + warp) * 2) * TU4;
-            stage_tile(slot, a.L.gate_q(e), a.L.gate_s(e), rt * kg_h + warp);
-            stage_tile(slot + TU4, a.L.up_q(e), a.L.up_s(e), rt * kg_h + warp);
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
     WTile<Q> wg0, wu0, wg1, wu1;
     if (n_st < n_my) load_gu(it0 + n_st * G, wg1, wu1);
-
-    // down tiles of this CTA's output rows: request the first pf_slots items of every warp now
-    const bool has_down = cta < a.L.rt_h;
-    const int n_down = U * kg_i;
-    if (has_down) {
-        for (int i = 0; i < pf_slots; ++i) {
-            const int n = warp + FW * i;
-            if (n < n_down) {
-                const int uu = n / kg_i, kg = n - uu * kg_i;
-                const int ee = rs.ue[uu];
-                stage_tile(pf + ((size_t)warp * pf_slots + i) * TU4, a.L.down_q(ee), a.L.down_s(ee), cta * kg_i + kg);
-            }
-        }
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
 
     // gate/up + SwiGLU
     auto compute_gu = [&](int it, const WTile<Q>& g, const WTile<Q>& up) {
@@ -455,10 +503,9 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
 #pragma unroll 1
     for (int j = 0; j < n_my; ++j) {
         if (j < n_st) {
-            // item j's group is complete once at most (n_st - 1 - j) + 1 younger groups are pending;
-            // a warp only reads the tiles its own lanes copied
-            cp_async_wait_pending(n_st - j);
-            __syncwarp();
+            // item j's group is complete once at most (n_st - 1 - j) + 1 younger groups are pending
+            cp_async_wait_pending(n_st - j);  // (threads that requested nothing have nothing pending)
+            __syncthreads();                  // tiles are staged by other warps than the ones that use them
             if (warp < kg_h) {
                 const uint4* slot = gs + ((size_t)(j * FW + warp) * 2) * TU4;
                 read_staged_tile<Q>(wg0, slot, lane);

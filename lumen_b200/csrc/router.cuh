@@ -147,6 +147,49 @@ __device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, i
     __syncwarp();
 }
 
+// Sets, in mask (one bit per expert, shared memory, zeroed by the caller), the K experts
+// with the largest raw logits, lowest index first among equals: a prediction of the
+// selected SET that needs no exp (the gate functions are monotonic), used to start weight
+// traffic early; the caller verifies it against warp_select's result.
+__device__ __forceinline__ void warp_predict_mask(const float* logits, int E, int K, unsigned* mask) {
+    const int lane = threadIdx.x & 31;
+    unsigned key[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = lane + 32 * i;
+        const unsigned b = (e < E) ? __float_as_uint(logits[e]) : 0u;
+        // order-preserving map of finite floats to unsigned, shifted so that 0 stays free for "taken / padding"
+        const unsigned k = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+        key[i] = (e < E) ? max(k, 1u) : 0u;
+    }
+    unsigned mine[MAX_EXPERTS / 32] = {};
+#pragma unroll 1
+    for (int k = 0; k < K; ++k) {
+        unsigned hk = key[0];
+        int hi = 0;
+#pragma unroll
+        for (int i = 1; i < 8; ++i) {
+            if (key[i] > hk) {
+                hk = key[i];
+                hi = i;
+            }
+        }
+        const unsigned mk = __reduce_max_sync(0xffffffffu, hk);
+        const int win = __reduce_min_sync(0xffffffffu, (hk == mk) ? lane + 32 * hi : 0x7fffffff);
+        if (mk == 0u) break;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (lane + 32 * i == win) {
+                key[i] = 0u;
+                mine[i] |= 1u << lane;  // expert lane + 32 i lives in word i, bit lane
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (mine[i]) atomicOr(&mask[i], mine[i]);
+}
+
 __device__ __forceinline__ void warp_topk(const float* __restrict__ logits, int E, int K, int gating,
                                           float* smem_p, const unsigned long long* tab, uint32_t* out_ids,
                                           float* out_w) {

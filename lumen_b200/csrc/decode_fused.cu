@@ -131,6 +131,27 @@ struct RouteSm {
     unsigned pr_mask[MAX_EXPERTS / 32];
 };
 
+// Q4_0 gate/up at decode runs on the integer tensor-core path: the nibbles go in as
+// they are (unsigned, two AND/shift pairs per 32 weights instead of the sixteen
+// instructions of the exact-f16 unpack), the activations as a two-term int8 split
+// x ~ sx * (q0 + q1 / 254) with one f32 scale per 32-block (|error| <= amax_block * 1.6e-5),
+// q0 and q1 in adjacent MMA columns; the -8 offset of the nibbles is taken out with the
+// block's precomputed 8 * sx * sum(q0 + q1 / 254).
+constexpr bool kInt8GateUp = true;
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                         unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned pack_s8x4(float a, float b, float c, float d) {
+    return ((unsigned)(int)a & 0xffu) | (((unsigned)(int)b & 0xffu) << 8) | (((unsigned)(int)c & 0xffu) << 16) |
+           (((unsigned)(int)d & 0xffu) << 24);
+}
+
 struct TopkSm {
     float lg[FMAX_T][MAX_EXPERTS];
     float p[FMAX_T][MAX_EXPERTS];
@@ -266,8 +287,49 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     // activation fragments while the other CTAs catch up
     __syncthreads();
     if (want_logits) grid_arrive(a.bar);
-    // activation fragments of every token, private to this CTA
-    {
+    // activation operand of every token, private to this CTA
+    // int8 form: per token [2 terms][nblk_pad * 8 + 8 words] then [nblk_pad] {sx, 8 * sx * sum}; inside a block
+    // the word pair of lane quad t is adjacent: {inputs 4t..4t+3, inputs 16+4t..16+4t+3}
+    const int xq_term = nblk_pad * 8 + 8, xq_tok = 2 * xq_term + 2 * nblk_pad;  // in 32-bit words
+    unsigned* xq = reinterpret_cast<unsigned*>(xs);
+    if (Q == Q4_0 && kInt8GateUp) {
+        const int sub = tid & 7;
+        const unsigned gmask = 0xFFu << (lane & 24);
+#pragma unroll 1
+        for (int item = tid >> 3; item < T * nblk; item += FT / 8) {
+            const int t = item / nblk, b = item - t * nblk;
+            const float4 v = xn4[t * H4 + b * 8 + sub];  // inputs 4 sub .. 4 sub + 3 of the block
+            float am = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(gmask, am, o));
+            const float inv = (am > 0.0f) ? 127.0f / am : 0.0f;
+            const float sx = am * (1.0f / 127.0f);
+            const float r0 = v.x * inv, r1 = v.y * inv, r2 = v.z * inv, r3 = v.w * inv;
+            const float q00 = rintf(r0), q01 = rintf(r1), q02 = rintf(r2), q03 = rintf(r3);
+            const float q10 = rintf((r0 - q00) * 254.0f), q11 = rintf((r1 - q01) * 254.0f);
+            const float q12 = rintf((r2 - q02) * 254.0f), q13 = rintf((r3 - q03) * 254.0f);
+            float sum = (q00 + q01 + q02 + q03) + (q10 + q11 + q12 + q13) * (1.0f / 254.0f);
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(gmask, sum, o);
+            unsigned* base = xq + (size_t)t * xq_tok + b * 8 + (sub & 3) * 2 + (sub >> 2);
+            base[0] = pack_s8x4(q00, q01, q02, q03);
+            base[xq_term] = pack_s8x4(q10, q11, q12, q13);
+            if (sub == 0)
+                reinterpret_cast<float2*>(xq + (size_t)t * xq_tok + 2 * xq_term)[b] = make_float2(sx, 8.0f * sx * sum);
+        }
+        // padding blocks (kg_h * 4 > H / 32) must read as zero
+        const int padw = (nblk_pad - nblk) * 8;
+#pragma unroll 1
+        for (int i = tid; i < T * 2 * padw; i += FT) {
+            const int tt = i / padw, r = i - tt * padw;
+            xq[(size_t)(tt >> 1) * xq_tok + (tt & 1) * xq_term + nblk * 8 + r] = 0u;
+        }
+#pragma unroll 1
+        for (int i = tid; i < T * (nblk_pad - nblk); i += FT) {
+            const int t = i / (nblk_pad - nblk), b = nblk + i - t * (nblk_pad - nblk);
+            reinterpret_cast<float2*>(xq + (size_t)t * xq_tok + 2 * xq_term)[b] = make_float2(0.0f, 0.0f);
+        }
+    } else {
         const bool bf16_mode = (Q == BF16);
         const int sub = tid & 7, hl = sub >> 2, s4 = sub & 3;
 #pragma unroll 1
@@ -469,7 +531,34 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
         const bool bvalid = jcol < ncol;
         const int tok = bvalid ? rs.col_tok[c0 + jcol] : 0;
         float acc_g[4] = {0.f, 0.f, 0.f, 0.f}, acc_u[4] = {0.f, 0.f, 0.f, 0.f};
-        if (warp < kg_h) {
+        if (Q == Q4_0 && kInt8GateUp) {
+            // acc[0] / acc[2]: rows gq / gq + 8 of the lane's token column t4 (acc[1], acc[3] stay zero)
+            if (warp < kg_h) {
+                const unsigned* bq = xq + (size_t)tok * xq_tok + (gq & 1) * xq_term + (warp * 4) * 8 + t4 * 2;
+                const int tok_d = (t4 < ncol) ? rs.col_tok[c0 + t4] : 0;
+                const float2* sc = reinterpret_cast<const float2*>(xq + (size_t)tok_d * xq_tok + 2 * xq_term) + warp * 4;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    uint2 bb = make_uint2(0u, 0u);
+                    if (bvalid) bb = *reinterpret_cast<const uint2*>(bq + b * 8);
+                    const uint4 qg = g.q[b >> 1], qu = up.q[b >> 1];
+                    const unsigned g0 = (b & 1) ? qg.z : qg.x, g8 = (b & 1) ? qg.w : qg.y;
+                    const unsigned u0 = (b & 1) ? qu.z : qu.x, u8 = (b & 1) ? qu.w : qu.y;
+                    int cg[4] = {0, 0, 0, 0}, cu[4] = {0, 0, 0, 0};
+                    mma_u8s8(cg, g0 & 0x0F0F0F0Fu, g8 & 0x0F0F0F0Fu, (g0 >> 4) & 0x0F0F0F0Fu, (g8 >> 4) & 0x0F0F0F0Fu,
+                             bb.x, bb.y);
+                    mma_u8s8(cu, u0 & 0x0F0F0F0Fu, u8 & 0x0F0F0F0Fu, (u0 >> 4) & 0x0F0F0F0Fu, (u8 >> 4) & 0x0F0F0F0Fu,
+                             bb.x, bb.y);
+                    const float2 sxo = sc[b];  // {sx, 8 * sx * sum(q)}
+                    const float2 sg = block_scales<Q>(g, b), su = block_scales<Q>(up, b);
+                    const float k1 = 1.0f / 254.0f;
+                    acc_g[0] = fmaf(sg.x, fmaf(sxo.x, fmaf((float)cg[1], k1, (float)cg[0]), -sxo.y), acc_g[0]);
+                    acc_g[2] = fmaf(sg.y, fmaf(sxo.x, fmaf((float)cg[3], k1, (float)cg[2]), -sxo.y), acc_g[2]);
+                    acc_u[0] = fmaf(su.x, fmaf(sxo.x, fmaf((float)cu[1], k1, (float)cu[0]), -sxo.y), acc_u[0]);
+                    acc_u[2] = fmaf(su.y, fmaf(sxo.x, fmaf((float)cu[3], k1, (float)cu[2]), -sxo.y), acc_u[2]);
+                }
+            }
+        } else if (warp < kg_h) {
             const uint4* bp = xs + (size_t)tok * per_col + ((size_t)(gq & 1) * nblk_pad) * 4 + t4 + (size_t)warp * 16;
 #pragma unroll
             for (int b = 0; b < 4; ++b) {

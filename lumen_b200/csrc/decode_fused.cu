@@ -418,12 +418,57 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
 #pragma unroll 1
             for (int i = sub * 32 + lane; i < E; i += 128) ts.lg[tok][i] = __ldcg(lg + (size_t)tok * E + i);
             asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
+            warp_gate_probs(ts.lg[tok], E, a.gating, ts.p[tok], ts.tab, sub, 4);
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
             if (sub == 1) warp_predict_mask(ts.lg[tok], E, K, rs.pr_mask);
-            else warp_gate_probs(ts.lg[tok], E, a.gating, ts.p[tok], ts.tab, sub == 0 ? 2 : sub - 2, 3);  // the finishing warp takes the smallest share
-            if (sub != 1) asm volatile("bar.sync %0, 96;" ::"r"(7 + tok) : "memory");
         }
         if (selects) {
             warp_select(ts.p[tok], E, K, a.gating, reinterpret_cast<uint32_t*>(rs.ids) + tok * K, rs.w + tok * K);
+            // the sort only needs the finishing warps: it does not wait for the warps that request tiles
+            if (T > 1) asm volatile("bar.sync 11, %0;" ::"r"(T * 32) : "memory");
+            stamp(10);
+            if (warp == 0) {
+                // stable counting sort of the C <= 32 pairs by expert, one pair per lane
+                const int my = (lane < C) ? rs.ids[lane] : 0x7fffffff;
+                unsigned lt = 0u;  // pairs with a smaller expert
+#pragma unroll 4
+                for (int q = 0; q < C; ++q) lt |= (__shfl_sync(0xffffffffu, my, q) < my ? 1u : 0u) << q;
+                const unsigned same = __match_any_sync(0xffffffffu, my);
+                const int less = __popc(lt), cnt = __popc(same), eqb = __popc(same & ((1u << lane) - 1u));
+                const bool first = (lane < C) && (eqb == 0);
+                const unsigned fmask = __ballot_sync(0xffffffffu, first);
+                const int u = __popc(lt & fmask);  // distinct smaller experts
+                if (lane < C) {
+                    const int col = less + eqb;
+                    rs.d2c[lane] = col;
+                    rs.col_u[col] = u;
+                    rs.col_tok[col] = lane / K;
+                    if (first) {
+                        rs.ue[u] = my;
+                        rs.uc0[u] = col;
+                        rs.uncol[u] = cnt;
+                    }
+                    if (cta == 0) {
+                        a.R.ids[lane] = (uint32_t)my;
+                        a.R.weights[lane] = rs.w[lane];
+                        a.R.dst_to_col[lane] = col;
+                        a.R.col_expert[col] = my;
+                        a.R.col_src_tok[col] = lane / K;
+                        if (first) a.R.uexp[u] = my;
+                    }
+                }
+                if (lane == 0) {
+                    rs.U = __popc(fmask);
+                    if (cta == 0) *a.R.n_uexp = __popc(fmask);
+                }
+                if (cta == 0) {
+                    for (int e = lane; e <= E; e += 32) {
+                        int below = 0;
+                        for (int q = 0; q < C; ++q) below += (rs.ids[q] < e);
+                        a.R.expert_bounds[e] = below;
+                    }
+                }
+            }
         } else {
             const int n_sthreads = n_swarps * 32, stid = swarp * 32 + lane;
             asm volatile("bar.sync 6, %0;" ::"r"(n_sthreads) : "memory");
@@ -443,56 +488,6 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
             asm volatile("bar.sync 6, %0;" ::"r"(n_sthreads) : "memory");
             stage_all(rs.pr_ue, rs.pr_U, swarp, n_swarps);
             stamp(11);
-        }
-        __syncthreads();
-        stamp(10);
-        if (warp == 0) {
-            // stable counting sort of the C <= 32 pairs by expert, one pair per lane
-            const int my = (lane < C) ? rs.ids[lane] : 0x7fffffff;
-            int less = 0, eqb = 0, cnt = 0;
-            for (int q = 0; q < C; ++q) {
-                const int eq = __shfl_sync(0xffffffffu, my, q);
-                less += (eq < my);
-                cnt += (eq == my);
-                eqb += (eq == my && q < lane);
-            }
-            const bool first = (lane < C) && (eqb == 0);
-            const unsigned fmask = __ballot_sync(0xffffffffu, first);
-            int u = 0;
-            for (int q = 0; q < C; ++q) {
-                const int eq = __shfl_sync(0xffffffffu, my, q);
-                u += (((fmask >> q) & 1u) && eq < my);
-            }
-            if (lane < C) {
-                const int col = less + eqb;
-                rs.d2c[lane] = col;
-                rs.col_u[col] = u;
-                rs.col_tok[col] = lane / K;
-                if (first) {
-                    rs.ue[u] = my;
-                    rs.uc0[u] = col;
-                    rs.uncol[u] = cnt;
-                }
-                if (cta == 0) {
-                    a.R.ids[lane] = (uint32_t)my;
-                    a.R.weights[lane] = rs.w[lane];
-                    a.R.dst_to_col[lane] = col;
-                    a.R.col_expert[col] = my;
-                    a.R.col_src_tok[col] = lane / K;
-                    if (first) a.R.uexp[u] = my;
-                }
-            }
-            if (lane == 0) {
-                rs.U = __popc(fmask);
-                if (cta == 0) *a.R.n_uexp = __popc(fmask);
-            }
-            if (cta == 0) {
-                for (int e = lane; e <= E; e += 32) {
-                    int below = 0;
-                    for (int q = 0; q < C; ++q) below += (rs.ids[q] < e);
-                    a.R.expert_bounds[e] = below;
-                }
-            }
         }
         __syncthreads();
     }

@@ -71,12 +71,13 @@ __device__ __forceinline__ void warp_gate_probs(const float* __restrict__ logits
 
 // Normalisation (softmax), K selection rounds and renormalised weights from the gate
 // values in smem_p (all E of them visible to this warp).
-__device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, int gating, uint32_t* out_ids,
-                                            float* out_w) {
+template <int NS>  // NS * 32 >= E: slots (experts) per lane
+__device__ __forceinline__ void warp_select_n(const float* smem_p, int E, int K, int gating, uint32_t* out_ids,
+                                              float* out_w) {
     const int lane = threadIdx.x & 31;
-    float pe[8];
+    float pe[NS];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) pe[i] = (lane + 32 * i < E) ? smem_p[lane + 32 * i] : 0.0f;
+    for (int i = 0; i < NS; ++i) pe[i] = (lane + 32 * i < E) ? smem_p[lane + 32 * i] : 0.0f;
     if (gating == 0) {
         float sum = 0.0f;
         const int E16 = E & ~15;
@@ -104,12 +105,12 @@ __device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, i
 #pragma unroll 1
         for (; e < E; ++e) sum = __fadd_rn(sum, smem_p[e]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < NS; ++i)
             if (lane + 32 * i < E) pe[i] = __fdiv_rn(pe[i], sum);
     }
-    unsigned key[8];
+    unsigned key[NS];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) key[i] = (lane + 32 * i < E) ? __float_as_uint(pe[i]) + 1u : 0u;
+    for (int i = 0; i < NS; ++i) key[i] = (lane + 32 * i < E) ? __float_as_uint(pe[i]) + 1u : 0u;
     float my_sel = 0.0f, renorm = 0.0f;
     int my_id = 0;
 #pragma unroll 1
@@ -118,7 +119,7 @@ __device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, i
         unsigned hk = key[0];
         int hi = 0;
 #pragma unroll
-        for (int i = 1; i < 8; ++i) {
+        for (int i = 1; i < NS; ++i) {
             if (key[i] > hk) {
                 hk = key[i];
                 hi = i;
@@ -137,7 +138,7 @@ __device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, i
             my_id = win;
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
+        for (int i = 0; i < NS; ++i)
             if (lane + 32 * i == win) key[i] = 0u;
     }
     if (lane < K) {
@@ -145,6 +146,12 @@ __device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, i
         out_w[lane] = (renorm > 0.0f) ? __fdiv_rn(my_sel, renorm) : my_sel;
     }
     __syncwarp();
+}
+
+__device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, int gating, uint32_t* out_ids,
+                                            float* out_w) {
+    if (E <= 128) warp_select_n<4>(smem_p, E, K, gating, out_ids, out_w);
+    else warp_select_n<8>(smem_p, E, K, gating, out_ids, out_w);
 }
 
 // Sets, in mask (one bit per expert, shared memory, zeroed by the caller), the K experts

@@ -37,6 +37,12 @@ namespace lumen {
 // (warp_gate_probs with sub = 0..nsub-1, the caller synchronises them) before one
 // warp finishes the token (warp_select). warp_topk is the one-warp form.
 
+// One body for all call sites: the exp is ~60 double-precision instructions and the code of
+// these routines runs once per launch, so its size is paid in instruction fetches.
+__device__ __noinline__ float expf_exact_call(float x, const uint64_t* tab) {
+    return lumen_exact::expf_libm_tab(x, lumen_exact::Exp2TabPtr{tab});
+}
+
 // Unnormalised gate values into smem_p[e] for the experts of this warp's share:
 // 32-expert group (e >> 5) belongs to sub-warp (e >> 5) % nsub. Softmax: exp(logit - max);
 // sigmoid: the final 1 / (1 + exp(-logit)). `logits` may be shared or global memory.
@@ -63,7 +69,7 @@ __device__ __forceinline__ void warp_gate_probs(const float* __restrict__ logits
     for (int i = 0; i < 8; ++i) {
         const int e = lane + 32 * i;
         if (e < E && (i % nsub) == sub) {
-            const float ex = lumen_exact::expf_libm_tab((gating == 0) ? lg[i] - m : -lg[i], et);
+            const float ex = expf_exact_call((gating == 0) ? lg[i] - m : -lg[i], et.p);
             smem_p[e] = (gating == 0) ? ex : __fdiv_rn(1.0f, __fadd_rn(1.0f, ex));
         }
     }

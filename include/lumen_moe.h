@@ -45,7 +45,16 @@ typedef enum { LUMEN_MOE_Q8_0 = 0, LUMEN_MOE_Q4_0 = 1, LUMEN_MOE_BF16 = 2 } lume
 
 /* SOFTMAX_RENORM: cuda/moe.rs:6464-6504 (CPU reference) and cuda/shaders/moe_router.cu:85-128.
  * SIGMOID_RENORM: cuda/shaders/topk_moe_fused.cu:118-129 (the CUDA backend's default). */
-typedef enum { LUMEN_MOE_SOFTMAX_RENORM = 0, LUMEN_MOE_SIGMOID_RENORM = 1 } lumen_moe_gating_t;
+/* 0, 1: routed experts (softmax / sigmoid over E, top-k, weights renormalised).
+ * 2, 3: the always-on shared expert as a context with num_experts = top_k = 1
+ * (cuda/moe.rs:5455-5520): weight = sigmoid(dot(ffn_gate_inp_shexp, x)), or 1 when the
+ * model has no gate vector. */
+typedef enum {
+    LUMEN_MOE_SOFTMAX_RENORM = 0,
+    LUMEN_MOE_SIGMOID_RENORM = 1,
+    LUMEN_MOE_SIGMOID_GATE = 2,
+    LUMEN_MOE_UNIT_WEIGHT = 3
+} lumen_moe_gating_t;
 
 /* Activation element types of lumen_moe_prefill. */
 typedef enum { LUMEN_MOE_ACT_F32 = 0, LUMEN_MOE_ACT_BF16 = 1 } lumen_moe_act_t;
@@ -90,6 +99,22 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_layer_prepare(lumen_moe_ctx* ctx, con
                                            const uint64_t* down_offs, int32_t quant, void* stream,
                                            lumen_moe_layer** out_layer);
 LUMEN_MOE_API void lumen_moe_layer_destroy(lumen_moe_layer* layer);
+
+/* Replace encode_shared_expert_ffn_decode (cuda/moe.rs:5494) and
+ * encode_shared_expert_ffn_prefill_batched (cuda/moe.rs:2788): the always-on shared expert,
+ *   out[t] += g[t] * Down_sh(silu(Gate_sh x[t]) * Up_sh x[t]),
+ *   g[t] = sigmoid(dot(ffn_gate_inp_shexp, x[t]))   (LUMEN_MOE_SIGMOID_GATE) or 1 (LUMEN_MOE_UNIT_WEIGHT),
+ * accumulated INTO d_out, which already holds the routed experts' result. `ctx` is a
+ * context created with num_experts = top_k = 1, inter_dim = the shared expert's inter
+ * dim and gating_mode 2 or 3; `layer` was prepared on the same layer blob with
+ * router_off = offset of ffn_gate_inp_shexp (F32 [H]; any valid offset in mode 3) and the
+ * three shared-expert slices as one-element offset arrays. Decode: 1 <= T <= 16, f32. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_shared_expert_decode(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                                const float* d_normed, float* d_out,
+                                                                int32_t tokens, void* stream);
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_shared_expert_prefill(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                                 const void* d_normed, float* d_out,
+                                                                 int32_t tokens, int32_t act_dtype, void* stream);
 
 /* Replaces encode_moe_ffn_decode (cuda/moe.rs:1119): out[t] = residual[t] +
  * sum_k w[t,k] * Down_e(silu(Gate_e x[t]) * Up_e x[t]), f32 [T,H] in and out,

@@ -10,7 +10,7 @@ LIB_PATH = PKG / "liblumen_moe_b200.so"
 
 OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, TIMEOUT, NCCL_ERROR = range(6)
 Q8_0, Q4_0, BF16 = 0, 1, 2
-SOFTMAX_RENORM, SIGMOID_RENORM = 0, 1
+SOFTMAX_RENORM, SIGMOID_RENORM, SIGMOID_GATE, UNIT_WEIGHT = 0, 1, 2, 3
 ACT_F32, ACT_BF16 = 0, 1
 
 
@@ -54,6 +54,8 @@ SIGNATURES = {
     "lumen_moe_rmsnorm": [vp, vp, vp, i32, i32, f32, vp],
     "lumen_moe_stack_decode": [vp, vp, vp, i32, vp, f32, i32, vp],
     "lumen_moe_debug_expf": [vp, vp, i64, vp],
+    "lumen_moe_shared_expert_decode": [vp, vp, vp, vp, i32, vp],
+    "lumen_moe_shared_expert_prefill": [vp, vp, vp, vp, i32, i32, vp],
     "lumen_moe_debug_decode_trace": [vp, vp, vp, vp],
     "lumen_moe_debug_decode_phase": [vp, vp, i32, vp],
     "lumen_moe_layer_bytes": [vp],

@@ -159,6 +159,28 @@ lumen_moe_status_t lumen_moe_decode(lumen_moe_ctx* ctx, const lumen_moe_layer* l
                                              static_cast<cudaStream_t>(stream)));
 }
 
+static bool is_shared_ctx(const lumen_moe_ctx* ctx) {
+    return ctx->scratch.E == 1 && ctx->scratch.K == 1 && (ctx->scratch.gating == 2 || ctx->scratch.gating == 3);
+}
+
+lumen_moe_status_t lumen_moe_shared_expert_decode(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                  const float* d_normed, float* d_out, int32_t tokens,
+                                                  void* stream) {
+    if (!ctx || !layer) return fail(LUMEN_MOE_INVALID_ARG, "null context or layer");
+    if (!is_shared_ctx(ctx))
+        return fail(LUMEN_MOE_INVALID_ARG, "not a shared-expert context (num_experts = top_k = 1, gating_mode 2 or 3)");
+    return lumen_moe_decode(ctx, layer, d_normed, d_out, d_out, tokens, stream);
+}
+
+lumen_moe_status_t lumen_moe_shared_expert_prefill(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                   const void* d_normed, float* d_out, int32_t tokens,
+                                                   int32_t act_dtype, void* stream) {
+    if (!ctx || !layer) return fail(LUMEN_MOE_INVALID_ARG, "null context or layer");
+    if (!is_shared_ctx(ctx))
+        return fail(LUMEN_MOE_INVALID_ARG, "not a shared-expert context (num_experts = top_k = 1, gating_mode 2 or 3)");
+    return lumen_moe_prefill(ctx, layer, d_normed, d_out, d_out, tokens, act_dtype, stream);
+}
+
 lumen_moe_status_t lumen_moe_decode_fused_norm(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const float* d_x,
                                                const float* d_gamma, float* d_normed_out, float* d_out, float eps,
                                                int32_t tokens, void* stream) {

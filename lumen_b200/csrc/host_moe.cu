@@ -186,7 +186,7 @@ Status allocate_moe_scratch(int device, int H, int I, int E, int K, int gating, 
     if (H <= 0 || I <= 0 || H % 32 || I % 32) return Status::Err(1, "hidden_dim and inter_dim must be positive multiples of 32");
     if (E <= 0 || E > MAX_EXPERTS) return Status::Err(1, "num_experts must be in 1..256");
     if (K <= 0 || K > MAX_TOP_K || K > E) return Status::Err(1, "top_k must be in 1..16 and <= num_experts");
-    if (gating != 0 && gating != 1) return Status::Err(1, "unknown gating mode");
+    if (gating < 0 || gating > 3) return Status::Err(1, "unknown gating mode");
     CUDA_TRY(cudaSetDevice(device));
     CudaMoeScratch s;
     s.device = device;

@@ -12,7 +12,9 @@
 //   renorm = sel[0] + sel[1] + ...            (sequential f32, k ascending)
 //   w[k]  = sel[k] / renorm  if renorm > 0
 // SIGMOID_RENORM (cuda/shaders/topk_moe_fused.cu:118-129) replaces the first four
-// lines by p[e] = 1 / (1 + exp(-logit[e])).
+// lines by p[e] = 1 / (1 + exp(-logit[e])). Gating 2 is the same without the last two
+// lines (the shared expert's gate, cuda/shaders/moe_shared_accum.cu:1-12), gating 3
+// sets w[k] = 1.
 // Logits are assumed finite (NaN logits give in-range but unspecified ids).
 #pragma once
 #include "moe_internal.cuh"
@@ -39,7 +41,7 @@ namespace lumen {
 
 // One body for all call sites: the exp is ~60 double-precision instructions and the code of
 // these routines runs once per launch, so its size is paid in instruction fetches.
-__device__ __noinline__ float expf_exact_call(float x, const uint64_t* tab) {
+static __device__ __noinline__ float expf_exact_call(float x, const uint64_t* tab) {
     return lumen_exact::expf_libm_tab(x, lumen_exact::Exp2TabPtr{tab});
 }
 
@@ -149,7 +151,9 @@ __device__ __forceinline__ void warp_select_n(const float* smem_p, int E, int K,
     }
     if (lane < K) {
         out_ids[lane] = (uint32_t)my_id;
-        out_w[lane] = (renorm > 0.0f) ? __fdiv_rn(my_sel, renorm) : my_sel;
+        // gating 2: the sigmoid value itself (shared-expert gate); 3: unit weight
+        out_w[lane] = (gating == 3) ? 1.0f
+                      : (gating != 2 && renorm > 0.0f) ? __fdiv_rn(my_sel, renorm) : my_sel;
     }
     __syncwarp();
 }

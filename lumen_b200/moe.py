@@ -21,12 +21,13 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import (ACT_BF16, ACT_F32, BF16, Q4_0, Q8_0, SIGMOID_RENORM, SOFTMAX_RENORM, LumenMoeError, MoeConfig,
+from ._lib import (ACT_BF16, ACT_F32, BF16, Q4_0, Q8_0, SIGMOID_GATE, SIGMOID_RENORM, SOFTMAX_RENORM, UNIT_WEIGHT,
+                   LumenMoeError, MoeConfig,
                    check)
 
 __all__ = ["MoeMeta", "MoeScratch", "MoeLayer", "allocate_moe_scratch", "build_moe_meta", "encode_moe_ffn_decode",
            "encode_moe_ffn_decode_fused_norm", "encode_moe_ffn_prefill_grouped", "LumenMoeError", "Q8_0", "Q4_0",
-           "BF16", "SOFTMAX_RENORM", "SIGMOID_RENORM"]
+           "BF16", "SOFTMAX_RENORM", "SIGMOID_RENORM", "SIGMOID_GATE", "UNIT_WEIGHT"]
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -185,6 +186,26 @@ class MoeScratch:
             output = torch.empty_like(residual)
         check(_lib.lib().lumen_moe_prefill(self._h, layer._h, normed.data_ptr(), residual.data_ptr(),
                                            output.data_ptr(), T, act, _stream()))
+        return output
+
+    def shared_expert_decode(self, layer: MoeLayer, normed_x: torch.Tensor, output_x: torch.Tensor) -> torch.Tensor:
+        """lumen_moe_shared_expert_decode: output_x += gate * FFN_shared(normed_x), in place (this context
+        must be a shared-expert context: one expert, top-1, gating mode 2 or 3)."""
+        _need(normed_x, torch.float32, "normed_x")
+        _need(output_x, torch.float32, "output_x")
+        T = normed_x.numel() // self.H
+        check(_lib.lib().lumen_moe_shared_expert_decode(self._h, layer._h, normed_x.data_ptr(), output_x.data_ptr(),
+                                                        T, _stream()))
+        return output_x
+
+    def shared_expert_prefill(self, layer: MoeLayer, normed: torch.Tensor, output: torch.Tensor) -> torch.Tensor:
+        """lumen_moe_shared_expert_prefill: the batched form, any number of tokens."""
+        act = ACT_F32 if normed.dtype == torch.float32 else ACT_BF16
+        _need(normed, normed.dtype, "normed")
+        _need(output, torch.float32, "output")
+        T = normed.numel() // self.H
+        check(_lib.lib().lumen_moe_shared_expert_prefill(self._h, layer._h, normed.data_ptr(), output.data_ptr(),
+                                                         T, act, _stream()))
         return output
 
     def prefill_routed(self, layer: MoeLayer, normed: torch.Tensor, ids: torch.Tensor,

@@ -265,7 +265,11 @@ ORC_API void orc_router_logits(const float* x, const float* w, int H, int E, flo
 
 // Phases 2+3 (:6464-6504). gating: 0 = softmax then renormalise (the CPU
 // reference); 1 = sigmoid then renormalise (cuda/shaders/topk_moe_fused.cu:118-129,
-// the CUDA backend's production default; same ids, different weights).
+// the CUDA backend's production default; same ids, different weights);
+// 2 = sigmoid, weights NOT renormalised: with E = K = 1 this is the gate of the
+// always-on shared expert, sigmoid(dot(ffn_gate_inp_shexp, x))
+// (cuda/moe.rs:5455-5470, cuda/shaders/moe_shared_accum.cu:1-12);
+// 3 = unit weights (shared expert without a gate vector, cuda/moe.rs:5483-5485).
 // probs_scratch: E floats (clobbered).
 ORC_API void orc_topk_from_logits(const float* logits_in, int E, int K, int gating,
                                   uint32_t* ids, float* weights, float* probs_scratch) {
@@ -297,8 +301,11 @@ ORC_API void orc_topk_from_logits(const float* logits_in, int E, int K, int gati
         renorm += best;
         p[best_e] = -1.0f;
     }
-    if (renorm > 0.0f)
+    if (gating == 3) {
+        for (int k = 0; k < K; ++k) weights[k] = 1.0f;
+    } else if (gating != 2 && renorm > 0.0f) {
         for (int k = 0; k < K; ++k) weights[k] /= renorm;
+    }
 }
 
 ORC_API void orc_router_softmax(const float* x, const float* w, int H, int E, int K,

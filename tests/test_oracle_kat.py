@@ -270,3 +270,21 @@ def test_layer_matches_manual_composition(orc, quant):
             uu = wd(meta.expert_up_offs[e], I, H) @ x[t]
             acc = acc + float(wts[t, k]) * (wd(meta.expert_down_offs[e], H, I) @ (gg / (1 + np.exp(-gg)) * uu))
         assert np.linalg.norm(acc - out[t]) / np.linalg.norm(acc) < 1e-5
+
+
+def test_gating_modes_of_the_shared_expert(orc):
+    """gating 2 = sigmoid(logit) as the weight, no renormalisation; 3 = unit weight
+    (cuda/moe.rs:5455-5485; cuda/shaders/moe_shared_accum.cu:1-12)."""
+    lg = np.array([[0.75], [-3.0], [0.0]], np.float32)
+    ids, w = orc.topk_from_logits(lg, 1, gating=2)
+    assert (ids == 0).all()
+    want = (np.float32(1.0) / (np.float32(1.0) + np.exp(-lg[:, 0]).astype(np.float32))).astype(np.float32)
+    np.testing.assert_allclose(w[:, 0], want, rtol=1e-6)
+    assert w[2, 0] == np.float32(0.5)
+    ids, w = orc.topk_from_logits(lg, 1, gating=3)
+    assert (ids == 0).all() and (w == 1.0).all()
+    # with several experts mode 2 keeps the raw sigmoid values of the selected ones
+    lg2 = np.array([[2.0, -1.0, 0.5, 0.0]], np.float32)
+    ids, w = orc.topk_from_logits(lg2, 2, gating=2)
+    assert ids.tolist() == [[0, 2]]
+    np.testing.assert_allclose(w[0], 1.0 / (1.0 + np.exp(-lg2[0, [0, 2]].astype(np.float64))), rtol=1e-6)

@@ -92,7 +92,8 @@ router_logits_large_kernel(const XT* __restrict__ x, const float* __restrict__ w
 // once per call into two [E,H] f16 planes; X is split in registers (the lo*hi
 // product is skipped for a fragment whose low parts are all zero, which is the
 // usual case for bf16 activations).
-// CTA = 64 tokens x (up to) 128 experts, 4 warps of 16 tokens. Per 32-input slab
+// CTA = 64 tokens x (up to) 64 experts, 4 warps of 16 tokens (small tiles: at a few
+// thousand tokens the grid must still cover the SMs). Per 32-input slab
 // lane (g,t) owns inputs 8t..8t+7 of token rows g and g+8 (one 16-byte load each
 // for bf16) and of expert row 8n+g (one 16-byte shared load per plane): the same
 // input -> k-slot assignment on both operands, so the contraction is unchanged.
@@ -153,27 +154,28 @@ router_logits_mma_kernel(const XT* __restrict__ x, const __half* __restrict__ w1
                          int T, int H, int E) {
     constexpr int BM = 64, BK = 32;
     // [buffer][plane][expert row][32 inputs]: 64-byte rows, 16-byte fragment loads are conflict-free
-    __shared__ __align__(16) __half ws[2][2][128][BK];
+    constexpr int NE = 64;  // experts per CTA
+    __shared__ __align__(16) __half ws[2][2][NE][BK];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
-    const int t0 = blockIdx.x * BM, e0 = blockIdx.y * 128;
-    const int ne = min(128, E - e0);
+    const int t0 = blockIdx.x * BM, e0 = blockIdx.y * NE;
+    const int ne = min(NE, E - e0);
     const int ntile = (ne + 7) >> 3;
     const size_t plane = (size_t)E * H;
-    float acc[16][4];
+    float acc[NE / 8][4];
 #pragma unroll
-    for (int n = 0; n < 16; ++n)
+    for (int n = 0; n < NE / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.0f;
     const int ra = t0 + warp * 16 + g, rb = ra + 8;
     const XT* xa = x + (size_t)min(ra, T - 1) * H + 8 * t4;
     const XT* xb = x + (size_t)min(rb, T - 1) * H + 8 * t4;
     auto stage_w = [&](int buf, int k0) {
-        // 128 rows x 4 chunks x 2 planes = 1024 16-byte copies, 8 per thread
+        // NE rows x 4 chunks x 2 planes = 512 16-byte copies, 4 per thread
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
+        for (int i = 0; i < NE / 16; ++i) {
             const int c = tid + i * 128;
-            const int pl = c >> 9, row = (c >> 2) & 127, ch = c & 3;
+            const int pl = c / (NE * 4), row = (c >> 2) % NE, ch = c & 3;
             const __half* src = w16 + pl * plane + (size_t)min(e0 + row, E - 1) * H + k0 + ch * 8;
             cp_async16_rl(&ws[buf][pl][row][ch * 8], src);
         }
@@ -214,7 +216,7 @@ router_logits_mma_kernel(const XT* __restrict__ x, const __half* __restrict__ w1
             for (int i = 0; i < 4; ++i) lo_or |= al[j][i];
         const bool use_lo = __any_sync(0xffffffffu, (lo_or & 0x7fff7fffu) != 0);
 #pragma unroll
-        for (int n = 0; n < 16; ++n) {
+        for (int n = 0; n < NE / 8; ++n) {
             if (n < ntile) {
                 const uint4 bh = *reinterpret_cast<const uint4*>(&ws[buf][0][n * 8 + g][8 * t4]);
                 const uint4 bl = *reinterpret_cast<const uint4*>(&ws[buf][1][n * 8 + g][8 * t4]);
@@ -231,7 +233,7 @@ router_logits_mma_kernel(const XT* __restrict__ x, const __half* __restrict__ w1
         __syncthreads();
     }
 #pragma unroll
-    for (int n = 0; n < 16; ++n) {
+    for (int n = 0; n < NE / 8; ++n) {
         if (n < ntile) {
             const int ec = e0 + n * 8 + 2 * t4;
             if (ra < T) {
@@ -541,7 +543,7 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
             const size_t n = (size_t)E * H;
             split_router_w_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.L.router_w, a.w16, n);
             count_launch(1);
-            const dim3 grid((T + 63) / 64, (E + 127) / 128);
+            const dim3 grid((T + 63) / 64, (E + 63) / 64);
             if (a.act_dtype == 0)
                 router_logits_mma_kernel<float><<<grid, 128, 0, st>>>((const float*)a.x, a.w16, a.R.logits, T, H, E);
             else

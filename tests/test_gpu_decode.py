@@ -138,3 +138,27 @@ def test_argument_validation(cuda_lib):
     bad.expert_down_offs = bad.expert_down_offs + np.uint64(10 ** 9)
     with pytest.raises(moe.LumenMoeError):
         sc.prepare_layer(synth.make_layer_blob(lay, 1), bad)  # slice outside the blob
+
+
+@pytest.mark.parametrize("T", [1, 3])
+def test_decode_when_the_raw_logit_ranking_differs_from_the_exact_selection(cuda_lib, T):
+    """The fused kernel requests weights for the top-K by raw logit while the exact gating
+    runs, and must notice when the exact selection differs: here all but K-1 probabilities
+    underflow to 0, so the exact rule (lowest index among equals, cuda/moe.rs:6486-6497)
+    takes expert K-1 while the largest remaining raw logit sits at expert 100."""
+    H, I, E, K = 2048, 768, 128, 8
+    lay, meta, blob_np, sc, layer = make_layer(H, I, E, K, 1, seed=2)
+    x = torch.randn((T, H), generator=torch.Generator("cuda").manual_seed(9), device="cuda")
+    lg = np.full((T, E), -400.0, np.float32) - np.arange(E, dtype=np.float32)[None, :]
+    lg[:, : K - 1] = np.linspace(0.0, 1.0, K - 1, dtype=np.float32)[None, :]
+    lg[:, 100] = -300.0
+    lg_d = torch.from_numpy(lg).cuda()
+    sc.set_logits_override(lg_d)
+    out = sc.decode(layer, x, x.clone())
+    r = sc.get_routing(T)
+    sc.set_logits_override(None)
+    o_out, o_ids, o_w = oracle_layer(blob_np, meta, lay, K, x.cpu().numpy(), x.cpu().numpy(), logits=lg)
+    assert sorted(o_ids[0].tolist()) == list(range(K))  # the exact rule really picks expert K-1, not 100
+    assert np.array_equal(r["ids"], o_ids)
+    assert np.array_equal(r["weights"].view(np.uint32), o_w.view(np.uint32))
+    assert rel_l2(out.cpu().numpy() - x.cpu().numpy(), o_out - x.cpu().numpy()) < TOL_REL_L2

@@ -94,42 +94,29 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
         return v;
     };
 
-    // logits for this expert row, all tokens
+    // logits for this expert row, all tokens (token loop rolled: the code of this kernel runs
+    // once per launch, so its size is paid in instruction fetches)
     if (want_logits) {
-        float acc[DECODE_MAX_TOKENS];
+#pragma unroll 1
+        for (int t = 0; t < T; ++t) {
+            float acc = 0.0f;
 #pragma unroll
-        for (int t = 0; t < DECODE_MAX_TOKENS; ++t) acc[t] = 0.0f;
-#pragma unroll
-        for (int j = 0; j < MAXV; ++j) {
-            const int i4 = tid + j * RS_THREADS;
-            if (i4 < H4) {
-#pragma unroll
-                for (int t = 0; t < DECODE_MAX_TOKENS; ++t) {
-                    if (t < T) {
-                        const float4 xv = load_x4(t, i4);
-                        acc[t] += wv[j].x * xv.x + wv[j].y * xv.y + wv[j].z * xv.z + wv[j].w * xv.w;
-                    }
-                }
-            }
-        }
-        for (int i4 = tid + MAXV * RS_THREADS; i4 < H4; i4 += RS_THREADS) {  // H > 4096
-            const float4 w4 = __ldg(wrow + i4);
-#pragma unroll
-            for (int t = 0; t < DECODE_MAX_TOKENS; ++t) {
-                if (t < T) {
+            for (int j = 0; j < MAXV; ++j) {
+                const int i4 = tid + j * RS_THREADS;
+                if (i4 < H4) {
                     const float4 xv = load_x4(t, i4);
-                    acc[t] += w4.x * xv.x + w4.y * xv.y + w4.z * xv.z + w4.w * xv.w;
+                    acc += wv[j].x * xv.x + wv[j].y * xv.y + wv[j].z * xv.z + wv[j].w * xv.w;
                 }
             }
-        }
-#pragma unroll
-        for (int t = 0; t < DECODE_MAX_TOKENS; ++t) {
-            if (t < T) {
-                float v = acc[t];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                if (lane == 0) red_s[warp][t] = v;
+#pragma unroll 1
+            for (int i4 = tid + MAXV * RS_THREADS; i4 < H4; i4 += RS_THREADS) {  // H > 4096
+                const float4 w4 = __ldg(wrow + i4);
+                const float4 xv = load_x4(t, i4);
+                acc += w4.x * xv.x + w4.y * xv.y + w4.z * xv.z + w4.w * xv.w;
             }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (lane == 0) red_s[warp][t] = acc;
         }
         __syncthreads();
         if (tid < T) {

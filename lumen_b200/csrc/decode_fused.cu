@@ -405,7 +405,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     };
     {
         // Four warps per token share the exps; then warp 0 of the four finishes the token
-        // exactly while warp 1 ranks the raw logits. The warps that are not finishing a
+        // exactly while another warp ranks the raw logits. The warps that are not finishing a
         // token (16 - T of them) then turn the predicted mask into a list and request the tiles.
         const float* lg = want_logits ? a.R.logits : a.logits_override;
         const int tok = warp >> 2, sub = warp & 3;
@@ -420,7 +420,12 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
             asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
             warp_gate_probs(ts.lg[tok], E, a.gating, ts.p[tok], ts.tab, sub, 4);
             asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
-            if (sub == 1) warp_predict_mask(ts.lg[tok], E, K, rs.pr_mask);
+            if (T == FMAX_T && sub == 1) warp_predict_mask(ts.lg[tok], E, K, rs.pr_mask);
+        } else if (warp < 4 * T + T) {
+            // with T <= 3 there are idle warps: they predict straight from the logits in L2,
+            // without waiting for the exps
+            const int t = warp - 4 * T;
+            warp_predict_mask(lg + (size_t)t * E, E, K, rs.pr_mask, true);
         }
         if (selects) {
             warp_select(ts.p[tok], E, K, a.gating, reinterpret_cast<uint32_t*>(rs.ids) + tok * K, rs.w + tok * K);

@@ -168,13 +168,15 @@ __device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, i
 // with the largest raw logits, lowest index first among equals: a prediction of the
 // selected SET that needs no exp (the gate functions are monotonic), used to start weight
 // traffic early; the caller verifies it against warp_select's result.
-__device__ __forceinline__ void warp_predict_mask(const float* logits, int E, int K, unsigned* mask) {
+// from_l2: `logits` is global memory written by other SMs during this launch (read through L2).
+__device__ __forceinline__ void warp_predict_mask(const float* logits, int E, int K, unsigned* mask,
+                                                  bool from_l2 = false) {
     const int lane = threadIdx.x & 31;
     unsigned key[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int e = lane + 32 * i;
-        const unsigned b = (e < E) ? __float_as_uint(logits[e]) : 0u;
+        const unsigned b = (e < E) ? __float_as_uint(from_l2 ? __ldcg(logits + e) : logits[e]) : 0u;
         // order-preserving map of finite floats to unsigned, shifted so that 0 stays free for "taken / padding"
         const unsigned k = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
         key[i] = (e < E) ? max(k, 1u) : 0u;

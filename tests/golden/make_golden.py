@@ -1,7 +1,7 @@
 """Generates the committed golden vectors under tests/golden/.
 
-Run in a container that has the reference tree (REFERENCE_ROOT, default
-/root/reference): the expert outputs stored here come from the REFERENCE'S OWN
+Run where the reference tree is available (REFERENCE_ROOT; by default a checkout named
+`reference` next to this repository): the expert outputs stored here come from the REFERENCE'S OWN
 scalar kernels (cuda/shaders/moe_expert.cu, moe_expert_q4_0.cu, moe_accum.cu)
 compiled for the host by `make -C oracle ref`; routing comes from the oracle's
 restatement of cpu_router_softmax (the reference keeps that function inside a

@@ -95,25 +95,51 @@ __device__ __forceinline__ bool grid_wait(unsigned* bar, int* status, int G, uns
     return *fail_s == 0;
 }
 
-// Waits until at most n of this thread's cp.async groups are still pending.
-__device__ __forceinline__ void cp_async_wait_pending(int n) {
-    switch (n) {
-        case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-        case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-        case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-        case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-        case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-        case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-        case 6: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-        default: asm volatile("cp.async.wait_group 7;" ::: "memory"); break;
+// mbarrier + bulk-copy helpers: a weight tile range is contiguous in the fragment planes, so
+// one cp.async.bulk moves all input groups of a work item's matrix at once.
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(void* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy(void* dst, const void* src, unsigned bytes, void* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try(void* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait (one second); false when it expired or the status word is already raised.
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* status) {
+    if (mbar_try(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (unsigned i = 0;; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 63u) == 63u) {
+            if (global_ns() - t0 > 1000000000ull || *reinterpret_cast<volatile int*>(status) != 0) {
+                atomicCAS(status, 0, 4);  // LUMEN_MOE_TIMEOUT
+                return false;
+            }
+        }
     }
 }
 
+// One lane's share of a staged tile: q words of the tile at qp (lane-major), scale words at sp.
 template <int Q>
-__device__ __forceinline__ void read_staged_tile(WTile<Q>& w, const uint4* slot, int lane) {
+__device__ __forceinline__ void read_staged(WTile<Q>& w, const uint4* qp, const uint4* sp, int lane) {
 #pragma unroll
-    for (int j = 0; j < QTraits<Q>::NQ; ++j) w.q[j] = slot[j * 32 + lane];
-    if (Q != BF16) w.s = slot[QTraits<Q>::NQ * 32 + (lane >> 2)];
+    for (int j = 0; j < QTraits<Q>::NQ; ++j) w.q[j] = qp[j * 32 + lane];
+    if (Q != BF16) w.s = sp[lane >> 2];
 }
 
 struct RouteSm {
@@ -162,7 +188,7 @@ struct TopkSm {
 
 template <int Q>
 __global__ void __launch_bounds__(FT, 1)
-decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, const int gs_slots) {
+decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, const int gs_slots) {
     extern __shared__ uint4 dyn[];
     __shared__ __align__(16) TopkSm ts;
     __shared__ float red_a[FW][FMAX_T];
@@ -170,6 +196,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     __shared__ float red[FW][16][4][2];
     __shared__ RouteSm rs;
     __shared__ int fail_s;
+    __shared__ __align__(8) unsigned long long mbar[8];  // 0..6: staged gate/up items, 7: staged down tiles
 
     pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -178,7 +205,11 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     };
     stamp(0);
     if (tid < 32) ts.tab[tid] = lumen_exact::exp2_tab_entry(tid);
-    if (tid == 0) fail_s = 0;
+    if (tid == 0) {
+        fail_s = 0;
+        for (int i = 0; i < 8; ++i) mbar_init(&mbar[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     const int gq = lane >> 2, t4 = lane & 3;
     const int cta = blockIdx.x, G = gridDim.x;
     const int H = a.L.H, I = a.L.I, E = a.L.E, T = a.T, K = a.K;
@@ -197,8 +228,11 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     float* wd = part + (size_t)C * kg_i * 64;         // [C][16] weighted expert outputs
     // the f32 activations of phase A share the ss/part/wd region, whichever is larger
     const size_t mid_bytes = max((size_t)C * per_col_i * 16 + (size_t)C * kg_i * 256 + (size_t)C * 64, (size_t)T * H * 4);
-    uint4* pf = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(ss) + mid_bytes);  // [FW][pf_slots][TU4]
-    uint4* gs = pf + (size_t)FW * pf_slots * TU4;     // [gs_slots][FW][gate, up][TU4] staged gate/up tiles
+    // staged down tiles of this CTA's 16 output rows: [pf_experts][q of kg_i tiles | scales of kg_i tiles]
+    uint4* pf = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(ss) + mid_bytes);
+    // staged gate/up tiles: [gs_slots][gate | up][q of kg_h tiles | scales of kg_h tiles]
+    uint4* gs = pf + (size_t)pf_experts * kg_i * TU4;
+    constexpr int NQ32 = QTraits<Q>::NQ * 32;
 
     // ---------------- phase A ----------------
     // first router row in registers before waiting on the previous kernel (weights are static)
@@ -366,42 +400,41 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     const int rt_i = a.L.rt_i;
     const int it0 = G - 1 - cta;  // work items of this CTA: G-1-cta, then every G-th (CTAs without down rows first)
     const bool has_down = cta < a.L.rt_h;
-    auto stage_tile = [&](uint4* slot, const uint4* qbase, const uint4* sbase, int tile) {
-        const uint4* qp = qbase + ((size_t)tile * QTraits<Q>::NQ) * 32 + lane;
-#pragma unroll
-        for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(slot + j * 32 + lane, qp + j * 32);
-        if (Q != BF16 && lane < 8) cp_async16(slot + QTraits<Q>::NQ * 32 + lane, sbase + (size_t)tile * 8 + lane);
-    };
-    // Requests every byte this CTA needs for the experts ue[0..nu): the tiles of its first
-    // gs_slots gate/up items (one commit group per item), then the down tiles of its 16
-    // output rows (last group).
-    auto stage_all = [&](const int* ue, int nu, int swarp, int n_swarps) {
+    // Requests every byte this CTA needs for the experts ue[0..nu), called by ONE warp: the
+    // tiles of its first gs_slots gate/up items (all input groups of a matrix are contiguous:
+    // one bulk copy for the quants, one for the scales; barrier j counts item j's bytes), then
+    // the down tiles of its 16 output rows for the first pf_experts experts (barrier 7).
+    auto stage_all = [&](const int* ue, int nu) {
         const int n_items_ = nu * rt_i;
         const int n_my_ = (it0 < n_items_) ? (n_items_ - it0 + G - 1) / G : 0;
         const int n_st_ = min(n_my_, gs_slots);
+        const int n_pf_ = has_down ? min(nu, pf_experts) : 0;
+        const unsigned q_gu = (unsigned)kg_h * NQ32 * 16, s_gu = (Q != BF16) ? (unsigned)kg_h * 128 : 0u;
+        const unsigned q_dn = (unsigned)kg_i * NQ32 * 16, s_dn = (Q != BF16) ? (unsigned)kg_i * 128 : 0u;
+        if (lane < n_st_) mbar_expect_tx(&mbar[lane], 2u * (q_gu + s_gu));
+        if (lane == 7) mbar_expect_tx(&mbar[7], (unsigned)n_pf_ * (q_dn + s_dn));
+        __syncwarp();
+        constexpr int PER = (Q != BF16) ? 2 : 1;  // copies per matrix: quants, scales
 #pragma unroll 1
-        for (int j = 0; j < n_st_; ++j) {
+        for (int c = lane; c < n_st_ * 2 * PER; c += 32) {
+            const int j = c / (2 * PER), r = c - j * 2 * PER;
+            const int mat = r / PER, is_s = r - mat * PER;
             const int it = it0 + j * G;
             const int u = it / rt_i, rt = it - u * rt_i;
             const int e = ue[u];
-#pragma unroll 1
-            for (int kg = swarp; kg < kg_h; kg += n_swarps) {
-                uint4* slot = gs + ((size_t)(j * FW + kg) * 2) * TU4;
-                stage_tile(slot, a.L.gate_q(e), a.L.gate_s(e), rt * kg_h + kg);
-                stage_tile(slot + TU4, a.L.up_q(e), a.L.up_s(e), rt * kg_h + kg);
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+            uint4* dst = gs + ((size_t)(j * 2 + mat) * kg_h) * TU4 + (is_s ? kg_h * NQ32 : 0);
+            const uint4* src = is_s ? (mat ? a.L.up_s(e) : a.L.gate_s(e)) + (size_t)rt * kg_h * 8
+                                    : (mat ? a.L.up_q(e) : a.L.gate_q(e)) + (size_t)rt * kg_h * NQ32;
+            bulk_copy(dst, src, is_s ? s_gu : q_gu, &mbar[j]);
         }
-        if (has_down) {
-            const int n_down_ = min(nu * kg_i, FW * pf_slots);
 #pragma unroll 1
-            for (int n = swarp; n < n_down_; n += n_swarps) {
-                const int uu = n / kg_i, kg = n - uu * kg_i;
-                stage_tile(pf + ((size_t)(n % FW) * pf_slots + n / FW) * TU4, a.L.down_q(ue[uu]), a.L.down_s(ue[uu]),
-                           cta * kg_i + kg);
-            }
+        for (int c = lane; c < n_pf_ * PER; c += 32) {
+            const int uu = c / PER, is_s = c - uu * PER;
+            const int ee = ue[uu];
+            uint4* dst = pf + ((size_t)uu * kg_i) * TU4 + (is_s ? kg_i * NQ32 : 0);
+            const uint4* src = is_s ? a.L.down_s(ee) + (size_t)cta * kg_i * 8 : a.L.down_q(ee) + (size_t)cta * kg_i * NQ32;
+            bulk_copy(dst, src, is_s ? s_dn : q_dn, &mbar[7]);
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
     };
     {
         // Four warps per token share the exps; then warp 0 of the four finishes the token
@@ -491,8 +524,8 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
                 rs.pr_U = tot;
             }
             asm volatile("bar.sync 6, %0;" ::"r"(n_sthreads) : "memory");
-            stage_all(rs.pr_ue, rs.pr_U, swarp, n_swarps);
-            stamp(11);
+            if (swarp == 0) stage_all(rs.pr_ue, rs.pr_U);
+            if (a.trace != nullptr && tid == 32) a.trace[(size_t)blockIdx.x * 12 + 10] = global_ns();
         }
         __syncthreads();
     }
@@ -504,9 +537,23 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
         bool same = (U == rs.pr_U);
         if (same && tid < U) same = (rs.ue[tid] == rs.pr_ue[tid]);
         if (__syncthreads_or(same ? 0 : 1)) {
-            cp_async_wait_all();  // the copies of the wrong prediction land in the same slots
+            // wrong prediction: let its copies land (they target the same slots), start the
+            // barriers afresh and request the right tiles
+            const int n_items_p = rs.pr_U * rt_i;
+            const int n_my_p = (it0 < n_items_p) ? (n_items_p - it0 + G - 1) / G : 0;
+            bool ok = true;
+            for (int j = 0; j < min(n_my_p, gs_slots) && ok; ++j) ok = mbar_wait(&mbar[j], 0, a.status);
+            ok = ok && mbar_wait(&mbar[7], 0, a.status);
+            if (__syncthreads_or(ok ? 0 : 1)) return;
+            if (tid == 0) {
+                for (int i = 0; i < 8; ++i) {
+                    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_addr(&mbar[i])) : "memory");
+                    mbar_init(&mbar[i], 1);
+                }
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            }
             __syncthreads();
-            stage_all(rs.ue, U, warp, FW);
+            if (warp == 0) stage_all(rs.ue, U);
         }
     }
     auto load_gu = [&](int it, WTile<Q>& g, WTile<Q>& up) {
@@ -592,13 +639,13 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
 #pragma unroll 1
     for (int j = 0; j < n_my; ++j) {
         if (j < n_st) {
-            // item j's group is complete once at most (n_st - 1 - j) + 1 younger groups are pending
-            cp_async_wait_pending(n_st - j);  // (threads that requested nothing have nothing pending)
-            __syncthreads();                  // tiles are staged by other warps than the ones that use them
+            if (!mbar_wait(&mbar[j], 0, a.status)) return;  // every thread waits: all of them give up together
+            if (a.trace != nullptr && tid == 32 && j == n_st - 1) a.trace[(size_t)blockIdx.x * 12 + 11] = global_ns();
             if (warp < kg_h) {
-                const uint4* slot = gs + ((size_t)(j * FW + warp) * 2) * TU4;
-                read_staged_tile<Q>(wg0, slot, lane);
-                read_staged_tile<Q>(wu0, slot + TU4, lane);
+                const uint4* gq_ = gs + ((size_t)(j * 2) * kg_h) * TU4;
+                const uint4* uq_ = gq_ + (size_t)kg_h * TU4;
+                read_staged<Q>(wg0, gq_ + warp * NQ32, gq_ + kg_h * NQ32 + warp * 8, lane);
+                read_staged<Q>(wu0, uq_ + warp * NQ32, uq_ + kg_h * NQ32 + warp * 8, lane);
             }
         } else {
             wg0 = wg1;
@@ -614,19 +661,17 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     __syncthreads();
     grid_arrive(a.bar);
     if (!grid_wait(a.bar, a.status, G, ++epoch, &fail_s)) {
-        cp_async_wait_all();
+        mbar_wait(&mbar[7], 0, a.status);  // bounded: do not leave with the down copies in flight
         return;
     }
     if (tid == 0) a.bar[1 + cta] = epoch;
     stamp(6);
 
     // ---------------- phase C: down + combine ----------------
-    if (!has_down) {
-        cp_async_wait_all();
-        return;
-    }
+    if (!has_down) return;  // (no down tiles were requested for this CTA)
     for (int i = tid; i < C * per_col_i; i += FT) cp_async16(&ss[i], a.sf + i);
     cp_async_wait_all();
+    if (!mbar_wait(&mbar[7], 0, a.status)) return;
     __syncthreads();
     stamp(7);
     {
@@ -642,10 +687,11 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
             for (int j = 0; j < DG; ++j) {
                 const int i = i0 + j;
                 nn[j] = min(warp + FW * i, n_down - 1);
-                if (i < pf_slots) {
-                    read_staged_tile<Q>(w[j], pf + ((size_t)warp * pf_slots + i) * TU4, lane);
+                const int uu = nn[j] / kg_i, kg = nn[j] - uu * kg_i;
+                if (uu < pf_experts) {
+                    const uint4* base = pf + ((size_t)uu * kg_i) * TU4;
+                    read_staged<Q>(w[j], base + kg * NQ32, base + kg_i * NQ32 + kg * 8, lane);
                 } else {
-                    const int uu = nn[j] / kg_i, kg = nn[j] - uu * kg_i;
                     const int ee = rs.ue[uu];
                     load_wtile<Q>(w[j], a.L.down_q(ee), a.L.down_s(ee), rt * kg_i + kg, lane);
                 }
@@ -697,13 +743,14 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_slots, co
     stamp(9);
 }
 
-// Shared memory the fused kernel needs besides its static arrays; pf_slots = staged down tiles per warp.
-static size_t fused_smem_bytes(const DecodeArgs& a, int tile_u4, int pf_slots, int gs_slots = 0) {
+// Shared memory the fused kernel needs besides its static arrays; pf_experts = experts whose
+// down tiles are staged, gs_slots = staged gate/up work items.
+static size_t fused_smem_bytes(const DecodeArgs& a, int tile_u4, int pf_experts, int gs_slots = 0) {
     const size_t C = (size_t)a.T * a.K;
     const size_t mid = C * 2 * a.L.kg_i * 16 * 16 + C * a.L.kg_i * 256 + C * 64;
     const size_t xn = (size_t)a.T * a.L.H * 4;
-    return (size_t)a.T * 2 * a.L.kg_h * 16 * 16 + (mid > xn ? mid : xn) + (size_t)FW * pf_slots * tile_u4 * 16 +
-           (size_t)gs_slots * FW * 2 * tile_u4 * 16;
+    return (size_t)a.T * 2 * a.L.kg_h * 16 * 16 + (mid > xn ? mid : xn) +
+           (size_t)pf_experts * a.L.kg_i * tile_u4 * 16 + (size_t)gs_slots * 2 * a.L.kg_h * tile_u4 * 16;
 }
 
 static int tile_u4_of(int quant) {
@@ -747,13 +794,12 @@ static cudaError_t launch_fused_t(const DecodeArgs& a, int device, cudaStream_t 
     const FusedDeviceInfo& d = fused_device_info(device);
     const size_t static_smem = 20 * 1024;
     const int C = a.T * a.K;
-    const int want = (C * a.L.kg_i + FW - 1) / FW;  // down tiles per warp when every pair has its own expert
     // shared memory goes to the gate/up items of a CTA first (they are needed first), then to the down tiles
     const int nu_max = C < a.L.E ? C : a.L.E;
     int gs = (nu_max * a.L.rt_i + d.sms - 1) / d.sms;
     if (gs > 7) gs = 7;
     while (gs > 0 && fused_smem_bytes(a, TileU4<Q>::value, 0, gs) + static_smem > (size_t)d.smem_optin) --gs;
-    int pf = want;
+    int pf = nu_max;  // experts whose down tiles are staged
     while (pf > 0 && fused_smem_bytes(a, TileU4<Q>::value, pf, gs) + static_smem > (size_t)d.smem_optin) --pf;
     const size_t smem = fused_smem_bytes(a, TileU4<Q>::value, pf, gs);
     static size_t attr_smem[64] = {};

@@ -264,14 +264,16 @@ def run_gpu(args):
             tr = scratch.debug_decode_trace(layers[L - 1]).cpu().numpy().astype(np.int64)
             t0 = tr[:, 0].min()
             med = lambda i: float(np.median((tr[:, i][tr[:, i] > 0] - t0) / 1e3))
-            stamps = [med(i) for i in range(10)]
+            stamps = [med(i) for i in range(12)]
             kernel_us = {"decode_fused_kernel": k_ms * 1e3,
                          "phases_us_median_over_ctas": {
                              "wait_previous_kernel": stamps[1], "router_logits": stamps[2] - stamps[1],
                              "grid_barrier_1": stamps[3] - stamps[2], "topk_and_sort": stamps[4] - stamps[3],
                              "gate_up_swiglu": stamps[5] - stamps[4], "grid_barrier_2": stamps[6] - stamps[5],
                              "stage_swiglu": stamps[7] - stamps[6], "down": stamps[8] - stamps[7],
-                             "combine": stamps[9] - stamps[8]}}
+                             "combine": stamps[9] - stamps[8]},
+                         "since_kernel_start_us_median": {"tiles_requested": stamps[10], "last_gate_up_tile_arrived": stamps[11],
+                                                          "end": stamps[9]}}
         else:
             # each kernel of the chain alone, one launch per layer blob, CUDA events on the launch stream
             # (phase 1 = gate/up + SwiGLU is the dominant kernel)

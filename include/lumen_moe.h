@@ -259,8 +259,9 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_debug_decode_phase(lumen_moe_ctx* ctx
  * of 1..4 tokens) and records, per CTA, globaltimer stamps (ns): 0 entry, 1 after the
  * wait on the previous kernel, 2 logits done, 3 barrier 1 passed, 4 routing done,
  * 5 gate/up done, 6 barrier 2 passed, 7 SwiGLU fragments staged, 8 down products
- * done, 9 end (10, 11 unused). d_trace: [SM count][12] uint64 on the device, zeroed
- * by the caller.
+ * done, 9 end, 10 weight tiles requested (predicted expert set), 11 last staged
+ * gate/up tile arrived. d_trace: [SM count][12] uint64 on the device, zeroed by the
+ * caller.
  * LUMEN_MOE_UNSUPPORTED when the call's shape takes the three-kernel chain. */
 LUMEN_MOE_API lumen_moe_status_t lumen_moe_debug_decode_trace(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
                                                               uint64_t* d_trace, void* stream);

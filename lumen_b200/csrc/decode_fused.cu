@@ -438,13 +438,15 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     };
     {
         // Four warps per token share the exps; then warp 0 of the four finishes the token
-        // exactly while another warp ranks the raw logits. The warps that are not finishing a
-        // token (16 - T of them) then turn the predicted mask into a list and request the tiles.
+        // exactly while another warp ranks the raw logits and requests the tiles.
         const float* lg = want_logits ? a.R.logits : a.logits_override;
         const int tok = warp >> 2, sub = warp & 3;
         const bool selects = (tok < T) && (sub == 0);
-        const int n_swarps = FW - T;
-        const int swarp = warp - min(T, (warp + 3) >> 2);  // index among the staging warps
+        // predictor of token t: an idle warp when there is one (T <= 3; it reads the logits
+        // straight from L2 and does not wait for the exps), else warp 1 of the token's four
+        const bool idle_pred = (T < FMAX_T);
+        const bool predicts = idle_pred ? (warp >= 4 * T && warp < 5 * T) : (sub == 1);
+        const int pred_tok = idle_pred ? warp - 4 * T : tok;
         if (tid < MAX_EXPERTS / 32) rs.pr_mask[tid] = 0u;
         __syncthreads();
         if (tok < T) {
@@ -453,18 +455,32 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
             asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
             warp_gate_probs(ts.lg[tok], E, a.gating, ts.p[tok], ts.tab, sub, 4);
             asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
-            if (T == FMAX_T && sub == 1) warp_predict_mask(ts.lg[tok], E, K, rs.pr_mask);
-        } else if (warp < 4 * T + T) {
-            // with T <= 3 there are idle warps: they predict straight from the logits in L2,
-            // without waiting for the exps
-            const int t = warp - 4 * T;
-            warp_predict_mask(lg + (size_t)t * E, E, K, rs.pr_mask, true);
+        }
+        if (predicts) {
+            // rank the raw logits, merge the tokens' masks, and let the first predictor turn the
+            // mask into the ascending expert list and request the tiles: no other warp is involved
+            if (idle_pred) warp_predict_mask(lg + (size_t)pred_tok * E, E, K, rs.pr_mask, true);
+            else warp_predict_mask(ts.lg[tok], E, K, rs.pr_mask);
+            if (T > 1) asm volatile("bar.sync 6, %0;" ::"r"(T * 32) : "memory");
+            else __syncwarp();
+            if (pred_tok == 0) {
+                int below = 0;  // set bits in lower words
+#pragma unroll
+                for (int wi = 0; wi < MAX_EXPERTS / 32; ++wi) {
+                    const unsigned word = rs.pr_mask[wi];
+                    if ((word >> lane) & 1u) rs.pr_ue[below + __popc(word & ((1u << lane) - 1u))] = wi * 32 + lane;
+                    below += __popc(word);
+                }
+                if (lane == 0) rs.pr_U = below;
+                __syncwarp();
+                stage_all(rs.pr_ue, below);
+                if (a.trace != nullptr && lane == 0) a.trace[(size_t)blockIdx.x * 12 + 10] = global_ns();
+            }
         }
         if (selects) {
             warp_select(ts.p[tok], E, K, a.gating, reinterpret_cast<uint32_t*>(rs.ids) + tok * K, rs.w + tok * K);
             // the sort only needs the finishing warps: it does not wait for the warps that request tiles
             if (T > 1) asm volatile("bar.sync 11, %0;" ::"r"(T * 32) : "memory");
-            stamp(10);
             if (warp == 0) {
                 // stable counting sort of the C <= 32 pairs by expert, one pair per lane
                 const int my = (lane < C) ? rs.ids[lane] : 0x7fffffff;
@@ -507,25 +523,6 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
                     }
                 }
             }
-        } else {
-            const int n_sthreads = n_swarps * 32, stid = swarp * 32 + lane;
-            asm volatile("bar.sync 6, %0;" ::"r"(n_sthreads) : "memory");
-            for (int e = stid; e < E; e += n_sthreads) {
-                const unsigned word = rs.pr_mask[e >> 5];
-                if ((word >> (e & 31)) & 1u) {
-                    int pos = __popc(word & ((1u << (e & 31)) - 1u));
-                    for (int w = 0; w < (e >> 5); ++w) pos += __popc(rs.pr_mask[w]);
-                    rs.pr_ue[pos] = e;
-                }
-            }
-            if (stid == 0) {
-                int tot = 0;
-                for (int w = 0; w < MAX_EXPERTS / 32; ++w) tot += __popc(rs.pr_mask[w]);
-                rs.pr_U = tot;
-            }
-            asm volatile("bar.sync 6, %0;" ::"r"(n_sthreads) : "memory");
-            if (swarp == 0) stage_all(rs.pr_ue, rs.pr_U);
-            if (a.trace != nullptr && tid == 32) a.trace[(size_t)blockIdx.x * 12 + 10] = global_ns();
         }
         __syncthreads();
     }
@@ -640,7 +637,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     for (int j = 0; j < n_my; ++j) {
         if (j < n_st) {
             if (!mbar_wait(&mbar[j], 0, a.status)) return;  // every thread waits: all of them give up together
-            if (a.trace != nullptr && tid == 32 && j == n_st - 1) a.trace[(size_t)blockIdx.x * 12 + 11] = global_ns();
+            if (a.trace != nullptr && tid == 0 && j == n_st - 1) a.trace[(size_t)blockIdx.x * 12 + 11] = global_ns();
             if (warp < kg_h) {
                 const uint4* gq_ = gs + ((size_t)(j * 2) * kg_h) * TU4;
                 const uint4* uq_ = gq_ + (size_t)kg_h * TU4;

@@ -272,6 +272,7 @@ lumen_moe_status_t lumen_moe_get_routing(lumen_moe_ctx* ctx, int32_t tokens, uin
     if (dev_status != 0) {
         cudaMemset(s.status, 0, 4);
         cudaMemset(s.bar, 0, 1024 * 4);
+        cudaMemset(s.R.logits, 0, (size_t)s.cap_tokens * s.E * 4);  // tagged logit slots of the fused decode kernel
         return fail(dev_status, "a device-side bounded wait expired (grouped GEMM pipeline or decode grid barrier)");
     }
     return LUMEN_MOE_OK;

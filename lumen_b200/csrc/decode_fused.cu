@@ -59,6 +59,19 @@ __device__ __forceinline__ void red_release_add_u32(unsigned* p, unsigned v) {
     asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Barrier 1 carries its payload: each logit travels as one 8-byte word {value, launch tag},
+// written with a single store and polled by one thread per (token, expert) until the tag is
+// this launch's: when the wait is over the logits are already in hand (one L2 round trip
+// instead of flag + data).
+__device__ __forceinline__ void st_tagged(float* slot, float v, unsigned tag) {
+    asm volatile("st.relaxed.gpu.global.v2.b32 [%0], {%1, %2};" ::"l"(slot), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_tagged(const float* slot) {
+    uint2 r;
+    asm volatile("ld.relaxed.gpu.global.v2.b32 {%0, %1}, [%2];" : "=r"(r.x), "=r"(r.y) : "l"(slot) : "memory");
+    return r;
+}
+
 // Grid barrier: one arrival counter that only grows (bar[0]); barrier number `epoch`
 // (counted per CTA in bar[1 + cta], written by that CTA alone) is passed when the
 // counter reaches epoch * G, compared modulo 2^32, so nothing is reset between
@@ -312,15 +325,13 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
                 float v = 0.0f;
 #pragma unroll
                 for (int w = 0; w < FW; ++w) v += red_a[w][tid];
-                a.R.logits[(size_t)tid * E + e] = v;
+                st_tagged(a.R.logits + 2 * ((size_t)tid * E + e), v, epoch + 1u);  // tag = this launch's barrier number
             }
             __syncthreads();
         }
     }
-    // logits are out (the loop above ends on a CTA barrier): arrive now, build the
-    // activation fragments while the other CTAs catch up
+    // logits are out: build the activation operand while the other CTAs catch up
     __syncthreads();
-    if (want_logits) grid_arrive(a.bar);
     // activation operand of every token, private to this CTA
     // int8 form: per token [2 terms][nblk_pad * 8 + 8 words] then [nblk_pad] {sx, 8 * sx * sum}; inside a block
     // the word pair of lane quad t is adjacent: {inputs 4t..4t+3, inputs 16+4t..16+4t+3}
@@ -382,10 +393,41 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
         }
     }
     stamp(2);
-    if (want_logits) {
-        if (!grid_wait(a.bar, a.status, G, ++epoch, &fail_s)) return;
-    } else {
+    // barrier 1: wait for (and fetch) every logit of this launch
+    {
+        const float* lg = a.logits_override;
+        bool ok = true;
+#pragma unroll 1
+        for (int i = tid; i < T * E; i += FT) {
+            const int t = i / E, e = i - t * E;
+            float v;
+            if (want_logits) {
+                const float* slot = a.R.logits + 2 * (size_t)i;
+                uint2 r = ld_tagged(slot);
+                unsigned long long t0 = 0;
+                unsigned spins = 0;
+                while (r.y != epoch + 1u) {
+                    if ((++spins & 63u) == 0) {
+                        if (t0 == 0) t0 = global_ns();
+                        if (global_ns() - t0 > 1000000000ull || *reinterpret_cast<volatile int*>(a.status) != 0) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    r = ld_tagged(slot);
+                }
+                v = __uint_as_float(r.x);
+            } else {
+                v = __ldcg(lg + i);
+            }
+            ts.lg[t][e] = v;
+        }
+        if (!ok) {
+            atomicCAS(a.status, 0, 4);  // LUMEN_MOE_TIMEOUT
+            fail_s = 1;
+        }
         __syncthreads();
+        if (fail_s) return;
     }
     stamp(3);
 
@@ -439,28 +481,23 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     {
         // Four warps per token share the exps; then warp 0 of the four finishes the token
         // exactly while another warp ranks the raw logits and requests the tiles.
-        const float* lg = want_logits ? a.R.logits : a.logits_override;
         const int tok = warp >> 2, sub = warp & 3;
         const bool selects = (tok < T) && (sub == 0);
-        // predictor of token t: an idle warp when there is one (T <= 3; it reads the logits
-        // straight from L2 and does not wait for the exps), else warp 1 of the token's four
+        // predictor of token t: an idle warp when there is one (T <= 3; it does not wait for
+        // the exps), else warp 1 of the token's four
         const bool idle_pred = (T < FMAX_T);
         const bool predicts = idle_pred ? (warp >= 4 * T && warp < 5 * T) : (sub == 1);
         const int pred_tok = idle_pred ? warp - 4 * T : tok;
         if (tid < MAX_EXPERTS / 32) rs.pr_mask[tid] = 0u;
         __syncthreads();
         if (tok < T) {
-#pragma unroll 1
-            for (int i = sub * 32 + lane; i < E; i += 128) ts.lg[tok][i] = __ldcg(lg + (size_t)tok * E + i);
-            asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
             warp_gate_probs(ts.lg[tok], E, a.gating, ts.p[tok], ts.tab, sub, 4);
             asm volatile("bar.sync %0, 128;" ::"r"(1 + tok) : "memory");
         }
         if (predicts) {
             // rank the raw logits, merge the tokens' masks, and let the first predictor turn the
             // mask into the ascending expert list and request the tiles: no other warp is involved
-            if (idle_pred) warp_predict_mask(lg + (size_t)pred_tok * E, E, K, rs.pr_mask, true);
-            else warp_predict_mask(ts.lg[tok], E, K, rs.pr_mask);
+            warp_predict_mask(ts.lg[pred_tok], E, K, rs.pr_mask);
             if (T > 1) asm volatile("bar.sync 6, %0;" ::"r"(T * 32) : "memory");
             else __syncwarp();
             if (pred_tok == 0) {

@@ -168,26 +168,25 @@ __device__ __forceinline__ void warp_select(const float* smem_p, int E, int K, i
 // with the largest raw logits, lowest index first among equals: a prediction of the
 // selected SET that needs no exp (the gate functions are monotonic), used to start weight
 // traffic early; the caller verifies it against warp_select's result.
-// from_l2: `logits` is global memory written by other SMs during this launch (read through L2).
-__device__ __forceinline__ void warp_predict_mask(const float* logits, int E, int K, unsigned* mask,
-                                                  bool from_l2 = false) {
+template <int NS>  // NS * 32 >= E
+__device__ __forceinline__ void warp_predict_mask_n(const float* logits, int E, int K, unsigned* mask) {
     const int lane = threadIdx.x & 31;
-    unsigned key[8];
+    unsigned key[NS];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < NS; ++i) {
         const int e = lane + 32 * i;
-        const unsigned b = (e < E) ? __float_as_uint(from_l2 ? __ldcg(logits + e) : logits[e]) : 0u;
+        const unsigned b = (e < E) ? __float_as_uint(logits[e]) : 0u;
         // order-preserving map of finite floats to unsigned, shifted so that 0 stays free for "taken / padding"
         const unsigned k = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
         key[i] = (e < E) ? max(k, 1u) : 0u;
     }
-    unsigned mine[MAX_EXPERTS / 32] = {};
+    int my_win = -1;  // lane k keeps the k-th winner
 #pragma unroll 1
     for (int k = 0; k < K; ++k) {
         unsigned hk = key[0];
         int hi = 0;
 #pragma unroll
-        for (int i = 1; i < 8; ++i) {
+        for (int i = 1; i < NS; ++i) {
             if (key[i] > hk) {
                 hk = key[i];
                 hi = i;
@@ -196,17 +195,17 @@ __device__ __forceinline__ void warp_predict_mask(const float* logits, int E, in
         const unsigned mk = __reduce_max_sync(0xffffffffu, hk);
         const int win = __reduce_min_sync(0xffffffffu, (hk == mk) ? lane + 32 * hi : 0x7fffffff);
         if (mk == 0u) break;
+        if (lane == k) my_win = win;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            if (lane + 32 * i == win) {
-                key[i] = 0u;
-                mine[i] |= 1u << lane;  // expert lane + 32 i lives in word i, bit lane
-            }
-        }
+        for (int i = 0; i < NS; ++i)
+            if (lane + 32 * i == win) key[i] = 0u;
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-        if (mine[i]) atomicOr(&mask[i], mine[i]);
+    if (my_win >= 0) atomicOr(&mask[my_win >> 5], 1u << (my_win & 31));
+}
+
+__device__ __forceinline__ void warp_predict_mask(const float* logits, int E, int K, unsigned* mask) {
+    if (E <= 128) warp_predict_mask_n<4>(logits, E, K, mask);
+    else warp_predict_mask_n<8>(logits, E, K, mask);
 }
 
 __device__ __forceinline__ void warp_topk(const float* __restrict__ logits, int E, int K, int gating,

@@ -98,10 +98,10 @@ cudaError_t launch_repack(const uint8_t* blob, const uint64_t* d_gate_offs, cons
                           const uint64_t* d_down_offs, const LayerDev& L, uint4* q, uint4* s,
                           cudaStream_t st);
 cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t st);
-cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st);
+cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st);  // router + tables only (T <= 16)
 bool decode_fused_applicable(const DecodeArgs& a);
 cudaError_t launch_decode_fused(const DecodeArgs& a, cudaStream_t st);
-cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st);  // router + tables only (T<=16)
+cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st);  // one kernel of the three-kernel chain: 0 router, 1 gate/up, 2 down
 cudaError_t launch_quantize(const float* src, int64_t n, int quant, void* dst, cudaStream_t st);
 cudaError_t launch_rmsnorm(const float* x, const float* gamma, float* out, int T, int H, float eps,
                            cudaStream_t st);

@@ -142,7 +142,6 @@ struct Args {
     int kdim;               // H (gate/up) or I (down)
     int out_ld;             // I or H
     const int32_t* out_row_map;  // down mode: output row of compact column c (null = c itself)
-    int dbg;                // timing experiments only (LUMEN_TC_DBG): 1 skip dequant, 2 skip activation copies, 4 skip stores
 };
 
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
@@ -287,7 +286,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 tmem_ld_wait();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    if (n0 + j < ncols && !(a.dbg & 4)) {
+                    if (n0 + j < ncols) {
                         int orow_idx = tile.y + n0 + j;
                         if (MODE == 1 && a.out_row_map != nullptr) orow_idx = a.out_row_map[orow_idx];
                         __half* dst = a.out16 + (size_t)orow_idx * a.out_ld;
@@ -342,7 +341,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                     const uint32_t sbase = stage0 + s * STAGE_BYTES;
 #pragma unroll
                     for (int op = 0; op < NA; ++op)
-                        if (!(a.dbg & 1)) dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
+                        dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
                     fence_proxy_async();
                     mbar_arrive(smem_u32(&full_bar[s]));
                 }
@@ -381,10 +380,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&full_bar[s]);
                 const uint32_t bbase = stage0 + s * STAGE_BYTES + NA * SUB_BYTES;
-                if (a.dbg & 2) {
-                    mbar_arrive(bar);
-                    continue;
-                }
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nbox * SUB_BYTES)
                              : "memory");
                 for (int q = 0; q < nbox; ++q)
@@ -534,10 +529,6 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     gu.status = p.status;
     gu.kdim = p.L.H;
     gu.out_ld = p.L.I;
-    {
-        const char* d = std::getenv("LUMEN_TC_DBG");
-        gu.dbg = d ? std::atoi(d) : 0;
-    }
     tc::Args dn = gu;
     te = make_tmap(p.s16, (uint64_t)C, (uint64_t)p.L.I, &dn.tmap);
     if (te != cudaSuccess) return te;

@@ -226,6 +226,15 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_get_routing_device(lumen_moe_ctx* ctx
                                                               int32_t* d_col_expert, int32_t* d_expert_bounds,
                                                               void* stream);
 
+/* Expert-parallel send side, after lumen_moe_route_only on the same context: in one launch,
+ * d_rows_bf16 [T*K, H] = the activation rows in compact-column order (rows for rank r are
+ * contiguous, experts being contiguous per rank), d_local_ids [T*K] = expert id relative to
+ * its rank, d_send_counts [E / experts_per_rank] (int64) = rows per destination rank.
+ * (The reference is single-GPU; this belongs to the additive expert-parallel form.) */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_ep_prepare(lumen_moe_ctx* ctx, const void* d_normed, int32_t act_dtype,
+                                                      int32_t tokens, int32_t experts_per_rank, void* d_rows_bf16,
+                                                      int32_t* d_local_ids, int64_t* d_send_counts, void* stream);
+
 /* Device restatement of quantize_f32_to_q4_0 / _q8_0
  * (crates/lumen-convert/src/dequant.rs:791-906) and of round-to-nearest-even BF16,
  * used to synthesise weights in HBM. n_elements multiple of 32. */

@@ -50,6 +50,7 @@ SIGNATURES = {
     "lumen_moe_set_logits_override": [vp, vp],
     "lumen_moe_get_routing": [vp, i32, vp, vp, vp, vp, vp, vp],
     "lumen_moe_get_routing_device": [vp, i32, vp, vp, vp, vp, vp],
+    "lumen_moe_ep_prepare": [vp, vp, i32, i32, i32, vp, vp, vp, vp],
     "lumen_moe_quantize": [vp, i64, i32, vp, vp],
     "lumen_moe_rmsnorm": [vp, vp, vp, i32, i32, f32, vp],
     "lumen_moe_stack_decode": [vp, vp, vp, i32, vp, f32, i32, vp],

@@ -296,6 +296,24 @@ lumen_moe_status_t lumen_moe_get_routing_device(lumen_moe_ctx* ctx, int32_t toke
     return LUMEN_MOE_OK;
 }
 
+lumen_moe_status_t lumen_moe_ep_prepare(lumen_moe_ctx* ctx, const void* d_normed, int32_t act_dtype, int32_t tokens,
+                                        int32_t experts_per_rank, void* d_rows_bf16, int32_t* d_local_ids,
+                                        int64_t* d_send_counts, void* stream) {
+    if (!ctx || !d_normed || !d_rows_bf16 || !d_local_ids || !d_send_counts)
+        return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    const lumen::CudaMoeScratch& s = ctx->scratch;
+    if (tokens < 1 || tokens > s.cap_tokens) return fail(LUMEN_MOE_INVALID_ARG, "tokens exceeds the last call's capacity");
+    if (experts_per_rank < 1 || s.E % experts_per_rank != 0)
+        return fail(LUMEN_MOE_INVALID_ARG, "experts_per_rank must divide num_experts");
+    if (s.H % 8 != 0) return fail(LUMEN_MOE_UNSUPPORTED, "hidden_dim must be a multiple of 8");
+    if (act_dtype != 0 && act_dtype != 1) return fail(LUMEN_MOE_INVALID_ARG, "unknown activation dtype");
+    cudaError_t e = lumen::launch_ep_prepare(d_normed, act_dtype, s.R, tokens * s.K, s.H, s.E, experts_per_rank, d_rows_bf16,
+                                             d_local_ids, reinterpret_cast<long long*>(d_send_counts),
+                                             static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
+}
+
 lumen_moe_status_t lumen_moe_quantize(const float* d_src, int64_t n_elements, int32_t quant, void* d_dst,
                                       void* stream) {
     if (!d_src || !d_dst) return fail(LUMEN_MOE_INVALID_ARG, "null argument");

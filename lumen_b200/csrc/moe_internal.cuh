@@ -98,6 +98,8 @@ cudaError_t launch_repack(const uint8_t* blob, const uint64_t* d_gate_offs, cons
                           const uint64_t* d_down_offs, const LayerDev& L, uint4* q, uint4* s,
                           cudaStream_t st);
 cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t st);
+cudaError_t launch_ep_prepare(const void* x, int act_dtype, const RouteDev& R, int C, int H, int E, int epr, void* rows,
+                              int32_t* local_ids, long long* send_counts, cudaStream_t st);
 cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st);  // router + tables only (T <= 16)
 bool decode_fused_applicable(const DecodeArgs& a);
 cudaError_t launch_decode_fused(const DecodeArgs& a, cudaStream_t st);

@@ -578,4 +578,41 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// Expert-parallel send side in one launch: activation rows gathered in compact-column
+// order (= destination-rank order, experts being contiguous per rank) as bf16, the
+// expert id of every row relative to its rank, and the number of rows per rank.
+// ---------------------------------------------------------------------------
+template <typename XT>
+__global__ void __launch_bounds__(256)
+ep_prepare_kernel(const XT* __restrict__ x, RouteDev R, int H, int E, int epr, __nv_bfloat16* __restrict__ rows,
+                  int32_t* __restrict__ local_ids, long long* __restrict__ send_counts) {
+    const int col = blockIdx.x;
+    const int tok = R.col_src_tok[col];
+    const XT* src = x + (size_t)tok * H;
+    __nv_bfloat16* dst = rows + (size_t)col * H;
+    for (int i = threadIdx.x * 8; i < H; i += 256 * 8) {
+        __align__(16) __nv_bfloat16 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __float2bfloat16_rn(x_to_f32<XT>(src[i + j]));
+        *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(v);
+    }
+    if (threadIdx.x == 0) local_ids[col] = R.col_expert[col] % epr;
+    if (col == 0) {
+        for (int r = threadIdx.x; r * epr < E; r += 256)
+            send_counts[r] = (long long)(R.expert_bounds[min((r + 1) * epr, E)] - R.expert_bounds[r * epr]);
+    }
+}
+
+cudaError_t launch_ep_prepare(const void* x, int act_dtype, const RouteDev& R, int C, int H, int E, int epr, void* rows,
+                              int32_t* local_ids, long long* send_counts, cudaStream_t st) {
+    count_launch();
+    if (act_dtype == 0)
+        ep_prepare_kernel<float><<<C, 256, 0, st>>>((const float*)x, R, H, E, epr, (__nv_bfloat16*)rows, local_ids, send_counts);
+    else
+        ep_prepare_kernel<__nv_bfloat16><<<C, 256, 0, st>>>((const __nv_bfloat16*)x, R, H, E, epr, (__nv_bfloat16*)rows,
+                                                            local_ids, send_counts);
+    return cudaGetLastError();
+}
+
 }  // namespace lumen

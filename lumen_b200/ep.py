@@ -96,7 +96,13 @@ class ExpertParallelMoe:
         routed = self.route_fn(normed)
         ids, w = routed[0], routed[1]
         self._mark("route")
-        if len(routed) > 2:
+        rows = None
+        if len(routed) > 2 and "rows" in routed[2]:
+            # the library produced the whole send side in one launch
+            tables = routed[2]
+            rows, local_ids, send_counts = tables["rows"], tables["local_ids"], tables["send_counts"]
+            order = None
+        elif len(routed) > 2:
             # the router's own counting sort is the send plan (compact-column order)
             tables = routed[2]
             tok = tables["col_src_tok"].to(torch.int64)
@@ -119,7 +125,8 @@ class ExpertParallelMoe:
         send_l, recv_l = sc.tolist(), rc.tolist()  # the one host sync of the call (NCCL sizes are host arguments)
         self._mark("plan+counts")
         # (3) dispatch rows and local expert ids
-        rows = normed[tok].to(self.wire_dtype)
+        if rows is None:
+            rows = normed[tok].to(self.wire_dtype)
         recv_rows = all_to_all_v(rows, send_l, recv_l, self.group)
         recv_ids = all_to_all_v(local_ids, send_l, recv_l, self.group)
         self._mark("dispatch")
@@ -172,7 +179,10 @@ def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.
 
     def route_fn(x):
         ids, w = route_sc.route_only(route_layer, x.float().contiguous())
-        return ids, w, route_sc.get_routing_device(x.shape[0], x.device)
+        rows, local_ids, send_counts = route_sc.ep_prepare(x.contiguous(), epr)
+        d2c = torch.empty(x.shape[0] * K, dtype=torch.int32, device=x.device)
+        route_sc.get_routing_device_into(x.shape[0], dst_to_col=d2c)
+        return ids, w, {"rows": rows, "local_ids": local_ids, "send_counts": send_counts, "dst_to_col": d2c}
 
     def expert_fn(rows, local_ids):
         if rows.shape[0] == 0:

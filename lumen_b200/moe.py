@@ -259,6 +259,13 @@ class MoeScratch:
         self._override = logits
         check(_lib.lib().lumen_moe_set_logits_override(self._h, _ptr(logits)))
 
+    def get_routing_device_into(self, tokens: int, dst_to_col=None, col_src_tok=None, col_expert=None,
+                                expert_bounds=None) -> None:
+        """Copies the chosen sort tables of the last routing call into the caller's int32 device tensors."""
+        p = lambda t: t.data_ptr() if t is not None else None
+        check(_lib.lib().lumen_moe_get_routing_device(self._h, tokens, p(dst_to_col), p(col_src_tok), p(col_expert),
+                                                      p(expert_bounds), _stream()))
+
     def get_routing_device(self, tokens: int, device):
         """Sort tables of the last routing call as device tensors (no host sync)."""
         C = tokens * self.K
@@ -269,6 +276,18 @@ class MoeScratch:
         check(_lib.lib().lumen_moe_get_routing_device(self._h, tokens, d2c.data_ptr(), cst.data_ptr(), cex.data_ptr(),
                                                       bounds.data_ptr(), _stream()))
         return {"dst_to_col": d2c, "col_src_tok": cst, "col_expert": cex, "expert_bounds": bounds}
+
+    def ep_prepare(self, normed: torch.Tensor, experts_per_rank: int):
+        """lumen_moe_ep_prepare after route_only: (rows bf16 [T*K,H], local_ids int32 [T*K], send_counts int64 [G])."""
+        act = ACT_F32 if normed.dtype == torch.float32 else ACT_BF16
+        T = normed.numel() // self.H
+        dev = normed.device
+        rows = torch.empty((T * self.K, self.H), dtype=torch.bfloat16, device=dev)
+        local_ids = torch.empty(T * self.K, dtype=torch.int32, device=dev)
+        send_counts = torch.empty(self.E // experts_per_rank, dtype=torch.int64, device=dev)
+        check(_lib.lib().lumen_moe_ep_prepare(self._h, normed.data_ptr(), act, T, experts_per_rank, rows.data_ptr(),
+                                              local_ids.data_ptr(), send_counts.data_ptr(), _stream()))
+        return rows, local_ids, send_counts
 
     def get_routing(self, tokens: int):
         C = tokens * self.K

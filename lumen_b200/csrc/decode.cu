@@ -402,9 +402,19 @@ gate_up_kernel(const __grid_constant__ DecodeArgs a) {
 // ---------------------------------------------------------------------------
 // down + weighted combine (decode: every expert has at most 16 columns)
 // ---------------------------------------------------------------------------
-constexpr int DC_THREADS = 256;
+constexpr int DC_THREADS = 512;
 constexpr int DC_WARPS = DC_THREADS / 32;
 constexpr int DC_MAX_COLS = DECODE_MAX_TOKENS * MAX_TOP_K;
+
+template <int Q>
+struct DcRing {  // weight tiles in flight per warp
+    static constexpr int value = (Q == Q4_0) ? 6 : (Q == Q8_0) ? 4 : 3;
+};
+
+__device__ __forceinline__ void cp_async16_dc(void* smem_dst, const void* gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
 
 template <int Q>
 __global__ void __launch_bounds__(DC_THREADS)
@@ -419,31 +429,45 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
     const int kg_i = a.L.kg_i, H = a.L.H, K = a.K, T = a.T;
     const int nblk_i_pad = kg_i * 4;
 
-    // flattened (expert, k-group) items of this warp, one tile prefetched ahead
+    // flattened (expert, k-group) items of this warp; a ring of DC_RING tiles per warp is kept
+    // in flight with cp.async (one commit group per item, empty past the end), so that the
+    // bytes in flight per SM cover the HBM latency
+    extern __shared__ uint4 dc_ring[];  // [DC_WARPS][DC_RING][NQ * 32 + 8]
+    constexpr int NQ32 = QTraits<Q>::NQ * 32, TU4 = NQ32 + 8;
+    uint4* my_ring = dc_ring + (size_t)warp * DcRing<Q>::value * TU4;
     const int n_exp_w = (U > warp) ? (U - warp + DC_WARPS - 1) / DC_WARPS : 0;
     const int nitems = n_exp_w * kg_i;
-    auto item_tile = [&](int n, const uint4*& qb, const uint4*& sb) -> int {
-        const int uu = warp + DC_WARPS * (n / kg_i), kg = n % kg_i;
-        const int ee = a.R.uexp[uu];
-        qb = a.L.down_q(ee);
-        sb = a.L.down_s(ee);
-        return rt * kg_i + kg;
+    auto issue = [&](int n) {
+        if (n < nitems) {
+            const int uu = warp + DC_WARPS * (n / kg_i), kg = n % kg_i;
+            const int ee = a.R.uexp[uu];
+            const int tile = rt * kg_i + kg;
+            uint4* slot = my_ring + (size_t)(n % DcRing<Q>::value) * TU4;
+            const uint4* qp = a.L.down_q(ee) + (size_t)tile * NQ32 + lane;
+#pragma unroll
+            for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16_dc(slot + j * 32 + lane, qp + j * 32);
+            if (Q != BF16 && lane < 8) cp_async16_dc(slot + NQ32 + lane, a.L.down_s(ee) + (size_t)tile * 8 + lane);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    WTile<Q> cur, nxt;
-    if (nitems > 0) {
-        const uint4 *qb, *sb;
-        const int tile = item_tile(0, qb, sb);
-        load_wtile<Q>(cur, qb, sb, tile, lane);
-    }
+#pragma unroll 1
+    for (int i = 0; i < DcRing<Q>::value; ++i) issue(i);
     float acc[4][4];
     const uint4* bbase[4] = {nullptr, nullptr, nullptr, nullptr};
     int c0 = 0, ncol = 0, ng = 0;
+#pragma unroll 1
     for (int n = 0; n < nitems; ++n) {
-        if (n + 1 < nitems) {
-            const uint4 *qb, *sb;
-            const int tile = item_tile(n + 1, qb, sb);
-            load_wtile<Q>(nxt, qb, sb, tile, lane);
+        asm volatile("cp.async.wait_group %0;" ::"n"(DcRing<Q>::value - 1) : "memory");
+        __syncwarp();
+        WTile<Q> cur;
+        {
+            const uint4* slot = my_ring + (size_t)(n % DcRing<Q>::value) * TU4;
+#pragma unroll
+            for (int j = 0; j < QTraits<Q>::NQ; ++j) cur.q[j] = slot[j * 32 + lane];
+            if (Q != BF16) cur.s = slot[NQ32 + (lane >> 2)];
         }
+        __syncwarp();
+        issue(n + DcRing<Q>::value);  // refill the slot just read
         const int kg = n % kg_i;
         if (kg == 0) {
             const int uu = warp + DC_WARPS * (n / kg_i);
@@ -475,8 +499,8 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
                 }
             }
         }
-        if (n + 1 < nitems) cur = nxt;
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     {
         const int row = tid & 15, t = tid >> 4;
@@ -593,6 +617,29 @@ static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, cudaStream_t st,
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
+template <int Q>
+static cudaError_t launch_down_combine(const DecodeArgs& a, dim3 grid, cudaStream_t st) {
+    const size_t smem = (size_t)DC_WARPS * DcRing<Q>::value * (QTraits<Q>::NQ * 32 + 8) * 16;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(down_combine_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(DC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    count_launch();
+    return cudaLaunchKernelEx(&cfg, down_combine_kernel<Q>, a);
+}
+
 cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st) {
     return launch_pdl(router_small_kernel, dim3(a.L.E), dim3(RS_THREADS), st, a);
 }
@@ -614,9 +661,9 @@ cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st)
         }
     }
     switch (a.L.quant) {
-        case Q4_0: return launch_pdl(down_combine_kernel<Q4_0>, g_dc, dim3(DC_THREADS), st, a);
-        case Q8_0: return launch_pdl(down_combine_kernel<Q8_0>, g_dc, dim3(DC_THREADS), st, a);
-        default: return launch_pdl(down_combine_kernel<BF16>, g_dc, dim3(DC_THREADS), st, a);
+        case Q4_0: return launch_down_combine<Q4_0>(a, g_dc, st);
+        case Q8_0: return launch_down_combine<Q8_0>(a, g_dc, st);
+        default: return launch_down_combine<BF16>(a, g_dc, st);
     }
 }
 

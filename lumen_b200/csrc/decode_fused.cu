@@ -39,6 +39,21 @@ constexpr int FT = FW * 32;   // threads per CTA
 constexpr int FMAX_T = 4;     // tokens
 constexpr int FMAX_C = 32;    // (token, slot) pairs
 
+// n / d for 0 <= n < 2^20 and a divisor known when the kernel starts: one multiply by the
+// float reciprocal and a fix-up instead of the ~25-instruction integer division sequence
+// (these quotients sit in dependency chains that run once per launch).
+struct SmallDiv {
+    int d;
+    float inv;
+    __device__ __forceinline__ explicit SmallDiv(int dd) : d(dd), inv(1.0f / (float)dd) {}
+    __device__ __forceinline__ int div(int n) const {
+        int q = (int)(((float)n + 0.5f) * inv);
+        const int r = n - q * d;
+        q += (r >= d) - (r < 0);
+        return q;
+    }
+};
+
 template <int Q>
 struct TileU4 {  // uint4 words of one weight tile staged in shared memory: lane-major q words, then 8 scale words
     static constexpr int value = QTraits<Q>::NQ * 32 + 8;
@@ -246,6 +261,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     // staged gate/up tiles: [gs_slots][gate | up][q of kg_h tiles | scales of kg_h tiles]
     uint4* gs = pf + (size_t)pf_experts * kg_i * TU4;
     constexpr int NQ32 = QTraits<Q>::NQ * 32;
+    const SmallDiv div_kgi(kg_i), div_rti(a.L.rt_i), div_g(G);
 
     // ---------------- phase A ----------------
     // first router row in registers before waiting on the previous kernel (weights are static)
@@ -448,7 +464,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     // the down tiles of its 16 output rows for the first pf_experts experts (barrier 7).
     auto stage_all = [&](const int* ue, int nu) {
         const int n_items_ = nu * rt_i;
-        const int n_my_ = (it0 < n_items_) ? (n_items_ - it0 + G - 1) / G : 0;
+        const int n_my_ = (it0 < n_items_) ? div_g.div(n_items_ - it0 + G - 1) : 0;
         const int n_st_ = min(n_my_, gs_slots);
         const int n_pf_ = has_down ? min(nu, pf_experts) : 0;
         const unsigned q_gu = (unsigned)kg_h * NQ32 * 16, s_gu = (Q != BF16) ? (unsigned)kg_h * 128 : 0u;
@@ -462,7 +478,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
             const int j = c / (2 * PER), r = c - j * 2 * PER;
             const int mat = r / PER, is_s = r - mat * PER;
             const int it = it0 + j * G;
-            const int u = it / rt_i, rt = it - u * rt_i;
+            const int u = div_rti.div(it), rt = it - u * rt_i;
             const int e = ue[u];
             uint4* dst = gs + ((size_t)(j * 2 + mat) * kg_h) * TU4 + (is_s ? kg_h * NQ32 : 0);
             const uint4* src = is_s ? (mat ? a.L.up_s(e) : a.L.gate_s(e)) + (size_t)rt * kg_h * 8
@@ -574,7 +590,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
             // wrong prediction: let its copies land (they target the same slots), start the
             // barriers afresh and request the right tiles
             const int n_items_p = rs.pr_U * rt_i;
-            const int n_my_p = (it0 < n_items_p) ? (n_items_p - it0 + G - 1) / G : 0;
+            const int n_my_p = (it0 < n_items_p) ? div_g.div(n_items_p - it0 + G - 1) : 0;
             bool ok = true;
             for (int j = 0; j < min(n_my_p, gs_slots) && ok; ++j) ok = mbar_wait(&mbar[j], 0, a.status);
             ok = ok && mbar_wait(&mbar[7], 0, a.status);
@@ -591,21 +607,21 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
         }
     }
     auto load_gu = [&](int it, WTile<Q>& g, WTile<Q>& up) {
-        const int u = it / rt_i, rt = it - u * rt_i;
+        const int u = div_rti.div(it), rt = it - u * rt_i;
         const int e = rs.ue[u];
         if (warp < kg_h) {
             load_wtile<Q>(g, a.L.gate_q(e), a.L.gate_s(e), rt * kg_h + warp, lane);
             load_wtile<Q>(up, a.L.up_q(e), a.L.up_s(e), rt * kg_h + warp, lane);
         }
     };
-    const int n_my = (it0 < n_items) ? (n_items - it0 + G - 1) / G : 0;
+    const int n_my = (it0 < n_items) ? div_g.div(n_items - it0 + G - 1) : 0;
     const int n_st = min(n_my, gs_slots);
     WTile<Q> wg0, wu0, wg1, wu1;
     if (n_st < n_my) load_gu(it0 + n_st * G, wg1, wu1);
 
     // gate/up + SwiGLU
     auto compute_gu = [&](int it, const WTile<Q>& g, const WTile<Q>& up) {
-        const int u = it / rt_i, rt = it - u * rt_i;
+        const int u = div_rti.div(it), rt = it - u * rt_i;
         const int c0 = rs.uc0[u];
         const int ncol = min(4, rs.uncol[u]);
         const int jcol = gq >> 1;
@@ -721,7 +737,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
             for (int j = 0; j < DG; ++j) {
                 const int i = i0 + j;
                 nn[j] = min(warp + FW * i, n_down - 1);
-                const int uu = nn[j] / kg_i, kg = nn[j] - uu * kg_i;
+                const int uu = div_kgi.div(nn[j]), kg = nn[j] - uu * kg_i;
                 if (uu < pf_experts) {
                     const uint4* base = pf + ((size_t)uu * kg_i) * TU4;
                     read_staged<Q>(w[j], base + kg * NQ32, base + kg_i * NQ32 + kg * 8, lane);
@@ -732,7 +748,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
             }
 #pragma unroll
             for (int j = 0; j < DG; ++j) {
-                const int uu = nn[j] / kg_i, kg = nn[j] - uu * kg_i;
+                const int uu = div_kgi.div(nn[j]), kg = nn[j] - uu * kg_i;
                 const int c0 = rs.uc0[uu];
                 const int ncol = min(4, rs.uncol[uu]);
                 const int jcol = gq >> 1;

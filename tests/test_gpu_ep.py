@@ -30,7 +30,11 @@ def _worker(rank, world, port, q):
         sl = slice(rank * Tl, (rank + 1) * Tl)
         route_fn, expert_fn, keep = ep.cuda_layer_fns(H, I, E, K, 1, blob, rank, world, Tl)
         layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, combine_fn=keep["combine_fn"])
-        out = layer.forward(x_all[sl].contiguous(), res_all[sl].contiguous())
+        # three calls: the first is eager, the second captures the routing side into a CUDA graph,
+        # the third replays it; all must give the same result
+        outs = [layer.forward(x_all[sl].contiguous(), res_all[sl].contiguous()).clone() for _ in range(3)]
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+        out = outs[2]
         sc = moe.allocate_moe_scratch(H, I, E, K, T, device=rank)  # contexts are per device
         full = sc.prepare_layer(blob, lay.meta())
         ref = sc.prefill(full, x_all, res_all)[sl]

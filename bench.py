@@ -37,6 +37,12 @@ BLK = {0: 34, 1: 18, 2: 64}
 NCU_DRAM_BYTES_PER_LAUNCH = {("decode_fused_kernel", "q4_0", 1): 22_372_000}
 
 
+# arithmetic of the decode path per weight format (f32 activations in and out in all cases)
+DECODE_DTYPE = {"q4_0": "u8*s8->s32 (gate/up) and f16*f16->f32 (down) tensor-core products, f32 scales and sums",
+                "q8_0": "f16*f16->f32 tensor-core products (exact-integer weights, hi+lo activations), f32 scales and sums",
+                "bf16": "bf16*bf16->f32 tensor-core products (hi+lo activations), f32 sums"}
+
+
 def algorithmic_bytes(T: int, U: int, quant: int) -> int:
     """Compulsory traffic of one layer call: router weight, the three matrices of
     every distinct expert hit, activations in / residual in / output out."""
@@ -310,7 +316,7 @@ def run_gpu(args):
         cpu = cpu_reference_leg(quant, T, 12.0, blob0)
         line = {"metric": "moe_layer_decode_tokens_per_s", "value": value, "unit": "layer_tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DECODE_DTYPE[args.quant],
                 "data": "synthetic", "config": workload_config(args),
                 "e2e": {"value": e2e, "unit": "layer_tokens/s", "h2d_bytes_per_step": T * H * 4,
                         "d2h_bytes_per_step": T * H * 4},

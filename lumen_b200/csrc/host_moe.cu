@@ -135,12 +135,12 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
     // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf, w16
     const size_t C = (size_t)cap * s.K;
     const size_t nblk_h_pad = (size_t)((s.H / 32 + 3) / 4) * 4, nblk_i_pad = (size_t)((s.I / 32 + 3) / 4) * 4;
-    const size_t max_ct = C / 256 + s.E;
-    const size_t mt = (size_t)s.I / 128 + (size_t)s.H / 256 + 1;
+    const size_t max_ct = C / 256 + s.E, max_ct_dn = C / 128 + s.E;  // gate/up tiles of 256 columns, down tiles of 128
+    const size_t n_tile_entries = max_ct * ((size_t)s.I / 128 + 1) + max_ct_dn * ((size_t)s.H / 256 + 1);
     size_t sizes[14] = {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,
         (size_t)((cap + 31) / 32) * s.E * 4,
-        max_ct * (mt ? mt : 1) * sizeof(int4),
+        n_tile_entries * sizeof(int4),
         C * s.I * 2, C * s.H * 2, C * s.H * 2,
         (size_t)cap * 2 * nblk_h_pad * 64, C * 2 * nblk_i_pad * 64,
         (size_t)s.E * s.H * 4};

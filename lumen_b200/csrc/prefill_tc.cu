@@ -208,20 +208,23 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
 template <int Q, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
-    // Two 128-row weight operands share every 256-column activation stage (gate and
-    // up rows of the same I range; two adjacent row tiles of the down matrix): the
-    // activation operand, which comes from L2 at 2 bytes per element, is then read
-    // at 32 B/clk/SM instead of 64. The two 256-column f32 accumulators fill TMEM
-    // (512 columns), so there is one accumulator set and the epilogue of a tile is
-    // not overlapped with the next tile's MMAs (its producers do run ahead).
+    // Two 128-row weight operands share every activation stage (gate and up rows of the
+    // same I range; two adjacent row tiles of the down matrix): the activation operand,
+    // which comes from L2 at 2 bytes per element, is then read at half the rate.
+    // gate/up: 256-column tiles; the two 256-column f32 accumulators fill TMEM (512
+    // columns), one accumulator set, the epilogue of a tile is not overlapped with the next
+    // tile's MMAs (its producers do run ahead); with K = H the main loop is long.
+    // down: K = I is short (12 stages at I = 768), so the epilogue weighs more: 128-column
+    // tiles and TWO accumulator sets, the epilogue of tile i runs under the MMAs of tile i+1.
     constexpr int NA = 2;
-    constexpr int BN = 256;                            // columns per tile
-    constexpr int STAGES = 3;                          // one stage = 64 inputs (one swizzle atom in K)
+    constexpr int BN = (MODE == 1) ? 128 : 256;        // columns per tile
+    constexpr int NACC = (MODE == 1) ? 2 : 1;          // accumulator sets in TMEM
+    constexpr int STAGES = (MODE == 1) ? 4 : 3;        // one stage = 64 inputs (one swizzle atom in K)
     constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operands then B
-    constexpr int TMEM_COLS = NA * BN;
+    constexpr int TMEM_COLS = NA * BN * NACC;
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar, acc_empty_bar;
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[NACC], acc_empty_bar[NACC];
     __shared__ uint32_t tmem_base_s;
     __shared__ uint32_t abort_s;
 
@@ -235,8 +238,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             mbar_init(smem_u32(&full_bar[s]), A_WARPS * 32 + 1);  // weight producers + the TMA thread's expect_tx arrive
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        mbar_init(smem_u32(&acc_full_bar), 1);
-        mbar_init(smem_u32(&acc_empty_bar), EPI_WARPS * 32);
+        for (int b = 0; b < NACC; ++b) {
+            mbar_init(smem_u32(&acc_full_bar[b]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[b]), EPI_WARPS * 32);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == MMA_WARP) {
@@ -258,19 +263,20 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 
     if (warp < EPI_WARPS) {
         // ------------------------------ epilogue ------------------------------
-        // warp w reads TMEM lanes 32*(w%4).. (hardware rule); warps 0-3 take columns
-        // 0-127 of the tile, warps 4-7 columns 128-255
+        // warp w reads TMEM lanes 32*(w%4).. (hardware rule); warps 0-3 take the first half
+        // of the tile's columns, warps 4-7 the second half
         const int row = (warp & 3) * 32 + lane;
-        const int chalf = (warp >> 2) * 128;
+        const int chalf = (warp >> 2) * (BN / 2);
         int tl = 0;
         bool ok = true;
         for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
             const int4 tile = a.tiles[ti];
             const int ncols = tile.z;
-            ok = mbar_wait(smem_u32(&acc_full_bar), tl & 1, abort_flag);
+            const int ab = tl % NACC, use = tl / NACC;  // accumulator set and how often it has been used
+            ok = mbar_wait(smem_u32(&acc_full_bar[ab]), use & 1, abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ab * NA * BN;
             size_t off0, off1 = 0;
             if (MODE == 0) {
                 const int irow = tile.w * 128 + row;  // SwiGLU output is stored in the permuted order
@@ -279,7 +285,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 off0 = (size_t)(tile.w * 256 + row);
                 off1 = off0 + 128;
             }
-            for (int n0 = chalf; n0 < ncols && n0 < chalf + 128; n0 += 16) {
+            for (int n0 = chalf; n0 < ncols && n0 < chalf + BN / 2; n0 += 16) {
                 uint32_t v0[16], v1[16];
                 tmem_ld16(taddr + n0, v0);
                 tmem_ld16(taddr + BN + n0, v1);
@@ -301,7 +307,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 }
             }
             tc_fence_before();
-            mbar_arrive(smem_u32(&acc_empty_bar));
+            mbar_arrive(smem_u32(&acc_empty_bar[ab]));
         }
     } else if (warp < B_WARP0) {
         // --------------------------- weight producers --------------------------
@@ -373,7 +379,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 if (kh == 0) {
                     const int4 tile = a.tiles[blockIdx.x + (n / khs) * gridDim.x];
                     row0 = tile.y;
-                    nbox = (tile.z > 128) ? 2 : 1;
+                    nbox = (BN > 128 && tile.z > 128) ? 2 : 1;
                 }
                 const int s = n % STAGES, ph = (n / STAGES) & 1;
                 ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
@@ -400,7 +406,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 const int4 tile = a.tiles[ti];
                 const int n16 = (tile.z + 15) & ~15;
                 const uint32_t idesc = make_idesc(n16, bf16_mode);
-                ok = mbar_wait(smem_u32(&acc_empty_bar), (tl & 1) ^ 1, abort_flag);
+                const int ab = tl % NACC, use = tl / NACC;
+                ok = mbar_wait(smem_u32(&acc_empty_bar[ab]), (use & 1) ^ 1, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 for (int kh = 0; kh < khs; ++kh, ++it) {
@@ -417,13 +424,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 #pragma unroll
                         for (int op = 0; op < NA; ++op) {
                             const uint64_t adesc = make_desc(sbase + op * SUB_BYTES + j * 32);
-                            umma(tmem_base + op * BN, adesc, bdesc, idesc, acc);
+                            umma(tmem_base + ab * NA * BN + op * BN, adesc, bdesc, idesc, acc);
                         }
                     }
                     umma_commit(smem_u32(&empty_bar[s]));
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&acc_full_bar));
+                umma_commit(smem_u32(&acc_full_bar[ab]));
             }
         }
         __syncwarp();
@@ -498,8 +505,9 @@ static cudaError_t make_tmap(const void* base, uint64_t rows, uint64_t cols, CUt
 template <int Q, int MODE>
 static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
     constexpr int NA = 2;
-    constexpr int BN = 256;
-    const int smem = 3 * (NA * tc::SUB_BYTES + BN * 128) + 1024;
+    constexpr int BN = (MODE == 1) ? 128 : 256;      // must match the kernel
+    constexpr int STAGES = (MODE == 1) ? 4 : 3;
+    const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(tc::grouped_gemm_tc_kernel<Q, MODE>,
@@ -533,7 +541,7 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     te = make_tmap(p.s16, (uint64_t)C, (uint64_t)p.L.I, &dn.tmap);
     if (te != cudaSuccess) return te;
     dn.col_src_tok = nullptr;
-    dn.tiles = p.tiles + (size_t)max_ct * mt_gu;
+    dn.tiles = p.tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1);  // as laid out by launch_route_large
     dn.b_src = p.s16;
     // out16_rows: write the down product straight into caller rows (row = col_src_tok[column])
     dn.out16 = out16_rows ? out16_rows : p.d16;

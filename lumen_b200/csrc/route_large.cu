@@ -314,7 +314,7 @@ sort_rowscan_kernel(int32_t* __restrict__ blk_hist, int nchunks, RouteDev R) {
 // One CTA of 256 threads (E <= 256): expert segment bounds from the row totals and the
 // tile lists. tile entry: {expert, col_start, ncols, m_tile}.
 __global__ void __launch_bounds__(256)
-sort_scan_kernel(int nchunks, int E, RouteDev R, int tile_cols,
+sort_scan_kernel(int nchunks, int E, RouteDev R, int tile_cols, int tile_cols_dn,
                  int mt_gu, int mt_dn, int4* __restrict__ tiles_gu, int4* __restrict__ tiles_dn,
                  int32_t* __restrict__ n_tiles, int max_tiles_gu, int max_tiles_dn) {
     __shared__ int cnt_s[MAX_EXPERTS];
@@ -325,16 +325,17 @@ sort_scan_kernel(int nchunks, int E, RouteDev R, int tile_cols,
     if (tid < E) cnt_s[tid] = R.expert_bounds[tid];
     __syncthreads();
     if (warp == 0) {
-        int local[8], ltiles[8], lsum = 0, lnz = 0, ltl = 0, ltd = 0;
+        int local[8], ltiles[8], ltiles_dn[8], lsum = 0, lnz = 0, ltl = 0, ltd = 0;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int ee = lane * 8 + j;
             local[j] = (ee < E) ? cnt_s[ee] : 0;
             ltiles[j] = (local[j] + tile_cols - 1) / tile_cols;
+            ltiles_dn[j] = (local[j] + tile_cols_dn - 1) / tile_cols_dn;
             lsum += local[j];
             lnz += (local[j] > 0);
             ltl += ltiles[j];
-            ltd += ltiles[j];
+            ltd += ltiles_dn[j];
         }
         int isum = lsum, inz = lnz, itl = ltl, itd = ltd;
 #pragma unroll
@@ -362,7 +363,7 @@ sort_scan_kernel(int nchunks, int E, RouteDev R, int tile_cols,
                 if (local[j] > 0) R.uexp[unz++] = ee;
                 run += local[j];
                 trun += ltiles[j];
-                drun += ltiles[j];
+                drun += ltiles_dn[j];
             }
         }
         if (lane == 31) {
@@ -391,8 +392,8 @@ sort_scan_kernel(int nchunks, int E, RouteDev R, int tile_cols,
         }
         const int dt0 = tile_off_dn_s[tid], ndt = tile_off_dn_s[tid + 1] - dt0;
         for (int ct = 0; ct < ndt; ++ct) {
-            const int cs = c0 + ct * tile_cols;
-            const int nc = min(tile_cols, n - ct * tile_cols);
+            const int cs = c0 + ct * tile_cols_dn;
+            const int nc = min(tile_cols_dn, n - ct * tile_cols_dn);
             for (int mt = 0; mt < mt_dn; ++mt) {
                 const int idx = (dt0 + ct) * mt_dn + mt;
                 if (idx < max_tiles_dn) tiles_dn[idx] = make_int4(tid, cs, nc, mt);
@@ -566,14 +567,15 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const int nchunks = (T + SORT_TOK - 1) / SORT_TOK;
     sort_hist_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist);
     const int C = T * K;
-    const int tile_cols = 256;  // columns per grouped-GEMM tile (both products)
-    const int max_ct = C / tile_cols + E;
+    // columns per grouped-GEMM tile: 256 for gate/up, 128 for down (two accumulator sets in TMEM)
+    const int tile_cols = 256, tile_cols_dn = 128;
+    const int max_ct = C / tile_cols + E, max_ct_dn = C / tile_cols_dn + E;
     const int mt_gu = a.L.I / 128, mt_dn = a.L.H / 256;  // m-tiles: 128 gate + 128 up rows | 256 down rows
     int4* tiles_gu = a.tiles;
     int4* tiles_dn = a.tiles ? a.tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1) : nullptr;
     sort_rowscan_kernel<<<E, 32, 0, st>>>(a.blk_hist, nchunks, a.R);
-    sort_scan_kernel<<<1, 256, 0, st>>>(nchunks, E, a.R, tile_cols, mt_gu, mt_dn, tiles_gu, tiles_dn,
-                                        a.n_tiles, max_ct * mt_gu, max_ct * mt_dn);
+    sort_scan_kernel<<<1, 256, 0, st>>>(nchunks, E, a.R, tile_cols, tile_cols_dn, mt_gu, mt_dn, tiles_gu, tiles_dn,
+                                        a.n_tiles, max_ct * mt_gu, max_ct_dn * mt_dn);
     sort_place_kernel<<<(nchunks + 7) / 8, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist, nchunks, a.R);
     return cudaGetLastError();
 }

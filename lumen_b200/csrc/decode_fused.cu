@@ -216,7 +216,7 @@ struct TopkSm {
 
 template <int Q>
 __global__ void __launch_bounds__(FT, 1)
-decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, const int gs_slots) {
+decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, const int gs_slots, const int gs_alias) {
     extern __shared__ uint4 dyn[];
     __shared__ __align__(16) TopkSm ts;
     __shared__ float red_a[FW][FMAX_T];
@@ -258,9 +258,15 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     const size_t mid_bytes = max((size_t)C * per_col_i * 16 + (size_t)C * kg_i * 256 + (size_t)C * 64, (size_t)T * H * 4);
     // staged down tiles of this CTA's 16 output rows: [pf_experts][q of kg_i tiles | scales of kg_i tiles]
     uint4* pf = reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(ss) + mid_bytes);
-    // staged gate/up tiles: [gs_slots][gate | up][q of kg_h tiles | scales of kg_h tiles]
+    // staged gate/up tiles: a ring of gs_slots work items, each [gate | up][q of kg_h tiles | scales
+    // of kg_h tiles]. The first gs_alias slots lie over the ss/part/wd region, which is only
+    // written after every gate/up item has been consumed (phase C); the rest follow the down tiles.
     uint4* gs = pf + (size_t)pf_experts * kg_i * TU4;
     constexpr int NQ32 = QTraits<Q>::NQ * 32;
+    const size_t item_u4 = (size_t)2 * kg_h * TU4;
+    auto gs_slot = [&](int sl) -> uint4* {
+        return sl < gs_alias ? ss + (size_t)sl * item_u4 : gs + (size_t)(sl - gs_alias) * item_u4;
+    };
     const SmallDiv div_kgi(kg_i), div_rti(a.L.rt_i), div_g(G);
 
     // ---------------- phase A ----------------
@@ -462,6 +468,19 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     // tiles of its first gs_slots gate/up items (all input groups of a matrix are contiguous:
     // one bulk copy for the quants, one for the scales; barrier j counts item j's bytes), then
     // the down tiles of its 16 output rows for the first pf_experts experts (barrier 7).
+    // copy r of work item j (its j-th for this CTA) into ring slot j % gs_slots: r = matrix * PER + {quants, scales}
+    auto copy_gu = [&](int j, int r, const int* ue) {
+        constexpr int PER_ = (Q != BF16) ? 2 : 1;
+        const int mat = r / PER_, is_s = r - mat * PER_;
+        const int it = it0 + j * G;
+        const int u = div_rti.div(it), rt = it - u * rt_i;
+        const int e = ue[u];
+        const int sl = j % gs_slots;
+        uint4* dst = gs_slot(sl) + (size_t)mat * kg_h * TU4 + (is_s ? kg_h * NQ32 : 0);
+        const uint4* src = is_s ? (mat ? a.L.up_s(e) : a.L.gate_s(e)) + (size_t)rt * kg_h * 8
+                                : (mat ? a.L.up_q(e) : a.L.gate_q(e)) + (size_t)rt * kg_h * NQ32;
+        bulk_copy(dst, src, is_s ? (unsigned)kg_h * 128 : (unsigned)kg_h * NQ32 * 16, &mbar[sl]);
+    };
     auto stage_all = [&](const int* ue, int nu) {
         const int n_items_ = nu * rt_i;
         const int n_my_ = (it0 < n_items_) ? div_g.div(n_items_ - it0 + G - 1) : 0;
@@ -474,17 +493,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
         __syncwarp();
         constexpr int PER = (Q != BF16) ? 2 : 1;  // copies per matrix: quants, scales
 #pragma unroll 1
-        for (int c = lane; c < n_st_ * 2 * PER; c += 32) {
-            const int j = c / (2 * PER), r = c - j * 2 * PER;
-            const int mat = r / PER, is_s = r - mat * PER;
-            const int it = it0 + j * G;
-            const int u = div_rti.div(it), rt = it - u * rt_i;
-            const int e = ue[u];
-            uint4* dst = gs + ((size_t)(j * 2 + mat) * kg_h) * TU4 + (is_s ? kg_h * NQ32 : 0);
-            const uint4* src = is_s ? (mat ? a.L.up_s(e) : a.L.gate_s(e)) + (size_t)rt * kg_h * 8
-                                    : (mat ? a.L.up_q(e) : a.L.gate_q(e)) + (size_t)rt * kg_h * NQ32;
-            bulk_copy(dst, src, is_s ? s_gu : q_gu, &mbar[j]);
-        }
+        for (int c = lane; c < n_st_ * 2 * PER; c += 32) copy_gu(c / (2 * PER), c % (2 * PER), ue);
 #pragma unroll 1
         for (int c = lane; c < n_pf_ * PER; c += 32) {
             const int uu = c / PER, is_s = c - uu * PER;
@@ -615,9 +624,8 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
         }
     };
     const int n_my = (it0 < n_items) ? div_g.div(n_items - it0 + G - 1) : 0;
-    const int n_st = min(n_my, gs_slots);
     WTile<Q> wg0, wu0, wg1, wu1;
-    if (n_st < n_my) load_gu(it0 + n_st * G, wg1, wu1);
+    if (gs_slots == 0 && n_my > 0) load_gu(it0, wg1, wu1);  // no ring: tiles go through registers, one item ahead
 
     // gate/up + SwiGLU
     auto compute_gu = [&](int it, const WTile<Q>& g, const WTile<Q>& up) {
@@ -688,11 +696,13 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     };
 #pragma unroll 1
     for (int j = 0; j < n_my; ++j) {
-        if (j < n_st) {
-            if (!mbar_wait(&mbar[j], 0, a.status)) return;  // every thread waits: all of them give up together
-            if (a.trace != nullptr && tid == 0 && j == n_st - 1) a.trace[(size_t)blockIdx.x * 12 + 11] = global_ns();
+        if (gs_slots > 0) {
+            // ring slot j % gs_slots, filled for the (j / gs_slots)-th time
+            const int sl = j % gs_slots;
+            if (!mbar_wait(&mbar[sl], (unsigned)(j / gs_slots) & 1u, a.status)) return;  // all threads give up together
+            if (a.trace != nullptr && tid == 0 && j == n_my - 1) a.trace[(size_t)blockIdx.x * 12 + 11] = global_ns();
             if (warp < kg_h) {
-                const uint4* gq_ = gs + ((size_t)(j * 2) * kg_h) * TU4;
+                const uint4* gq_ = gs_slot(sl);
                 const uint4* uq_ = gq_ + (size_t)kg_h * TU4;
                 read_staged<Q>(wg0, gq_ + warp * NQ32, gq_ + kg_h * NQ32 + warp * 8, lane);
                 read_staged<Q>(wu0, uq_ + warp * NQ32, uq_ + kg_h * NQ32 + warp * 8, lane);
@@ -703,6 +713,13 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
             if (j + 1 < n_my) load_gu(it0 + (j + 1) * G, wg1, wu1);
         }
         compute_gu(it0 + j * G, wg0, wu0);
+        // every warp has its tiles of slot j % gs_slots in registers (compute_gu ends on CTA barriers):
+        // refill the slot with the item gs_slots further on
+        if (gs_slots > 0 && tid == 0 && j + gs_slots < n_my) {
+            constexpr int PER_ = (Q != BF16) ? 2 : 1;
+            mbar_expect_tx(&mbar[j % gs_slots], 2u * ((unsigned)kg_h * NQ32 * 16 + ((Q != BF16) ? (unsigned)kg_h * 128 : 0u)));
+            for (int r = 0; r < 2 * PER_; ++r) copy_gu(j + gs_slots, r, rs.ue);
+        }
     }
     // residual of this CTA's output rows, requested before the barrier
     float resid = 0.0f;
@@ -795,11 +812,15 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
 
 // Shared memory the fused kernel needs besides its static arrays; pf_experts = experts whose
 // down tiles are staged, gs_slots = staged gate/up work items.
-static size_t fused_smem_bytes(const DecodeArgs& a, int tile_u4, int pf_experts, int gs_slots = 0) {
+// gs_slots counts only the ring slots with storage of their own (see fused_mid_bytes).
+static size_t fused_mid_bytes(const DecodeArgs& a) {
     const size_t C = (size_t)a.T * a.K;
     const size_t mid = C * 2 * a.L.kg_i * 16 * 16 + C * a.L.kg_i * 256 + C * 64;
     const size_t xn = (size_t)a.T * a.L.H * 4;
-    return (size_t)a.T * 2 * a.L.kg_h * 16 * 16 + (mid > xn ? mid : xn) +
+    return mid > xn ? mid : xn;
+}
+static size_t fused_smem_bytes(const DecodeArgs& a, int tile_u4, int pf_experts, int gs_slots = 0) {
+    return (size_t)a.T * 2 * a.L.kg_h * 16 * 16 + fused_mid_bytes(a) +
            (size_t)pf_experts * a.L.kg_i * tile_u4 * 16 + (size_t)gs_slots * 2 * a.L.kg_h * tile_u4 * 16;
 }
 
@@ -846,9 +867,15 @@ static cudaError_t launch_fused_t(const DecodeArgs& a, int device, cudaStream_t 
     const int C = a.T * a.K;
     // shared memory goes to the gate/up items of a CTA first (they are needed first), then to the down tiles
     const int nu_max = C < a.L.E ? C : a.L.E;
-    int gs = (nu_max * a.L.rt_i + d.sms - 1) / d.sms;
-    if (gs > 7) gs = 7;
-    while (gs > 0 && fused_smem_bytes(a, TileU4<Q>::value, 0, gs) + static_smem > (size_t)d.smem_optin) --gs;
+    // ring of gate/up work items: as many as a CTA can have, at most 3 (three items in flight cover the
+    // HBM latency); slots that fit over the phase C region cost nothing, the others get storage of their own
+    int ring = (nu_max * a.L.rt_i + d.sms - 1) / d.sms;
+    if (ring > 3) ring = 3;
+    const size_t item_bytes = (size_t)2 * a.L.kg_h * TileU4<Q>::value * 16;
+    int alias = (int)(fused_mid_bytes(a) / item_bytes);
+    if (alias > ring) alias = ring;
+    while (ring > alias && fused_smem_bytes(a, TileU4<Q>::value, 0, ring - alias) + static_smem > (size_t)d.smem_optin) --ring;
+    const int gs = ring - alias;  // slots with storage of their own
     int pf = nu_max;  // experts whose down tiles are staged
     while (pf > 0 && fused_smem_bytes(a, TileU4<Q>::value, pf, gs) + static_smem > (size_t)d.smem_optin) --pf;
     const size_t smem = fused_smem_bytes(a, TileU4<Q>::value, pf, gs);
@@ -875,7 +902,7 @@ static cudaError_t launch_fused_t(const DecodeArgs& a, int device, cudaStream_t 
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     count_launch();
-    return cudaLaunchKernelEx(&cfg, decode_fused_kernel<Q>, a, pf, gs);
+    return cudaLaunchKernelEx(&cfg, decode_fused_kernel<Q>, a, pf, ring, alias);
 }
 
 cudaError_t launch_decode_fused(const DecodeArgs& a, cudaStream_t st) {

@@ -644,12 +644,12 @@ cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st) {
     return launch_pdl(router_small_kernel, dim3(a.L.E), dim3(RS_THREADS), st, a);
 }
 
-bool decode_small_applicable(const DecodeArgs& a);
+bool decode_small_applicable(const DecodeArgs& a, int phase);
 cudaError_t launch_decode_small_phase(const DecodeArgs& a, int phase, cudaStream_t st);
 
 cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st) {
     if (phase == 0) return launch_route_small(a, st);
-    if (decode_small_applicable(a)) return launch_decode_small_phase(a, phase, st);
+    if (decode_small_applicable(a, phase)) return launch_decode_small_phase(a, phase, st);
     const int C = a.T * a.K;
     const int nu = C < a.L.E ? C : a.L.E;
     const dim3 g_gu(a.L.rt_i, nu), g_dc(a.L.rt_h);

@@ -63,7 +63,6 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
     const int gq = lane >> 2, t4 = lane & 3;
     const int rt = blockIdx.x;
     const int e = wd.x, c0 = wd.y;
-    const int ncol = min(4, wd.z);
     const int kg_h = a.L.kg_h, I = a.L.I;
     const int nblk_pad = kg_h * 4, nblk_i_pad = a.L.kg_i * 4;
 
@@ -83,55 +82,63 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
             }
         }
     }
-    // stage the activation fragments of this expert's tokens while the weights are in flight
+    // The expert's columns are taken four at a time (one MMA column group: an expert has at
+    // most four columns at batches up to 4, rarely more at batches up to 16); the weights stay
+    // in registers across the chunks.
     const int per_col = 2 * nblk_pad * 4;
-    const int toks[4] = {wt.x, wt.y, wt.z, wt.w};
+    for (int cb = 0; cb < wd.z; cb += 4) {
+        const int ncol = min(4, wd.z - cb);
+        // stage the activation fragments of these columns' tokens (first chunk: while the weights are in flight)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        if (j < ncol) {
-            const uint4* src = a.xf + (size_t)toks[j] * per_col;
-            for (int i = tid; i < per_col; i += WARPS * 32) cp_async16(&xs[j * per_col + i], src + i);
+        for (int j = 0; j < 4; ++j) {
+            if (j < ncol) {
+                const int tok = (cb == 0) ? (j == 0 ? wt.x : j == 1 ? wt.y : j == 2 ? wt.z : wt.w)
+                                          : a.R.col_src_tok[c0 + cb + j];
+                const uint4* src = a.xf + (size_t)tok * per_col;
+                for (int i = tid; i < per_col; i += WARPS * 32) cp_async16(&xs[j * per_col + i], src + i);
+            }
         }
-    }
-    cp_async_wait_all();
-    __syncthreads();
+        cp_async_wait_all();
+        __syncthreads();
 
-    const int jcol = gq >> 1;
-    const bool bvalid = jcol < ncol;
-    const uint4* bbase = xs + ((size_t)(jcol * 2 + (gq & 1)) * nblk_pad) * 4 + t4;
-    float acc_g[4] = {0.f, 0.f, 0.f, 0.f}, acc_u[4] = {0.f, 0.f, 0.f, 0.f};
+        const int jcol = gq >> 1;
+        const bool bvalid = jcol < ncol;
+        const uint4* bbase = xs + ((size_t)(jcol * 2 + (gq & 1)) * nblk_pad) * 4 + t4;
+        float acc_g[4] = {0.f, 0.f, 0.f, 0.f}, acc_u[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it) {
-        const int kg = warp + it * WARPS;
-        if (kg < kg_h) {
-            const uint4* bp = bbase + (size_t)kg * 16;
+        for (int it = 0; it < ITERS; ++it) {
+            const int kg = warp + it * WARPS;
+            if (kg < kg_h) {
+                const uint4* bp = bbase + (size_t)kg * 16;
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
-                block_mma_smem<Q>(wg[it], b, bp, bvalid, acc_g);
-                block_mma_smem<Q>(wu[it], b, bp, bvalid, acc_u);
+                for (int b = 0; b < 4; ++b) {
+                    block_mma_smem<Q>(wg[it], b, bp, bvalid, acc_g);
+                    block_mma_smem<Q>(wu[it], b, bp, bvalid, acc_u);
+                }
             }
         }
-    }
-    red[warp][gq][t4][0] = acc_g[0] + acc_g[1];
-    red[warp][gq][t4][1] = acc_u[0] + acc_u[1];
-    red[warp][gq + 8][t4][0] = acc_g[2] + acc_g[3];
-    red[warp][gq + 8][t4][1] = acc_u[2] + acc_u[3];
-    __syncthreads();
-    if (tid < 64) {
-        const int row = tid & 15, tokc = tid >> 4;
-        if (tokc < ncol) {
-            float gate = 0.0f, up = 0.0f;
+        red[warp][gq][t4][0] = acc_g[0] + acc_g[1];
+        red[warp][gq][t4][1] = acc_u[0] + acc_u[1];
+        red[warp][gq + 8][t4][0] = acc_g[2] + acc_g[3];
+        red[warp][gq + 8][t4][1] = acc_u[2] + acc_u[3];
+        __syncthreads();
+        if (tid < 64) {
+            const int row = tid & 15, tokc = tid >> 4;
+            if (tokc < ncol) {
+                float gate = 0.0f, up = 0.0f;
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) {
-                gate += red[w][row][tokc][0];
-                up += red[w][row][tokc][1];
+                for (int w = 0; w < WARPS; ++w) {
+                    gate += red[w][row][tokc][0];
+                    up += red[w][row][tokc][1];
+                }
+                const float sv = (gate / (1.0f + expf(-gate))) * up;
+                const int col = c0 + cb + tokc;
+                const int irow = rt * 16 + row;
+                if (a.s_f32 != nullptr) a.s_f32[(size_t)col * I + irow] = sv;
+                store_swiglu_frag<Q>(a.sf, col, irow, nblk_i_pad, sv);
             }
-            const float sv = (gate / (1.0f + expf(-gate))) * up;
-            const int col = c0 + tokc;
-            const int irow = rt * 16 + row;
-            if (a.s_f32 != nullptr) a.s_f32[(size_t)col * I + irow] = sv;
-            store_swiglu_frag<Q>(a.sf, col, irow, nblk_i_pad, sv);
         }
+        __syncthreads();  // red and xs are reused by the next chunk
     }
 }
 
@@ -238,15 +245,17 @@ static cudaError_t launch_pdl_smem(Kern kern, dim3 grid, dim3 block, size_t smem
 
 // Whether the small-batch kernels apply (shape limits of the register staging
 // and of shared memory); otherwise the caller uses the general kernels.
-bool decode_small_applicable(const DecodeArgs& a) {
-    if (a.T > 4) return false;
+bool decode_small_applicable(const DecodeArgs& a, int phase) {
+    // gate/up walks an expert's columns four at a time, so it serves every decode batch; the down
+    // kernel keeps all SwiGLU fragments in shared memory, which limits it to four tokens
+    if (phase != 1 && a.T > 4) return false;
     const int q = a.L.quant;
     const int warps = (q == BF16) ? 16 : 8;
     const int iters = (q == BF16) ? 1 : 2;
     if (a.L.kg_h > warps * iters) return false;
     const size_t gu_smem = (size_t)4 * 2 * a.L.kg_h * 4 * 4 * 16;
     const size_t dn_smem = (size_t)a.T * a.K * (2 * a.L.kg_i * 4 * 4 * 16 + 64);
-    return gu_smem <= 160 * 1024 && dn_smem <= 200 * 1024;
+    return (phase == 1) ? gu_smem <= 160 * 1024 : dn_smem <= 200 * 1024;
 }
 
 template <int Q>

@@ -420,6 +420,7 @@ template <int Q>
 __global__ void __launch_bounds__(DC_THREADS)
 down_combine_kernel(const __grid_constant__ DecodeArgs a) {
     __shared__ float dsm[DC_MAX_COLS][16];
+    __shared__ int exp_s[MAX_EXPERTS], c0_s[MAX_EXPERTS], nc_s[MAX_EXPERTS];
     pdl_trigger();
     pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -428,6 +429,16 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
     const int U = *a.R.n_uexp;
     const int kg_i = a.L.kg_i, H = a.L.H, K = a.K, T = a.T;
     const int nblk_i_pad = kg_i * 4;
+    // expert id, first column and column count of every expert with work, once per CTA: the
+    // per-item lookups below then stay out of the chain of dependent global loads
+    for (int u = tid; u < U; u += DC_THREADS) {
+        const int ee = a.R.uexp[u];
+        const int b0 = a.R.expert_bounds[ee];
+        exp_s[u] = ee;
+        c0_s[u] = b0;
+        nc_s[u] = min(16, a.R.expert_bounds[ee + 1] - b0);
+    }
+    __syncthreads();
 
     // flattened (expert, k-group) items of this warp; a ring of DC_RING tiles per warp is kept
     // in flight with cp.async (one commit group per item, empty past the end), so that the
@@ -440,7 +451,7 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
     auto issue = [&](int n) {
         if (n < nitems) {
             const int uu = warp + DC_WARPS * (n / kg_i), kg = n % kg_i;
-            const int ee = a.R.uexp[uu];
+            const int ee = exp_s[uu];
             const int tile = rt * kg_i + kg;
             uint4* slot = my_ring + (size_t)(n % DcRing<Q>::value) * TU4;
             const uint4* qp = a.L.down_q(ee) + (size_t)tile * NQ32 + lane;
@@ -455,6 +466,20 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
     float acc[4][4];
     const uint4* bbase[4] = {nullptr, nullptr, nullptr, nullptr};
     int c0 = 0, ncol = 0, ng = 0;
+    // activation fragments of the first column group (an expert rarely has more than four columns
+    // here) are fetched one item ahead, so that their L2 latency is not paid tile by tile
+    auto b0_ptr = [&](int n) -> const uint4* {
+        const int uu = warp + DC_WARPS * (n / kg_i), kg = n % kg_i;
+        const int colr = gq >> 1;
+        if (n >= nitems || colr >= nc_s[uu]) return nullptr;
+        return a.sf + ((size_t)((c0_s[uu] + colr) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4 + (size_t)kg * 16;
+    };
+    uint4 bnx[4];
+    {
+        const uint4* p0 = b0_ptr(0);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) bnx[b] = p0 ? ldg_cached(p0 + b * 4) : make_uint4(0u, 0u, 0u, 0u);
+    }
 #pragma unroll 1
     for (int n = 0; n < nitems; ++n) {
         asm volatile("cp.async.wait_group %0;" ::"n"(DcRing<Q>::value - 1) : "memory");
@@ -468,12 +493,19 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
         }
         __syncwarp();
         issue(n + DcRing<Q>::value);  // refill the slot just read
+        uint4 bcur[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) bcur[b] = bnx[b];
+        {
+            const uint4* p1 = b0_ptr(n + 1);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) bnx[b] = p1 ? ldg_cached(p1 + b * 4) : make_uint4(0u, 0u, 0u, 0u);
+        }
         const int kg = n % kg_i;
         if (kg == 0) {
             const int uu = warp + DC_WARPS * (n / kg_i);
-            const int ee = a.R.uexp[uu];
-            c0 = a.R.expert_bounds[ee];
-            ncol = min(16, a.R.expert_bounds[ee + 1] - c0);
+            c0 = c0_s[uu];
+            ncol = nc_s[uu];
             ng = (ncol + 3) >> 2;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -485,10 +517,32 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
                 for (int i = 0; i < 4; ++i) acc[g][i] = 0.0f;
             }
         }
-        const uint4* bp[4];
+        // group 0 from the prefetched registers, further groups (rare) through their pointers
 #pragma unroll
-        for (int g = 0; g < 4; ++g) bp[g] = bbase[g] ? bbase[g] + (size_t)kg * 16 : nullptr;
-        tile_mma<Q, 4>(cur, bp, ng, acc);
+        for (int b = 0; b < 4; ++b) {
+            uint32_t a_lo[4], a_hi[4];
+            unpack_block<Q>(cur, b, a_lo, a_hi);
+            const float2 sc = block_scales<Q>(cur, b);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                if (g < ng) {
+                    uint4 bf = bcur[b];
+                    if (g > 0) bf = bbase[g] ? ldg_cached(bbase[g] + (size_t)kg * 16 + b * 4) : make_uint4(0u, 0u, 0u, 0u);
+                    float c[4] = {0.f, 0.f, 0.f, 0.f};
+                    if (Q == BF16) {
+                        mma_bf16(c, a_lo, bf.x, bf.y);
+                        mma_bf16(c, a_hi, bf.z, bf.w);
+                    } else {
+                        mma_f16(c, a_lo, bf.x, bf.y);
+                        mma_f16(c, a_hi, bf.z, bf.w);
+                    }
+                    acc[g][0] = fmaf(sc.x, c[0], acc[g][0]);
+                    acc[g][1] = fmaf(sc.x, c[1], acc[g][1]);
+                    acc[g][2] = fmaf(sc.y, c[2], acc[g][2]);
+                    acc[g][3] = fmaf(sc.y, c[3], acc[g][3]);
+                }
+            }
+        }
         if (kg == kg_i - 1) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {

@@ -27,7 +27,7 @@ namespace lumen {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-constexpr int RS_THREADS = 256;
+constexpr int RS_THREADS = 512;  // 16 warps: the last CTA gates one token per warp at batches up to 16
 constexpr int RS_WARPS = RS_THREADS / 32;
 
 __global__ void __launch_bounds__(RS_THREADS)
@@ -97,7 +97,7 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
     // logits for this expert row, all tokens (token loop rolled: the code of this kernel runs
     // once per launch, so its size is paid in instruction fetches)
     if (want_logits) {
-#pragma unroll 1
+#pragma unroll 4
         for (int t = 0; t < T; ++t) {
             float acc = 0.0f;
 #pragma unroll
@@ -166,11 +166,9 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
     }
     __syncthreads();
     const int C = T * K;
-    if (tid < E) {
-        int c = 0;
-        for (int p = 0; p < C; ++p) c += (ids_s[p] == tid);
-        cnt_s[tid] = c;
-    }
+    if (tid < E) cnt_s[tid] = 0;
+    __syncthreads();
+    for (int p = tid; p < C; p += RS_THREADS) atomicAdd(&cnt_s[ids_s[p]], 1);
     __syncthreads();
     if (warp == 0) {
         // exclusive scan over experts, 8 per lane (E <= 256), and the ascending

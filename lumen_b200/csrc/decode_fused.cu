@@ -468,14 +468,13 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     // tiles of its first gs_slots gate/up items (all input groups of a matrix are contiguous:
     // one bulk copy for the quants, one for the scales; barrier j counts item j's bytes), then
     // the down tiles of its 16 output rows for the first pf_experts experts (barrier 7).
-    // copy r of work item j (its j-th for this CTA) into ring slot j % gs_slots: r = matrix * PER + {quants, scales}
-    auto copy_gu = [&](int j, int r, const int* ue) {
+    // copy r of work item j (its j-th for this CTA) into ring slot sl: r = matrix * PER + {quants, scales}
+    auto copy_gu = [&](int j, int sl, int r, const int* ue) {
         constexpr int PER_ = (Q != BF16) ? 2 : 1;
         const int mat = r / PER_, is_s = r - mat * PER_;
         const int it = it0 + j * G;
         const int u = div_rti.div(it), rt = it - u * rt_i;
         const int e = ue[u];
-        const int sl = j % gs_slots;
         uint4* dst = gs_slot(sl) + (size_t)mat * kg_h * TU4 + (is_s ? kg_h * NQ32 : 0);
         const uint4* src = is_s ? (mat ? a.L.up_s(e) : a.L.gate_s(e)) + (size_t)rt * kg_h * 8
                                 : (mat ? a.L.up_q(e) : a.L.gate_q(e)) + (size_t)rt * kg_h * NQ32;
@@ -493,7 +492,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
         __syncwarp();
         constexpr int PER = (Q != BF16) ? 2 : 1;  // copies per matrix: quants, scales
 #pragma unroll 1
-        for (int c = lane; c < n_st_ * 2 * PER; c += 32) copy_gu(c / (2 * PER), c % (2 * PER), ue);
+        for (int c = lane; c < n_st_ * 2 * PER; c += 32) copy_gu(c / (2 * PER), c / (2 * PER), c % (2 * PER), ue);
 #pragma unroll 1
         for (int c = lane; c < n_pf_ * PER; c += 32) {
             const int uu = c / PER, is_s = c - uu * PER;
@@ -694,12 +693,12 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
         }
         __syncthreads();
     };
+    int sl = 0;          // ring slot of item j: j % gs_slots
+    unsigned ring_ph = 0;  // parity of (j / gs_slots): how often the slot has been filled
 #pragma unroll 1
     for (int j = 0; j < n_my; ++j) {
         if (gs_slots > 0) {
-            // ring slot j % gs_slots, filled for the (j / gs_slots)-th time
-            const int sl = j % gs_slots;
-            if (!mbar_wait(&mbar[sl], (unsigned)(j / gs_slots) & 1u, a.status)) return;  // all threads give up together
+            if (!mbar_wait(&mbar[sl], ring_ph, a.status)) return;  // all threads give up together
             if (a.trace != nullptr && tid == 0 && j == n_my - 1) a.trace[(size_t)blockIdx.x * 12 + 11] = global_ns();
             if (warp < kg_h) {
                 const uint4* gq_ = gs_slot(sl);
@@ -717,8 +716,12 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
         // refill the slot with the item gs_slots further on
         if (gs_slots > 0 && tid == 0 && j + gs_slots < n_my) {
             constexpr int PER_ = (Q != BF16) ? 2 : 1;
-            mbar_expect_tx(&mbar[j % gs_slots], 2u * ((unsigned)kg_h * NQ32 * 16 + ((Q != BF16) ? (unsigned)kg_h * 128 : 0u)));
-            for (int r = 0; r < 2 * PER_; ++r) copy_gu(j + gs_slots, r, rs.ue);
+            mbar_expect_tx(&mbar[sl], 2u * ((unsigned)kg_h * NQ32 * 16 + ((Q != BF16) ? (unsigned)kg_h * 128 : 0u)));
+            for (int r = 0; r < 2 * PER_; ++r) copy_gu(j + gs_slots, sl, r, rs.ue);
+        }
+        if (++sl == gs_slots) {
+            sl = 0;
+            ring_ph ^= 1u;
         }
     }
     // residual of this CTA's output rows, requested before the barrier

@@ -103,3 +103,33 @@ def test_quantizers_bit_exact(cuda_lib):
         got = moe.quantize(w, quant).cpu().numpy()
         ref = oracle.quantize(w.cpu().numpy(), quant)
         assert np.array_equal(got, ref), quant
+
+
+@pytest.mark.parametrize("T,epr", [(200, 16), (37, 4)])
+def test_ep_prepare_and_device_tables(cuda_lib, T, epr):
+    """lumen_moe_ep_prepare (send side of the expert-parallel form) and
+    lumen_moe_get_routing_device against the host copy of the same routing tables."""
+    H, I, E, K = 256, 128, 32, 4
+    lay = synth.LayerLayout(H, I, E, 1)
+    blob = synth.make_layer_blob(lay, 9)
+    sc = moe.allocate_moe_scratch(H, I, E, K, T)
+    layer = sc.prepare_router_only(blob, lay.meta().router_weight_off)
+    x = torch.randn((T, H), generator=torch.Generator("cuda").manual_seed(T), device="cuda").to(torch.bfloat16)
+    ids, w = sc.route_only(layer, x.float().contiguous())
+    rows, local_ids, send_counts = sc.ep_prepare(x, epr)
+    dev = sc.get_routing_device(T, x.device)
+    torch.cuda.synchronize()
+    r = sc.get_routing(T)
+    assert np.array_equal(dev["dst_to_col"].cpu().numpy(), r["dst_to_col"])
+    assert np.array_equal(dev["expert_bounds"].cpu().numpy(), r["expert_bounds"])
+    cst = dev["col_src_tok"].cpu().numpy()
+    cex = dev["col_expert"].cpu().numpy()
+    # column c holds pair p with dst_to_col[p] == c: its token is p // K and its expert ids[p]
+    p_of_col = np.empty(T * K, np.int64)
+    p_of_col[r["dst_to_col"]] = np.arange(T * K)
+    assert np.array_equal(cst, p_of_col // K)
+    assert np.array_equal(cex, r["ids"].reshape(-1)[p_of_col])
+    assert torch.equal(rows, x[torch.from_numpy(cst).cuda().long()])
+    assert np.array_equal(local_ids.cpu().numpy(), cex % epr)
+    b = r["expert_bounds"]
+    assert np.array_equal(send_counts.cpu().numpy(), np.diff(b[::epr]))

@@ -69,6 +69,14 @@ def test_prefill_tc_path_small(cuda_lib, quant, act):
     assert err < TOL_REL_L2, err
 
 
+@pytest.mark.parametrize("E,K", [(256, 16), (64, 16), (256, 1)])
+@pytest.mark.parametrize("impl", ["", "mma"])
+def test_prefill_limits_of_expert_and_slot_counts(cuda_lib, E, K, impl):
+    # K <= 16 and E in {64, 128, 256} are what the reference's router serves (topk_moe_fused.cu:298-358)
+    err, *_ = run_case(256, 128, E, K, 1, impl, 300, "bf16", "zipf", seed=5)
+    assert err < TOL_REL_L2, err
+
+
 @pytest.mark.parametrize("quant", [1, 0])
 def test_prefill_tc_path_full_shape(cuda_lib, quant):
     err, *_ = run_case(2048, 768, 128, 8, quant, "", 96, "bf16", "zipf")

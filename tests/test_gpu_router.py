@@ -66,6 +66,26 @@ def test_topk_and_permutation_bit_exact(cuda_lib, T, kind):
     np.testing.assert_allclose(r["weights"].sum(axis=1), 1.0, atol=1e-5)
 
 
+@pytest.mark.parametrize("E,K", [(256, 16), (64, 16), (256, 1), (16, 16)])
+@pytest.mark.parametrize("gating", [0, 1])
+def test_topk_limits_of_expert_and_slot_counts(cuda_lib, E, K, gating):
+    """The reference's fused router serves K <= 16 and E in {64, 128, 256}
+    (topk_moe_fused.cu:298-358): ids, weights and permutation stay bit-exact at those
+    limits, through the small-batch and the large-batch kernels."""
+    for T in (1, 3, 16, 700):
+        lg = torch.round(synth.uniform_logits(T, E, 11 + T, tau=0.5) * 64) / 64  # some exact ties
+        sc = moe.allocate_moe_scratch(256, 128, E, K, T, gating)
+        ids, w = sc.topk_from_logits(lg)
+        r = sc.get_routing(T)
+        o_ids, o_w = oracle.topk_from_logits(lg.cpu().numpy(), K, gating)
+        assert np.array_equal(ids.cpu().numpy().astype(np.uint32), o_ids)
+        assert np.array_equal(w.cpu().numpy().view(np.uint32), o_w.view(np.uint32))
+        ce, cst, d2c, bounds = oracle.counting_sort(o_ids, E)
+        assert np.array_equal(r["expert_bounds"], bounds)
+        assert np.array_equal(r["col_src_tok"], cst)
+        assert np.array_equal(r["dst_to_col"], d2c)
+
+
 @pytest.mark.parametrize("T", [1, 16, 200])
 def test_route_only_against_cpu_router(cuda_lib, T):
     """Logits computed on the GPU sum in a different order than the sequential CPU

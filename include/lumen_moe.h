@@ -87,7 +87,9 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_ensure_prefill(lumen_moe_ctx* ctx, in
  * gate_offs[e], up [I,H] at up_offs[e], down [H,I] at down_offs[e]; raw GGML
  * Q8_0 / Q4_0 blocks or BF16, rows contiguous along the input dimension). The
  * offset arrays are HOST arrays of num_experts entries. The blob is left
- * untouched and must outlive the layer (the router weight is read in place); the
+ * untouched and must outlive the layer (the router weight is read in place when it
+ * sits on a 16-byte boundary of device memory; a file's layer blob only promises
+ * 4 bytes, and then the layer keeps its own aligned copy); the
  * expert weights are repacked once into aligned planes owned by the layer.
  * Passing NULL for all three offset tables prepares a router-only layer (nothing
  * repacked; valid for lumen_moe_route_only only), which is what an expert-parallel
@@ -234,6 +236,79 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_get_routing_device(lumen_moe_ctx* ctx
 LUMEN_MOE_API lumen_moe_status_t lumen_moe_ep_prepare(lumen_moe_ctx* ctx, const void* d_normed, int32_t act_dtype,
                                                       int32_t tokens, int32_t experts_per_rank, void* d_rows_bf16,
                                                       int32_t* d_local_ids, int64_t* d_send_counts, void* stream);
+
+/* ---- LBC container: header and layer index (host only, no device work) ----------------
+ * The reference's backend uploads a MoE layer's blob byte for byte
+ * (cuda/gpu_buffers.rs:1404-1409) and derives the operator's offsets from the layer's
+ * index entry (build_moe_meta, cuda/moe.rs:223-262). These two calls read the same
+ * index from an LBC file held in host memory, so that a checkpoint's layer goes to
+ * lumen_moe_layer_prepare with the offsets the file itself records. */
+
+/* TensorSlice of crates/lumen-format/src/index.rs:158-164: a byte range relative to the
+ * layer blob start and its scheme tag (quantization.rs:123-137: 0 F32, 1 F16, 2 BF16,
+ * 3 Q8_0, 4 Q4_0, ...). present = 0 for an optional slice the entry does not carry. */
+typedef struct {
+    uint64_t offset;
+    uint64_t length;
+    uint32_t quant;
+    uint32_t present;
+} lumen_lbc_slice;
+
+/* The header fields the operator's caller needs (header.rs:41-78, hyperparams of
+ * reader.rs:383-481). */
+typedef struct {
+    uint32_t version;            /* <= 4 */
+    uint32_t num_layers;
+    uint32_t num_heads, num_kv_heads, head_dim;
+    uint32_t hidden_dim;         /* H */
+    uint32_t intermediate_dim;
+    uint32_t vocab_size, max_seq_len;
+    uint32_t num_experts;        /* 0 for a dense model */
+    uint32_t num_active_experts; /* top-k; 0 for a dense model */
+    float norm_eps;
+    uint32_t primary_quant;      /* scheme tag of the primary descriptor */
+    uint32_t has_expert_index;
+    uint64_t alignment;
+    uint64_t layer_index_offset;
+    uint64_t payload_offset;
+    uint64_t header_bytes;       /* 183 (v2), 207 (v3), 208 or 224 (v4) */
+} lumen_lbc_header;
+
+/* One layer's entry, reduced to the MoE feed-forward path (~ CudaMoeMeta, cuda/moe.rs:39-59). */
+typedef struct {
+    uint64_t layer_offset_bytes; /* absolute position of the layer blob in the file */
+    uint64_t layer_length_bytes;
+    uint32_t is_moe;             /* router present and at least one expert */
+    uint32_t num_experts;
+    uint32_t expert_gate_quant;  /* scheme tag of expert 0's gate (= up) and down slices */
+    uint32_t expert_down_quant;
+    uint64_t expert_gate_bytes;  /* length of expert 0's gate slice: I = bytes / row bytes(H) */
+    uint64_t expert_down_bytes;
+    lumen_lbc_slice router_weight;       /* F32 [E, H] */
+    lumen_lbc_slice ffn_norm;            /* F32 [H] */
+    lumen_lbc_slice shared_expert_gate, shared_expert_up, shared_expert_down;
+    lumen_lbc_slice ffn_gate_inp_shexp;  /* F32 [H] */
+    uint32_t has_layer_type;
+    uint32_t layer_type;
+} lumen_lbc_moe_layer;
+
+/* Replaces the header half of LbcFile::from_bytes (reader.rs:134-170, parse_lbc :212-357):
+ * magic, version, checksum, alignment and layer-count checks with the reference's error
+ * cases (INVALID_ARG: bad magic, truncated, checksum mismatch, bad alignment, layer count
+ * mismatch; UNSUPPORTED: version > 4, big-endian). `data` needs to hold the header only. */
+LUMEN_MOE_API lumen_moe_status_t lumen_lbc_read_header(const void* data, size_t bytes, lumen_lbc_header* out);
+
+/* Replaces parse_layer_index (reader.rs:522-760) + LayerIndex::validate (index.rs:229-378)
+ * + build_moe_meta (cuda/moe.rs:223-262) for layer `layer`: `data` holds the file from byte
+ * 0 through the end of the layer index at least. The three offset tables (host, `capacity`
+ * entries each, all or none) receive the per-expert byte offsets relative to the layer
+ * blob, ready for lumen_moe_layer_prepare. A dense layer returns OK with is_moe = 0. */
+LUMEN_MOE_API lumen_moe_status_t lumen_lbc_read_moe_layer(const void* data, size_t bytes, uint32_t layer,
+                                                          lumen_lbc_moe_layer* out, uint64_t* gate_offs,
+                                                          uint64_t* up_offs, uint64_t* down_offs, uint32_t capacity);
+
+/* LBC scheme tag -> lumen_moe_quant_t, or -1 when the operator has no kernel for it. */
+LUMEN_MOE_API int32_t lumen_lbc_quant_to_moe(uint32_t lbc_tag);
 
 /* Device restatement of quantize_f32_to_q4_0 / _q8_0
  * (crates/lumen-convert/src/dequant.rs:791-906) and of round-to-nearest-even BF16,

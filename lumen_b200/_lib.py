@@ -19,6 +19,31 @@ class MoeConfig(ctypes.Structure):
                 ("hidden_dim", "inter_dim", "num_experts", "top_k", "max_tokens", "gating_mode", "device", "reserved")]
 
 
+class LbcSlice(ctypes.Structure):
+    _fields_ = [("offset", ctypes.c_uint64), ("length", ctypes.c_uint64), ("quant", ctypes.c_uint32),
+                ("present", ctypes.c_uint32)]
+
+
+class LbcHeader(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_uint32) for n in
+                ("version", "num_layers", "num_heads", "num_kv_heads", "head_dim", "hidden_dim", "intermediate_dim",
+                 "vocab_size", "max_seq_len", "num_experts", "num_active_experts")] + [
+        ("norm_eps", ctypes.c_float), ("primary_quant", ctypes.c_uint32), ("has_expert_index", ctypes.c_uint32),
+        ("alignment", ctypes.c_uint64), ("layer_index_offset", ctypes.c_uint64), ("payload_offset", ctypes.c_uint64),
+        ("header_bytes", ctypes.c_uint64)]
+
+
+class LbcMoeLayer(ctypes.Structure):
+    _fields_ = [("layer_offset_bytes", ctypes.c_uint64), ("layer_length_bytes", ctypes.c_uint64),
+                ("is_moe", ctypes.c_uint32), ("num_experts", ctypes.c_uint32),
+                ("expert_gate_quant", ctypes.c_uint32), ("expert_down_quant", ctypes.c_uint32),
+                ("expert_gate_bytes", ctypes.c_uint64), ("expert_down_bytes", ctypes.c_uint64),
+                ("router_weight", LbcSlice), ("ffn_norm", LbcSlice),
+                ("shared_expert_gate", LbcSlice), ("shared_expert_up", LbcSlice), ("shared_expert_down", LbcSlice),
+                ("ffn_gate_inp_shexp", LbcSlice),
+                ("has_layer_type", ctypes.c_uint32), ("layer_type", ctypes.c_uint32)]
+
+
 class LumenMoeError(RuntimeError):
     """Mirror of RuntimeError::Compute / ::Unsupported (crates/lumen-runtime/src/error.rs:6-31)."""
 
@@ -51,6 +76,9 @@ SIGNATURES = {
     "lumen_moe_get_routing": [vp, i32, vp, vp, vp, vp, vp, vp],
     "lumen_moe_get_routing_device": [vp, i32, vp, vp, vp, vp, vp],
     "lumen_moe_ep_prepare": [vp, vp, i32, i32, i32, vp, vp, vp, vp],
+    "lumen_lbc_read_header": [vp, sz, ctypes.POINTER(LbcHeader)],
+    "lumen_lbc_read_moe_layer": [vp, sz, ctypes.c_uint32, ctypes.POINTER(LbcMoeLayer), vp, vp, vp, ctypes.c_uint32],
+    "lumen_lbc_quant_to_moe": [ctypes.c_uint32],
     "lumen_moe_quantize": [vp, i64, i32, vp, vp],
     "lumen_moe_rmsnorm": [vp, vp, vp, i32, i32, f32, vp],
     "lumen_moe_stack_decode": [vp, vp, vp, i32, vp, f32, i32, vp],

@@ -90,13 +90,21 @@ lumen_moe_status_t lumen_moe_layer_prepare(lumen_moe_ctx* ctx, const void* d_lay
     }
     if (!gate_offs && !up_offs && !down_offs) {
         // router-only layer: nothing is repacked; usable with lumen_moe_route_only
-        if (router_off % 4 != 0 || router_off + (uint64_t)sc.E * sc.H * 4 > blob_bytes ||
-            (reinterpret_cast<uintptr_t>(d_layer_blob) + router_off) % 16 != 0)
+        if (router_off % 4 != 0 || router_off + (uint64_t)sc.E * sc.H * 4 > blob_bytes)
             return fail(LUMEN_MOE_INVALID_ARG, "router weight misaligned or outside the layer blob");
         lumen_moe_layer* r = new (std::nothrow) lumen_moe_layer();
         if (!r) return fail(LUMEN_MOE_CUDA_ERROR, "out of host memory");
         r->layer.dev.blob = static_cast<const uint8_t*>(d_layer_blob);
-        r->layer.dev.router_w = reinterpret_cast<const float*>(r->layer.dev.blob + router_off);
+        {
+            lumen::Status rs = lumen::aligned_router(d_layer_blob, router_off, sc.E, sc.H, st, &r->layer.repacked,
+                                                     &r->layer.dev.router_w);
+            if (rs.ok() && cudaStreamSynchronize(st) != cudaSuccess) rs = lumen::Status::Err(LUMEN_MOE_CUDA_ERROR, "copy of the router weight failed");
+            if (!rs.ok()) {
+                lumen::free_moe_layer(&r->layer);
+                delete r;
+                return fail(static_cast<lumen_moe_status_t>(rs.code), rs.msg);
+            }
+        }
         r->layer.dev.H = sc.H;
         r->layer.dev.I = sc.I;
         r->layer.dev.E = sc.E;

@@ -94,8 +94,6 @@ Status build_repacked(const CudaMoeScratch& sc, const void* layer_buf, size_t bl
     if (meta.router_weight_off % 4 != 0) return Status::Err(1, "router weight offset is not 4-byte aligned");
     if (meta.router_weight_off + (uint64_t)E * H * 4 > blob_bytes)
         return Status::Err(1, "router weight exceeds the layer blob");
-    if ((reinterpret_cast<uintptr_t>(layer_buf) + meta.router_weight_off) % 16 != 0)
-        return Status::Err(1, "router weight is not 16-byte aligned in device memory");
     const size_t gu_bytes = (size_t)I * row_bytes(H, quant), dn_bytes = (size_t)H * row_bytes(I, quant);
     for (int e = 0; e < E; ++e) {
         if (meta.expert_gate_offs[e] + gu_bytes > blob_bytes || meta.expert_up_offs[e] + gu_bytes > blob_bytes ||
@@ -104,7 +102,10 @@ Status build_repacked(const CudaMoeScratch& sc, const void* layer_buf, size_t bl
     }
     LayerDev L{};
     L.blob = static_cast<const uint8_t*>(layer_buf);
-    L.router_w = reinterpret_cast<const float*>(L.blob + meta.router_weight_off);
+    {
+        Status rs = aligned_router(layer_buf, meta.router_weight_off, E, H, st, out, &L.router_w);
+        if (!rs.ok()) return rs;
+    }
     L.quant = quant;
     L.H = H;
     L.I = I;
@@ -237,7 +238,22 @@ void free_moe_scratch(CudaMoeScratch* s) {
     *s = CudaMoeScratch();
 }
 
+Status aligned_router(const void* layer_buf, uint64_t router_off, int E, int H, cudaStream_t st,
+                      CudaMoeRepacked* out, const float** router_w) {
+    const uint8_t* src = static_cast<const uint8_t*>(layer_buf) + router_off;
+    if (reinterpret_cast<uintptr_t>(src) % 16 == 0) {
+        *router_w = reinterpret_cast<const float*>(src);
+        return Status::Ok();
+    }
+    const size_t bytes = (size_t)E * H * sizeof(float);
+    CUDA_TRY(cudaMalloc(&out->router_copy, bytes));
+    CUDA_TRY(cudaMemcpyAsync(out->router_copy, src, bytes, cudaMemcpyDeviceToDevice, st));
+    *router_w = out->router_copy;
+    return Status::Ok();
+}
+
 void free_moe_layer(MoeLayer* l) {
+    if (l->repacked.router_copy) cudaFree(l->repacked.router_copy);
     if (l->offsets.gate_up_offsets) cudaFree(l->offsets.gate_up_offsets);
     if (l->repacked.q) cudaFree(l->repacked.q);
     if (l->repacked.s) cudaFree(l->repacked.s);

@@ -76,7 +76,15 @@ struct CudaMoeRepacked {
     uint4* q = nullptr;
     uint4* s = nullptr;
     size_t q_bytes = 0, s_bytes = 0;
+    // 16-byte-aligned copy of the router weight, made only when the blob holds it at an
+    // address the vector loads cannot take (a file's layer blob aligns tensors to 4 bytes)
+    float* router_copy = nullptr;
 };
+
+// Router weight pointer for the kernels: in place when 16-byte aligned in device memory,
+// else a copy owned by `out` (enqueued on `st`).
+Status aligned_router(const void* layer_buf, uint64_t router_off, int E, int H, cudaStream_t st,
+                      CudaMoeRepacked* out, const float** router_w);
 
 // CudaMoeScratch + CudaMoePrefillGrouped, cuda/moe.rs:101-210.
 struct CudaMoeScratch {

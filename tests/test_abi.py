@@ -9,7 +9,7 @@ ROOT = Path(__file__).resolve().parent.parent
 
 def declared_symbols():
     text = (ROOT / "include" / "lumen_moe.h").read_text()
-    return sorted(set(re.findall(r"\b(lumen_moe_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(lumen_(?:moe|lbc)_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_header_and_loader_agree():

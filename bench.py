@@ -452,9 +452,83 @@ def run_ep_prefill(args):
         dist.destroy_process_group()
 
 
+def run_stack_prefill(args):
+    """Secondary workload: the stack of `--layers` MoE FFN layers (RMSNorm eps 1e-6 + residual,
+    identity mixers) as one prefill of `--tokens` tokens in total, real router, f32 residual
+    stream. N = 1: lumen_moe_stack_prefill. N > 1: tokens sharded over the ranks, experts
+    sharded E/N, per-layer NCCL dispatch/combine (strong scaling: total work fixed)."""
+    import torch
+    import torch.distributed as dist
+    from lumen_b200 import build, ep, moe, synth
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if rank == 0:
+        build.build()
+    if world > 1:
+        dist.barrier()
+    quant, T, L = QUANTS[args.quant], args.tokens, args.layers
+    Tl = T // world
+    lay = synth.LayerLayout(H, I, E, quant)
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    x_all = torch.randn((T, H), generator=g, device=dev)
+    gammas = [torch.ones(H, device=dev) for _ in range(L)]
+    x0 = x_all[rank * Tl:(rank + 1) * Tl].contiguous()
+    blobs = (synth.make_layer_blob(lay, l, device=dev) for l in range(L))  # identical on every rank
+    if world == 1:
+        sc = moe.allocate_moe_scratch(H, I, E, K, T, device=local)
+        layers = [sc.prepare_layer(b, lay.meta()) for b in blobs]
+        normed = torch.empty_like(x0)
+        fwd = lambda: sc.stack_prefill(layers, gammas, x0.clone(), 1e-6, normed)
+    else:
+        stack = ep.ExpertParallelStack(H, I, E, K, quant, blobs, gammas, rank, world, Tl, 1e-6)
+        fwd = lambda: stack.forward(x0)
+    for _ in range(max(3, args.warmup)):
+        out = fwd()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        out = fwd()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    checksum = float(out.double().abs().sum())
+    if world > 1:
+        t = torch.tensor([ms, checksum], device=dev, dtype=torch.float64)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, checksum = float(tmax[0]), float(t[1])
+    if rank == 0:
+        flops = L * T * (2 * E * H + K * 6 * I * H)
+        peaks_d = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+        peak = float(peaks_d.get("bf16_tflops_sustained", peaks_d.get("bf16_tflops", 1590.0)))
+        tf = flops / (ms / 1e3) / 1e12
+        print(json.dumps({"metric": "moe_stack_prefill_tokens_per_s", "value": T / (ms / 1e3), "unit": "tokens/s",
+                          "n_gpus": world, "steps": args.steps, "ms_per_step": ms, "ms_per_layer": ms / L,
+                          "scaling": "strong", "dtype": "f16 operands, f32 accumulate and residual stream",
+                          "config": {"workload": f"moe_stack_prefill_{args.quant}_L{L}_T{T}_router", "layers": L,
+                                     "tokens_per_gpu": Tl, "experts_per_gpu": E // world,
+                                     "wire_dtype": "f16" if world > 1 else None},
+                          "roofline": {"bound": "tensor", "achieved": tf, "peak": peak * world, "unit": "TFLOP/s",
+                                       "frac": tf / (peak * world), "flops_per_step": flops},
+                          "abs_sum_of_output": checksum}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_prefill"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "ep_prefill", "stack_prefill"])
     ap.add_argument("--routing", default="zipf", choices=["zipf", "uniform", "router"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -471,6 +545,8 @@ def main():
         run_prefill(args)
     elif args.workload == "ep_prefill":
         run_ep_prefill(args)
+    elif args.workload == "stack_prefill":
+        run_stack_prefill(args)
     else:
         run_gpu(args)
 

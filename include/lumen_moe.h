@@ -57,7 +57,10 @@ typedef enum {
 } lumen_moe_gating_t;
 
 /* Activation element types of lumen_moe_prefill. */
-typedef enum { LUMEN_MOE_ACT_F32 = 0, LUMEN_MOE_ACT_BF16 = 1 } lumen_moe_act_t;
+/* LUMEN_MOE_ACT_F16 is accepted only where the caller supplies the routing
+ * (lumen_moe_prefill_routed, lumen_moe_experts_routed_f16): it is the wire type of
+ * f32 activations between expert-parallel ranks. */
+typedef enum { LUMEN_MOE_ACT_F32 = 0, LUMEN_MOE_ACT_BF16 = 1, LUMEN_MOE_ACT_F16 = 2 } lumen_moe_act_t;
 
 typedef struct {
     int32_t hidden_dim;   /* H, multiple of 32 */
@@ -229,12 +232,14 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_get_routing_device(lumen_moe_ctx* ctx
                                                               void* stream);
 
 /* Expert-parallel send side, after lumen_moe_route_only on the same context: in one launch,
- * d_rows_bf16 [T*K, H] = the activation rows in compact-column order (rows for rank r are
- * contiguous, experts being contiguous per rank), d_local_ids [T*K] = expert id relative to
+ * d_rows16 [T*K, H] = the activation rows in compact-column order (rows for rank r are
+ * contiguous, experts being contiguous per rank) as 16-bit values: bf16 (exact) when the
+ * activations are bf16, f16 (the rounding the single-GPU grouped GEMM applies to its
+ * operand) when they are f32; d_local_ids [T*K] = expert id relative to
  * its rank, d_send_counts [E / experts_per_rank] (int64) = rows per destination rank.
  * (The reference is single-GPU; this belongs to the additive expert-parallel form.) */
 LUMEN_MOE_API lumen_moe_status_t lumen_moe_ep_prepare(lumen_moe_ctx* ctx, const void* d_normed, int32_t act_dtype,
-                                                      int32_t tokens, int32_t experts_per_rank, void* d_rows_bf16,
+                                                      int32_t tokens, int32_t experts_per_rank, void* d_rows16,
                                                       int32_t* d_local_ids, int64_t* d_send_counts, void* stream);
 
 /* ---- LBC container: header and layer index (host only, no device work) ----------------
@@ -327,6 +332,14 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_rmsnorm(const float* d_x, const float
 LUMEN_MOE_API lumen_moe_status_t lumen_moe_stack_decode(lumen_moe_ctx* ctx, const lumen_moe_layer* const* layers,
                                           const float* const* d_gammas, int32_t n_layers,
                                           float* d_x, float eps, int32_t tokens, void* stream);
+
+/* The same stack for a multi-token batch (any number of tokens): per layer
+ * normed <- rmsnorm(x; gamma_l, eps), x <- x + MoE_l(normed), in place on d_x f32 [T,H];
+ * d_normed is caller-owned scratch f32 [T,H]. The FFN half of the prefill layer loop,
+ * cuda/backend_impl.rs:9150-9176 (normed -> encode_moe_ffn_prefill_grouped -> x). */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_stack_prefill(lumen_moe_ctx* ctx, const lumen_moe_layer* const* layers,
+                                           const float* const* d_gammas, int32_t n_layers, float* d_x,
+                                           float* d_normed, float eps, int32_t tokens, void* stream);
 
 /* Device check of the library's exp used by the router (see exact_expf.h). */
 LUMEN_MOE_API lumen_moe_status_t lumen_moe_debug_expf(const float* d_in, float* d_out, int64_t n, void* stream);

@@ -11,7 +11,7 @@ LIB_PATH = PKG / "liblumen_moe_b200.so"
 OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, TIMEOUT, NCCL_ERROR = range(6)
 Q8_0, Q4_0, BF16 = 0, 1, 2
 SOFTMAX_RENORM, SIGMOID_RENORM, SIGMOID_GATE, UNIT_WEIGHT = 0, 1, 2, 3
-ACT_F32, ACT_BF16 = 0, 1
+ACT_F32, ACT_BF16, ACT_F16 = 0, 1, 2
 
 
 class MoeConfig(ctypes.Structure):
@@ -82,6 +82,7 @@ SIGNATURES = {
     "lumen_moe_quantize": [vp, i64, i32, vp, vp],
     "lumen_moe_rmsnorm": [vp, vp, vp, i32, i32, f32, vp],
     "lumen_moe_stack_decode": [vp, vp, vp, i32, vp, f32, i32, vp],
+    "lumen_moe_stack_prefill": [vp, vp, vp, i32, vp, vp, f32, i32, vp],
     "lumen_moe_debug_expf": [vp, vp, i64, vp],
     "lumen_moe_shared_expert_decode": [vp, vp, vp, vp, i32, vp],
     "lumen_moe_shared_expert_prefill": [vp, vp, vp, vp, i32, i32, vp],

@@ -305,9 +305,9 @@ lumen_moe_status_t lumen_moe_get_routing_device(lumen_moe_ctx* ctx, int32_t toke
 }
 
 lumen_moe_status_t lumen_moe_ep_prepare(lumen_moe_ctx* ctx, const void* d_normed, int32_t act_dtype, int32_t tokens,
-                                        int32_t experts_per_rank, void* d_rows_bf16, int32_t* d_local_ids,
+                                        int32_t experts_per_rank, void* d_rows16, int32_t* d_local_ids,
                                         int64_t* d_send_counts, void* stream) {
-    if (!ctx || !d_normed || !d_rows_bf16 || !d_local_ids || !d_send_counts)
+    if (!ctx || !d_normed || !d_rows16 || !d_local_ids || !d_send_counts)
         return fail(LUMEN_MOE_INVALID_ARG, "null argument");
     const lumen::CudaMoeScratch& s = ctx->scratch;
     if (tokens < 1 || tokens > s.cap_tokens) return fail(LUMEN_MOE_INVALID_ARG, "tokens exceeds the last call's capacity");
@@ -315,7 +315,7 @@ lumen_moe_status_t lumen_moe_ep_prepare(lumen_moe_ctx* ctx, const void* d_normed
         return fail(LUMEN_MOE_INVALID_ARG, "experts_per_rank must divide num_experts");
     if (s.H % 8 != 0) return fail(LUMEN_MOE_UNSUPPORTED, "hidden_dim must be a multiple of 8");
     if (act_dtype != 0 && act_dtype != 1) return fail(LUMEN_MOE_INVALID_ARG, "unknown activation dtype");
-    cudaError_t e = lumen::launch_ep_prepare(d_normed, act_dtype, s.R, tokens * s.K, s.H, s.E, experts_per_rank, d_rows_bf16,
+    cudaError_t e = lumen::launch_ep_prepare(d_normed, act_dtype, s.R, tokens * s.K, s.H, s.E, experts_per_rank, d_rows16,
                                              d_local_ids, reinterpret_cast<long long*>(d_send_counts),
                                              static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
@@ -350,6 +350,24 @@ lumen_moe_status_t lumen_moe_stack_decode(lumen_moe_ctx* ctx, const lumen_moe_la
         // x <- x + MoE(rmsnorm(x)); residual and output are the same buffer (cuda/backend_impl.rs:3570-3573)
         lumen::Status s = lumen::encode_moe_ffn_decode_fused_norm(&ctx->scratch, layers[l]->layer, d_x, d_gammas[l],
                                                                   nullptr, d_x, eps, tokens, st);
+        if (!s.ok()) return done(s);
+    }
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_stack_prefill(lumen_moe_ctx* ctx, const lumen_moe_layer* const* layers,
+                                           const float* const* d_gammas, int32_t n_layers, float* d_x, float* d_normed,
+                                           float eps, int32_t tokens, void* stream) {
+    if (!ctx || !layers || !d_gammas || !d_x || !d_normed || n_layers < 1 || tokens < 1)
+        return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int l = 0; l < n_layers; ++l) {
+        if (!layers[l] || !d_gammas[l]) return fail(LUMEN_MOE_INVALID_ARG, "null layer or gamma");
+        cudaError_t e = lumen::launch_rmsnorm(d_x, d_gammas[l], d_normed, tokens, ctx->scratch.H, eps, st);
+        if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+        // residual and output are the same buffer: the combine reads and writes each element in one thread
+        lumen::Status s = lumen::encode_moe_ffn_prefill_grouped(&ctx->scratch, layers[l]->layer, d_normed, 0, d_x, d_x,
+                                                                tokens, st, nullptr, nullptr, nullptr);
         if (!s.ok()) return done(s);
     }
     return LUMEN_MOE_OK;

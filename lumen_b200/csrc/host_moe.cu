@@ -389,7 +389,8 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     } else if (!normed || !residual || !output) {
         return Status::Err(1, "null activation pointer");
     }
-    if (act_dtype != 0 && act_dtype != 1) return Status::Err(2, "activation dtype must be f32 or bf16");
+    if (act_dtype == 2 && !ids_in) return Status::Err(2, "f16 activations need caller-supplied routing");
+    if (act_dtype < 0 || act_dtype > 2) return Status::Err(2, "activation dtype must be f32, bf16 or f16");
     Status c = check_layer(s, layer);
     if (!c.ok()) return c;
     Status g = ensure_prefill_grouped(s, batch);

@@ -449,7 +449,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 // activations -> f16, gathered into compact-column order (row c = token
 // col_src_tok[c]) and permuted within each 32-block: the grouped GEMM then reads
 // plain 2-D boxes of it with TMA
-template <typename XT>
+template <typename XT, bool IS_F16 = false>
 __global__ void __launch_bounds__(256)
 gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ col_src_tok, int H,
                           uint16_t* __restrict__ out) {
@@ -458,10 +458,11 @@ gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ 
     const XT* src = x + (size_t)tok * H;
     uint16_t* dst = out + (size_t)c * H;
     for (int i = threadIdx.x; i < H; i += 256) {
-        float v;
-        if (sizeof(XT) == 4) v = reinterpret_cast<const float*>(src)[i];
-        else v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[i]);
-        dst[(i & ~31) + perm_pos(i & 31)] = __half_as_ushort(__float2half_rn(v));
+        uint16_t h;
+        if (sizeof(XT) == 4) h = __half_as_ushort(__float2half_rn(reinterpret_cast<const float*>(src)[i]));
+        else if (IS_F16) h = reinterpret_cast<const uint16_t*>(src)[i];
+        else h = __half_as_ushort(__float2half_rn(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[i])));
+        dst[(i & ~31) + perm_pos(i & 31)] = h;
     }
 }
 
@@ -472,6 +473,8 @@ cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_
     count_launch();
     if (act_dtype == 0)
         tc::gather_permute_x16_kernel<float><<<C, 256, 0, st>>>((const float*)x, col_src_tok, H, (uint16_t*)out);
+    else if (act_dtype == 2)
+        tc::gather_permute_x16_kernel<__half, true><<<C, 256, 0, st>>>((const __half*)x, col_src_tok, H, (uint16_t*)out);
     else
         tc::gather_permute_x16_kernel<__nv_bfloat16><<<C, 256, 0, st>>>((const __nv_bfloat16*)x, col_src_tok, H,
                                                                         (uint16_t*)out);

@@ -31,6 +31,8 @@ template <>
 __device__ __forceinline__ float x_to_f32<float>(float v) { return v; }
 template <>
 __device__ __forceinline__ float x_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <>
+__device__ __forceinline__ float x_to_f32<__half>(__half v) { return __half2float(v); }
 
 template <typename XT>
 __global__ void __launch_bounds__(256)
@@ -465,9 +467,9 @@ build_xf_kernel(const XT* __restrict__ x, int T, int H, int nblk_pad, bool bf16_
 // scatter-accumulate
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-scatter_accum_kernel(const __half* __restrict__ d16, const float* __restrict__ residual,
+scatter_accum_kernel(const __half* __restrict__ d16, const float* residual,
                      const float* __restrict__ weights, const int32_t* __restrict__ dst_to_col,
-                     float* __restrict__ out, int T, int H, int K) {
+                     float* out, int T, int H, int K) {  // residual may be out (in-place layer stacks)
     const int t = blockIdx.x;  // tokens on grid.x: the y dimension is limited to 65535
     const int h2 = blockIdx.y * 256 + threadIdx.x;  // pair index
     if (h2 * 2 >= H) return;
@@ -514,6 +516,9 @@ cudaError_t launch_build_xf(const void* x, int act_dtype, int T, int H, int nblk
     if (act_dtype == 0)
         build_xf_kernel<float><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const float*)x, T, H, nblk_pad,
                                                                                bf16_mode, xf);
+    else if (act_dtype == 2)
+        build_xf_kernel<__half><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __half*)x, T, H, nblk_pad,
+                                                                                bf16_mode, xf);
     else
         build_xf_kernel<__nv_bfloat16><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
             (const __nv_bfloat16*)x, T, H, nblk_pad, bf16_mode, xf);
@@ -585,18 +590,23 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
 // order (= destination-rank order, experts being contiguous per rank) as bf16, the
 // expert id of every row relative to its rank, and the number of rows per rank.
 // ---------------------------------------------------------------------------
+// XT = float: rows leave as f16 (round to nearest, what the grouped GEMM's gather applies to
+// f32 activations); XT = bf16: rows leave as bf16, unchanged.
 template <typename XT>
 __global__ void __launch_bounds__(256)
-ep_prepare_kernel(const XT* __restrict__ x, RouteDev R, int H, int E, int epr, __nv_bfloat16* __restrict__ rows,
+ep_prepare_kernel(const XT* __restrict__ x, RouteDev R, int H, int E, int epr, uint16_t* __restrict__ rows,
                   int32_t* __restrict__ local_ids, long long* __restrict__ send_counts) {
     const int col = blockIdx.x;
     const int tok = R.col_src_tok[col];
     const XT* src = x + (size_t)tok * H;
-    __nv_bfloat16* dst = rows + (size_t)col * H;
+    uint16_t* dst = rows + (size_t)col * H;
     for (int i = threadIdx.x * 8; i < H; i += 256 * 8) {
-        __align__(16) __nv_bfloat16 v[8];
+        __align__(16) uint16_t v[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __float2bfloat16_rn(x_to_f32<XT>(src[i + j]));
+        for (int j = 0; j < 8; ++j) {
+            if (sizeof(XT) == 4) v[j] = __half_as_ushort(__float2half_rn(x_to_f32<XT>(src[i + j])));
+            else v[j] = reinterpret_cast<const uint16_t*>(src)[i + j];
+        }
         *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(v);
     }
     if (threadIdx.x == 0) local_ids[col] = R.col_expert[col] % epr;
@@ -610,9 +620,9 @@ cudaError_t launch_ep_prepare(const void* x, int act_dtype, const RouteDev& R, i
                               int32_t* local_ids, long long* send_counts, cudaStream_t st) {
     count_launch();
     if (act_dtype == 0)
-        ep_prepare_kernel<float><<<C, 256, 0, st>>>((const float*)x, R, H, E, epr, (__nv_bfloat16*)rows, local_ids, send_counts);
+        ep_prepare_kernel<float><<<C, 256, 0, st>>>((const float*)x, R, H, E, epr, (uint16_t*)rows, local_ids, send_counts);
     else
-        ep_prepare_kernel<__nv_bfloat16><<<C, 256, 0, st>>>((const __nv_bfloat16*)x, R, H, E, epr, (__nv_bfloat16*)rows,
+        ep_prepare_kernel<__nv_bfloat16><<<C, 256, 0, st>>>((const __nv_bfloat16*)x, R, H, E, epr, (uint16_t*)rows,
                                                             local_ids, send_counts);
     return cudaGetLastError();
 }

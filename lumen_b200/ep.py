@@ -158,20 +158,27 @@ class ExpertParallelMoe:
 
 
 def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.Tensor, rank: int, world: int,
-                   max_tokens: int, gating_mode: int = 0) -> Tuple[Callable, Callable, dict]:
+                   max_tokens: int, gating_mode: int = 0, contexts=None) -> Tuple[Callable, Callable, dict]:
     """Builds route_fn / expert_fn on the CUDA library for this rank.
 
     `full_blob` is the complete layer blob (router + all experts) in the reference
     layout; only this rank's expert slice is repacked and kept by the expert
-    context (K = 1, E/G experts); a second, router-only context routes."""
+    context (K = 1, E/G experts); a second, router-only context routes from its own
+    copy of the router weight, so the caller may drop `full_blob` afterwards.
+    `contexts` = (route context, expert context) of an earlier call shares them between
+    the layers of a stack (the calls of a stack are sequential)."""
     from . import moe, synth
     epr = E // world
     dev = full_blob.device.index
     lay = synth.LayerLayout(H, I, E, quant)
     meta = lay.meta()
-    route_sc = moe.allocate_moe_scratch(H, I, E, K, max_tokens, gating_mode, dev)
-    route_layer = route_sc.prepare_router_only(full_blob, meta.router_weight_off)
-    exp_sc = moe.allocate_moe_scratch(H, I, epr, 1, max_tokens * K, gating_mode, dev)
+    if contexts is None:
+        route_sc = moe.allocate_moe_scratch(H, I, E, K, max_tokens, gating_mode, dev)
+        exp_sc = moe.allocate_moe_scratch(H, I, epr, 1, max_tokens * K, gating_mode, dev)
+    else:
+        route_sc, exp_sc = contexts
+    router_blob = full_blob[meta.router_weight_off: meta.router_weight_off + E * H * 4].clone()
+    route_layer = route_sc.prepare_router_only(router_blob, 0)
     sl = slice(rank * epr, (rank + 1) * epr)
     local_meta = moe.MoeMeta(0, meta.expert_gate_offs[sl].copy(), meta.expert_up_offs[sl].copy(),
                              meta.expert_down_offs[sl].copy(), quant, quant)
@@ -222,4 +229,29 @@ def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.
     def combine_fn(back, residual, w, inv):
         return moe.combine_f16(back.contiguous(), residual, w.contiguous(), inv)
 
-    return route_fn, expert_fn, {"combine_fn": combine_fn, "route": route_sc, "experts": exp_sc, "layers": (route_layer, exp_layer)}
+    return route_fn, expert_fn, {"combine_fn": combine_fn, "route": route_sc, "experts": exp_sc,
+                                 "layers": (route_layer, exp_layer), "router_blob": router_blob}
+
+
+class ExpertParallelStack:
+    """Stack of MoE FFN layers with identity mixers over G ranks, tokens sharded:
+    x <- x + MoE_l(rmsnorm(x; gamma_l, eps)) per layer, the expert-parallel form of
+    lumen_moe_stack_prefill. The norm and the residual are local to the token's home rank;
+    f32 activations cross the wire as f16, the rounding the single-GPU grouped GEMM applies
+    to its operand."""
+
+    def __init__(self, H: int, I: int, E: int, K: int, quant: int, layer_blobs, gammas, rank: int, world: int,
+                 max_tokens: int, eps: float, gating_mode: int = 0, group=None):
+        from . import moe
+        self.eps, self.gammas, self._rmsnorm = eps, list(gammas), moe.rmsnorm
+        self.layers, self._keep, ctx = [], [], None
+        for blob in layer_blobs:  # any iterable: a generator lets each full blob be freed after its slice is repacked
+            route_fn, expert_fn, keep = cuda_layer_fns(H, I, E, K, quant, blob, rank, world, max_tokens, gating_mode, ctx)
+            ctx = (keep["route"], keep["experts"])
+            self._keep.append(keep)
+            self.layers.append(ExpertParallelMoe(E, K, route_fn, expert_fn, group=group, combine_fn=keep["combine_fn"]))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        for layer, gamma in zip(self.layers, self.gammas):
+            x = layer.forward(self._rmsnorm(x, gamma, self.eps), x)
+        return x

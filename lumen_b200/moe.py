@@ -21,7 +21,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import (ACT_BF16, ACT_F32, BF16, Q4_0, Q8_0, SIGMOID_GATE, SIGMOID_RENORM, SOFTMAX_RENORM, UNIT_WEIGHT,
+from ._lib import (ACT_BF16, ACT_F16, ACT_F32, BF16, Q4_0, Q8_0, SIGMOID_GATE, SIGMOID_RENORM, SOFTMAX_RENORM, UNIT_WEIGHT,
                    LumenMoeError, MoeConfig,
                    check)
 
@@ -212,7 +212,7 @@ class MoeScratch:
                        weights: Optional[torch.Tensor], residual: torch.Tensor,
                        output: Optional[torch.Tensor] = None) -> torch.Tensor:
         """lumen_moe_prefill_routed: expert products + combine for caller-supplied routing."""
-        act = ACT_F32 if normed.dtype == torch.float32 else ACT_BF16
+        act = {torch.float32: ACT_F32, torch.bfloat16: ACT_BF16, torch.float16: ACT_F16}[normed.dtype]
         _need(normed, normed.dtype, "normed")
         _need(ids, torch.int32, "ids")
         _need(residual, torch.float32, "residual")
@@ -225,7 +225,7 @@ class MoeScratch:
 
     def experts_routed_f16(self, layer: MoeLayer, rows: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
         """lumen_moe_experts_routed_f16 (context with top_k = 1): f16 [R,H] expert outputs in row order."""
-        act = ACT_F32 if rows.dtype == torch.float32 else ACT_BF16
+        act = {torch.float32: ACT_F32, torch.bfloat16: ACT_BF16, torch.float16: ACT_F16}[rows.dtype]
         _need(rows, rows.dtype, "rows")
         _need(ids, torch.int32, "ids")
         R = rows.numel() // self.H
@@ -278,11 +278,12 @@ class MoeScratch:
         return {"dst_to_col": d2c, "col_src_tok": cst, "col_expert": cex, "expert_bounds": bounds}
 
     def ep_prepare(self, normed: torch.Tensor, experts_per_rank: int):
-        """lumen_moe_ep_prepare after route_only: (rows bf16 [T*K,H], local_ids int32 [T*K], send_counts int64 [G])."""
+        """lumen_moe_ep_prepare after route_only: (rows [T*K,H], local_ids int32 [T*K], send_counts int64 [G]);
+        rows are bf16 for bf16 activations and f16 for f32 activations."""
         act = ACT_F32 if normed.dtype == torch.float32 else ACT_BF16
         T = normed.numel() // self.H
         dev = normed.device
-        rows = torch.empty((T * self.K, self.H), dtype=torch.bfloat16, device=dev)
+        rows = torch.empty((T * self.K, self.H), dtype=torch.float16 if act == ACT_F32 else torch.bfloat16, device=dev)
         local_ids = torch.empty(T * self.K, dtype=torch.int32, device=dev)
         send_counts = torch.empty(self.E // experts_per_rank, dtype=torch.int64, device=dev)
         check(_lib.lib().lumen_moe_ep_prepare(self._h, normed.data_ptr(), act, T, experts_per_rank, rows.data_ptr(),
@@ -318,6 +319,22 @@ class MoeScratch:
         gp = (ctypes.c_void_p * n)(*[g.data_ptr() for g in gammas])
         T = x.numel() // self.H
         check(_lib.lib().lumen_moe_stack_decode(self._h, lh, gp, n, x.data_ptr(), eps, T, _stream()))
+        return x
+
+
+    def stack_prefill(self, layers: Sequence[MoeLayer], gammas: Sequence[torch.Tensor], x: torch.Tensor,
+                      eps: float, normed: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """lumen_moe_stack_prefill: x <- x + MoE_l(rmsnorm(x)) over the layers, in place, any token count."""
+        _need(x, torch.float32, "x")
+        if normed is None:
+            normed = torch.empty_like(x)
+        _need(normed, torch.float32, "normed")
+        n = len(layers)
+        lh = (ctypes.c_void_p * n)(*[l._h for l in layers])
+        gp = (ctypes.c_void_p * n)(*[g.data_ptr() for g in gammas])
+        T = x.numel() // self.H
+        check(_lib.lib().lumen_moe_stack_prefill(self._h, lh, gp, n, x.data_ptr(), normed.data_ptr(), eps, T,
+                                                 _stream()))
         return x
 
 

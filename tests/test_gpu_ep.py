@@ -41,7 +41,18 @@ def _worker(rank, world, port, q):
         rel = float(((out - ref) - 0).norm() / (ref - res_all[sl]).norm())
         r = sc.get_routing(T)
         ids_ok = bool((torch.from_numpy(r["ids"][sl].astype("int32")).to(dev) == layer.last["ids"]).all())
-        q.put((rank, rel, ids_ok))
+        # stack of 3 layers, f32 activations (f16 on the wire), against lumen_moe_stack_prefill on one GPU
+        L = 3
+        blobs = [synth.make_layer_blob(lay, 10 + l, device=dev) for l in range(L)]
+        gammas = [(1.0 + 0.1 * torch.randn(H, generator=g, device=dev)).contiguous() for _ in range(L)]
+        x0 = torch.randn((T, H), generator=g, device=dev)
+        stack = ep.ExpertParallelStack(H, I, E, K, 1, blobs, gammas, rank, world, Tl, 1e-6)
+        ys = [stack.forward(x0[sl].contiguous()).clone() for _ in range(3)]
+        assert torch.equal(ys[0], ys[1]) and torch.equal(ys[0], ys[2])
+        full_layers = [sc.prepare_layer(b, lay.meta()) for b in blobs]
+        want = sc.stack_prefill(full_layers, gammas, x0.clone(), 1e-6)[sl]
+        rel_stack = float((ys[2] - want).norm() / (want - x0[sl]).norm())
+        q.put((rank, max(rel, rel_stack), ids_ok))
     finally:
         dist.destroy_process_group()
 

@@ -173,3 +173,35 @@ def test_prefill_full_size_properties(cuda_lib):
                                    H, I, E, K, xs, np.zeros_like(xs), ids=r["ids"][sample],
                                    weights=r["weights"][sample], threads=8)
     assert rel_l2(out[sample].cpu().numpy(), o_out) < TOL_REL_L2
+
+
+@pytest.mark.parametrize("quant,T", [(1, 40), (0, 300)])
+def test_stack_prefill_matches_layer_by_layer(cuda_lib, quant, T):
+    """x <- x + MoE_l(rmsnorm(x)) over 3 layers in one call, in place: bit-identical to the
+    out-of-place loop of rmsnorm + prefill calls, and within tolerance of the CPU stack."""
+    H, I, E, K, L = 512, 256, 16, 4, 3
+    sc = moe.allocate_moe_scratch(H, I, E, K, T)
+    lay = synth.LayerLayout(H, I, E, quant)
+    blobs = [synth.make_layer_blob(lay, 40 + l) for l in range(L)]
+    layers = [sc.prepare_layer(b, lay.meta()) for b in blobs]
+    g = torch.Generator("cuda").manual_seed(3)
+    gammas = [(1.0 + 0.1 * torch.randn(H, generator=g, device="cuda")).contiguous() for _ in range(L)]
+    x0 = torch.randn((T, H), generator=g, device="cuda")
+    x = x0.clone()
+    sc.stack_prefill(layers, gammas, x, 1e-6)
+    y = x0.clone()
+    routing = []
+    for l in range(L):
+        normed = moe.rmsnorm(y, gammas[l], 1e-6)
+        y = sc.prefill(layers[l], normed, y)
+        routing.append(sc.get_routing(T))
+    assert torch.equal(x, y)
+    ref = x0.cpu().numpy().copy()
+    meta = lay.meta()
+    for l in range(L):
+        normed = oracle.rmsnorm(ref, gammas[l].cpu().numpy(), 1e-6)
+        # routed with the ids the GPU chose for this layer (their exactness is covered on identical logits)
+        ref, _, _ = oracle.moe_layer(blobs[l].cpu().numpy(), 0, meta.expert_gate_offs, meta.expert_up_offs,
+                                     meta.expert_down_offs, quant, H, I, E, K, normed, ref,
+                                     ids=routing[l]["ids"], weights=routing[l]["weights"], threads=8)
+    assert rel_l2(x.cpu().numpy() - x0.cpu().numpy(), ref - x0.cpu().numpy()) < TOL_REL_L2

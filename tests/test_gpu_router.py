@@ -125,8 +125,8 @@ def test_quantizers_bit_exact(cuda_lib):
         assert np.array_equal(got, ref), quant
 
 
-@pytest.mark.parametrize("T,epr", [(200, 16), (37, 4)])
-def test_ep_prepare_and_device_tables(cuda_lib, T, epr):
+@pytest.mark.parametrize("T,epr,act", [(200, 16, torch.bfloat16), (37, 4, torch.bfloat16), (90, 8, torch.float32)])
+def test_ep_prepare_and_device_tables(cuda_lib, T, epr, act):
     """lumen_moe_ep_prepare (send side of the expert-parallel form) and
     lumen_moe_get_routing_device against the host copy of the same routing tables."""
     H, I, E, K = 256, 128, 32, 4
@@ -134,7 +134,7 @@ def test_ep_prepare_and_device_tables(cuda_lib, T, epr):
     blob = synth.make_layer_blob(lay, 9)
     sc = moe.allocate_moe_scratch(H, I, E, K, T)
     layer = sc.prepare_router_only(blob, lay.meta().router_weight_off)
-    x = torch.randn((T, H), generator=torch.Generator("cuda").manual_seed(T), device="cuda").to(torch.bfloat16)
+    x = torch.randn((T, H), generator=torch.Generator("cuda").manual_seed(T), device="cuda").to(act)
     ids, w = sc.route_only(layer, x.float().contiguous())
     rows, local_ids, send_counts = sc.ep_prepare(x, epr)
     dev = sc.get_routing_device(T, x.device)
@@ -149,7 +149,9 @@ def test_ep_prepare_and_device_tables(cuda_lib, T, epr):
     p_of_col[r["dst_to_col"]] = np.arange(T * K)
     assert np.array_equal(cst, p_of_col // K)
     assert np.array_equal(cex, r["ids"].reshape(-1)[p_of_col])
-    assert torch.equal(rows, x[torch.from_numpy(cst).cuda().long()])
+    # bf16 activations travel unchanged; f32 ones as f16 (round to nearest)
+    wire = x if act == torch.bfloat16 else x.to(torch.float16)
+    assert rows.dtype == wire.dtype and torch.equal(rows, wire[torch.from_numpy(cst).cuda().long()])
     assert np.array_equal(local_ids.cpu().numpy(), cex % epr)
     b = r["expert_bounds"]
     assert np.array_equal(send_counts.cpu().numpy(), np.diff(b[::epr]))

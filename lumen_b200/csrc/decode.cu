@@ -19,7 +19,7 @@
 // All three are HBM-bound: each weight byte is read exactly once with 128-bit
 // streaming loads, every load of a warp's share is in flight before the first
 // use, and the arithmetic runs on the tensor cores (mma_frag.cuh).
-#include "mma_frag.cuh"
+#include "decode_common.cuh"
 #include "router.cuh"
 
 namespace lumen {
@@ -38,9 +38,11 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
     __shared__ __align__(16) float lg_s[RS_WARPS][MAX_EXPERTS];
     __shared__ int ids_s[DECODE_MAX_TOKENS * MAX_TOP_K];
     __shared__ int cnt_s[MAX_EXPERTS];
+    __shared__ int cntw_s[DECODE_MAX_TOKENS * MAX_TOP_K / 32][MAX_EXPERTS];
     __shared__ int bounds_s[MAX_EXPERTS + 1];
     __shared__ int uidx_s[MAX_EXPERTS];
     __shared__ int is_last_s;
+    __shared__ unsigned long long tab_s[32];
 
     pdl_trigger();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -126,8 +128,21 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
         }
     }
 
-    // activation fragments (and the normed output of the fused-norm entry point)
-    if (a.xf != nullptr) {
+    // activation operand of the gate/up kernel (and the normed output of the fused-norm entry
+    // point): two-term int8 blocks for Q4_0 weights, f16 hi+lo fragments otherwise
+    if (a.xq != nullptr) {
+        const int nblk = H >> 5, nblk_pad = a.L.kg_h * 4;
+        const int sub = tid & 7;
+        const int xq_tok = dcommon::xq_tok_words(nblk_pad);
+        for (int item = blockIdx.x * (RS_THREADS / 8) + (tid >> 3); item < T * nblk;
+             item += gridDim.x * (RS_THREADS / 8)) {
+            const int t = item / nblk, b = item - t * nblk;
+            const float4 v = load_x4(t, b * 8 + sub);
+            dcommon::build_xq_block(v, sub, lane, a.xq + (size_t)t * xq_tok, nblk_pad, b);
+            if (a.gamma != nullptr && a.normed_out != nullptr)
+                reinterpret_cast<float4*>(a.normed_out + (size_t)t * H)[b * 8 + sub] = v;
+        }
+    } else if (a.xf != nullptr) {
         const int nblk = H >> 5, nblk_pad = a.L.kg_h * 4;
         const bool bf16_mode = (a.L.quant == BF16);
         const int sub = tid & 7, hl = sub >> 2, t4 = sub & 3;
@@ -157,18 +172,48 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
     if (!is_last_s) return;
 
     const float* lg = want_logits ? a.R.logits : a.logits_override;
-    for (int t = warp; t < T; t += RS_WARPS) {
-        for (int i = lane; i < E; i += 32) lg_s[warp][i] = __ldcg(lg + (size_t)t * E + i);
-        __syncwarp();
-        warp_topk(lg_s[warp], E, K, a.gating, p_s[warp], nullptr, a.R.ids + (size_t)t * K,
-                  a.R.weights + (size_t)t * K);
-        if (lane < K) ids_s[t * K + lane] = (int)a.R.ids[(size_t)t * K + lane];
+    if (tid < 32) tab_s[tid] = lumen_exact::exp2_tab_entry(tid);
+    __syncthreads();
+    // The exact exps are the long part: the 16 warps share a token's exps 4-, 2- or 1-way
+    // (consecutive warps form a token's group), then the group's first warp selects.
+    {
+        const int nsub = (T <= 4) ? 4 : (T <= 8) ? 2 : 1;
+        const int t = warp / nsub, sub = warp - t * nsub;
+        if (t < T) {
+            for (int i = lane; i < E; i += 32) lg_s[warp][i] = __ldcg(lg + (size_t)t * E + i);
+            __syncwarp();
+            float* p = p_s[warp - sub];
+            warp_gate_probs(lg_s[warp], E, a.gating, p, tab_s, sub, nsub);
+            if (nsub > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + t), "r"(nsub * 32) : "memory");
+            else __syncwarp();
+            if (sub == 0) {
+                warp_select(p, E, K, a.gating, a.R.ids + (size_t)t * K, a.R.weights + (size_t)t * K);
+                if (lane < K) ids_s[t * K + lane] = (int)a.R.ids[(size_t)t * K + lane];
+            }
+        }
     }
     __syncthreads();
+    // Stable counting sort of the C = T*K <= 128 pairs by expert, one pair per thread: pairs
+    // of one warp that share an expert rank themselves with a match, and a small table of
+    // per-warp counts orders the warps; no loop over the pairs anywhere.
     const int C = T * K;
-    if (tid < E) cnt_s[tid] = 0;
+    const int npw = (C + 31) >> 5;
+    for (int i = tid; i < npw * E; i += RS_THREADS) cntw_s[i / E][i % E] = 0;
     __syncthreads();
-    for (int p = tid; p < C; p += RS_THREADS) atomicAdd(&cnt_s[ids_s[p]], 1);
+    int my_e = -1, my_rank = 0;
+    if (warp < npw) {
+        const int p = warp * 32 + lane;
+        my_e = (p < C) ? ids_s[p] : -1 - lane;  // padding lanes match nobody
+        const unsigned same = __match_any_sync(0xffffffffu, my_e);
+        my_rank = __popc(same & ((1u << lane) - 1u));
+        if (p < C && my_rank == 0) cntw_s[warp][my_e] = __popc(same);
+    }
+    __syncthreads();
+    if (tid < E) {
+        int c = 0;
+        for (int w = 0; w < npw; ++w) c += cntw_s[w][tid];
+        cnt_s[tid] = c;
+    }
     __syncthreads();
     if (warp == 0) {
         // exclusive scan over experts, 8 per lane (E <= 256), and the ascending
@@ -219,18 +264,17 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
         }
     }
     __syncthreads();
-    if (tid < E) {
-        int cur = bounds_s[tid];
-        const int first = cur;
-        int* wtok = reinterpret_cast<int*>(a.R.work) + 8 * max(uidx_s[tid], 0) + 4;
-        for (int p = 0; p < C; ++p) {
-            if (ids_s[p] == tid) {
-                a.R.col_expert[cur] = tid;
-                a.R.col_src_tok[cur] = p / K;
-                a.R.dst_to_col[p] = cur;
-                if (cur - first < 4) wtok[cur - first] = p / K;  // source tokens of the first four columns
-                ++cur;
-            }
+    if (warp < npw) {
+        const int p = warp * 32 + lane;
+        if (p < C) {
+            int before = my_rank;  // same expert, lower pair index
+            for (int w = 0; w < warp; ++w) before += cntw_s[w][my_e];
+            const int col = bounds_s[my_e] + before;
+            a.R.col_expert[col] = my_e;
+            a.R.col_src_tok[col] = p / K;
+            a.R.dst_to_col[p] = col;
+            // source tokens of the expert's first four columns ride in its work record
+            if (before < 4) reinterpret_cast<int*>(a.R.work)[8 * uidx_s[my_e] + 4 + before] = p / K;
         }
     }
     if (tid == 0) *a.R.ticket = 0u;
@@ -699,7 +743,10 @@ cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st) {
 bool decode_small_applicable(const DecodeArgs& a, int phase);
 cudaError_t launch_decode_small_phase(const DecodeArgs& a, int phase, cudaStream_t st);
 
-cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st) {
+cudaError_t launch_decode_phase(const DecodeArgs& a_in, int phase, cudaStream_t st) {
+    // the int8 activation form belongs to the Q4_0 gate/up kernel that walks columns four at a time
+    DecodeArgs a = a_in;
+    if (!(a.xq != nullptr && a.xf != nullptr && a.L.quant == Q4_0 && decode_small_applicable(a, 1))) a.xq = nullptr;
     if (phase == 0) return launch_route_small(a, st);
     if (decode_small_applicable(a, phase)) return launch_decode_small_phase(a, phase, st);
     const int C = a.T * a.K;

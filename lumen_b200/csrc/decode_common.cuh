@@ -21,6 +21,51 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
+// D (s32) += A (u8, 16 x 32) * B (s8, 32 x 8): Q4_0 nibbles go in raw as A.
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                         unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned pack_s8x4(float a, float b, float c, float d) {
+    return ((unsigned)(int)a & 0xffu) | (((unsigned)(int)b & 0xffu) << 8) | (((unsigned)(int)c & 0xffu) << 16) |
+           (((unsigned)(int)d & 0xffu) << 24);
+}
+
+// Two-term int8 form of the activations for the Q4_0 gate/up product: x ~ sx * (q0 + q1 / 254)
+// per 32-input block, sx = absmax / 127. Per token, in 32-bit words:
+//   [2 terms][nblk_pad * 8 + 8]   the word pair of lane quad t of a block is adjacent:
+//                                 {inputs 4t..4t+3, inputs 16+4t..16+4t+3} (the s8 B fragment)
+//   [nblk_pad] float2             {sx, 8 * sx * sum(q0 + q1 / 254)}: the nibbles enter unsigned,
+//                                 the second value removes their offset of 8
+__host__ __device__ __forceinline__ int xq_term_words(int nblk_pad) { return nblk_pad * 8 + 8; }
+__host__ __device__ __forceinline__ int xq_tok_words(int nblk_pad) { return 2 * xq_term_words(nblk_pad) + 2 * nblk_pad; }
+
+// The 8 lanes of a block (sub = 0..7, consecutive lanes of a warp) each bring inputs 4 sub .. 4 sub + 3.
+__device__ __forceinline__ void build_xq_block(float4 v, int sub, int lane, unsigned* xq_tok_base, int nblk_pad, int b) {
+    const unsigned gmask = 0xFFu << (lane & 24);
+    float am = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(gmask, am, o));
+    const float inv = (am > 0.0f) ? 127.0f / am : 0.0f;
+    const float sx = am * (1.0f / 127.0f);
+    const float r0 = v.x * inv, r1 = v.y * inv, r2 = v.z * inv, r3 = v.w * inv;
+    const float q00 = rintf(r0), q01 = rintf(r1), q02 = rintf(r2), q03 = rintf(r3);
+    const float q10 = rintf((r0 - q00) * 254.0f), q11 = rintf((r1 - q01) * 254.0f);
+    const float q12 = rintf((r2 - q02) * 254.0f), q13 = rintf((r3 - q03) * 254.0f);
+    float sum = (q00 + q01 + q02 + q03) + (q10 + q11 + q12 + q13) * (1.0f / 254.0f);
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(gmask, sum, o);
+    const int term = xq_term_words(nblk_pad);
+    unsigned* base = xq_tok_base + b * 8 + (sub & 3) * 2 + (sub >> 2);
+    base[0] = pack_s8x4(q00, q01, q02, q03);
+    base[term] = pack_s8x4(q10, q11, q12, q13);
+    if (sub == 0) reinterpret_cast<float2*>(xq_tok_base + 2 * term)[b] = make_float2(sx, 8.0f * sx * sum);
+}
+
 // One 32-input block (two MMAs) of one column group; the B fragment comes from shared memory.
 template <int Q>
 __device__ __forceinline__ void block_mma_smem(const WTile<Q>& w, int b, const uint4* bsm, bool bvalid,

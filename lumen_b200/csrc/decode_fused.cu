@@ -193,19 +193,6 @@ struct RouteSm {
 // block's precomputed 8 * sx * sum(q0 + q1 / 254).
 constexpr bool kInt8GateUp = true;
 
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
-                                         unsigned b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ unsigned pack_s8x4(float a, float b, float c, float d) {
-    return ((unsigned)(int)a & 0xffu) | (((unsigned)(int)b & 0xffu) << 8) | (((unsigned)(int)c & 0xffu) << 16) |
-           (((unsigned)(int)d & 0xffu) << 24);
-}
-
 struct TopkSm {
     float lg[FMAX_T][MAX_EXPERTS];
     float p[FMAX_T][MAX_EXPERTS];
@@ -357,32 +344,14 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     // activation operand of every token, private to this CTA
     // int8 form: per token [2 terms][nblk_pad * 8 + 8 words] then [nblk_pad] {sx, 8 * sx * sum}; inside a block
     // the word pair of lane quad t is adjacent: {inputs 4t..4t+3, inputs 16+4t..16+4t+3}
-    const int xq_term = nblk_pad * 8 + 8, xq_tok = 2 * xq_term + 2 * nblk_pad;  // in 32-bit words
+    const int xq_term = xq_term_words(nblk_pad), xq_tok = xq_tok_words(nblk_pad);  // in 32-bit words
     unsigned* xq = reinterpret_cast<unsigned*>(xs);
     if (Q == Q4_0 && kInt8GateUp) {
         const int sub = tid & 7;
-        const unsigned gmask = 0xFFu << (lane & 24);
 #pragma unroll 1
         for (int item = tid >> 3; item < T * nblk; item += FT / 8) {
             const int t = item / nblk, b = item - t * nblk;
-            const float4 v = xn4[t * H4 + b * 8 + sub];  // inputs 4 sub .. 4 sub + 3 of the block
-            float am = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) am = fmaxf(am, __shfl_xor_sync(gmask, am, o));
-            const float inv = (am > 0.0f) ? 127.0f / am : 0.0f;
-            const float sx = am * (1.0f / 127.0f);
-            const float r0 = v.x * inv, r1 = v.y * inv, r2 = v.z * inv, r3 = v.w * inv;
-            const float q00 = rintf(r0), q01 = rintf(r1), q02 = rintf(r2), q03 = rintf(r3);
-            const float q10 = rintf((r0 - q00) * 254.0f), q11 = rintf((r1 - q01) * 254.0f);
-            const float q12 = rintf((r2 - q02) * 254.0f), q13 = rintf((r3 - q03) * 254.0f);
-            float sum = (q00 + q01 + q02 + q03) + (q10 + q11 + q12 + q13) * (1.0f / 254.0f);
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) sum += __shfl_xor_sync(gmask, sum, o);
-            unsigned* base = xq + (size_t)t * xq_tok + b * 8 + (sub & 3) * 2 + (sub >> 2);
-            base[0] = pack_s8x4(q00, q01, q02, q03);
-            base[xq_term] = pack_s8x4(q10, q11, q12, q13);
-            if (sub == 0)
-                reinterpret_cast<float2*>(xq + (size_t)t * xq_tok + 2 * xq_term)[b] = make_float2(sx, 8.0f * sx * sum);
+            build_xq_block(xn4[t * H4 + b * 8 + sub], sub, lane, xq + (size_t)t * xq_tok, nblk_pad, b);
         }
         // padding blocks (kg_h * 4 > H / 32) must read as zero
         const int padw = (nblk_pad - nblk) * 8;

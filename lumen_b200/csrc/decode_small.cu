@@ -86,6 +86,8 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
     // most four columns at batches up to 4, rarely more at batches up to 16); the weights stay
     // in registers across the chunks.
     const int per_col = 2 * nblk_pad * 4;
+    const bool int8_act = (Q == Q4_0) && (a.xq != nullptr);
+    const int xq_term = xq_term_words(nblk_pad), xq_tok = xq_tok_words(nblk_pad);  // 32-bit words
     for (int cb = 0; cb < wd.z; cb += 4) {
         const int ncol = min(4, wd.z - cb);
         // stage the activation fragments of these columns' tokens (first chunk: while the weights are in flight)
@@ -94,8 +96,13 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
             if (j < ncol) {
                 const int tok = (cb == 0) ? (j == 0 ? wt.x : j == 1 ? wt.y : j == 2 ? wt.z : wt.w)
                                           : a.R.col_src_tok[c0 + cb + j];
-                const uint4* src = a.xf + (size_t)tok * per_col;
-                for (int i = tid; i < per_col; i += WARPS * 32) cp_async16(&xs[j * per_col + i], src + i);
+                if (int8_act) {
+                    const uint4* src = reinterpret_cast<const uint4*>(a.xq + (size_t)tok * xq_tok);
+                    for (int i = tid; i < xq_tok / 4; i += WARPS * 32) cp_async16(&xs[j * (xq_tok / 4) + i], src + i);
+                } else {
+                    const uint4* src = a.xf + (size_t)tok * per_col;
+                    for (int i = tid; i < per_col; i += WARPS * 32) cp_async16(&xs[j * per_col + i], src + i);
+                }
             }
         }
         cp_async_wait_all();
@@ -105,15 +112,51 @@ gate_up_small_kernel(const __grid_constant__ DecodeArgs a) {
         const bool bvalid = jcol < ncol;
         const uint4* bbase = xs + ((size_t)(jcol * 2 + (gq & 1)) * nblk_pad) * 4 + t4;
         float acc_g[4] = {0.f, 0.f, 0.f, 0.f}, acc_u[4] = {0.f, 0.f, 0.f, 0.f};
+        if (Q == Q4_0 && int8_act) {
+            // raw nibbles (u8) times the two int8 terms of the activations; n index = 2 * column + term,
+            // so acc[0] / acc[2] are rows gq / gq + 8 of the lane's column t4 (acc[1], acc[3] stay zero)
+            const unsigned* xqs = reinterpret_cast<const unsigned*>(xs);
+            const unsigned* bq0 = xqs + (size_t)jcol * xq_tok + (gq & 1) * xq_term + t4 * 2;
+            const float2* sc0 = reinterpret_cast<const float2*>(xqs + (size_t)(t4 < ncol ? t4 : 0) * xq_tok + 2 * xq_term);
 #pragma unroll
-        for (int it = 0; it < ITERS; ++it) {
-            const int kg = warp + it * WARPS;
-            if (kg < kg_h) {
-                const uint4* bp = bbase + (size_t)kg * 16;
+            for (int it = 0; it < ITERS; ++it) {
+                const int kg = warp + it * WARPS;
+                if (kg < kg_h) {
+                    const unsigned* bq = bq0 + (kg * 4) * 8;
+                    const float2* sc = sc0 + kg * 4;
 #pragma unroll
-                for (int b = 0; b < 4; ++b) {
-                    block_mma_smem<Q>(wg[it], b, bp, bvalid, acc_g);
-                    block_mma_smem<Q>(wu[it], b, bp, bvalid, acc_u);
+                    for (int b = 0; b < 4; ++b) {
+                        uint2 bb = make_uint2(0u, 0u);
+                        if (bvalid) bb = *reinterpret_cast<const uint2*>(bq + b * 8);
+                        const uint4 qg = wg[it].q[b >> 1], qu = wu[it].q[b >> 1];
+                        const unsigned g0 = (b & 1) ? qg.z : qg.x, g8 = (b & 1) ? qg.w : qg.y;
+                        const unsigned u0 = (b & 1) ? qu.z : qu.x, u8 = (b & 1) ? qu.w : qu.y;
+                        int cg[4] = {0, 0, 0, 0}, cu[4] = {0, 0, 0, 0};
+                        mma_u8s8(cg, g0 & 0x0F0F0F0Fu, g8 & 0x0F0F0F0Fu, (g0 >> 4) & 0x0F0F0F0Fu, (g8 >> 4) & 0x0F0F0F0Fu,
+                                 bb.x, bb.y);
+                        mma_u8s8(cu, u0 & 0x0F0F0F0Fu, u8 & 0x0F0F0F0Fu, (u0 >> 4) & 0x0F0F0F0Fu, (u8 >> 4) & 0x0F0F0F0Fu,
+                                 bb.x, bb.y);
+                        const float2 sxo = sc[b];  // {sx, 8 * sx * sum(q)}
+                        const float2 sg = block_scales<Q>(wg[it], b), su = block_scales<Q>(wu[it], b);
+                        const float k1 = 1.0f / 254.0f;
+                        acc_g[0] = fmaf(sg.x, fmaf(sxo.x, fmaf((float)cg[1], k1, (float)cg[0]), -sxo.y), acc_g[0]);
+                        acc_g[2] = fmaf(sg.y, fmaf(sxo.x, fmaf((float)cg[3], k1, (float)cg[2]), -sxo.y), acc_g[2]);
+                        acc_u[0] = fmaf(su.x, fmaf(sxo.x, fmaf((float)cu[1], k1, (float)cu[0]), -sxo.y), acc_u[0]);
+                        acc_u[2] = fmaf(su.y, fmaf(sxo.x, fmaf((float)cu[3], k1, (float)cu[2]), -sxo.y), acc_u[2]);
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int it = 0; it < ITERS; ++it) {
+                const int kg = warp + it * WARPS;
+                if (kg < kg_h) {
+                    const uint4* bp = bbase + (size_t)kg * 16;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        block_mma_smem<Q>(wg[it], b, bp, bvalid, acc_g);
+                        block_mma_smem<Q>(wu[it], b, bp, bvalid, acc_u);
+                    }
                 }
             }
         }

@@ -133,20 +133,21 @@ Status build_repacked(const CudaMoeScratch& sc, const void* layer_buf, size_t bl
 }
 
 static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
-    // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf, w16
+    // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf, w16, xq
     const size_t C = (size_t)cap * s.K;
     const size_t nblk_h_pad = (size_t)((s.H / 32 + 3) / 4) * 4, nblk_i_pad = (size_t)((s.I / 32 + 3) / 4) * 4;
     const size_t max_ct = C / 256 + s.E, max_ct_dn = C / 128 + s.E;  // gate/up tiles of 256 columns, down tiles of 128
     const size_t n_tile_entries = max_ct * ((size_t)s.I / 128 + 1) + max_ct_dn * ((size_t)s.H / 256 + 1);
-    size_t sizes[14] = {
+    size_t sizes[15] = {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,
         (size_t)((cap + 31) / 32) * s.E * 4,
         n_tile_entries * sizeof(int4),
         C * s.I * 2, C * s.H * 2, C * s.H * 2,
         (size_t)cap * 2 * nblk_h_pad * 64, C * 2 * nblk_i_pad * 64,
-        (size_t)s.E * s.H * 4};
+        (size_t)s.E * s.H * 4,
+        (size_t)DECODE_MAX_TOKENS * (18 * nblk_h_pad + 16) * 4};  // xq_tok_words(nblk_h_pad) words per token
     size_t off = 0;
-    for (int i = 0; i < 14; ++i) {
+    for (int i = 0; i < 15; ++i) {
         offs[i] = off;
         off += align_up(sizes[i], 256);
     }
@@ -154,7 +155,7 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
 }
 
 static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
-    size_t offs[14];
+    size_t offs[15];
     const size_t bytes = tok_arena_bytes(*s, cap, offs);
     void* p = nullptr;
     CUDA_TRY(cudaMalloc(&p, bytes));
@@ -178,6 +179,7 @@ static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
     s->xf = reinterpret_cast<uint4*>(b + offs[11]);
     s->sf = reinterpret_cast<uint4*>(b + offs[12]);
     s->w16 = reinterpret_cast<__half*>(b + offs[13]);
+    s->xq = reinterpret_cast<unsigned*>(b + offs[14]);
     return Status::Ok();
 }
 
@@ -281,6 +283,7 @@ static DecodeArgs make_decode_args(CudaMoeScratch* s, const MoeLayer& layer, int
     a.L = layer.dev;
     a.R = s->R;
     a.xf = s->xf;
+    a.xq = s->xq;
     a.sf = s->sf;
     a.s_f32 = nullptr;
     a.T = tokens;
@@ -351,6 +354,7 @@ Status encode_route_only(CudaMoeScratch* s, const MoeLayer* layer, const float* 
         a.gating = s->gating;
         a.logits_override = logits_in;
         a.xf = nullptr;
+        a.xq = nullptr;
         CUDA_TRY(launch_route_small(a, st));
     } else {
         PrefillArgs p{};

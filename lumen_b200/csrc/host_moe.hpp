@@ -93,6 +93,7 @@ struct CudaMoeScratch {
     int cap_tokens = 0;  // capacity of the token-sized buffers below
     RouteDev R{};
     uint4* xf = nullptr;    // decode activation fragments
+    unsigned* xq = nullptr; // decode activations as two-term int8 blocks (Q4_0 gate/up of the three-kernel chain)
     uint4* sf = nullptr;    // decode SwiGLU fragments
     float* s_f32 = nullptr; // optional debug copy
     // prefill (grow-only)

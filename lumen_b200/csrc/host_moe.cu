@@ -136,7 +136,7 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
     // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf, w16, xq
     const size_t C = (size_t)cap * s.K;
     const size_t nblk_h_pad = (size_t)((s.H / 32 + 3) / 4) * 4, nblk_i_pad = (size_t)((s.I / 32 + 3) / 4) * 4;
-    const size_t max_ct = C / 256 + s.E, max_ct_dn = C / 128 + s.E;  // gate/up tiles of 256 columns, down tiles of 128
+    const size_t max_ct = C / 128 + s.E, max_ct_dn = C / 128 + s.E;  // gate/up tiles of 128 or 256 columns (sized for 128), down tiles of 128
     const size_t n_tile_entries = max_ct * ((size_t)s.I / 128 + 1) + max_ct_dn * ((size_t)s.H / 256 + 1);
     size_t sizes[15] = {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,

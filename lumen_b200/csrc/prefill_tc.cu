@@ -205,21 +205,23 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
     }
 }
 
-template <int Q, int MODE>
+template <int Q, int MODE, int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     // Two 128-row weight operands share every activation stage (gate and up rows of the
     // same I range; two adjacent row tiles of the down matrix): the activation operand,
     // which comes from L2 at 2 bytes per element, is then read at half the rate.
-    // gate/up: 256-column tiles; the two 256-column f32 accumulators fill TMEM (512
-    // columns), one accumulator set, the epilogue of a tile is not overlapped with the next
-    // tile's MMAs (its producers do run ahead); with K = H the main loop is long.
-    // down: K = I is short (12 stages at I = 768), so the epilogue weighs more: 128-column
-    // tiles and TWO accumulator sets, the epilogue of tile i runs under the MMAs of tile i+1.
+    // 256-column tiles (gate/up once the experts average more than 128 columns): the two
+    // 256-column f32 accumulators fill TMEM (512 columns), one accumulator set, the epilogue
+    // of a tile is not overlapped with the next tile's MMAs (its producers do run ahead);
+    // each dequantised weight tile serves 256 columns, and with K = H the main loop is long.
+    // 128-column tiles (down: K = I is short, 12 stages at I = 768, so the epilogue weighs
+    // more; gate/up of small batches: fewer empty columns): TWO accumulator sets, the
+    // epilogue of tile i runs under the MMAs of tile i+1.
     constexpr int NA = 2;
-    constexpr int BN = (MODE == 1) ? 128 : 256;        // columns per tile
-    constexpr int NACC = (MODE == 1) ? 2 : 1;          // accumulator sets in TMEM
-    constexpr int STAGES = (MODE == 1) ? 4 : 3;        // one stage = 64 inputs (one swizzle atom in K)
+    // BN: columns per tile
+    constexpr int NACC = (BN == 128) ? 2 : 1;          // accumulator sets in TMEM
+    constexpr int STAGES = (BN == 128) ? 4 : 3;        // one stage = 64 inputs (one swizzle atom in K)
     constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operands then B
     constexpr int TMEM_COLS = NA * BN * NACC;
 
@@ -505,28 +507,28 @@ static cudaError_t make_tmap(const void* base, uint64_t rows, uint64_t cols, CUt
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int Q, int MODE>
+template <int Q, int MODE, int BN>
 static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
     constexpr int NA = 2;
-    constexpr int BN = (MODE == 1) ? 128 : 256;      // must match the kernel
-    constexpr int STAGES = (MODE == 1) ? 4 : 3;
+    constexpr int STAGES = (BN == 128) ? 4 : 3;
     const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(tc::grouped_gemm_tc_kernel<Q, MODE>,
+        cudaError_t e = cudaFuncSetAttribute(tc::grouped_gemm_tc_kernel<Q, MODE, BN>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
     count_launch();
-    tc::grouped_gemm_tc_kernel<Q, MODE><<<grid, tc::THREADS, smem, st>>>(a);
+    tc::grouped_gemm_tc_kernel<Q, MODE, BN><<<grid, tc::THREADS, smem, st>>>(a);
     return cudaGetLastError();
 }
 
 // gate/up + SwiGLU then down, both on tcgen05. x16: permuted 16-bit activations [T,H].
 cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st, __half* out16_rows) {
     const int C = p.T * p.K;
-    const int max_ct = C / 256 + p.L.E;
+    const int gu_cols = tc_gu_tile_cols(C, p.L.E);  // as launch_route_large built the tile lists
+    const int max_ct = C / gu_cols + p.L.E;
     const int mt_gu = p.L.I / 128;
     tc::Args gu{};
     cudaError_t te = make_tmap(x16, (uint64_t)C, (uint64_t)p.L.H, &gu.tmap);
@@ -554,17 +556,17 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     cudaError_t e;
     switch (p.L.quant) {
         case Q4_0:
-            e = launch_tc_one<Q4_0, 0>(gu, grid, st);
+            e = (gu_cols == 256) ? launch_tc_one<Q4_0, 0, 256>(gu, grid, st) : launch_tc_one<Q4_0, 0, 128>(gu, grid, st);
             if (e != cudaSuccess) return e;
-            return launch_tc_one<Q4_0, 1>(dn, grid, st);
+            return launch_tc_one<Q4_0, 1, 128>(dn, grid, st);
         case Q8_0:
-            e = launch_tc_one<Q8_0, 0>(gu, grid, st);
+            e = (gu_cols == 256) ? launch_tc_one<Q8_0, 0, 256>(gu, grid, st) : launch_tc_one<Q8_0, 0, 128>(gu, grid, st);
             if (e != cudaSuccess) return e;
-            return launch_tc_one<Q8_0, 1>(dn, grid, st);
+            return launch_tc_one<Q8_0, 1, 128>(dn, grid, st);
         default:
-            e = launch_tc_one<BF16, 0>(gu, grid, st);
+            e = (gu_cols == 256) ? launch_tc_one<BF16, 0, 256>(gu, grid, st) : launch_tc_one<BF16, 0, 128>(gu, grid, st);
             if (e != cudaSuccess) return e;
-            return launch_tc_one<BF16, 1>(dn, grid, st);
+            return launch_tc_one<BF16, 1, 128>(dn, grid, st);
     }
 }
 

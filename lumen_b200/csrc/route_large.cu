@@ -572,8 +572,8 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const int nchunks = (T + SORT_TOK - 1) / SORT_TOK;
     sort_hist_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist);
     const int C = T * K;
-    // columns per grouped-GEMM tile: 256 for gate/up, 128 for down (two accumulator sets in TMEM)
-    const int tile_cols = 256, tile_cols_dn = 128;
+    // columns per grouped-GEMM tile: 128 or 256 for gate/up, 128 for down
+    const int tile_cols = tc_gu_tile_cols(C, E), tile_cols_dn = 128;
     const int max_ct = C / tile_cols + E, max_ct_dn = C / tile_cols_dn + E;
     const int mt_gu = a.L.I / 128, mt_dn = a.L.H / 256;  // m-tiles: 128 gate + 128 up rows | 256 down rows
     int4* tiles_gu = a.tiles;

@@ -150,13 +150,13 @@ __device__ __forceinline__ void split_pair(float v0, float v1, uint32_t& hi, uin
     lo = *reinterpret_cast<const uint32_t*>(&l);
 }
 
-template <typename XT>
+// NE = experts per CTA: 64, or 32 for batches that would otherwise leave most SMs with a few warps
+template <typename XT, int NE>
 __global__ void __launch_bounds__(128)
 router_logits_mma_kernel(const XT* __restrict__ x, const __half* __restrict__ w16, float* __restrict__ logits,
                          int T, int H, int E) {
     constexpr int BM = 64, BK = 32;
     // [buffer][plane][expert row][32 inputs]: 64-byte rows, 16-byte fragment loads are conflict-free
-    constexpr int NE = 64;  // experts per CTA
     __shared__ __align__(16) __half ws[2][2][NE][BK];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t4 = lane & 3;
@@ -549,12 +549,21 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
             const size_t n = (size_t)E * H;
             split_router_w_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.L.router_w, a.w16, n);
             count_launch(1);
-            const dim3 grid((T + 63) / 64, (E + 63) / 64);
-            if (a.act_dtype == 0)
-                router_logits_mma_kernel<float><<<grid, 128, 0, st>>>((const float*)a.x, a.w16, a.R.logits, T, H, E);
-            else
-                router_logits_mma_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>((const __nv_bfloat16*)a.x, a.w16,
-                                                                             a.R.logits, T, H, E);
+            // experts per CTA: fewer for small batches, so that every SM still gets several warps
+            const int ne = (T <= 2048) ? 16 : (T <= 16384) ? 32 : 64;
+            const dim3 grid((T + 63) / 64, (E + ne - 1) / ne);
+#define LUMEN_LAUNCH_LOGITS(XT, NE_) \
+    router_logits_mma_kernel<XT, NE_><<<grid, 128, 0, st>>>((const XT*)a.x, a.w16, a.R.logits, T, H, E)
+            if (a.act_dtype == 0) {
+                if (ne == 16) LUMEN_LAUNCH_LOGITS(float, 16);
+                else if (ne == 32) LUMEN_LAUNCH_LOGITS(float, 32);
+                else LUMEN_LAUNCH_LOGITS(float, 64);
+            } else {
+                if (ne == 16) LUMEN_LAUNCH_LOGITS(__nv_bfloat16, 16);
+                else if (ne == 32) LUMEN_LAUNCH_LOGITS(__nv_bfloat16, 32);
+                else LUMEN_LAUNCH_LOGITS(__nv_bfloat16, 64);
+            }
+#undef LUMEN_LAUNCH_LOGITS
         } else {
             const dim3 grid((T + 63) / 64, (E + 63) / 64);
             if (a.act_dtype == 0)

@@ -419,7 +419,8 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     p.tiles = s->tiles;
     p.n_tiles = s->n_tiles;
     p.status = s->status;
-    const bool tc_ok = (s->H % 256 == 0) && (s->I % 128 == 0);
+    // the tcgen05 path reads activation rows with 16-byte loads (8-byte for 16-bit rows)
+    const bool tc_ok = (s->H % 256 == 0) && (s->I % 128 == 0) && (reinterpret_cast<uintptr_t>(normed) % 16 == 0);
     p.impl = (s->prefill_impl == 1 || !tc_ok) ? 1 : 0;
     CUDA_TRY(launch_route_large(p, st));
     const bool bf16_mode = (layer.dev.quant == BF16);

@@ -459,12 +459,21 @@ gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ 
     const int tok = col_src_tok[c];
     const XT* src = x + (size_t)tok * H;
     uint16_t* dst = out + (size_t)c * H;
-    for (int i = threadIdx.x; i < H; i += 256) {
-        uint16_t h;
-        if (sizeof(XT) == 4) h = __half_as_ushort(__float2half_rn(reinterpret_cast<const float*>(src)[i]));
-        else if (IS_F16) h = reinterpret_cast<const uint16_t*>(src)[i];
-        else h = __half_as_ushort(__float2half_rn(__bfloat162float(reinterpret_cast<const __nv_bfloat16*>(src)[i])));
-        dst[(i & ~31) + perm_pos(i & 31)] = h;
+    // one thread per output chunk of 8 values (16 bytes): chunk t of a 32-block holds inputs
+    // (4t, 4t+2, 16+4t, 16+4t+2, 4t+1, 4t+3, 16+4t+1, 16+4t+3), i.e. perm_pos of two runs of four
+    auto to_h = [](XT v) -> uint16_t {
+        if (sizeof(XT) == 4) return __half_as_ushort(__float2half_rn(*reinterpret_cast<const float*>(&v)));
+        if (IS_F16) return *reinterpret_cast<const uint16_t*>(&v);
+        return __half_as_ushort(__float2half_rn(__bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&v))));
+    };
+    struct __align__(4 * sizeof(XT)) Run { XT v[4]; };
+    for (int ch = threadIdx.x; ch < H / 8; ch += 256) {
+        const int blk = ch >> 2, t = ch & 3;
+        const Run a = *reinterpret_cast<const Run*>(src + blk * 32 + 4 * t);
+        const Run b = *reinterpret_cast<const Run*>(src + blk * 32 + 16 + 4 * t);
+        __align__(16) uint16_t o[8] = {to_h(a.v[0]), to_h(a.v[2]), to_h(b.v[0]), to_h(b.v[2]),
+                                       to_h(a.v[1]), to_h(a.v[3]), to_h(b.v[1]), to_h(b.v[3])};
+        *reinterpret_cast<uint4*>(dst + blk * 32 + t * 8) = *reinterpret_cast<const uint4*>(o);
     }
 }
 

@@ -381,7 +381,7 @@ def run_prefill(args):
 
 
 def run_ep_prefill(args):
-    """Secondary workload: expert-parallel prefill (BASELINE config 4). `--tokens` tokens
+    """Secondary workload: expert-parallel prefill. `--tokens` tokens
     in total, sharded over the ranks; 128 experts split evenly; NCCL all-to-all dispatch
     and combine. Strong scaling: total work fixed as N grows. At N = 1 the same tokens go
     through the single-GPU prefill entry point."""

@@ -30,7 +30,7 @@ def test_golden_small_layer(cuda_lib, name):
 @pytest.mark.parametrize("quant", [1, 0, 2])
 @pytest.mark.parametrize("T", [1, 4, 16])
 def test_decode_full_shape_identical_logits(cuda_lib, quant, T):
-    """BASELINE shapes (H=2048, E=128, K=8, I=768); both sides route on the same logits."""
+    """Headline shapes (H=2048, E=128, K=8, I=768); both sides route on the same logits."""
     H, I, E, K = 2048, 768, 128, 8
     lay, meta, blob_np, sc, layer = make_layer(H, I, E, K, quant, seed=0)
     g = torch.Generator("cuda").manual_seed(1)

@@ -144,7 +144,7 @@ def test_prefill_reference_pipeline_fixture(cuda_lib):
 
 
 def test_prefill_full_size_properties(cuda_lib):
-    """BASELINE config 3 size (T=4096, Zipf): size-independent checks plus a
+    """Full prefill size (T=4096, Zipf): size-independent checks plus a
     sample of tokens against the CPU reference."""
     H, I, E, K, T = 2048, 768, 128, 8, 4096
     lay, meta, blob_np, sc, layer = make(H, I, E, K, 1, "", 0, max_tokens=T)

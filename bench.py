@@ -414,8 +414,8 @@ def run_ep_prefill(args):
         fwd = lambda: sc.prefill(layer, x, res)
     else:
         route_fn, expert_fn, keep = ep.cuda_layer_fns(H, I, E, K, quant, blob, rank, world, Tl)
-        epl = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, combine_fn=keep["combine_fn"])
-        fwd = lambda: epl.forward(x, res)
+        epl = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, combine_fn=keep["combine_fn"], route_takes_slot=True)
+        fwd = (lambda: epl.forward(x, res)) if args.ep_chunks < 2 else (lambda: epl.forward_pipelined(x, res, args.ep_chunks))
     for _ in range(max(3, args.warmup)):
         out = fwd()
     torch.cuda.synchronize()
@@ -431,7 +431,7 @@ def run_ep_prefill(args):
     phases = None
     if world > 1:
         epl.profile = True
-        fwd()
+        epl.forward(x, res)
         phases = {k: round(v, 3) for k, v in epl.phase_times_ms()}
         epl.profile = False
     checksum = float(out.float().abs().sum())
@@ -445,7 +445,8 @@ def run_ep_prefill(args):
         print(json.dumps({"metric": "moe_layer_ep_prefill_tokens_per_s", "value": T / (ms / 1e3), "unit": "tokens/s",
                           "n_gpus": world, "steps": args.steps, "ms_per_call": ms, "scaling": "strong",
                           "config": {"workload": f"moe_ffn_ep_prefill_{args.quant}_T{T}", "experts_per_gpu": E // world,
-                                     "tokens_per_gpu": Tl, "wire_dtype": "bf16", "collective": "nccl all_to_all_single"},
+                                     "tokens_per_gpu": Tl, "wire_dtype": "bf16", "collective": "nccl all_to_all_single",
+                                     "pipelined_parts": args.ep_chunks if world > 1 else None},
                           "phase_ms_rank0": phases, "abs_sum_of_output": checksum}), flush=True)
     if world > 1:
         dist.barrier()
@@ -486,7 +487,7 @@ def run_stack_prefill(args):
         normed = torch.empty_like(x0)
         fwd = lambda: sc.stack_prefill(layers, gammas, x0.clone(), 1e-6, normed)
     else:
-        stack = ep.ExpertParallelStack(H, I, E, K, quant, blobs, gammas, rank, world, Tl, 1e-6)
+        stack = ep.ExpertParallelStack(H, I, E, K, quant, blobs, gammas, rank, world, Tl, 1e-6, chunks=args.ep_chunks)
         fwd = lambda: stack.forward(x0)
     for _ in range(max(3, args.warmup)):
         out = fwd()
@@ -517,7 +518,8 @@ def run_stack_prefill(args):
                           "scaling": "strong", "dtype": "f16 operands, f32 accumulate and residual stream",
                           "config": {"workload": f"moe_stack_prefill_{args.quant}_L{L}_T{T}_router", "layers": L,
                                      "tokens_per_gpu": Tl, "experts_per_gpu": E // world,
-                                     "wire_dtype": "f16" if world > 1 else None},
+                                     "wire_dtype": "f16" if world > 1 else None,
+                                     "pipelined_parts": args.ep_chunks if world > 1 else None},
                           "roofline": {"bound": "tensor", "achieved": tf, "peak": peak * world, "unit": "TFLOP/s",
                                        "frac": tf / (peak * world), "flops_per_step": flops},
                           "abs_sum_of_output": checksum}), flush=True)
@@ -537,6 +539,8 @@ def main():
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--quant", default="q4_0", choices=sorted(QUANTS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ep-chunks", type=int, default=1,
+                    help="expert-parallel workloads: parts whose dispatch / expert products / combine overlap (1 = off)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -429,6 +429,13 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
         int dev = 0, sms = 148;
         cudaGetDevice(&dev);
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        // LUMEN_MOE_TC_CTAS caps the persistent grid (one CTA per SM): an expert-parallel rank leaves
+        // a few SMs to the collective kernels that run beside the GEMMs
+        static const int cta_cap = [] {
+            const char* v = getenv("LUMEN_MOE_TC_CTAS");
+            return v ? atoi(v) : 0;
+        }();
+        if (cta_cap > 0 && cta_cap < sms) sms = cta_cap;
         CUDA_TRY(launch_grouped_tc(p, s->x16, sms, st, out16_rows));
     } else {
         CUDA_TRY(launch_build_xf(normed, act_dtype, batch, s->H, layer.dev.kg_h * 4, bf16_mode, s->xf, st));

@@ -62,7 +62,8 @@ class ExpertParallelMoe:
 
     def __init__(self, num_experts: int, top_k: int, route_fn: Callable, expert_fn: Callable, group=None,
                  combine_fn: Optional[Callable] = None,
-                 wire_dtype: torch.dtype = torch.bfloat16, combine_dtype: torch.dtype = torch.float16):
+                 wire_dtype: torch.dtype = torch.bfloat16, combine_dtype: torch.dtype = torch.float16,
+                 route_takes_slot: bool = False):
         self.E, self.K = num_experts, top_k
         self.group = group
         self.world = dist.get_world_size(group)
@@ -77,6 +78,8 @@ class ExpertParallelMoe:
         self.last = {}
         self.profile = False
         self._marks = []
+        self.route_takes_slot = route_takes_slot  # route_fn(x, slot): one set of output buffers per part of forward_pipelined
+        self._side_streams = None
 
     def _mark(self, name):
         if self.profile and torch.cuda.is_available():
@@ -89,46 +92,71 @@ class ExpertParallelMoe:
         torch.cuda.synchronize()
         return [(b[0], a[1].elapsed_time(b[1])) for a, b in zip(self._marks[:-1], self._marks[1:])]
 
-    def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
-        T, H = normed.shape
-        self._marks = []
-        self._mark("start")
-        routed = self.route_fn(normed)
+    def _send_side(self, normed: torch.Tensor, slot=None) -> dict:
+        """Route `normed` and lay out what leaves this rank: rows in destination order, the
+        rank-local expert id of every row, rows per destination rank, and what the combine needs."""
+        routed = self.route_fn(normed) if slot is None else self.route_fn(normed, slot)
         ids, w = routed[0], routed[1]
-        self._mark("route")
-        rows = None
+        side = {"ids": ids, "w": w, "order": None, "inv": None}
         if len(routed) > 2 and "rows" in routed[2]:
             # the library produced the whole send side in one launch
             tables = routed[2]
-            rows, local_ids, send_counts = tables["rows"], tables["local_ids"], tables["send_counts"]
-            order = None
-        elif len(routed) > 2:
+            side.update(rows=tables["rows"], local_ids=tables["local_ids"], sc=tables["send_counts"],
+                        inv=tables["dst_to_col"])
+            return side
+        if len(routed) > 2:
             # the router's own counting sort is the send plan (compact-column order)
             tables = routed[2]
             tok = tables["col_src_tok"].to(torch.int64)
-            order = None
+            side["inv"] = tables["dst_to_col"]
             if self.combine_fn is None:
                 d2c = tables["dst_to_col"].to(torch.int64)
                 order = torch.empty_like(d2c)
                 order[d2c] = torch.arange(d2c.numel(), device=d2c.device)
+                side["order"] = order
             b = tables["expert_bounds"].to(torch.int64)
             edges = b[torch.arange(0, self.E + 1, self.epr, device=b.device)]
-            send_counts = edges[1:] - edges[:-1]
-            local_ids = (tables["col_expert"] % self.epr).to(torch.int32)
+            side["sc"] = edges[1:] - edges[:-1]
+            side["local_ids"] = (tables["col_expert"] % self.epr).to(torch.int32)
         else:
             order, send_counts, local_ids = dispatch_plan(ids, self.epr, self.world)
             tok = torch.div(order, self.K, rounding_mode="floor")
+            side.update(order=order, sc=send_counts, local_ids=local_ids)
+        side["rows"] = normed[tok].to(self.wire_dtype)
+        return side
+
+    def _combine(self, back: torch.Tensor, residual: torch.Tensor, side: dict) -> torch.Tensor:
+        """out[t] = residual[t] + sum_slot w[t,slot] * d[t,slot] in slot order; `back` is in send order."""
+        T, H = residual.shape
+        w, order = side["w"], side["order"]
+        if self.combine_fn is not None:
+            inv = side["inv"]
+            if inv is None:
+                inv = torch.empty(T * self.K, dtype=torch.int32, device=residual.device)
+                inv[order] = torch.arange(T * self.K, dtype=torch.int32, device=residual.device)
+            return self.combine_fn(back, residual, w, inv)
+        dpair = torch.empty((T * self.K, H), dtype=torch.float32, device=residual.device)
+        dpair[order] = back.to(torch.float32)
+        dpair = dpair.view(T, self.K, H)
+        out = residual.clone()
+        for slot in range(self.K):
+            out += w[:, slot, None] * dpair[:, slot]
+        return out
+
+    def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        self._marks = []
+        self._mark("start")
+        side = self._send_side(normed)
+        self._mark("route")
         # (2) counts
-        sc = send_counts.to(torch.int64)
+        sc = side["sc"].to(torch.int64)
         rc = torch.empty_like(sc)
         dist.all_to_all_single(rc, sc, group=self.group)
         send_l, recv_l = sc.tolist(), rc.tolist()  # the one host sync of the call (NCCL sizes are host arguments)
         self._mark("plan+counts")
         # (3) dispatch rows and local expert ids
-        if rows is None:
-            rows = normed[tok].to(self.wire_dtype)
-        recv_rows = all_to_all_v(rows, send_l, recv_l, self.group)
-        recv_ids = all_to_all_v(local_ids, send_l, recv_l, self.group)
+        recv_rows = all_to_all_v(side["rows"], send_l, recv_l, self.group)
+        recv_ids = all_to_all_v(side["local_ids"], send_l, recv_l, self.group)
         self._mark("dispatch")
         # (4) local experts
         d = self.expert_fn(recv_rows, recv_ids)
@@ -137,24 +165,70 @@ class ExpertParallelMoe:
         back = all_to_all_v(d.to(self.combine_dtype), recv_l, send_l, self.group)
         self._mark("combine_a2a")
         # (6) weighted sum in slot order
-        self.last = {"ids": ids, "weights": w, "send_counts": send_l, "recv_counts": recv_l}
-        if self.combine_fn is not None:
-            if len(routed) > 2:
-                inv = routed[2]["dst_to_col"]
-            else:
-                inv = torch.empty(T * self.K, dtype=torch.int32, device=normed.device)
-                inv[order] = torch.arange(T * self.K, dtype=torch.int32, device=normed.device)
-            out = self.combine_fn(back, residual, w, inv)
-            self._mark("combine")
-            return out
-        dpair = torch.empty((T * self.K, H), dtype=torch.float32, device=normed.device)
-        dpair[order] = back.to(torch.float32)
-        dpair = dpair.view(T, self.K, H)
-        out = residual.clone()
-        for slot in range(self.K):
-            out += w[:, slot, None] * dpair[:, slot]
-        self.last = {"ids": ids, "weights": w, "send_counts": send_l, "recv_counts": recv_l}
+        self.last = {"ids": side["ids"], "weights": side["w"], "send_counts": send_l, "recv_counts": recv_l}
+        out = self._combine(back, residual, side)
+        self._mark("combine")
         return out
+
+    def forward_pipelined(self, normed: torch.Tensor, residual: torch.Tensor, chunks: int = 2) -> torch.Tensor:
+        """The same layer with the tokens cut into `chunks` parts whose dispatch, expert products and
+        combine overlap: all parts are routed first and their row counts exchanged in ONE
+        all-to-all (one host sync), then the collectives run on one side stream and the expert
+        products on another, so that part c+1 is on the wire while part c is in the GEMMs and part
+        c's outputs travel back under part c+1's GEMMs. `chunks` must be the same on every rank."""
+        T = normed.shape[0]
+        bounds = [T * c // chunks for c in range(chunks + 1)]
+        parts = [(bounds[c], bounds[c + 1]) for c in range(chunks)]
+        sides = [self._send_side(normed[b0:b1], c if self.route_takes_slot else None) for c, (b0, b1) in enumerate(parts)]
+        sc = torch.stack([s["sc"].to(torch.int64) for s in sides])  # [chunks, G]
+        sc_t = sc.t().contiguous()                                  # per destination rank: its `chunks` counts
+        rc_t = torch.empty_like(sc_t)
+        dist.all_to_all_single(rc_t, sc_t, group=self.group)
+        send_l, recv_l = sc.tolist(), rc_t.t().tolist()             # the one host sync of the call
+        cuda = normed.is_cuda
+        if cuda:
+            main = torch.cuda.current_stream()
+            if self._side_streams is None:
+                self._side_streams = (torch.cuda.Stream(), torch.cuda.Stream())
+            s_comm, s_comp = self._side_streams
+            s_comm.wait_stream(main)
+            s_comp.wait_stream(main)
+            on = lambda st: torch.cuda.stream(st)
+        else:
+            import contextlib
+            s_comm = s_comp = None
+            on = lambda st: contextlib.nullcontext()
+
+        def mark(st):
+            if not cuda:
+                return None
+            ev = torch.cuda.Event()
+            ev.record(st)
+            return ev
+
+        recv, d_out, backs = [], [], []
+        for c in range(chunks):
+            with on(s_comm):
+                rr = all_to_all_v(sides[c]["rows"], send_l[c], recv_l[c], self.group)
+                ri = all_to_all_v(sides[c]["local_ids"], send_l[c], recv_l[c], self.group)
+                recv.append((rr, ri, mark(s_comm)))
+        for c in range(chunks):
+            with on(s_comp):
+                if cuda:
+                    s_comp.wait_event(recv[c][2])
+                d = self.expert_fn(recv[c][0], recv[c][1]).to(self.combine_dtype)
+                d_out.append((d, mark(s_comp)))
+        for c in range(chunks):
+            with on(s_comm):
+                if cuda:
+                    s_comm.wait_event(d_out[c][1])
+                backs.append(all_to_all_v(d_out[c][0], recv_l[c], send_l[c], self.group))
+        if cuda:
+            main.wait_stream(s_comm)
+            main.wait_stream(s_comp)
+        self.last = {"ids": torch.cat([s["ids"] for s in sides]), "weights": torch.cat([s["w"] for s in sides]),
+                     "send_counts": [sum(v) for v in zip(*send_l)], "recv_counts": [sum(v) for v in zip(*recv_l)]}
+        return torch.cat([self._combine(backs[c], residual[b0:b1], sides[c]) for c, (b0, b1) in enumerate(parts)])
 
 
 def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.Tensor, rank: int, world: int,
@@ -196,8 +270,8 @@ def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.
     # rank holds only a few thousand tokens and the launches, not the kernels, set the time.
     graphs = {}
 
-    def route_fn(x):
-        key = (tuple(x.shape), x.dtype)
+    def route_fn(x, slot=0):
+        key = (tuple(x.shape), x.dtype, slot)  # a slot has its own graph and static output buffers
         entry = graphs.get(key)
         if entry is None:
             out = route_eager(x)  # first call: eager (one-time set-up inside the library must not be captured)
@@ -229,7 +303,7 @@ def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.
     def combine_fn(back, residual, w, inv):
         return moe.combine_f16(back.contiguous(), residual, w.contiguous(), inv)
 
-    return route_fn, expert_fn, {"combine_fn": combine_fn, "route": route_sc, "experts": exp_sc,
+    return route_fn, expert_fn, {"combine_fn": combine_fn, "route_takes_slot": True, "route": route_sc, "experts": exp_sc,
                                  "layers": (route_layer, exp_layer), "router_blob": router_blob}
 
 
@@ -241,17 +315,20 @@ class ExpertParallelStack:
     to its operand."""
 
     def __init__(self, H: int, I: int, E: int, K: int, quant: int, layer_blobs, gammas, rank: int, world: int,
-                 max_tokens: int, eps: float, gating_mode: int = 0, group=None):
+                 max_tokens: int, eps: float, gating_mode: int = 0, group=None, chunks: int = 1):
         from . import moe
         self.eps, self.gammas, self._rmsnorm = eps, list(gammas), moe.rmsnorm
+        self.chunks = chunks  # > 1: every layer runs forward_pipelined with that many parts
         self.layers, self._keep, ctx = [], [], None
         for blob in layer_blobs:  # any iterable: a generator lets each full blob be freed after its slice is repacked
             route_fn, expert_fn, keep = cuda_layer_fns(H, I, E, K, quant, blob, rank, world, max_tokens, gating_mode, ctx)
             ctx = (keep["route"], keep["experts"])
             self._keep.append(keep)
-            self.layers.append(ExpertParallelMoe(E, K, route_fn, expert_fn, group=group, combine_fn=keep["combine_fn"]))
+            self.layers.append(ExpertParallelMoe(E, K, route_fn, expert_fn, group=group, combine_fn=keep["combine_fn"],
+                                                 route_takes_slot=True))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         for layer, gamma in zip(self.layers, self.gammas):
-            x = layer.forward(self._rmsnorm(x, gamma, self.eps), x)
+            normed = self._rmsnorm(x, gamma, self.eps)
+            x = layer.forward(normed, x) if self.chunks < 2 else layer.forward_pipelined(normed, x, self.chunks)
         return x

@@ -22,7 +22,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, tokens_per_rank, result_q):
+def _worker(rank, world, port, tokens_per_rank, result_q, chunks=1):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -57,7 +57,10 @@ def _worker(rank, world, port, tokens_per_rank, result_q):
             return torch.from_numpy(out)
 
         layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, wire_dtype=torch.float32, combine_dtype=torch.float32)
-        out = layer.forward(torch.from_numpy(x), torch.from_numpy(x)).numpy()
+        if chunks > 1:
+            out = layer.forward_pipelined(torch.from_numpy(x), torch.from_numpy(x), chunks).numpy()
+        else:
+            out = layer.forward(torch.from_numpy(x), torch.from_numpy(x)).numpy()
         if T > 0:
             ref, ids, _ = oracle.moe_layer(blob, 0, meta.expert_gate_offs, meta.expert_up_offs, meta.expert_down_offs,
                                            QUANT, H, I, E, K, x, x)
@@ -72,13 +75,15 @@ def _worker(rank, world, port, tokens_per_rank, result_q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("tokens_per_rank", [(5, 9), (4, 0)])
-def test_expert_parallel_two_ranks_gloo(tokens_per_rank):
+@pytest.mark.parametrize("tokens_per_rank,chunks", [((5, 9), 1), ((4, 0), 1), ((5, 9), 2), ((7, 1), 3)])
+def test_expert_parallel_two_ranks_gloo(tokens_per_rank, chunks):
+    """chunks > 1: the pipelined form (tokens cut into parts, one exchange of all parts' counts);
+    a rank with fewer tokens than parts has empty parts."""
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, tokens_per_rank, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, tokens_per_rank, q, chunks)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=120) for _ in range(world)]

@@ -29,12 +29,15 @@ def _worker(rank, world, port, q):
         Tl = T // world
         sl = slice(rank * Tl, (rank + 1) * Tl)
         route_fn, expert_fn, keep = ep.cuda_layer_fns(H, I, E, K, 1, blob, rank, world, Tl)
-        layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, combine_fn=keep["combine_fn"])
+        layer = ep.ExpertParallelMoe(E, K, route_fn, expert_fn, combine_fn=keep["combine_fn"], route_takes_slot=True)
         # three calls: the first is eager, the second captures the routing side into a CUDA graph,
         # the third replays it; all must give the same result
         outs = [layer.forward(x_all[sl].contiguous(), res_all[sl].contiguous()).clone() for _ in range(3)]
         assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
         out = outs[2]
+        # the pipelined form (two parts on side streams; eager, capture, replay): same bits
+        for _ in range(3):
+            assert torch.equal(layer.forward_pipelined(x_all[sl].contiguous(), res_all[sl].contiguous(), 2), out)
         sc = moe.allocate_moe_scratch(H, I, E, K, T, device=rank)  # contexts are per device
         full = sc.prepare_layer(blob, lay.meta())
         ref = sc.prefill(full, x_all, res_all)[sl]
@@ -49,6 +52,9 @@ def _worker(rank, world, port, q):
         stack = ep.ExpertParallelStack(H, I, E, K, 1, blobs, gammas, rank, world, Tl, 1e-6)
         ys = [stack.forward(x0[sl].contiguous()).clone() for _ in range(3)]
         assert torch.equal(ys[0], ys[1]) and torch.equal(ys[0], ys[2])
+        stack.chunks = 2
+        for _ in range(3):
+            assert torch.equal(stack.forward(x0[sl].contiguous()), ys[0])
         full_layers = [sc.prepare_layer(b, lay.meta()) for b in blobs]
         want = sc.stack_prefill(full_layers, gammas, x0.clone(), 1e-6)[sl]
         rel_stack = float((ys[2] - want).norm() / (want - x0[sl]).norm())

@@ -157,7 +157,9 @@ void lumen_moe_layer_destroy(lumen_moe_layer* layer) {
 
 size_t lumen_moe_layer_bytes(const lumen_moe_layer* layer) {
     if (!layer) return 0;
-    return layer->layer.repacked.q_bytes + layer->layer.repacked.s_bytes + 5 * sizeof(uint64_t) * layer->layer.dev.E;
+    const size_t router_copy = layer->layer.repacked.router_copy ? (size_t)layer->layer.dev.E * layer->layer.dev.H * sizeof(float) : 0;
+    return layer->layer.repacked.q_bytes + layer->layer.repacked.s_bytes + router_copy +
+           5 * sizeof(uint64_t) * layer->layer.dev.E;
 }
 
 lumen_moe_status_t lumen_moe_decode(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const float* d_normed,

@@ -52,3 +52,20 @@ def test_build_moe_meta_returns_none_for_dense_layers():
     from lumen_b200.moe import build_moe_meta
     assert build_moe_meta(None, [{"gate": (0, 1), "up": (0, 1), "down": (0, 1)}]) is None
     assert build_moe_meta(0, []) is None
+
+
+def test_integration_binding_matches_the_header():
+    """Every function of the Rust extern block shown in INTEGRATION.md is declared in the
+    header with the same number of parameters."""
+    header = (ROOT / "include" / "lumen_moe.h").read_text()
+    doc = (ROOT / "INTEGRATION.md").read_text()
+    block = doc[doc.index('extern "C" {'):]
+    block = block[:block.index("```")]
+    rust = re.findall(r"pub fn (lumen_\w+)\s*\(([^)]*)\)", block, flags=re.S)
+    assert len(rust) >= 10
+    for name, params in rust:
+        m = re.search(r"\b" + name + r"\s*\(([^;]*?)\)\s*;", header, flags=re.S)
+        assert m, name
+        c_params = [p for p in m.group(1).split(",") if p.strip() and p.strip() != "void"]
+        r_params = [p for p in params.split(",") if p.strip()]
+        assert len(c_params) == len(r_params), (name, len(c_params), len(r_params))

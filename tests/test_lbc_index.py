@@ -203,3 +203,30 @@ def test_slice_outside_the_layer_blob_is_rejected(cuda_lib):
     L = W.Layer(router_weight=(0, 32, W.F32), experts=[((32, 512, 77), (544, 512, W.Q8_0), (1056, 512, W.Q8_0))])
     data = W.write_lbc(m, [L], [bytes(6848)])
     assert read_layer_raw(data, 0)[0] == _lib.UNSUPPORTED
+
+
+def test_truncated_and_corrupted_files_never_read_out_of_bounds(cuda_lib):
+    """Every prefix of a file and a sweep of single-byte corruptions of its index: the reader
+    returns a status (no crash), OK only when the data really holds the whole index."""
+    m, data, Ls, blobs = qwen_like_file(E=4, H=32, I=32, layers=2, with_bias=True)
+    idx = lbc.LbcIndex(data)
+    index_end = None
+    # the index ends where the next section starts: find it as the shortest prefix that parses layer 1
+    lo = int(idx.header.header_bytes)
+    for n in list(range(0, lo + 1)) + list(range(lo, lo + 2200, 7)):
+        code, out, _ = read_layer_raw(data[:n], 1)
+        if code == _lib.OK and index_end is None:
+            index_end = n
+        if n < lo:
+            assert code != _lib.OK
+    assert index_end is not None and index_end > lo
+    rng = np.random.default_rng(0)
+    for _ in range(300):
+        bad = bytearray(data[: index_end + 64])
+        pos = int(rng.integers(lo, index_end))
+        bad[pos] = int(rng.integers(0, 256))
+        code, out, _ = read_layer_raw(bytes(bad), 1)
+        assert code in (_lib.OK, _lib.INVALID_ARG, _lib.UNSUPPORTED)
+        # huge expert counts must be refused, not allocated
+        if code == _lib.OK:
+            assert out.num_experts <= 256

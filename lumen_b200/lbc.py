@@ -92,6 +92,20 @@ class LbcIndex:
         _lib.check(_lib.lib().lumen_lbc_read_header(buf, len(data), ctypes.byref(h)))
         return h
 
+    def read_layer_blob(self, source, layer: "LbcMoeLayer") -> np.ndarray:
+        """The layer's blob bytes (what the backend uploads unchanged, cuda/gpu_buffers.rs:1404-1409)
+        from the file (path) or from a buffer holding the whole file."""
+        lo, n = layer.layer_offset_bytes, layer.layer_length_bytes
+        if isinstance(source, (str, Path)):
+            with open(source, "rb") as f:
+                f.seek(lo)
+                data = f.read(n)
+        else:
+            data = bytes(memoryview(source)[lo: lo + n])
+        if len(data) != n:
+            raise _lib.LumenMoeError(_lib.INVALID_ARG, f"layer {layer.layer}: the file ends inside the layer blob")
+        return np.frombuffer(data, dtype=np.uint8)
+
     @property
     def num_layers(self) -> int:
         return int(self.header.num_layers)

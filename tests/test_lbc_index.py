@@ -156,6 +156,10 @@ def test_dense_moe_and_optional_sections(cuda_lib, quant, ours):
         p = lbc.LbcIndex(f.name)
         assert p._n == idx.header.payload_offset
         assert p.moe_layer(2).meta.expert_down_offs.tolist() == r2.meta.expert_down_offs.tolist()
+        # the layer blob, from the path and from the bytes
+        assert p.read_layer_blob(f.name, r2).tobytes() == blobs[2] == idx.read_layer_blob(data, r2).tobytes()
+        with pytest.raises(_lib.LumenMoeError):
+            idx.read_layer_blob(data[: r2.layer_offset_bytes + 10], r2)
 
 
 def test_error_cases_of_the_reference_reader(cuda_lib):

@@ -11,6 +11,11 @@ run as independent replicas ("weak" scaling, no collective in the data path).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--quant q4_0|q8_0|bf16]
     python bench.py --impl reference ...   # the CPU reference path on the host cores
+
+Secondary workloads (their own JSON line, not the headline):
+    --workload prefill --tokens T [--routing zipf|uniform|router]     one prefill call, tensor roofline
+    --workload ep_prefill --tokens T [--ep-chunks C]   (torchrun)     expert-parallel prefill, strong scaling
+    --workload stack_prefill --tokens T --layers L     (torchrun)     the stack of L layers as one prefill
 """
 from __future__ import annotations
 

@@ -69,3 +69,28 @@ def test_integration_binding_matches_the_header():
         c_params = [p for p in m.group(1).split(",") if p.strip() and p.strip() != "void"]
         r_params = [p for p in params.split(",") if p.strip()]
         assert len(c_params) == len(r_params), (name, len(c_params), len(r_params))
+
+
+def test_header_is_plain_c_and_a_c_program_reads_an_lbc_index(cuda_lib, tmp_path):
+    """include/lumen_moe.h compiles as C99 (-pedantic) and a C consumer linked against the
+    library gets the offsets of an LBC layer (the path a non-Python host takes)."""
+    import subprocess
+    from lumen_b200 import _lib
+    from oracle import lbc_writer as W
+    exe = tmp_path / "lbc_c_consumer"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", str(ROOT / "include"),
+                    str(ROOT / "tests" / "native" / "lbc_c_consumer.c"), "-o", str(exe),
+                    str(_lib.LIB_PATH), f"-Wl,-rpath,{_lib.LIB_PATH.parent}"], check=True)
+    m = W.Model(num_layers=1, hidden_dim=64, intermediate_dim=32, num_experts=3, num_active_experts=2)
+    gb, db = 32 * 2 * 18, 64 * 1 * 18
+    experts = [((1000 + e * (2 * gb + db), gb, W.Q4_0), (1000 + e * (2 * gb + db) + gb, gb, W.Q4_0),
+                (1000 + e * (2 * gb + db) + 2 * gb, db, W.Q4_0)) for e in range(3)]
+    L = W.Layer(router_weight=(232, 3 * 64 * 4, W.F32), experts=experts)
+    path = tmp_path / "m.lbc"
+    path.write_bytes(W.write_lbc(m, [L], [bytes(1000 + 3 * (2 * gb + db))]))
+    r = subprocess.run([str(exe), str(path), "0"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    lines = r.stdout.splitlines()
+    assert lines[0] == "version 4 layers 1 hidden 64 experts 3 top_k 2"
+    assert lines[1] == f"is_moe 1 num_experts 3 quant {_lib.Q4_0} router_off 232"
+    assert lines[2] == f"expert0 1000 {1000 + gb} {1000 + 2 * gb} last_down {1000 + 2 * (2 * gb + db) + 2 * gb}"

@@ -70,8 +70,21 @@ typedef struct {
     int32_t max_tokens;   /* initial prefill capacity; grows on demand */
     int32_t gating_mode;  /* lumen_moe_gating_t */
     int32_t device;       /* CUDA ordinal */
-    int32_t reserved;
+    int32_t flags;        /* 0, or LUMEN_MOE_FLAG_* or'ed together */
 } lumen_moe_config;
+
+/* Kernel selection is part of the configuration, never of the environment (the reference
+ * selects its kernel generations through ~30 environment variables, cuda/moe.rs:1304-1561;
+ * this library reads none).
+ * DECODE_SPLIT: 1..4-token decode on the three-kernel chain instead of the persistent
+ *   cooperative kernel (for a process that cannot give the kernel every SM of the device).
+ * PREFILL_MMA: grouped products on mma.sync instead of tcgen05 (values outside f16 range).
+ * SHORT_WAITS: device-side bounded waits give up after 2 ms instead of 1-2 s (tests).
+ * TC_CTAS(n): cap of the persistent tcgen05 grid, n CTAs (one per SM), 0 = every SM. */
+#define LUMEN_MOE_FLAG_DECODE_SPLIT 0x1
+#define LUMEN_MOE_FLAG_PREFILL_MMA 0x2
+#define LUMEN_MOE_FLAG_SHORT_WAITS 0x4
+#define LUMEN_MOE_FLAG_TC_CTAS(n) (((n) & 0xff) << 8)
 
 typedef struct lumen_moe_ctx lumen_moe_ctx;     /* ~ CudaMoeScratch, cuda/moe.rs:101-170 */
 typedef struct lumen_moe_layer lumen_moe_layer; /* ~ CudaMoeMeta + CudaMoeBatchedOffsets + CudaMoeRepacked */
@@ -217,10 +230,40 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_set_logits_override(lumen_moe_ctx* ct
 /* Readback of the routing tables of the most recent call (debug / parity; the
  * counterpart of the MOE_EXPERT_DUMP lines, cuda/moe.rs:1484-1492). Host output
  * arrays, any may be NULL: ids [T,K], weights [T,K], dst_to_col [T*K],
- * col_src_tok [T*K], expert_bounds [E+1] (cuda/moe.rs:2115-2147). Synchronises `stream`. */
+ * col_src_tok [T*K], expert_bounds [E+1] (cuda/moe.rs:2115-2147). Synchronises `stream`.
+ * If the context's error word is set it returns that code and clears it (as
+ * lumen_moe_clear_status does). */
 LUMEN_MOE_API lumen_moe_status_t lumen_moe_get_routing(lumen_moe_ctx* ctx, int32_t tokens, uint32_t* ids,
                                          float* weights, int32_t* dst_to_col, int32_t* col_src_tok,
                                          int32_t* expert_bounds, void* stream);
+
+/* The ids of the most recent routing call in the layout of the reference's batched id
+ * buffer: u32 [T, E] with row stride E, the first K entries of a row valid and the rest 0
+ * (cuda/shaders/topk_moe_fused.cu:189-191, read back at cuda/moe.rs:2116-2121), for a
+ * byte-level diff against a reference dump. Host output. Synchronises `stream`. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_get_routing_ids_stride_e(lumen_moe_ctx* ctx, int32_t tokens,
+                                                                    uint32_t* ids_stride_e, void* stream);
+
+/* Error state of the context (the counterpart of the Result<(), RuntimeError> every launch of
+ * the reference returns, error.rs:6-31, cuda/moe.rs:1497-1502). Kernels cannot return a code, so a
+ * kernel that gives up (a bounded wait that ran out: LUMEN_MOE_TIMEOUT; an expert id >= E in
+ * caller-supplied routing: LUMEN_MOE_INVALID_ARG) records the code in a word of pinned host
+ * memory owned by the context. lumen_moe_poll_status reads that word: no device work, no
+ * synchronisation; it reflects every kernel that has finished. Once the word is set, every
+ * entry point that would launch on the context fails with that code instead of launching
+ * (outputs of the failed call and of calls enqueued behind it are undefined).
+ * lumen_moe_clear_status synchronises `stream`, resets the word and the device-side barrier
+ * state, and makes the context usable again. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_poll_status(const lumen_moe_ctx* ctx);
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_clear_status(lumen_moe_ctx* ctx, void* stream);
+
+/* Test hook for the give-up paths, without faulting or hanging anything: the NEXT kernel of
+ * the given kind launched on this context waits for something that cannot happen (which = 0:
+ * the grid barrier of the persistent decode kernel expects one arrival more than there are
+ * CTAs; which = 1: a stage barrier of the tcgen05 grouped GEMM expects one byte more than the
+ * copies deliver), so its bounded wait runs out, the kernel records LUMEN_MOE_TIMEOUT, releases
+ * what it holds and returns. Use with LUMEN_MOE_FLAG_SHORT_WAITS. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_debug_expire_next_wait(lumen_moe_ctx* ctx, int32_t which);
 
 /* Device-to-device copy of the sort tables of the most recent routing call (no
  * synchronisation): dst_to_col [T*K], col_src_tok [T*K], col_expert [T*K],

@@ -12,11 +12,17 @@ OK, INVALID_ARG, UNSUPPORTED, CUDA_ERROR, TIMEOUT, NCCL_ERROR = range(6)
 Q8_0, Q4_0, BF16 = 0, 1, 2
 SOFTMAX_RENORM, SIGMOID_RENORM, SIGMOID_GATE, UNIT_WEIGHT = 0, 1, 2, 3
 ACT_F32, ACT_BF16, ACT_F16 = 0, 1, 2
+# lumen_moe_config.flags
+FLAG_DECODE_SPLIT, FLAG_PREFILL_MMA, FLAG_SHORT_WAITS = 0x1, 0x2, 0x4
+
+
+def flag_tc_ctas(n: int) -> int:
+    return (n & 0xFF) << 8
 
 
 class MoeConfig(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in
-                ("hidden_dim", "inter_dim", "num_experts", "top_k", "max_tokens", "gating_mode", "device", "reserved")]
+                ("hidden_dim", "inter_dim", "num_experts", "top_k", "max_tokens", "gating_mode", "device", "flags")]
 
 
 class LbcSlice(ctypes.Structure):
@@ -75,6 +81,10 @@ SIGNATURES = {
     "lumen_moe_set_logits_override": [vp, vp],
     "lumen_moe_get_routing": [vp, i32, vp, vp, vp, vp, vp, vp],
     "lumen_moe_get_routing_device": [vp, i32, vp, vp, vp, vp, vp],
+    "lumen_moe_get_routing_ids_stride_e": [vp, i32, vp, vp],
+    "lumen_moe_poll_status": [vp],
+    "lumen_moe_clear_status": [vp, vp],
+    "lumen_moe_debug_expire_next_wait": [vp, i32],
     "lumen_moe_ep_prepare": [vp, vp, i32, i32, i32, vp, vp, vp, vp],
     "lumen_lbc_read_header": [vp, sz, ctypes.POINTER(LbcHeader)],
     "lumen_lbc_read_moe_layer": [vp, sz, ctypes.c_uint32, ctypes.POINTER(LbcMoeLayer), vp, vp, vp, ctypes.c_uint32],

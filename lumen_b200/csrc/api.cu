@@ -51,8 +51,13 @@ lumen_moe_status_t lumen_moe_create(const lumen_moe_config* cfg, lumen_moe_ctx**
         return fail(LUMEN_MOE_UNSUPPORTED, "this build contains sm_100a code only (Blackwell B200 required)");
     lumen_moe_ctx* ctx = new (std::nothrow) lumen_moe_ctx();
     if (!ctx) return fail(LUMEN_MOE_CUDA_ERROR, "out of host memory");
+    if (cfg->flags & ~(0x7 | 0xff00)) {
+        delete ctx;
+        return fail(LUMEN_MOE_INVALID_ARG, "unknown bits in lumen_moe_config.flags");
+    }
     lumen::Status s = lumen::allocate_moe_scratch(cfg->device, cfg->hidden_dim, cfg->inter_dim, cfg->num_experts,
-                                                  cfg->top_k, cfg->gating_mode, cfg->max_tokens, &ctx->scratch);
+                                                  cfg->top_k, cfg->gating_mode, cfg->max_tokens, cfg->flags,
+                                                  &ctx->scratch);
     if (!s.ok()) {
         delete ctx;
         return done(s);
@@ -276,15 +281,48 @@ lumen_moe_status_t lumen_moe_get_routing(lumen_moe_ctx* ctx, int32_t tokens, uin
     if (e == cudaSuccess && col_src_tok) e = cudaMemcpy(col_src_tok, s.R.col_src_tok, C * 4, cudaMemcpyDeviceToHost);
     if (e == cudaSuccess && expert_bounds)
         e = cudaMemcpy(expert_bounds, s.R.expert_bounds, (size_t)(s.E + 1) * 4, cudaMemcpyDeviceToHost);
-    int32_t dev_status = 0;
-    if (e == cudaSuccess) e = cudaMemcpy(&dev_status, s.status, 4, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
-    if (dev_status != 0) {
-        cudaMemset(s.status, 0, 4);
-        cudaMemset(s.bar, 0, 1024 * 4);
-        cudaMemset(s.R.logits, 0, (size_t)s.cap_tokens * s.E * 4);  // tagged logit slots of the fused decode kernel
-        return fail(dev_status, "a device-side bounded wait expired (grouped GEMM pipeline or decode grid barrier)");
+    // the stream is idle: the host copy of the status word is final for everything enqueued so far
+    lumen::Status st_word = lumen::check_status_word(&s);
+    if (!st_word.ok()) {
+        lumen::Status c = lumen::clear_status_word(&ctx->scratch, st);
+        if (!c.ok()) return done(c);
+        return done(st_word);
     }
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_get_routing_ids_stride_e(lumen_moe_ctx* ctx, int32_t tokens, uint32_t* ids_stride_e,
+                                                      void* stream) {
+    if (!ctx || !ids_stride_e) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    const lumen::CudaMoeScratch& s = ctx->scratch;
+    if (tokens < 1 || tokens > s.cap_tokens) return fail(LUMEN_MOE_INVALID_ARG, "tokens exceeds the last call's capacity");
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    // ids live with row stride K on the device: widen on the way out (a strided 2-D copy)
+    if (e == cudaSuccess) {
+        for (size_t i = 0; i < (size_t)tokens * s.E; ++i) ids_stride_e[i] = 0u;
+        e = cudaMemcpy2D(ids_stride_e, (size_t)s.E * 4, s.R.ids, (size_t)s.K * 4, (size_t)s.K * 4, (size_t)tokens,
+                         cudaMemcpyDeviceToHost);
+    }
+    if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_poll_status(const lumen_moe_ctx* ctx) {
+    if (!ctx) return fail(LUMEN_MOE_INVALID_ARG, "null context");
+    return done(lumen::check_status_word(&ctx->scratch));
+}
+
+lumen_moe_status_t lumen_moe_clear_status(lumen_moe_ctx* ctx, void* stream) {
+    if (!ctx) return fail(LUMEN_MOE_INVALID_ARG, "null context");
+    return done(lumen::clear_status_word(&ctx->scratch, static_cast<cudaStream_t>(stream)));
+}
+
+lumen_moe_status_t lumen_moe_debug_expire_next_wait(lumen_moe_ctx* ctx, int32_t which) {
+    if (!ctx || which < 0 || which > 1) return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    if (ctx->scratch.wait_limit_us == 0)
+        return fail(LUMEN_MOE_INVALID_ARG, "create the context with LUMEN_MOE_FLAG_SHORT_WAITS for this test hook");
+    ctx->scratch.expire_next[which] = 1;
     return LUMEN_MOE_OK;
 }
 

@@ -716,11 +716,10 @@ static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, cudaStream_t st,
 template <int Q>
 static cudaError_t launch_down_combine(const DecodeArgs& a, dim3 grid, cudaStream_t st) {
     const size_t smem = (size_t)DC_WARPS * DcRing<Q>::value * (QTraits<Q>::NQ * 32 + 8) * 16;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(down_combine_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemOptIn optin;
+    {
+        cudaError_t e = ensure_dyn_smem(down_combine_kernel<Q>, smem, optin);
         if (e != cudaSuccess) return e;
-        attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;

@@ -98,16 +98,23 @@ __device__ __forceinline__ void grid_arrive(unsigned* bar) {
 
 // Returns false when the wait expired (one second) or another CTA already raised the
 // status word.
-__device__ __forceinline__ bool grid_wait(unsigned* bar, int* status, int G, unsigned epoch, int* fail_s) {
+struct WaitCtl {
+    int* status;
+    int* status_host;
+    unsigned long long limit_ns;
+};
+
+__device__ __forceinline__ bool grid_wait(unsigned* bar, const WaitCtl& wc, int G, unsigned epoch, int extra,
+                                          int* fail_s) {
     if (threadIdx.x == 0) {
-        const unsigned target = epoch * (unsigned)G;
+        const unsigned target = epoch * (unsigned)G + (unsigned)extra;
         unsigned long long t0 = 0;
         unsigned spins = 0;
         bool ok = true;
         while ((int)(ld_relaxed_u32(bar) - target) < 0) {
             if ((++spins & 63u) == 0) {
                 if (t0 == 0) t0 = global_ns();
-                if (global_ns() - t0 > 1000000000ull || *reinterpret_cast<volatile int*>(status) != 0) {
+                if (global_ns() - t0 > wc.limit_ns || *reinterpret_cast<volatile int*>(wc.status) != 0) {
                     ok = false;
                     break;
                 }
@@ -115,7 +122,7 @@ __device__ __forceinline__ bool grid_wait(unsigned* bar, int* status, int G, uns
         }
         __threadfence();
         if (!ok) {
-            atomicCAS(status, 0, 4);  // LUMEN_MOE_TIMEOUT
+            raise_status(wc.status, wc.status_host, 4);  // LUMEN_MOE_TIMEOUT
             *fail_s = 1;
         }
     }
@@ -147,15 +154,16 @@ __device__ __forceinline__ bool mbar_try(void* bar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait (one second); false when it expired or the status word is already raised.
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* status) {
+// Bounded wait (one second unless the launch says otherwise); false when it expired or the
+// status word is already raised.
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, const WaitCtl& wc) {
     if (mbar_try(bar, parity)) return true;
     const unsigned long long t0 = global_ns();
     for (unsigned i = 0;; ++i) {
         if (mbar_try(bar, parity)) return true;
         if ((i & 63u) == 63u) {
-            if (global_ns() - t0 > 1000000000ull || *reinterpret_cast<volatile int*>(status) != 0) {
-                atomicCAS(status, 0, 4);  // LUMEN_MOE_TIMEOUT
+            if (global_ns() - t0 > wc.limit_ns || *reinterpret_cast<volatile int*>(wc.status) != 0) {
+                raise_status(wc.status, wc.status_host, 4);  // LUMEN_MOE_TIMEOUT
                 return false;
             }
         }
@@ -235,6 +243,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     const int per_col = 2 * nblk_pad * 4, per_col_i = 2 * nblk_i_pad * 4;
     const bool want_logits = (a.logits_override == nullptr);
     constexpr int TU4 = TileU4<Q>::value;
+    const WaitCtl wc{a.status, a.status_host, a.wait_limit_us ? (unsigned long long)a.wait_limit_us * 1000ull : 1000000000ull};
 
     // dynamic shared memory: activation fragments | SwiGLU fragments | down partial sums | staged down tiles
     uint4* xs = dyn;                                  // [T][per_col]
@@ -400,7 +409,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
                 while (r.y != epoch + 1u) {
                     if ((++spins & 63u) == 0) {
                         if (t0 == 0) t0 = global_ns();
-                        if (global_ns() - t0 > 1000000000ull || *reinterpret_cast<volatile int*>(a.status) != 0) {
+                        if (global_ns() - t0 > wc.limit_ns || *reinterpret_cast<volatile int*>(a.status) != 0) {
                             ok = false;
                             break;
                         }
@@ -414,7 +423,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
             ts.lg[t][e] = v;
         }
         if (!ok) {
-            atomicCAS(a.status, 0, 4);  // LUMEN_MOE_TIMEOUT
+            raise_status(a.status, a.status_host, 4);  // LUMEN_MOE_TIMEOUT
             fail_s = 1;
         }
         __syncthreads();
@@ -569,8 +578,8 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
             const int n_items_p = rs.pr_U * rt_i;
             const int n_my_p = (it0 < n_items_p) ? div_g.div(n_items_p - it0 + G - 1) : 0;
             bool ok = true;
-            for (int j = 0; j < min(n_my_p, gs_slots) && ok; ++j) ok = mbar_wait(&mbar[j], 0, a.status);
-            ok = ok && mbar_wait(&mbar[7], 0, a.status);
+            for (int j = 0; j < min(n_my_p, gs_slots) && ok; ++j) ok = mbar_wait(&mbar[j], 0, wc);
+            ok = ok && mbar_wait(&mbar[7], 0, wc);
             if (__syncthreads_or(ok ? 0 : 1)) return;
             if (tid == 0) {
                 for (int i = 0; i < 8; ++i) {
@@ -667,7 +676,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
 #pragma unroll 1
     for (int j = 0; j < n_my; ++j) {
         if (gs_slots > 0) {
-            if (!mbar_wait(&mbar[sl], ring_ph, a.status)) return;  // all threads give up together
+            if (!mbar_wait(&mbar[sl], ring_ph, wc)) return;  // all threads give up together
             if (a.trace != nullptr && tid == 0 && j == n_my - 1) a.trace[(size_t)blockIdx.x * 12 + 11] = global_ns();
             if (warp < kg_h) {
                 const uint4* gq_ = gs_slot(sl);
@@ -699,8 +708,8 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     stamp(5);
     __syncthreads();
     grid_arrive(a.bar);
-    if (!grid_wait(a.bar, a.status, G, ++epoch, &fail_s)) {
-        mbar_wait(&mbar[7], 0, a.status);  // bounded: do not leave with the down copies in flight
+    if (!grid_wait(a.bar, wc, G, ++epoch, a.debug_extra_arrivals, &fail_s)) {
+        mbar_wait(&mbar[7], 0, wc);  // bounded: do not leave with the down copies in flight
         return;
     }
     if (tid == 0) a.bar[1 + cta] = epoch;
@@ -710,7 +719,7 @@ decode_fused_kernel(const __grid_constant__ DecodeArgs a, const int pf_experts, 
     if (!has_down) return;  // (no down tiles were requested for this CTA)
     for (int i = tid; i < C * per_col_i; i += FT) cp_async16(&ss[i], a.sf + i);
     cp_async_wait_all();
-    if (!mbar_wait(&mbar[7], 0, a.status)) return;
+    if (!mbar_wait(&mbar[7], 0, wc)) return;
     __syncthreads();
     stamp(7);
     {

@@ -307,22 +307,15 @@ static cudaError_t launch_small_t(const DecodeArgs& a, int phase, cudaStream_t s
     const int nu = C < a.L.E ? C : a.L.E;
     if (phase == 1) {
         const size_t smem = (size_t)min(a.T, 4) * 2 * a.L.kg_h * 4 * 4 * 16;
-        static size_t attr_smem = 0;
-        if (smem > 48 * 1024 && smem > attr_smem) {
-            cudaError_t e = cudaFuncSetAttribute(gate_up_small_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 (int)smem);
-            if (e != cudaSuccess) return e;
-            attr_smem = smem;
-        }
+        static SmemOptIn optin_gu;
+        cudaError_t e = ensure_dyn_smem(gate_up_small_kernel<Q>, smem, optin_gu);
+        if (e != cudaSuccess) return e;
         return launch_pdl_smem(gate_up_small_kernel<Q>, dim3(a.L.rt_i, nu), dim3(SmallCfg<Q>::GU_WARPS * 32), smem, st, a);
     }
     const size_t smem = (size_t)C * (2 * a.L.kg_i * 4 * 4 * 16 + 64);
-    static size_t attr_smem_dn = 0;
-    if (smem > 48 * 1024 && smem > attr_smem_dn) {
-        cudaError_t e = cudaFuncSetAttribute(down_small_kernel<Q>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        attr_smem_dn = smem;
-    }
+    static SmemOptIn optin_dn;
+    cudaError_t e = ensure_dyn_smem(down_small_kernel<Q>, smem, optin_dn);
+    if (e != cudaSuccess) return e;
     return launch_pdl_smem(down_small_kernel<Q>, dim3(a.L.rt_h), dim3(DS_WARPS * 32), smem, st, a);
 }
 

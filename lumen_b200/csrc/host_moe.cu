@@ -161,6 +161,7 @@ static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
     CUDA_TRY(cudaMalloc(&p, bytes));
     CUDA_TRY(cudaMemset(p, 0, bytes));  // fragment padding blocks must read as zero
     if (s->arena_tok) cudaFree(s->arena_tok);
+    s->has_last_decode = false;  // its arguments pointed into the old arena
     s->arena_tok = p;
     s->arena_tok_bytes = bytes;
     s->cap_tokens = cap;
@@ -184,7 +185,7 @@ static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
 }
 
 // cuda/moe.rs:968-1013
-Status allocate_moe_scratch(int device, int H, int I, int E, int K, int gating, int max_tokens,
+Status allocate_moe_scratch(int device, int H, int I, int E, int K, int gating, int max_tokens, int flags,
                             CudaMoeScratch* out) {
     if (H <= 0 || I <= 0 || H % 32 || I % 32) return Status::Err(1, "hidden_dim and inter_dim must be positive multiples of 32");
     if (E <= 0 || E > MAX_EXPERTS) return Status::Err(1, "num_experts must be in 1..256");
@@ -213,14 +214,21 @@ Status allocate_moe_scratch(int device, int H, int I, int E, int K, int gating, 
     s.status = reinterpret_cast<int32_t*>(b + 768);
     s.R.work = reinterpret_cast<int4*>(b + 1024);
     s.bar = reinterpret_cast<unsigned int*>(b + 1024 + (size_t)MAX_EXPERTS * 2 * sizeof(int4));  // 1024 per-CTA flags
-    const char* dimpl = std::getenv("LUMEN_MOE_DECODE_IMPL");
-    s.decode_impl = (dimpl && std::strcmp(dimpl, "split") == 0) ? 1 : 0;
-    const char* impl = std::getenv("LUMEN_MOE_PREFILL_IMPL");
-    s.prefill_impl = (impl && std::strcmp(impl, "mma") == 0) ? 1 : 0;
+    s.flags = flags;
+    s.decode_impl = (flags & 0x1) ? 1 : 0;   // LUMEN_MOE_FLAG_DECODE_SPLIT
+    s.prefill_impl = (flags & 0x2) ? 1 : 0;  // LUMEN_MOE_FLAG_PREFILL_MMA
+    s.wait_limit_us = (flags & 0x4) ? 2000u : 0u;  // LUMEN_MOE_FLAG_SHORT_WAITS
+    s.tc_ctas = (flags >> 8) & 0xff;
+    CUDA_TRY(cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, device));
+    // the status word's host copy: kernels write it at most once per failure, the host reads it for free
+    CUDA_TRY(cudaHostAlloc(&s.h_status, sizeof(int32_t), cudaHostAllocMapped));
+    *s.h_status = 0;
+    CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&s.status_host), s.h_status, 0));
     const int cap = max_tokens > DECODE_MAX_TOKENS ? max_tokens : DECODE_MAX_TOKENS;
     Status st = alloc_tok_arena(&s, cap);
     if (!st.ok()) {
         cudaFree(s.arena);
+        cudaFreeHost(s.h_status);
         return st;
     }
     *out = s;
@@ -234,7 +242,29 @@ Status ensure_prefill_grouped(CudaMoeScratch* s, int batch) {
     return alloc_tok_arena(s, batch);
 }
 
+Status check_status_word(const CudaMoeScratch* s) {
+    const int code = s->h_status ? *reinterpret_cast<volatile int32_t*>(s->h_status) : 0;
+    if (code == 0) return Status::Ok();
+    if (code == 4)
+        return Status::Err(4, "a device-side bounded wait expired in an earlier call on this context (grouped GEMM "
+                              "pipeline or decode grid barrier); outputs since then are undefined; "
+                              "lumen_moe_clear_status makes the context usable again");
+    return Status::Err(code, "an earlier call on this context was given an expert id >= num_experts; "
+                             "lumen_moe_clear_status makes the context usable again");
+}
+
+Status clear_status_word(CudaMoeScratch* s, cudaStream_t st) {
+    CUDA_TRY(cudaStreamSynchronize(st));
+    CUDA_TRY(cudaMemset(s->status, 0, 4));
+    CUDA_TRY(cudaMemset(s->bar, 0, 1024 * 4));
+    CUDA_TRY(cudaMemset(s->R.logits, 0, (size_t)s->cap_tokens * s->E * 4));  // tagged logit slots of the fused decode kernel
+    CUDA_TRY(cudaDeviceSynchronize());
+    *reinterpret_cast<volatile int32_t*>(s->h_status) = 0;
+    return Status::Ok();
+}
+
 void free_moe_scratch(CudaMoeScratch* s) {
+    if (s->h_status) cudaFreeHost(s->h_status);
     if (s->arena) cudaFree(s->arena);
     if (s->arena_tok) cudaFree(s->arena_tok);
     *s = CudaMoeScratch();
@@ -272,6 +302,8 @@ static Status check_device(const CudaMoeScratch* s) {
 static Status check_layer(const CudaMoeScratch* s, const MoeLayer& layer) {
     Status d = check_device(s);
     if (!d.ok()) return d;
+    d = check_status_word(s);
+    if (!d.ok()) return d;
     if (layer.dev.H != s->H || layer.dev.I != s->I || layer.dev.E != s->E)
         return Status::Err(1, "layer shape does not match the context");
     if (layer.dev.quant < 0) return Status::Err(1, "router-only layer: expert weights were not prepared");
@@ -292,6 +324,9 @@ static DecodeArgs make_decode_args(CudaMoeScratch* s, const MoeLayer& layer, int
     a.logits_override = s->logits_override;
     a.bar = (s->decode_impl == 0) ? s->bar : nullptr;
     a.status = s->status;
+    a.status_host = s->status_host;
+    a.wait_limit_us = s->wait_limit_us;
+    a.debug_extra_arrivals = 0;
     a.trace = nullptr;
     return a;
 }
@@ -310,6 +345,10 @@ Status encode_moe_ffn_decode(CudaMoeScratch* s, const MoeLayer& layer, const flo
     a.out = output_x;
     s->last_decode = a;
     s->has_last_decode = true;
+    if (s->expire_next[0] && decode_fused_applicable(a)) {
+        a.debug_extra_arrivals = 1;
+        s->expire_next[0] = 0;
+    }
     CUDA_TRY(launch_decode(a, st));
     return Status::Ok();
 }
@@ -339,6 +378,8 @@ Status encode_route_only(CudaMoeScratch* s, const MoeLayer* layer, const float* 
     if (!logits_in && (!layer || !normed)) return Status::Err(1, "route_only needs a layer and activations");
     Status dv = check_device(s);
     if (!dv.ok()) return dv;
+    dv = check_status_word(s);
+    if (!dv.ok()) return dv;
     Status g = ensure_prefill_grouped(s, tokens);
     if (!g.ok()) return g;
     const size_t C = (size_t)tokens * s->K;
@@ -363,6 +404,8 @@ Status encode_route_only(CudaMoeScratch* s, const MoeLayer* layer, const float* 
         p.L.E = s->E;
         p.L.I = s->I;
         p.R = s->R;
+        p.status = s->status;
+        p.status_host = s->status_host;
         p.x = normed;
         p.act_dtype = 0;
         p.T = tokens;
@@ -419,6 +462,9 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     p.tiles = s->tiles;
     p.n_tiles = s->n_tiles;
     p.status = s->status;
+    p.status_host = s->status_host;
+    p.wait_limit_us = s->wait_limit_us;
+    p.tc_ctas = s->tc_ctas;
     // the tcgen05 path reads activation rows with 16-byte loads (8-byte for 16-bit rows)
     const bool tc_ok = (s->H % 256 == 0) && (s->I % 128 == 0) && (reinterpret_cast<uintptr_t>(normed) % 16 == 0);
     p.impl = (s->prefill_impl == 1 || !tc_ok) ? 1 : 0;
@@ -426,16 +472,13 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     const bool bf16_mode = (layer.dev.quant == BF16);
     if (p.impl == 0) {
         CUDA_TRY(launch_gather_permute_x16(normed, act_dtype, s->R.col_src_tok, batch * s->K, s->H, s->x16, st));
-        int dev = 0, sms = 148;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        // LUMEN_MOE_TC_CTAS caps the persistent grid (one CTA per SM): an expert-parallel rank leaves
-        // a few SMs to the collective kernels that run beside the GEMMs
-        static const int cta_cap = [] {
-            const char* v = getenv("LUMEN_MOE_TC_CTAS");
-            return v ? atoi(v) : 0;
-        }();
-        if (cta_cap > 0 && cta_cap < sms) sms = cta_cap;
+        // persistent grid, one CTA per SM; LUMEN_MOE_FLAG_TC_CTAS leaves some SMs to kernels that run beside it
+        int sms = s->sms;
+        if (s->tc_ctas > 0 && s->tc_ctas < sms) sms = s->tc_ctas;
+        if (s->expire_next[1]) {
+            p.debug_extra_tx = 1;
+            s->expire_next[1] = 0;
+        }
         CUDA_TRY(launch_grouped_tc(p, s->x16, sms, st, out16_rows));
     } else {
         CUDA_TRY(launch_build_xf(normed, act_dtype, batch, s->H, layer.dev.kg_h * 4, bf16_mode, s->xf, st));

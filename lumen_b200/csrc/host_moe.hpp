@@ -106,6 +106,13 @@ struct CudaMoeScratch {
     int32_t* n_tiles = nullptr;
     unsigned int* tile_counter = nullptr;
     int32_t* status = nullptr;
+    int32_t* h_status = nullptr;       // pinned host word the kernels mirror the status code into
+    int32_t* status_host = nullptr;    // device-side address of h_status
+    int flags = 0;                     // lumen_moe_config.flags
+    unsigned wait_limit_us = 0;        // 0 = the kernels' defaults (1-2 s); 2000 with LUMEN_MOE_FLAG_SHORT_WAITS
+    int tc_ctas = 0;                   // cap of the persistent tcgen05 grid (0 = every SM)
+    int sms = 0;                       // multiprocessors of the device
+    int expire_next[2] = {0, 0};       // test hook (lumen_moe_debug_expire_next_wait): one-shot per kernel kind
     const float* logits_override = nullptr;
     DecodeArgs last_decode{};   // arguments of the most recent decode call (instrumentation)
     bool has_last_decode = false;
@@ -130,8 +137,11 @@ Status build_batched_offsets(const CudaMoeMeta& meta, cudaStream_t st, CudaMoeBa
 Status build_repacked(const CudaMoeScratch& scratch, const void* layer_buf, size_t blob_bytes,
                       const CudaMoeMeta& meta, const CudaMoeBatchedOffsets& offs, int H, int I, int E,
                       cudaStream_t st, CudaMoeRepacked* out, LayerDev* dev);
-Status allocate_moe_scratch(int device, int H, int expert_I, int E, int K, int gating, int max_tokens,
+Status allocate_moe_scratch(int device, int H, int expert_I, int E, int K, int gating, int max_tokens, int flags,
                             CudaMoeScratch* out);
+// LUMEN_MOE_TIMEOUT / LUMEN_MOE_INVALID_ARG once a kernel of this context has given up (host read, no sync)
+Status check_status_word(const CudaMoeScratch* scratch);
+Status clear_status_word(CudaMoeScratch* scratch, cudaStream_t st);
 Status ensure_prefill_grouped(CudaMoeScratch* scratch, int batch);
 void free_moe_scratch(CudaMoeScratch* scratch);
 void free_moe_layer(MoeLayer* layer);

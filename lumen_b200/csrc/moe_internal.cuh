@@ -95,8 +95,21 @@ struct DecodeArgs {
     int T, K, gating;
     unsigned int* bar;      // grid barrier of the fused kernel: arrival counter + per-CTA barrier counts (1024 words); null = three-kernel chain
     int32_t* status;        // context status word (non-zero after a bounded wait expired)
+    int32_t* status_host;   // the same code for the host: a word of mapped pinned host memory (null = none)
+    unsigned wait_limit_us; // limit of every device-side wait of this launch (0 = one second)
+    int debug_extra_arrivals;  // test hook: the grid barrier expects this many arrivals more than there are CTAs
     unsigned long long* trace;  // optional [grid][12] globaltimer stamps of the fused kernel's phases (null = off)
 };
+
+#ifdef __CUDACC__
+// A kernel that gives up records why: the first code wins; the host copy is written once.
+__device__ __forceinline__ void raise_status(int32_t* status, int32_t* status_host, int code) {
+    if (atomicCAS(status, 0, code) == 0 && status_host != nullptr) {
+        *reinterpret_cast<volatile int32_t*>(status_host) = code;
+        __threadfence_system();
+    }
+}
+#endif
 
 // launchers (kernels.cu files)
 cudaError_t launch_repack(const uint8_t* blob, const uint64_t* d_gate_offs, const uint64_t* d_up_offs,
@@ -132,7 +145,11 @@ struct PrefillArgs {
     int4* tiles;            // tile list for the grouped GEMMs
     int32_t* n_tiles;       // [2]: gate/up tiles, down tiles
     unsigned int* tile_counter;  // [2] dynamic tile scheduler counters
-    int32_t* status;        // [1] device-side error flag (bounded waits)
+    int32_t* status;        // [1] device-side error flag (bounded waits, invalid caller-supplied ids)
+    int32_t* status_host;   // the same code in mapped pinned host memory (null = none)
+    unsigned wait_limit_us; // limit of the device-side waits (0 = two seconds)
+    int debug_extra_tx;     // test hook: the first stage barrier expects this many bytes more than arrive
+    int tc_ctas;            // cap of the persistent tcgen05 grid (0 = every SM)
     int impl;               // 0 = tcgen05 path, 1 = mma.sync grouped fallback
     const uint32_t* ids_in;  // caller-supplied routing [T,K] (null = route here)
     const float* weights_in; // [T,K] or null (= 1)
@@ -141,5 +158,23 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st);
 cudaError_t launch_prefill(const PrefillArgs& a, cudaStream_t st);
 
 void count_launch(int n = 1);
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only, and one
+// process may own contexts on several GPUs: the opt-in is remembered per device ordinal
+// (`cache` is a function-local static of the launcher, one per kernel instantiation).
+struct SmemOptIn {
+    size_t bytes[64] = {};
+};
+template <typename Kern>
+inline cudaError_t ensure_dyn_smem(Kern kern, size_t bytes, SmemOptIn& cache) {
+    if (bytes <= 48 * 1024) return cudaSuccess;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (bytes <= cache.bytes[device & 63]) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess) cache.bytes[device & 63] = bytes;
+    return e;
+}
 
 }  // namespace lumen

@@ -63,15 +63,19 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 // Bounded wait. Returns false when another role aborted or the limit expired
 // (in which case it raises the abort flag itself).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag) {
+struct AbortCtl {
+    volatile uint32_t* flag;  // CTA-wide abort flag in shared memory
+    uint64_t limit_ns;
+};
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl& ac) {
     if (mbar_try(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t i = 0;; ++i) {
         if (mbar_try(bar, parity)) return true;
         if ((i & 63u) == 63u) {
-            if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-                *abort_flag = 1u;
+            if (*ac.flag) return false;
+            if (globaltimer_ns() - t0 > ac.limit_ns) {
+                *ac.flag = 1u;
                 return false;
             }
         }
@@ -139,6 +143,9 @@ struct Args {
     const void* b_src;      // 16-bit activations [rows, kdim], permuted order
     __half* out16;          // gate/up: S16 [C, I] permuted order; down: D16 [C, H] natural order
     int32_t* status;
+    int32_t* status_host;   // mapped pinned copy of the status word for the host (null = none)
+    uint64_t wait_limit_ns; // limit of every mbarrier wait
+    int debug_extra_tx;     // test hook: the first stage's barrier expects this many bytes too many
     int kdim;               // H (gate/up) or I (down)
     int out_ld;             // I or H
     const int32_t* out_row_map;  // down mode: output row of compact column c (null = c itself)
@@ -232,7 +239,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    volatile uint32_t* abort_flag = &abort_s;
+    const AbortCtl abort_flag{&abort_s, a.wait_limit_ns};
 
     if (tid == 0) {
         abort_s = 0u;
@@ -388,7 +395,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&full_bar[s]);
                 const uint32_t bbase = stage0 + s * STAGE_BYTES + NA * SUB_BYTES;
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(nbox * SUB_BYTES)
+                // (test hook: with debug_extra_tx the very first stage can never complete)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                             "r"(nbox * SUB_BYTES + (n == 0 ? a.debug_extra_tx : 0))
                              : "memory");
                 for (int q = 0; q < nbox; ++q)
                     asm volatile(
@@ -445,7 +454,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS)
                      : "memory");
     }
-    if (tid == 0 && abort_s) atomicExch(a.status, 4);  // LUMEN_MOE_TIMEOUT
+    if (tid == 0 && abort_s) raise_status(a.status, a.status_host, 4);  // LUMEN_MOE_TIMEOUT
 }
 
 // activations -> f16, gathered into compact-column order (row c = token
@@ -521,12 +530,10 @@ static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
     constexpr int NA = 2;
     constexpr int STAGES = (BN == 128) ? 4 : 3;
     const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(tc::grouped_gemm_tc_kernel<Q, MODE, BN>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    static SmemOptIn optin;
+    {
+        cudaError_t e = ensure_dyn_smem(tc::grouped_gemm_tc_kernel<Q, MODE, BN>, (size_t)smem, optin);
         if (e != cudaSuccess) return e;
-        attr_set = true;
     }
     count_launch();
     tc::grouped_gemm_tc_kernel<Q, MODE, BN><<<grid, tc::THREADS, smem, st>>>(a);
@@ -549,12 +556,16 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     gu.b_src = x16;
     gu.out16 = p.s16;
     gu.status = p.status;
+    gu.status_host = p.status_host;
+    gu.wait_limit_ns = p.wait_limit_us ? (uint64_t)p.wait_limit_us * 1000ull : tc::WAIT_LIMIT_NS;
+    gu.debug_extra_tx = p.debug_extra_tx;
     gu.kdim = p.L.H;
     gu.out_ld = p.L.I;
     tc::Args dn = gu;
     te = make_tmap(p.s16, (uint64_t)C, (uint64_t)p.L.I, &dn.tmap);
     if (te != cudaSuccess) return te;
     dn.col_src_tok = nullptr;
+    dn.debug_extra_tx = 0;  // the hook applies to the first kernel of the pair
     dn.tiles = p.tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1);  // as laid out by launch_route_large
     dn.b_src = p.s16;
     // out16_rows: write the down product straight into caller rows (row = col_src_tok[column])

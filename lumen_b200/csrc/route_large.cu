@@ -526,13 +526,25 @@ cudaError_t launch_build_xf(const void* x, int act_dtype, int T, int H, int nblk
 }
 
 // Caller-supplied routing (expert-parallel ranks receive rows that were routed
-// elsewhere): copy the ids, weights default to 1.
-__global__ void set_routing_kernel(const uint32_t* __restrict__ ids_in, const float* __restrict__ w_in, int n,
-                                   uint32_t* __restrict__ ids, float* __restrict__ w) {
+// elsewhere): copy the ids, weights default to 1. The reference checks expert_id < E on
+// its host path (cuda/moe.rs:1776-1780); here the ids are device data, so the check runs
+// on the device: an id >= E raises the context's status word (LUMEN_MOE_INVALID_ARG) and
+// the pair is routed to expert 0 with weight 0, so that no table or histogram is ever
+// indexed out of range.
+__global__ void set_routing_kernel(const uint32_t* __restrict__ ids_in, const float* __restrict__ w_in, int n, int E,
+                                   uint32_t* __restrict__ ids, float* __restrict__ w, int32_t* status,
+                                   int32_t* status_host) {
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i < n) {
-        ids[i] = ids_in[i];
-        w[i] = w_in ? w_in[i] : 1.0f;
+        uint32_t id = ids_in[i];
+        float wt = w_in ? w_in[i] : 1.0f;
+        if (id >= (uint32_t)E) {
+            if (status != nullptr) raise_status(status, status_host, 1);
+            id = 0u;
+            wt = 0.0f;
+        }
+        ids[i] = id;
+        w[i] = wt;
     }
 }
 
@@ -542,7 +554,8 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const float* lg = a.logits_override;
     if (a.ids_in != nullptr) {
         count_launch();
-        set_routing_kernel<<<(T * K + 255) / 256, 256, 0, st>>>(a.ids_in, a.weights_in, T * K, a.R.ids, a.R.weights);
+        set_routing_kernel<<<(T * K + 255) / 256, 256, 0, st>>>(a.ids_in, a.weights_in, T * K, E, a.R.ids, a.R.weights,
+                                                                a.status, a.status_host);
     } else if (lg == nullptr) {
         count_launch();
         if (H % 32 == 0 && a.w16 != nullptr && reinterpret_cast<uintptr_t>(a.x) % 16 == 0) {

@@ -98,10 +98,10 @@ class MoeScratch:
     """CudaMoeScratch (cuda/moe.rs:101-210) behind lumen_moe_ctx."""
 
     def __init__(self, hidden_dim: int, inter_dim: int, num_experts: int, top_k: int, max_tokens: int = 16,
-                 gating_mode: int = SOFTMAX_RENORM, device: int = 0):
+                 gating_mode: int = SOFTMAX_RENORM, device: int = 0, flags: int = 0):
         self.H, self.I, self.E, self.K = hidden_dim, inter_dim, num_experts, top_k
         self.device = device
-        cfg = MoeConfig(hidden_dim, inter_dim, num_experts, top_k, max_tokens, gating_mode, device, 0)
+        cfg = MoeConfig(hidden_dim, inter_dim, num_experts, top_k, max_tokens, gating_mode, device, flags)
         h = ctypes.c_void_p()
         check(_lib.lib().lumen_moe_create(ctypes.byref(cfg), ctypes.byref(h)))
         self._h = h.value
@@ -301,6 +301,22 @@ class MoeScratch:
                                                cst.ctypes.data, bounds.ctypes.data, _stream()))
         return {"ids": ids, "weights": w, "dst_to_col": d2c, "col_src_tok": cst, "expert_bounds": bounds}
 
+    def get_routing_ids_stride_e(self, tokens: int) -> np.ndarray:
+        """ids of the last routing call as the reference's batched buffer lays them out: [T, E], first K valid."""
+        ids = np.zeros((tokens, self.E), np.uint32)
+        check(_lib.lib().lumen_moe_get_routing_ids_stride_e(self._h, tokens, ids.ctypes.data, _stream()))
+        return ids
+
+    def poll_status(self) -> int:
+        """lumen_moe_poll_status: 0, or the code a kernel of this context recorded when it gave up (no sync)."""
+        return int(_lib.lib().lumen_moe_poll_status(self._h))
+
+    def clear_status(self) -> None:
+        check(_lib.lib().lumen_moe_clear_status(self._h, _stream()))
+
+    def debug_expire_next_wait(self, which: int) -> None:
+        check(_lib.lib().lumen_moe_debug_expire_next_wait(self._h, which))
+
     def debug_decode_trace(self, layer):
         """Per-CTA phase stamps (ns) of the fused decode kernel for the last decode call: int64 [SMs, 12]."""
         sms = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -339,9 +355,10 @@ class MoeScratch:
 
 
 def allocate_moe_scratch(hidden_dim: int, expert_inter_dim: int, num_experts: int, top_k: int,
-                         max_tokens: int = 16, gating_mode: int = SOFTMAX_RENORM, device: int = 0) -> MoeScratch:
+                         max_tokens: int = 16, gating_mode: int = SOFTMAX_RENORM, device: int = 0,
+                         flags: int = 0) -> MoeScratch:
     """allocate_moe_scratch (cuda/moe.rs:968)."""
-    return MoeScratch(hidden_dim, expert_inter_dim, num_experts, top_k, max_tokens, gating_mode, device)
+    return MoeScratch(hidden_dim, expert_inter_dim, num_experts, top_k, max_tokens, gating_mode, device, flags)
 
 
 def encode_moe_ffn_decode(scratch: MoeScratch, layer: MoeLayer, normed_x, residual, output_x):

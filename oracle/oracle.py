@@ -141,13 +141,13 @@ def accum_batched_b(residual, expert_outputs, expert_weights, expert_ids, H, K):
     return out
 
 
-def counting_sort(ids, E, ids_stride=None):
+def counting_sort(ids, E, K=None):
+    """Host counting sort of cuda/moe.rs:2115-2147. `ids` is [T, K], or, with K given, the reference's
+    batched id buffer [T, stride] whose rows hold K valid ids first (stride E, topk_moe_fused.cu:189-191)."""
     ids = np.ascontiguousarray(ids, dtype=np.uint32)
-    T, K = ids.shape if ids_stride is None else (ids.shape[0], None)
-    if ids_stride is None:
-        ids_stride = K
-    else:
-        raise ValueError("pass a [T,K] array; stride-E buffers should be sliced first")
+    T, ids_stride = ids.shape
+    if K is None:
+        K = ids_stride
     C = T * K
     col_expert = np.zeros(C, np.int32)
     col_src_tok = np.zeros(C, np.int32)

@@ -1,13 +1,11 @@
 """Prefill path (any number of tokens) against the CPU reference, through the
 C ABI: device routing + stable counting sort + grouped expert products
 (tcgen05 path and the mma.sync grouped path) + scatter-accumulate."""
-import os
-
 import numpy as np
 import pytest
 import torch
 
-from lumen_b200 import moe, synth
+from lumen_b200 import _lib, moe, synth
 from oracle import oracle
 from tests.gpu_util import TOL_REL_L2, oracle_layer, rel_l2
 
@@ -15,14 +13,10 @@ pytestmark = pytest.mark.gpu
 
 
 def make(H, I, E, K, quant, impl, seed=0, max_tokens=64):
-    os.environ["LUMEN_MOE_PREFILL_IMPL"] = impl
-    try:
-        lay = synth.LayerLayout(H, I, E, quant)
-        blob = synth.make_layer_blob(lay, seed)
-        sc = moe.allocate_moe_scratch(H, I, E, K, max_tokens)
-        layer = sc.prepare_layer(blob, lay.meta())
-    finally:
-        os.environ.pop("LUMEN_MOE_PREFILL_IMPL", None)
+    lay = synth.LayerLayout(H, I, E, quant)
+    blob = synth.make_layer_blob(lay, seed)
+    sc = moe.allocate_moe_scratch(H, I, E, K, max_tokens, flags=_lib.FLAG_PREFILL_MMA if impl == "mma" else 0)
+    layer = sc.prepare_layer(blob, lay.meta())
     torch.cuda.synchronize()
     return lay, lay.meta(), blob.cpu().numpy(), sc, layer
 
@@ -170,6 +164,30 @@ def test_prefill_full_size_properties(cuda_lib):
     sample = [0, 1, 777, 2048, 4095]
     xs = x[sample].float().cpu().numpy()
     o_out, _, _ = oracle.moe_layer(blob_np, 0, meta.expert_gate_offs, meta.expert_up_offs, meta.expert_down_offs, 1,
+                                   H, I, E, K, xs, np.zeros_like(xs), ids=r["ids"][sample],
+                                   weights=r["weights"][sample], threads=8)
+    assert rel_l2(out[sample].cpu().numpy(), o_out) < TOL_REL_L2
+
+
+@pytest.mark.parametrize("quant,T,routing", [(0, 2304, "uniform"), (2, 2304, "zipf"), (0, 4096, "zipf")])
+def test_prefill_full_shape_other_formats_against_oracle(cuda_lib, quant, T, routing):
+    """Q8_0 and BF16 experts at the headline shape with more than 2048 tokens, where the gate/up
+    product takes its 256-column tiles: a sample of tokens against the CPU reference."""
+    H, I, E, K = 2048, 768, 128, 8
+    lay, meta, blob_np, sc, layer = make(H, I, E, K, quant, "", 0, max_tokens=T)
+    g = torch.Generator("cuda").manual_seed(7)
+    x = torch.randn((T, H), generator=g, device="cuda").to(torch.bfloat16)
+    res = torch.zeros((T, H), device="cuda")
+    lg = synth.zipf_logits(T, E, 2) if routing == "zipf" else synth.uniform_logits(T, E, 2)
+    sc.set_logits_override(lg)
+    out = sc.prefill(layer, x, res)
+    r = sc.get_routing(T)
+    o_ids, o_w = oracle.topk_from_logits(lg.cpu().numpy(), K, 0)
+    assert np.array_equal(r["ids"], o_ids) and np.array_equal(r["weights"].view(np.uint32), o_w.view(np.uint32))
+    assert torch.isfinite(out).all()
+    sample = [0, 5, T // 2, T - 2, T - 1]
+    xs = x[sample].float().cpu().numpy()
+    o_out, _, _ = oracle.moe_layer(blob_np, 0, meta.expert_gate_offs, meta.expert_up_offs, meta.expert_down_offs, quant,
                                    H, I, E, K, xs, np.zeros_like(xs), ids=r["ids"][sample],
                                    weights=r["weights"][sample], threads=8)
     assert rel_l2(out[sample].cpu().numpy(), o_out) < TOL_REL_L2

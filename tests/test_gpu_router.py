@@ -112,6 +112,45 @@ def test_route_only_against_cpu_router(cuda_lib, T):
     assert np.array_equal(w.cpu().numpy().view(np.uint32), o_w.view(np.uint32))
 
 
+@pytest.mark.parametrize("T,act", [(1, torch.float32), (3, torch.float32), (16, torch.float32), (4096, torch.float32),
+                                   (4096, torch.bfloat16)])
+def test_router_logits_at_the_headline_shape(cuda_lib, T, act):
+    """logit[t,e] = sum_j W_r[e,j] x[t,j] (cuda/moe.rs:6456-6463) at H = 2048, E = 128 for the
+    small-batch router (T <= 16) and the batched one (any T, f32 and bf16 activations). (The
+    persistent decode kernel keeps its logits in shared memory; tests/test_gpu_decode.py checks
+    the experts it selects from them.)"""
+    H, I, E, K = 2048, 768, 128, 8
+    lay = synth.LayerLayout(H, I, E, 1)
+    blob = synth.make_layer_blob(lay, 21)
+    sc = moe.allocate_moe_scratch(H, I, E, K, T)
+    layer = sc.prepare_router_only(blob, lay.meta().router_weight_off)
+    x = torch.randn((T, H), generator=torch.Generator("cuda").manual_seed(T), device="cuda").to(act)
+    router = blob[:lay.router_bytes].cpu().numpy().view(np.float32).reshape(E, H)
+    xn = x.float().cpu().numpy()
+    sample = sorted(set([0, T // 3, T - 1]))
+    if act == torch.float32:
+        ids, w, lg = sc.route_only(layer, x, want_logits=True)
+        for t in sample:
+            o_lg = oracle.router_logits(xn[t], router, H, E)
+            np.testing.assert_allclose(lg[t].cpu().numpy(), o_lg, rtol=0, atol=3e-5)
+        o_ids, o_w = oracle.topk_from_logits(lg.cpu().numpy(), K, 0)
+        assert np.array_equal(ids.cpu().numpy().astype(np.uint32), o_ids)
+        assert np.array_equal(w.cpu().numpy().view(np.uint32), o_w.view(np.uint32))
+    else:
+        # bf16 activations only enter through the prefill call: ids must be the CPU top-k of logits
+        # that agree with the CPU dot products (checked through the set of chosen experts)
+        full = synth.make_layer_blob(lay, 21)
+        fl = sc.prepare_layer(full, lay.meta())
+        sc.prefill(fl, x, torch.zeros((T, H), device="cuda"))
+        r = sc.get_routing(T)
+        for t in sample:
+            o_lg = oracle.router_logits(xn[t], router, H, E)
+            o_ids, _ = oracle.topk_from_logits(o_lg[None, :], K, 0)
+            srt = np.sort(o_lg)[::-1]
+            if np.min(np.abs(np.diff(srt[:K + 1]))) > 1e-4:
+                assert np.array_equal(r["ids"][t], o_ids[0])
+
+
 def test_quantizers_bit_exact(cuda_lib):
     g = torch.Generator("cuda").manual_seed(9)
     w = torch.randn(32 * 4096, generator=g, device="cuda") * 0.02

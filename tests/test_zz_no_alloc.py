@@ -1,7 +1,8 @@
 """lumen_moe_route_small_static, the entry point for hosts that cannot allocate
 device memory (all of it belongs to their own pool, or their decode loop must
 not enter the driver allocator): it has to give exactly what the context-based
-lumen_moe_topk_from_logits gives -- ids, weights and sort tables, bit for bit --
+lumen_moe_topk_from_logits gives -- ids, weights and sort tables, bit for bit, which
+are also the CPU reference's (cpu_router_softmax + the host counting sort) --
 and keep doing so call after call, since every call reuses the same static
 working array inside the library.
 
@@ -13,6 +14,7 @@ import pytest
 import torch
 
 from lumen_b200 import moe, synth
+from oracle import oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -38,6 +40,13 @@ def test_static_scratch_routing_matches_context_routing_twice(cuda_lib):
         assert np.array_equal(w.cpu().numpy().view(np.uint32), r_w.view(np.uint32))
         assert np.array_equal(d2c.cpu().numpy(), r_d2c)
         assert np.array_equal(bounds.cpu().numpy(), r_bounds)
+        # and against the CPU reference's routing and host counting sort on the same logits
+        o_ids, o_w = oracle.topk_from_logits(lg.cpu().numpy(), K, gating)
+        _, _, o_d2c, o_bounds = oracle.counting_sort(o_ids, E)
+        assert np.array_equal(ids.cpu().numpy().astype(np.uint32), o_ids)
+        assert np.array_equal(w.cpu().numpy().view(np.uint32), o_w.view(np.uint32))
+        assert np.array_equal(d2c.cpu().numpy(), o_d2c)
+        assert np.array_equal(bounds.cpu().numpy(), o_bounds)
     # same input twice: identical output (nothing left over changes the result)
     lg = synth.zipf_logits(16, 128, 9)
     a = moe.route_small_static(lg, 8, want_tables=True)

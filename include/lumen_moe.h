@@ -285,6 +285,55 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_ep_prepare(lumen_moe_ctx* ctx, const 
                                                       int32_t tokens, int32_t experts_per_rank, void* d_rows16,
                                                       int32_t* d_local_ids, int64_t* d_send_counts, void* stream);
 
+/* ---- Expert-parallel prefill over several GPUs (one process per GPU) -------------------
+ * No counterpart in the reference, which is single-GPU (one context, one stream,
+ * cuda/ffi.rs:61-87): the multi-GPU form of encode_moe_ffn_prefill_grouped (cuda/moe.rs:1900)
+ * for multi-token batches. Tokens are sharded over `world` ranks, experts E / world per rank
+ * (rank r owns experts [r * E / world, (r + 1) * E / world)), the router weight is replicated.
+ * The ranks exchange rows and results by plain stores into each other's device memory over
+ * NVLink (CUDA IPC mappings); the library calls no collective and the host is not in the
+ * loop: a layer call is one asynchronous call per rank on its stream.
+ *
+ * Set-up, once per rank, on a context created with the GLOBAL num_experts and top_k:
+ *   lumen_moe_ep_create   allocates this rank's window (receive buffers and flags) and writes
+ *                         its 64-byte IPC handle to handle_out. max_tokens = most tokens THIS
+ *                         rank passes per call; recv_rows = rows this rank can receive per call,
+ *                         0 = max_tokens * top_k * world (no routing skew can overflow that;
+ *                         every rank must use the same values). Synchronous (allocates).
+ *   (the host gathers the `world` handles in rank order: its own transport, e.g. the launcher's
+ *    rendezvous; the handle of a rank's own slot is ignored)
+ *   lumen_moe_ep_attach   maps the peers' windows. Synchronous.
+ *   lumen_moe_ep_layer_prepare   as lumen_moe_layer_prepare, with the offset tables of ALL
+ *                         num_experts experts: keeps the router weight and repacks only this
+ *                         rank's experts.
+ * Per layer call, on every rank (a collective call: all ranks make the same sequence of
+ * calls, each on its own tokens; tokens may differ per rank, 1 <= tokens <= max_tokens):
+ *   lumen_moe_prefill_ep  out[t] = residual[t] + sum_k w[t,k] * FFN_{e(t,k)}(normed[t]) for this
+ *                         rank's tokens; bit-identical to lumen_moe_prefill on one GPU for the
+ *                         same tokens. d_normed [T,H] f32 or bf16, 16-byte aligned.
+ *   lumen_moe_stack_prefill_ep   the layer stack of lumen_moe_stack_prefill in this form.
+ * Every cross-rank wait is bounded (2 s; 2 ms with LUMEN_MOE_FLAG_SHORT_WAITS): a rank whose
+ * peer does not show up gets LUMEN_MOE_TIMEOUT through lumen_moe_poll_status, and an overflow
+ * of recv_rows gives LUMEN_MOE_INVALID_ARG the same way; no index ever leaves a window.
+ * A rank must not destroy its context while a peer may still write to it. */
+#define LUMEN_MOE_EP_HANDLE_BYTES 64
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_ep_create(lumen_moe_ctx* ctx, int32_t rank, int32_t world,
+                                                     int32_t max_tokens, int32_t recv_rows, void* handle_out);
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_ep_attach(lumen_moe_ctx* ctx, const void* handles, int32_t rank,
+                                                     int32_t world);
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_ep_layer_prepare(lumen_moe_ctx* ctx, const void* d_layer_blob,
+                                                            size_t blob_bytes, uint64_t router_off,
+                                                            const uint64_t* gate_offs, const uint64_t* up_offs,
+                                                            const uint64_t* down_offs, int32_t quant, void* stream,
+                                                            lumen_moe_layer** out_layer);
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_prefill_ep(lumen_moe_ctx* ctx, const lumen_moe_layer* layer,
+                                                      const void* d_normed, const float* d_residual, float* d_out,
+                                                      int32_t tokens, int32_t act_dtype, void* stream);
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_stack_prefill_ep(lumen_moe_ctx* ctx, const lumen_moe_layer* const* layers,
+                                                            const float* const* d_gammas, int32_t n_layers,
+                                                            float* d_x, float* d_normed, float eps, int32_t tokens,
+                                                            void* stream);
+
 /* ---- LBC container: header and layer index (host only, no device work) ----------------
  * The reference's backend uploads a MoE layer's blob byte for byte
  * (cuda/gpu_buffers.rs:1404-1409) and derives the operator's offsets from the layer's

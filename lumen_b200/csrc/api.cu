@@ -12,6 +12,7 @@ cudaError_t launch_scatter_accum(const __half* d16, const float* residual, const
 
 struct lumen_moe_ctx {
     lumen::CudaMoeScratch scratch;
+    lumen::EpState* ep = nullptr;  // expert-parallel state (lumen_moe_ep_create), or null
 };
 struct lumen_moe_layer {
     lumen::MoeLayer layer;
@@ -68,6 +69,7 @@ lumen_moe_status_t lumen_moe_create(const lumen_moe_config* cfg, lumen_moe_ctx**
 
 void lumen_moe_destroy(lumen_moe_ctx* ctx) {
     if (!ctx) return;
+    lumen::ep_free(ctx->ep);
     lumen::free_moe_scratch(&ctx->scratch);
     delete ctx;
 }
@@ -441,6 +443,100 @@ lumen_moe_status_t lumen_moe_debug_decode_trace(lumen_moe_ctx* ctx, const lumen_
     if (!lumen::decode_fused_applicable(a)) return fail(LUMEN_MOE_UNSUPPORTED, "the fused decode kernel does not apply to this call");
     cudaError_t e = lumen::launch_decode_fused(a, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_ep_create(lumen_moe_ctx* ctx, int32_t rank, int32_t world, int32_t max_tokens,
+                                       int32_t recv_rows, void* handle_out) {
+    if (!ctx || !handle_out) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    if (ctx->ep) return fail(LUMEN_MOE_INVALID_ARG, "the context already has an expert-parallel window");
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != ctx->scratch.device)
+        return fail(LUMEN_MOE_INVALID_ARG, "the context belongs to another CUDA device than the current one");
+    return done(lumen::ep_create(&ctx->scratch, rank, world, max_tokens, recv_rows, &ctx->ep, handle_out));
+}
+
+lumen_moe_status_t lumen_moe_ep_attach(lumen_moe_ctx* ctx, const void* handles, int32_t rank, int32_t world) {
+    if (!ctx || !handles) return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    if (!ctx->ep) return fail(LUMEN_MOE_INVALID_ARG, "call lumen_moe_ep_create first");
+    if (rank != lumen::ep_rank(ctx->ep) || world != lumen::ep_world(ctx->ep))
+        return fail(LUMEN_MOE_INVALID_ARG, "rank / world differ from lumen_moe_ep_create");
+    return done(lumen::ep_attach(ctx->ep, handles));
+}
+
+lumen_moe_status_t lumen_moe_ep_layer_prepare(lumen_moe_ctx* ctx, const void* d_layer_blob, size_t blob_bytes,
+                                              uint64_t router_off, const uint64_t* gate_offs, const uint64_t* up_offs,
+                                              const uint64_t* down_offs, int32_t quant, void* stream,
+                                              lumen_moe_layer** out_layer) {
+    if (!ctx || !d_layer_blob || !out_layer || !gate_offs || !up_offs || !down_offs)
+        return fail(LUMEN_MOE_INVALID_ARG, "null argument");
+    if (!ctx->ep) return fail(LUMEN_MOE_INVALID_ARG, "call lumen_moe_ep_create first");
+    if (quant < 0 || quant > 2) return fail(LUMEN_MOE_UNSUPPORTED, "unsupported quant scheme");
+    const lumen::CudaMoeScratch& sc = ctx->scratch;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != sc.device)
+        return fail(LUMEN_MOE_INVALID_ARG, "the context belongs to another CUDA device than the current one");
+    if (router_off % 4 != 0 || router_off + (uint64_t)sc.E * sc.H * 4 > blob_bytes)
+        return fail(LUMEN_MOE_INVALID_ARG, "router weight misaligned or outside the layer blob");
+    const int epr = lumen::ep_experts_per_rank(ctx->ep), first = lumen::ep_rank(ctx->ep) * epr;
+    lumen_moe_layer* l = new (std::nothrow) lumen_moe_layer();
+    if (!l) return fail(LUMEN_MOE_CUDA_ERROR, "out of host memory");
+    lumen::CudaMoeMeta& m = l->layer.meta;
+    m.router_weight_off = router_off;
+    m.expert_gate_offs.assign(gate_offs + first, gate_offs + first + epr);
+    m.expert_up_offs.assign(up_offs + first, up_offs + first + epr);
+    m.expert_down_offs.assign(down_offs + first, down_offs + first + epr);
+    m.expert_gate_quant = m.expert_down_quant = quant;
+    lumen::Status s = lumen::build_batched_offsets(m, st, &l->layer.offsets);
+    if (s.ok())
+        s = lumen::build_repacked(sc, d_layer_blob, blob_bytes, m, l->layer.offsets, sc.H, sc.I, epr, st,
+                                  &l->layer.repacked, &l->layer.dev);
+    if (s.ok() && l->layer.repacked.router_copy) {
+        // the aligned copy made there covers this rank's experts only: the router needs all E rows
+        cudaStreamSynchronize(st);
+        cudaFree(l->layer.repacked.router_copy);
+        l->layer.repacked.router_copy = nullptr;
+        s = lumen::aligned_router(d_layer_blob, router_off, sc.E, sc.H, st, &l->layer.repacked, &l->layer.dev.router_w);
+    }
+    if (s.ok()) {
+        cudaError_t e = cudaStreamSynchronize(st);
+        if (e != cudaSuccess) s = lumen::Status::Err(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+    }
+    if (!s.ok()) {
+        lumen::free_moe_layer(&l->layer);
+        delete l;
+        return done(s);
+    }
+    l->layer.blob_bytes = blob_bytes;
+    *out_layer = l;
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_prefill_ep(lumen_moe_ctx* ctx, const lumen_moe_layer* layer, const void* d_normed,
+                                        const float* d_residual, float* d_out, int32_t tokens, int32_t act_dtype,
+                                        void* stream) {
+    if (!ctx || !layer) return fail(LUMEN_MOE_INVALID_ARG, "null handle");
+    if (!ctx->ep) return fail(LUMEN_MOE_INVALID_ARG, "call lumen_moe_ep_create and lumen_moe_ep_attach first");
+    return done(lumen::encode_moe_ffn_prefill_ep(&ctx->scratch, ctx->ep, layer->layer, d_normed, act_dtype, d_residual,
+                                                 d_out, tokens, static_cast<cudaStream_t>(stream)));
+}
+
+lumen_moe_status_t lumen_moe_stack_prefill_ep(lumen_moe_ctx* ctx, const lumen_moe_layer* const* layers,
+                                              const float* const* d_gammas, int32_t n_layers, float* d_x,
+                                              float* d_normed, float eps, int32_t tokens, void* stream) {
+    if (!ctx || !layers || !d_gammas || !d_x || !d_normed || n_layers < 1 || tokens < 1)
+        return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    if (!ctx->ep) return fail(LUMEN_MOE_INVALID_ARG, "call lumen_moe_ep_create and lumen_moe_ep_attach first");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    for (int l = 0; l < n_layers; ++l) {
+        if (!layers[l] || !d_gammas[l]) return fail(LUMEN_MOE_INVALID_ARG, "null layer or gamma");
+        cudaError_t e = lumen::launch_rmsnorm(d_x, d_gammas[l], d_normed, tokens, ctx->scratch.H, eps, st);
+        if (e != cudaSuccess) return fail(LUMEN_MOE_CUDA_ERROR, cudaGetErrorString(e));
+        lumen::Status s = lumen::encode_moe_ffn_prefill_ep(&ctx->scratch, ctx->ep, layers[l]->layer, d_normed, 0, d_x, d_x,
+                                                           tokens, st);
+        if (!s.ok()) return done(s);
+    }
     return LUMEN_MOE_OK;
 }
 

@@ -16,7 +16,8 @@ cudaError_t launch_build_xf(const void* x, int act_dtype, int T, int H, int nblk
                             uint4* xf, cudaStream_t st);
 cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_t* col_src_tok, int C, int H, void* out,
                                       cudaStream_t st);
-cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st, __half* out16_rows);
+cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st, __half* out16_rows,
+                              const TcPlan* plan = nullptr, const TcPeerOut* peer = nullptr);
 cudaError_t launch_rows_from_cols(const __half* d16, const int32_t* dst_to_col, __half* out16, int T, int H, cudaStream_t st);
 
 static std::atomic<long long> g_launches{0};

@@ -159,4 +159,18 @@ Status encode_route_only(CudaMoeScratch* scratch, const MoeLayer* layer, const f
                          const float* logits_in, int tokens, uint32_t* d_ids, float* d_weights,
                          float* d_logits_out, cudaStream_t st);
 
+
+// Expert-parallel prefill (ep_push.cu): per-rank state behind lumen_moe_ep_create / _attach.
+struct EpState;
+Status ep_create(CudaMoeScratch* scratch, int rank, int world, int max_tokens, int recv_rows, EpState** out,
+                 void* handle64);
+Status ep_attach(EpState* ep, const void* handles64);
+void ep_free(EpState* ep);
+int ep_rank(const EpState* ep);
+int ep_world(const EpState* ep);
+int ep_experts_per_rank(const EpState* ep);
+size_t ep_window_bytes(const EpState* ep);
+Status encode_moe_ffn_prefill_ep(CudaMoeScratch* scratch, EpState* ep, const MoeLayer& layer, const void* normed,
+                                 int act_dtype, const float* residual, float* output, int batch, cudaStream_t st);
+
 }  // namespace lumen

@@ -155,6 +155,25 @@ struct PrefillArgs {
     const float* weights_in; // [T,K] or null (= 1)
 };
 cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st);
+
+// Expert-parallel form of the grouped products: the rows of the activation operand are not this
+// rank's T*K compact columns but whatever the peers pushed into its receive window, and the down
+// product's output rows go back to the ranks they came from.
+constexpr int MAX_EP_RANKS = 16;
+struct TcPeerOut {
+    const int32_t* ret_map;        // [rows] (source rank << 24) | row in that rank's return buffer; null = off
+    __half* base[MAX_EP_RANKS];    // every rank's return buffer [rows_cap, H] f16 as mapped into this process
+    int world;
+    int rows_cap;                  // rows of a return buffer: indices are checked against it
+};
+struct TcPlan {
+    int rows;      // rows of the activation operand = capacity the tile lists were laid out for
+    int gu_cols;   // columns per gate/up tile the tile lists were built with (128 or 256)
+};
+// tile lists {expert, col_start, ncols, m_tile} of both grouped GEMMs from per-expert column counts
+// left in R.expert_bounds[0..E) (turned into bounds in place), plus R.uexp / R.n_uexp
+cudaError_t launch_tile_plan(const RouteDev& R, int E, int H, int I, int rows_cap, int gu_cols, int4* tiles,
+                             int32_t* n_tiles, cudaStream_t st);
 cudaError_t launch_prefill(const PrefillArgs& a, cudaStream_t st);
 
 void count_launch(int n = 1);

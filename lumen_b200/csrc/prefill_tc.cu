@@ -149,6 +149,7 @@ struct Args {
     int kdim;               // H (gate/up) or I (down)
     int out_ld;             // I or H
     const int32_t* out_row_map;  // down mode: output row of compact column c (null = c itself)
+    TcPeerOut peer;              // down mode, expert parallel: output rows go to other ranks' buffers (ret_map null = off)
 };
 
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
@@ -305,6 +306,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                         int orow_idx = tile.y + n0 + j;
                         if (MODE == 1 && a.out_row_map != nullptr) orow_idx = a.out_row_map[orow_idx];
                         __half* dst = a.out16 + (size_t)orow_idx * a.out_ld;
+                        if (MODE == 1 && a.peer.ret_map != nullptr) {
+                            // plain stores into the return buffer of the rank the row came from
+                            const int m = a.peer.ret_map[orow_idx];
+                            const int pr = (m >> 24) & 0xff, prow = m & 0xffffff;
+                            if (pr >= a.peer.world || prow >= a.peer.rows_cap) continue;  // never leave the buffers
+                            dst = a.peer.base[pr] + (size_t)prow * a.out_ld;
+                        }
                         if (MODE == 0) {
                             const float gt = __uint_as_float(v0[j]);
                             dst[off0] = __float2half_rn((gt / (1.0f + __expf(-gt))) * __uint_as_float(v1[j]));
@@ -541,9 +549,10 @@ static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
 }
 
 // gate/up + SwiGLU then down, both on tcgen05. x16: permuted 16-bit activations [T,H].
-cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st, __half* out16_rows) {
-    const int C = p.T * p.K;
-    const int gu_cols = tc_gu_tile_cols(C, p.L.E);  // as launch_route_large built the tile lists
+cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st, __half* out16_rows,
+                              const TcPlan* plan, const TcPeerOut* peer) {
+    const int C = plan ? plan->rows : p.T * p.K;
+    const int gu_cols = plan ? plan->gu_cols : tc_gu_tile_cols(C, p.L.E);  // as the tile lists were built
     const int max_ct = C / gu_cols + p.L.E;
     const int mt_gu = p.L.I / 128;
     tc::Args gu{};
@@ -571,6 +580,7 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     // out16_rows: write the down product straight into caller rows (row = col_src_tok[column])
     dn.out16 = out16_rows ? out16_rows : p.d16;
     dn.out_row_map = out16_rows ? p.R.col_src_tok : nullptr;
+    if (peer) dn.peer = *peer;
     dn.kdim = p.L.I;
     dn.out_ld = p.L.H;
     cudaError_t e;

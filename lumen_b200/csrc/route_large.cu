@@ -607,6 +607,17 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+cudaError_t launch_tile_plan(const RouteDev& R, int E, int H, int I, int rows_cap, int gu_cols, int4* tiles,
+                             int32_t* n_tiles, cudaStream_t st) {
+    const int max_ct = rows_cap / gu_cols + E, max_ct_dn = rows_cap / 128 + E;
+    const int mt_gu = I / 128, mt_dn = H / 256;
+    count_launch();
+    sort_scan_kernel<<<1, 256, 0, st>>>(0, E, R, gu_cols, 128, mt_gu, mt_dn, tiles,
+                                        tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1), n_tiles, max_ct * mt_gu,
+                                        max_ct_dn * mt_dn);
+    return cudaGetLastError();
+}
+
 // ---------------------------------------------------------------------------
 // Expert-parallel send side in one launch: activation rows gathered in compact-column
 // order (= destination-rank order, experts being contiguous per rank) as bf16, the

@@ -231,6 +231,63 @@ class ExpertParallelMoe:
         return torch.cat([self._combine(backs[c], residual[b0:b1], sides[c]) for c, (b0, b1) in enumerate(parts)])
 
 
+def push_layout(counts, experts_per_rank: int):
+    """Host restatement of the layout every rank derives, on the device, from the count matrix
+    (ep_dispatch_kernel): counts[s][e] = pairs of source rank s for global expert e. Returns
+    base[s][e], the row in the window of e's owner where source s's pairs of expert e start
+    (rows grouped by expert, inside an expert by source rank, inside a source in its own
+    compact-column order), and rows[r], the rows rank r receives."""
+    import numpy as np
+    counts = np.asarray(counts, dtype=np.int64)
+    G, E = counts.shape
+    tot = counts.sum(axis=0)
+    base = np.zeros((G, E), dtype=np.int64)
+    rows = np.zeros(E // experts_per_rank, dtype=np.int64)
+    for e in range(E):
+        first = (e // experts_per_rank) * experts_per_rank
+        lower = int(tot[first:e].sum())
+        base[:, e] = lower + np.concatenate(([0], np.cumsum(counts[:-1, e])))
+    for r in range(E // experts_per_rank):
+        rows[r] = int(tot[r * experts_per_rank:(r + 1) * experts_per_rank].sum())
+    return base, rows
+
+
+class PushExpertParallel:
+    """lumen_moe_prefill_ep behind a torch.distributed rendezvous. The process group is used for
+    one thing only, at set-up: gathering the 64-byte handles of the ranks' windows (what a Rust
+    host would do over its own launcher's channel). A layer call is one library call per rank;
+    rows and results travel by plain peer stores over NVLink, issued by the library's kernels."""
+
+    def __init__(self, H: int, I: int, E: int, K: int, max_tokens: int, rank: int, world: int, device: int,
+                 gating_mode: int = 0, group=None, flags: int = 0, recv_rows: int = 0):
+        from . import moe
+        self.rank, self.world = rank, world
+        self.sc = moe.allocate_moe_scratch(H, I, E, K, max_tokens, gating_mode, device, flags)
+        handle = self.sc.ep_create(rank, world, max_tokens, recv_rows)
+        handles = [handle]
+        if world > 1:
+            handles = [None] * world
+            dist.all_gather_object(handles, handle, group=group)
+        self.sc.ep_attach(handles)
+        self.group = group
+
+    def prepare_layer(self, full_blob: torch.Tensor, meta):
+        return self.sc.ep_prepare_layer(full_blob, meta)
+
+    def forward(self, layer, normed: torch.Tensor, residual: torch.Tensor, out: Optional[torch.Tensor] = None):
+        return self.sc.prefill_ep(layer, normed, residual, out)
+
+    def stack_forward(self, layers, gammas, x: torch.Tensor, eps: float, normed: Optional[torch.Tensor] = None):
+        return self.sc.stack_prefill_ep(layers, gammas, x, eps, normed)
+
+    def close(self):
+        """Collective: no rank frees its window while a peer may still write to it."""
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)
+        self.sc.close()
+
+
 def cuda_layer_fns(H: int, I: int, E: int, K: int, quant: int, full_blob: torch.Tensor, rank: int, world: int,
                    max_tokens: int, gating_mode: int = 0, contexts=None) -> Tuple[Callable, Callable, dict]:
     """Builds route_fn / expert_fn on the CUDA library for this rank.

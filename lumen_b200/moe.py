@@ -301,6 +301,59 @@ class MoeScratch:
                                                cst.ctypes.data, bounds.ctypes.data, _stream()))
         return {"ids": ids, "weights": w, "dst_to_col": d2c, "col_src_tok": cst, "expert_bounds": bounds}
 
+    # -- expert parallel (lumen_moe_ep_*) ----------------------------------
+    def ep_create(self, rank: int, world: int, max_tokens: int, recv_rows: int = 0) -> bytes:
+        """lumen_moe_ep_create: allocates this rank's window; returns its 64-byte IPC handle."""
+        buf = ctypes.create_string_buffer(64)
+        check(_lib.lib().lumen_moe_ep_create(self._h, rank, world, max_tokens, recv_rows, buf))
+        self.ep_rank, self.ep_world = rank, world
+        return buf.raw
+
+    def ep_attach(self, handles: Sequence[bytes]) -> None:
+        """lumen_moe_ep_attach: `handles` = every rank's handle, in rank order."""
+        blob = b"".join(handles)
+        assert len(blob) == 64 * self.ep_world
+        check(_lib.lib().lumen_moe_ep_attach(self._h, blob, self.ep_rank, self.ep_world))
+
+    def ep_prepare_layer(self, blob: torch.Tensor, meta: MoeMeta) -> MoeLayer:
+        """lumen_moe_ep_layer_prepare: router + this rank's experts of a full layer blob."""
+        _need(blob, torch.uint8, "layer blob")
+        go = np.ascontiguousarray(meta.expert_gate_offs, dtype=np.uint64)
+        uo = np.ascontiguousarray(meta.expert_up_offs, dtype=np.uint64)
+        do = np.ascontiguousarray(meta.expert_down_offs, dtype=np.uint64)
+        if not (len(go) == len(uo) == len(do) == self.E):
+            raise LumenMoeError(_lib.INVALID_ARG, "offset tables must have num_experts entries")
+        h = ctypes.c_void_p()
+        check(_lib.lib().lumen_moe_ep_layer_prepare(self._h, blob.data_ptr(), blob.numel(), meta.router_weight_off,
+                                                    go.ctypes.data, uo.ctypes.data, do.ctypes.data,
+                                                    meta.expert_gate_quant, _stream(), ctypes.byref(h)))
+        return MoeLayer(h.value, blob, meta)
+
+    def prefill_ep(self, layer: MoeLayer, normed: torch.Tensor, residual: torch.Tensor,
+                   output: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """lumen_moe_prefill_ep: one expert-parallel layer call on this rank's tokens (collective)."""
+        act = {torch.float32: ACT_F32, torch.bfloat16: ACT_BF16}[normed.dtype]
+        _need(normed, normed.dtype, "normed")
+        _need(residual, torch.float32, "residual")
+        T = normed.numel() // self.H
+        if output is None:
+            output = torch.empty_like(residual)
+        check(_lib.lib().lumen_moe_prefill_ep(self._h, layer._h, normed.data_ptr(), residual.data_ptr(),
+                                              output.data_ptr(), T, act, _stream()))
+        return output
+
+    def stack_prefill_ep(self, layers: Sequence[MoeLayer], gammas: Sequence[torch.Tensor], x: torch.Tensor,
+                         eps: float, normed: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _need(x, torch.float32, "x")
+        if normed is None:
+            normed = torch.empty_like(x)
+        n = len(layers)
+        lh = (ctypes.c_void_p * n)(*[l._h for l in layers])
+        gp = (ctypes.c_void_p * n)(*[g.data_ptr() for g in gammas])
+        check(_lib.lib().lumen_moe_stack_prefill_ep(self._h, lh, gp, n, x.data_ptr(), normed.data_ptr(), eps,
+                                                    x.numel() // self.H, _stream()))
+        return x
+
     def get_routing_ids_stride_e(self, tokens: int) -> np.ndarray:
         """ids of the last routing call as the reference's batched buffer lays them out: [T, E], first K valid."""
         ids = np.zeros((tokens, self.E), np.uint32)

@@ -106,3 +106,62 @@ def test_dispatch_plan_groups_by_rank_in_compact_column_order():
     assert (ids.reshape(-1)[order]).tolist() == [0, 1, 1, 1, 3, 3, 3, 5]
     assert order.tolist() == [5, 1, 2, 6, 0, 4, 7, 3]     # stable: tokens ascending inside an expert
     assert local.tolist() == [0, 1, 1, 1, 0, 0, 0, 2]
+
+
+def _push_worker(rank, world, port, tokens_per_rank, q):
+    """The push form's layout logic on CPU ranks: every rank routes its own tokens, the ranks
+    exchange only their per-expert counts, and from the count matrix each derives where its
+    rows land in the owners' windows (ep.push_layout restates ep_dispatch_kernel). The 'stores'
+    are emulated by gathering (owner, row, tag) triples."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from lumen_b200 import ep
+        from oracle import oracle
+        epr = E // world
+        T = tokens_per_rank[rank]
+        rng = np.random.default_rng(7 + rank)
+        ids = np.stack([rng.choice(E, K, replace=False) for _ in range(T)]).astype(np.uint32) if T else np.zeros((0, K), np.uint32)
+        col_expert, col_src_tok, dst_to_col, bounds = oracle.counting_sort(ids, E) if T else (
+            np.zeros(0, np.int32), np.zeros(0, np.int32), np.zeros(0, np.int32), np.zeros(E + 1, np.int32))
+        mine = np.diff(bounds).astype(np.int64)
+        allc = [None] * world
+        dist.all_gather_object(allc, mine.tolist())
+        base, rows = ep.push_layout(np.array(allc), epr)
+        pushes = []
+        for c in range(T * K):
+            e = int(col_expert[c])
+            pushes.append((e // epr, int(base[rank, e] + (c - bounds[e])), (rank, c, e, int(col_src_tok[c]))))
+        everything = [None] * world
+        dist.all_gather_object(everything, pushes)
+        q.put((rank, rows.tolist(), [p for src in everything for p in src if p[0] == rank]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("tokens_per_rank", [(6, 11), (5, 0)])
+def test_push_layout_two_ranks_gloo(tokens_per_rank):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_push_worker, args=(r, world, port, tokens_per_rank, q), daemon=True) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    epr = E // world
+    total = 0
+    for rank, rows, landed in results:
+        landed.sort(key=lambda p: p[1])
+        # every row of the window is written exactly once, none beyond what the rank is sent
+        assert [p[1] for p in landed] == list(range(rows[rank]))
+        # grouped by expert, then by source rank, then in the source's own compact-column order:
+        # the stable order of cuda/moe.rs:2115-2147 applied to all ranks' tokens together
+        keys = [(tag[2], tag[0], tag[1]) for _, _, tag in landed]
+        assert keys == sorted(keys)
+        assert all(rank * epr <= tag[2] < (rank + 1) * epr for _, _, tag in landed)
+        total += len(landed)
+    assert total == sum(tokens_per_rank) * K

@@ -12,10 +12,24 @@ run as independent replicas ("weak" scaling, no collective in the data path).
     python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens T] [--quant q4_0|q8_0|bf16]
     python bench.py --impl reference ...   # the CPU reference path on the host cores
 
+The same JSON line carries sub-records for the other configurations of the metric, measured
+after the headline in the same run (skip them with --no-sub):
+    N = 1:  "decode"  Q4_0 at 4 and 16 tokens, Q8_0 at 1 token (us per call, fraction of the HBM peak)
+            "prefill" one 4096-token call, Zipf(1.1) expert loads, Q4_0 / Q8_0 / BF16 experts
+                      (ms, tokens/s, TFLOP/s against the measured bf16 peaks, realised expert loads)
+            "stack"   the 48-layer stack (RMSNorm + residual, identity mixers): batch-1 decode and an
+                      8192-token prefill
+    N > 1:  "ep_prefill"    expert-parallel prefill (lumen_moe_prefill_ep) at 16384 and 256 tokens in
+                            total, uniform and Zipf(1.1) routing: ms per call, the same call on ONE
+                            GPU timed on rank 0 in the same process, speed-up, per-phase ms, and every
+                            rank's rows against the one-GPU output (rel-L2, ids compared exactly)
+            "stack_prefill" the 48-layer stack at 8192 tokens the same way
+each with the CPU reference path timed on a stated token subset (all host threads and one).
+
 Secondary workloads (their own JSON line, not the headline):
     --workload prefill --tokens T [--routing zipf|uniform|router]     one prefill call, tensor roofline
-    --workload ep_prefill --tokens T [--ep-chunks C]   (torchrun)     expert-parallel prefill, strong scaling
-    --workload stack_prefill --tokens T --layers L     (torchrun)     the stack of L layers as one prefill
+    --workload ep_prefill --tokens T [--ep-chunks C]   (torchrun)     NCCL all-to-all form of expert parallelism
+    --workload stack_prefill --tokens T --layers L     (torchrun)     the stack of L layers, NCCL form
 """
 from __future__ import annotations
 
@@ -101,9 +115,11 @@ class ClockSampler:
                 "reasons": reasons}
 
 
-def cpu_reference_leg(quant: int, T: int, budget_s: float, blob_np=None):
-    """Times the CPU reference path (oracle restatement, all host threads) on a
-    bounded sample of the same workload: single layer calls on one layer blob."""
+def cpu_reference_leg(quant: int, T: int, budget_s: float, blob_np=None, threads=None, max_calls: int = 2000):
+    """Times the CPU reference path (oracle restatement) on a bounded sample of the same
+    workload: single layer calls of T tokens on one layer blob (340 MB for Q4_0). Every call
+    takes different tokens (64 seeded batches in rotation), so successive calls hit different
+    experts and the weights come from DRAM, not from the host's last-level cache."""
     import numpy as np
     from oracle import oracle
     from lumen_b200.synth import LayerLayout, make_layer_blob_numpy
@@ -112,19 +128,28 @@ def cpu_reference_leg(quant: int, T: int, budget_s: float, blob_np=None):
         # 128 experts of seeded N(0,0.02) weights quantised by the oracle's quantiser
         blob_np = make_layer_blob_numpy(lay, 0, oracle.quantize)
     meta = lay.meta()
-    threads = oracle.hardware_threads()
+    threads = threads or oracle.hardware_threads()
     rng = np.random.default_rng(1)
-    x = rng.standard_normal((T, H)).astype(np.float32)
+    xs = rng.standard_normal((64, T, H)).astype(np.float32)
     calls, t0 = 0, time.perf_counter()
     while True:
+        x = xs[calls % 64]
         oracle.moe_layer(blob_np, 0, meta.expert_gate_offs, meta.expert_up_offs, meta.expert_down_offs, quant, H, I, E,
                          K, x, x, threads=threads)
         calls += 1
         dt = time.perf_counter() - t0
-        if dt > budget_s or calls >= 2000:
+        if dt > budget_s or calls >= max_calls:
             break
     return {"value": calls * T / dt, "unit": "layer_tokens/s", "cores": threads, "kind": "port",
-            "sample": f"{calls} single-layer calls of {T} token(s) on one layer blob, {dt:.1f} s"}
+            "sample": f"{calls} single-layer calls of {T} token(s) (different tokens every call) on one layer blob, {dt:.1f} s"}
+
+
+def cpu_pair(quant: int, T: int, blob_np, budget_s: float = 2.5):
+    """all-threads and single-thread CPU figures for a sub-record, on a bounded token subset."""
+    a = cpu_reference_leg(quant, T, budget_s, blob_np)
+    one = cpu_reference_leg(quant, min(T, 4), budget_s * 0.6, blob_np, threads=1)
+    a["single_thread"] = {"value": one["value"], "unit": one["unit"], "sample": one["sample"]}
+    return a
 
 
 def run_reference(args):
@@ -160,6 +185,324 @@ def workload_config(args):
             "parallelism": "replicas only (batch-1 decode does not shard)"}
 
 
+
+# ---------------------------------------------------------------------------------------------
+# sub-records: the other configurations of the metric, measured after the headline
+# ---------------------------------------------------------------------------------------------
+def tensor_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    d = json.loads(p.read_text()) if p.exists() else {}
+    return (float(d.get("bf16_tflops", 1590.0)), float(d.get("bf16_tflops_sustained", 1400.0)),
+            "measured (MEASURED_PEAKS.json)" if d else "fallback (no MEASURED_PEAKS.json)")
+
+
+def event_ms(torch, fn, n):
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    ev0.record()
+    for _ in range(n):
+        fn()
+    ev1.record()
+    torch.cuda.synchronize()
+    return ev0.elapsed_time(ev1) / n
+
+
+def sub_decode(torch, np, moe, synth, dev, quant_name, T, n_layers, layers=None, scratch=None, steps=10):
+    """One decode sub-record: T tokens per call, the calls rotating over n_layers distinct layer
+    blobs (working set larger than L2), launches replayed from a CUDA graph."""
+    quant = QUANTS[quant_name]
+    lay = synth.LayerLayout(H, I, E, quant)
+    own = layers is None
+    if own:
+        scratch = moe.allocate_moe_scratch(H, I, E, K, 16, device=dev.index)
+        layers, blob0 = [], None
+        for l in range(n_layers):
+            blob = synth.make_layer_blob(lay, l, device=dev)
+            layers.append(scratch.prepare_layer(blob, lay.meta()))
+    blob0 = layers[0].blob.cpu().numpy()
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    x = torch.randn((T, H), generator=g, device=dev)
+    outs = torch.empty((len(layers), T, H), device=dev)
+
+    def step():
+        for l, layer in enumerate(layers):
+            scratch.decode(layer, x, x, outs[l])
+    for _ in range(3):
+        step()
+    U = []
+    for l, layer in enumerate(layers):
+        scratch.decode(layer, x, x, outs[l])
+        U.append(len(np.unique(scratch.get_routing(T)["ids"])))
+    moe.launch_count(reset=True)
+    step()
+    launches = moe.launch_count(reset=True)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for _ in range(3):
+        graph.replay()
+    ms = event_ms(torch, graph.replay, steps) / len(layers)
+    peak, _ = peaks()
+    nbytes = sum(algorithmic_bytes(T, u, quant) for u in U) / len(U)
+    gbs = nbytes / (ms / 1e3) / 1e9
+    rec = {"workload": f"moe_ffn_decode_{quant_name}_T{T}", "us_per_call": ms * 1e3, "layer_tokens_per_s": T / (ms / 1e3),
+           "distinct_layer_blobs": len(layers), "launches_per_call": launches / len(layers),
+           "distinct_experts_per_call": sum(U) / len(U), "algorithmic_bytes_per_call": nbytes,
+           "achieved_gbs": gbs, "frac_of_measured_peak": gbs / peak, "frac_of_8tbs": gbs / 8000.0,
+           "cpu_baseline": cpu_pair(quant, T, blob0, 2.0)}
+    if own:
+        for layer in layers:
+            layer.close()
+        scratch.close()
+    return rec
+
+
+def sub_prefill(torch, np, moe, synth, dev, quant_name, T, routing="zipf", steps=10, n_layers=2):
+    """One prefill call of T tokens (bf16 activations), Zipf(1.1)-skewed expert loads through the
+    logits entry, rotating over n_layers layer blobs."""
+    quant = QUANTS[quant_name]
+    lay = synth.LayerLayout(H, I, E, quant)
+    sc = moe.allocate_moe_scratch(H, I, E, K, T, device=dev.index)
+    layers = [sc.prepare_layer(synth.make_layer_blob(lay, l, device=dev), lay.meta()) for l in range(n_layers)]
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    x = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16)
+    res = torch.zeros((T, H), device=dev)
+    out = torch.empty_like(res)
+    if routing != "router":
+        sc.set_logits_override(synth.zipf_logits(T, E, 2, device=dev) if routing == "zipf" else
+                               synth.uniform_logits(T, E, 2, device=dev))
+
+    def step():
+        for layer in layers:
+            sc.prefill(layer, x, res, out)
+    for _ in range(3):
+        step()
+    r = sc.get_routing(T)  # raises if a device-side wait expired
+    loads = np.diff(r["expert_bounds"])
+    moe.launch_count(reset=True)
+    step()
+    launches = moe.launch_count(reset=True) / n_layers
+    ms = event_ms(torch, step, steps) / n_layers
+    flops = T * (2 * E * H + K * 6 * I * H)
+    burst, sustained, src = tensor_peaks()
+    tf = flops / (ms / 1e3) / 1e12
+    blob0 = layers[0].blob.cpu().numpy()
+    cpu = cpu_pair(quant, 64, blob0, 3.0)
+    cpu["sample"] = "token subset: " + cpu["sample"]
+    cpu["extrapolated_ms_for_this_call"] = 1e3 * T / cpu["value"]
+    rec = {"workload": f"moe_ffn_prefill_{quant_name}_T{T}_{routing}", "ms_per_call": ms, "tokens_per_s": T / (ms / 1e3),
+           "tflops": tf, "flops_per_call": flops, "frac_of_burst_peak": tf / burst, "frac_of_sustained_peak": tf / sustained,
+           "peak_source": src, "launches_per_call": launches,
+           "expert_load": {"max": int(loads.max()), "median": float(np.median(loads)), "min": int(loads.min())},
+           "activations": "bf16", "operands": "f16 x f16 -> f32 (tcgen05, accumulators in TMEM)", "cpu_baseline": cpu}
+    for layer in layers:
+        layer.close()
+    sc.close()
+    return rec
+
+
+def sub_stack(torch, np, moe, synth, dev, layers, scratch, steps=3):
+    """The 48-layer stack (RMSNorm eps 1e-6 + residual, identity mixers) on one GPU: batch-1
+    decode (one token through the stack per step) and an 8192-token prefill."""
+    L = len(layers)
+    gammas = [torch.ones(H, device=dev) for _ in range(L)]
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    x0 = torch.randn((1, H), generator=g, device=dev)
+    xw = x0.clone()
+
+    def dstep():
+        xw.copy_(x0)
+        scratch.stack_decode(layers, gammas, xw, 1e-6)
+    for _ in range(3):
+        dstep()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        dstep()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        dstep()
+    for _ in range(3):
+        graph.replay()
+    ms_d = event_ms(torch, graph.replay, 20)
+    peak, _ = peaks()
+    nbytes = L * (algorithmic_bytes(1, K, 1) + H * 4)
+    rec = {"decode": {"workload": f"moe_stack_decode_q4_0_L{L}_T1", "ms_per_token": ms_d, "tokens_per_s": 1e3 / ms_d,
+                      "algorithmic_bytes_per_token": nbytes, "achieved_gbs": nbytes / (ms_d / 1e3) / 1e9,
+                      "frac_of_measured_peak": nbytes / (ms_d / 1e3) / 1e9 / peak}}
+    T = 8192
+    sc = moe.allocate_moe_scratch(H, I, E, K, T, device=dev.index)
+    xp = torch.randn((T, H), generator=g, device=dev)
+    normed = torch.empty_like(xp)
+    work = xp.clone()
+
+    def pstep():
+        work.copy_(xp)
+        sc.stack_prefill(layers, gammas, work, 1e-6, normed)
+    pstep()
+    ms_p = event_ms(torch, pstep, steps)
+    flops = L * T * (2 * E * H + K * 6 * I * H)
+    burst, sustained, _ = tensor_peaks()
+    tf = flops / (ms_p / 1e3) / 1e12
+    rec["prefill"] = {"workload": f"moe_stack_prefill_q4_0_L{L}_T{T}_router", "ms_per_pass": ms_p, "ms_per_layer": ms_p / L,
+                      "tokens_per_s": T / (ms_p / 1e3), "tflops": tf, "frac_of_sustained_peak": tf / sustained,
+                      "frac_of_burst_peak": tf / burst}
+    sc.close()
+    return rec
+
+
+def sub_ep(torch, np, dist, moe, synth, ep, dev, rank, world, layers, args):
+    """Expert-parallel sub-records (N > 1): lumen_moe_prefill_ep against the same call on one
+    GPU (timed on rank 0 in this process), with every rank's output rows compared with the
+    one-GPU output. Strong scaling: the total work is fixed, tokens and experts are sharded."""
+    lay = synth.LayerLayout(H, I, E, 1)
+    meta = lay.meta()
+    Tmax = 16384
+    pe = ep.PushExpertParallel(H, I, E, K, Tmax // world, rank, world, dev.index)
+    ep_layers = [pe.prepare_layer(l.blob, meta) for l in layers]   # identical blobs on every rank
+    sc1 = moe.allocate_moe_scratch(H, I, E, K, Tmax, device=dev.index) if rank == 0 else None
+
+    def maxr(v):
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed_all(fn, n):
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(n):
+            fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        return maxr(ev0.elapsed_time(ev1) / n)
+
+    records = []
+    for T, steps in ((16384, 10), (256, 20)):
+        Tl = T // world
+        sl = slice(rank * Tl, (rank + 1) * Tl)
+        g = torch.Generator(device=dev)
+        g.manual_seed(1)
+        x_all = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16)   # same on every rank
+        res_all = torch.zeros((T, H), device=dev)
+        x, res = x_all[sl].contiguous(), res_all[sl].contiguous()
+        out = torch.empty_like(res)
+        for routing in ("uniform", "zipf"):
+            lg_all = (synth.zipf_logits(T, E, 2, device=dev) if routing == "zipf" else
+                      synth.uniform_logits(T, E, 2, device=dev))
+            pe.sc.set_logits_override(lg_all[sl].contiguous())
+            fwd = lambda: pe.forward(ep_layers[0], x, res, out)
+            for _ in range(3):
+                fwd()
+            ms = timed_all(fwd, steps)
+            pe.sc.ep_profile(True)
+            fwd()
+            ph = pe.sc.ep_phase_ms()
+            pe.sc.ep_profile(False)
+            ph_t = torch.tensor([ph[k] for k in moe.MoeScratch.EP_PHASES], device=dev, dtype=torch.float64)
+            ph_max = ph_t.clone()
+            dist.all_reduce(ph_max, op=dist.ReduceOp.MAX)
+            mine = pe.sc.get_routing(Tl)   # raises if this rank's context recorded a failure
+            # the same call on one GPU, on rank 0, in this process
+            ref = torch.empty((T, H), device=dev)
+            ids_ref = torch.empty((T, K), device=dev, dtype=torch.int32)
+            ms1 = 0.0
+            if rank == 0:
+                sc1.set_logits_override(lg_all)
+                one = lambda: sc1.prefill(layers[0], x_all, res_all, ref)
+                for _ in range(3):
+                    one()
+                ms1 = event_ms(torch, one, steps)
+                ids_ref.copy_(torch.from_numpy(sc1.get_routing(T)["ids"].astype(np.int32)))
+            dist.barrier()
+            dist.broadcast(ref, 0)
+            dist.broadcast(ids_ref, 0)
+            ms1 = maxr(ms1)
+            mine_ref = ref[sl]
+            rel = float((out.double() - mine_ref.double()).norm() / mine_ref.double().norm().clamp_min(1e-30))
+            ids_ok = bool((torch.from_numpy(mine["ids"].astype(np.int32)).to(dev) == ids_ref[sl]).all())
+            bit = bool(torch.equal(out, mine_ref))
+            rel_max = maxr(rel)
+            flags = torch.tensor([1.0 if ids_ok else 0.0, 1.0 if bit else 0.0], device=dev, dtype=torch.float64)
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+            loads = np.diff(sc1.get_routing(T)["expert_bounds"]) if rank == 0 else None
+            if rank == 0:
+                records.append({
+                    "workload": f"moe_ffn_ep_prefill_q4_0_T{T}_{routing}", "tokens_total": T, "tokens_per_gpu": Tl,
+                    "experts_per_gpu": E // world, "ms_per_call": ms, "tokens_per_s": T / (ms / 1e3),
+                    "ms_per_call_1gpu": ms1, "speedup_vs_1gpu": ms1 / ms,
+                    "rel_l2_vs_1gpu_max_over_ranks": rel_max, "ids_exact": bool(flags[0].item() > 0.5),
+                    "bit_identical_to_1gpu": bool(flags[1].item() > 0.5),
+                    "phase_ms_rank0": {k: round(ph[k], 4) for k in moe.MoeScratch.EP_PHASES},
+                    "phase_ms_max_over_ranks": {k: round(float(v), 4) for k, v in zip(moe.MoeScratch.EP_PHASES, ph_max.tolist())},
+                    "expert_load": {"max": int(loads.max()), "median": float(np.median(loads))},
+                    "transport": "plain peer stores into CUDA-IPC windows over NVLink, release/acquire flags; "
+                                 "no collective, no host synchronisation in the call",
+                    "wire": "f16 rows (the rounding the one-GPU GEMM applies to its operand), f16 results"})
+    # the 48-layer stack at 8192 tokens
+    T, L = 8192, len(layers)
+    Tl = T // world
+    sl = slice(rank * Tl, (rank + 1) * Tl)
+    pe.sc.set_logits_override(None)
+    gammas = [torch.ones(H, device=dev) for _ in range(L)]
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    x0 = torch.randn((T, H), generator=g, device=dev)
+    mine0 = x0[sl].contiguous()
+    work = mine0.clone()
+    normed = torch.empty_like(work)
+
+    def sfwd():
+        work.copy_(mine0)
+        pe.stack_forward(ep_layers, gammas, work, 1e-6, normed)
+    sfwd()
+    ms = timed_all(sfwd, 3)
+    ref = torch.empty((T, H), device=dev)
+    ms1 = 0.0
+    if rank == 0:
+        sc1.set_logits_override(None)
+        n1 = torch.empty_like(x0)
+
+        def one():
+            ref.copy_(x0)
+            sc1.stack_prefill(layers, gammas, ref, 1e-6, n1)
+        one()
+        ms1 = event_ms(torch, one, 2)
+    dist.barrier()
+    dist.broadcast(ref, 0)
+    ms1 = maxr(ms1)
+    d = (ref[sl] - mine0).double()
+    rel = maxr(float((work.double() - ref[sl].double()).norm() / d.norm().clamp_min(1e-30)))
+    bit = torch.tensor([1.0 if torch.equal(work, ref[sl]) else 0.0], device=dev, dtype=torch.float64)
+    dist.all_reduce(bit, op=dist.ReduceOp.MIN)
+    stack = None
+    if rank == 0:
+        flops = L * T * (2 * E * H + K * 6 * I * H)
+        _, sustained, _ = tensor_peaks()
+        tf = flops / (ms / 1e3) / 1e12
+        stack = {"workload": f"moe_stack_prefill_q4_0_L{L}_T{T}_router", "ms_per_pass": ms, "ms_per_layer": ms / L,
+                 "tokens_per_s": T / (ms / 1e3), "ms_per_pass_1gpu": ms1, "speedup_vs_1gpu": ms1 / ms,
+                 "rel_l2_vs_1gpu_max_over_ranks": rel, "bit_identical_to_1gpu": bool(bit.item() > 0.5),
+                 "tflops": tf, "frac_of_sustained_peak_all_gpus": tf / (sustained * world)}
+    pe.sc.get_routing(Tl)
+    pe.close()
+    if sc1 is not None:
+        sc1.close()
+    return records, stack
+
+
 def run_gpu(args):
     import numpy as np
     import torch
@@ -178,7 +521,7 @@ def run_gpu(args):
     scratch = moe.allocate_moe_scratch(H, I, E, K, 16, device=local)
     layers, blob0 = [], None
     for l in range(L):
-        blob = synth.make_layer_blob(lay, 1000 * rank + l, device=f"cuda:{local}")
+        blob = synth.make_layer_blob(lay, l, device=f"cuda:{local}")  # the same blobs on every replica
         layers.append(scratch.prepare_layer(blob, lay.meta()))
         if l == 0 and rank == 0:
             blob0 = blob.cpu().numpy()
@@ -319,6 +662,8 @@ def run_gpu(args):
                          "down_combine_kernel": phase_ms[2] * 1e3}
         traffic = NCU_DRAM_BYTES_PER_LAUNCH.get((k_name, args.quant, T))
         cpu = cpu_reference_leg(quant, T, 12.0, blob0)
+        one = cpu_reference_leg(quant, T, 3.0, blob0, threads=1)
+        cpu["single_thread"] = {"value": one["value"], "unit": one["unit"], "sample": one["sample"]}
         line = {"metric": "moe_layer_decode_tokens_per_s", "value": value, "unit": "layer_tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms / args.steps,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DECODE_DTYPE[args.quant],
@@ -334,6 +679,25 @@ def run_gpu(args):
                                    "achieved_gbs": layer_gbs, "frac_of_measured_peak": layer_gbs / peak,
                                    "frac_of_8tbs": layer_gbs / 8000.0},
                 "cpu_baseline": cpu, "clocks": clocks}
+    # ---- sub-records (after the headline; nothing below changes the numbers above) ----
+    dev = torch.device("cuda", local)
+    subs = {}
+    if not args.no_sub and quant == 1 and T == 1:
+        try:
+            if world == 1:
+                subs["decode"] = [sub_decode(torch, np, moe, synth, dev, "q4_0", 4, L, layers, scratch),
+                                  sub_decode(torch, np, moe, synth, dev, "q4_0", 16, L, layers, scratch),
+                                  sub_decode(torch, np, moe, synth, dev, "q8_0", 1, 8)]
+                subs["prefill"] = [sub_prefill(torch, np, moe, synth, dev, q, 4096) for q in ("q4_0", "q8_0", "bf16")]
+                subs["stack"] = sub_stack(torch, np, moe, synth, dev, layers, scratch)
+            else:
+                from lumen_b200 import ep
+                recs, stack = sub_ep(torch, np, dist, moe, synth, ep, dev, rank, world, layers, args)
+                subs["ep_prefill"], subs["stack_prefill"] = recs, stack
+        except Exception as exc:  # a failing sub-record must not cost the headline
+            subs["error"] = repr(exc)
+    if rank == 0:
+        line.update(subs)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -547,6 +911,7 @@ def main():
     ap.add_argument("--ep-chunks", type=int, default=1,
                     help="expert-parallel workloads: parts whose dispatch / expert products / combine overlap (1 = off)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-sub", action="store_true", help="headline only: skip the sub-records of the other configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

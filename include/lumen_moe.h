@@ -334,6 +334,14 @@ LUMEN_MOE_API lumen_moe_status_t lumen_moe_stack_prefill_ep(lumen_moe_ctx* ctx, 
                                                             float* d_x, float* d_normed, float eps, int32_t tokens,
                                                             void* stream);
 
+/* Timing aid: with profiling on, lumen_moe_prefill_ep records CUDA events between its launches;
+ * lumen_moe_ep_phase_ms waits for the last profiled call and returns its six phases in ms:
+ * route + sort | counts + dispatch (includes waiting for every rank's counts) | waiting for
+ * every rank's rows + tile plan | gate/up + SwiGLU + down | waiting for every rank's results |
+ * combine. */
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_ep_profile(lumen_moe_ctx* ctx, int32_t enable);
+LUMEN_MOE_API lumen_moe_status_t lumen_moe_ep_phase_ms(lumen_moe_ctx* ctx, float* out_ms6);
+
 /* ---- LBC container: header and layer index (host only, no device work) ----------------
  * The reference's backend uploads a MoE layer's blob byte for byte
  * (cuda/gpu_buffers.rs:1404-1409) and derives the operator's offsets from the layer's

@@ -91,6 +91,8 @@ SIGNATURES = {
     "lumen_moe_ep_layer_prepare": [vp, vp, sz, u64, vp, vp, vp, i32, vp, ctypes.POINTER(vp)],
     "lumen_moe_prefill_ep": [vp, vp, vp, vp, vp, i32, i32, vp],
     "lumen_moe_stack_prefill_ep": [vp, vp, vp, i32, vp, vp, f32, i32, vp],
+    "lumen_moe_ep_profile": [vp, i32],
+    "lumen_moe_ep_phase_ms": [vp, vp],
     "lumen_lbc_read_header": [vp, sz, ctypes.POINTER(LbcHeader)],
     "lumen_lbc_read_moe_layer": [vp, sz, ctypes.c_uint32, ctypes.POINTER(LbcMoeLayer), vp, vp, vp, ctypes.c_uint32],
     "lumen_lbc_quant_to_moe": [ctypes.c_uint32],

@@ -522,6 +522,17 @@ lumen_moe_status_t lumen_moe_prefill_ep(lumen_moe_ctx* ctx, const lumen_moe_laye
                                                  d_out, tokens, static_cast<cudaStream_t>(stream)));
 }
 
+lumen_moe_status_t lumen_moe_ep_profile(lumen_moe_ctx* ctx, int32_t enable) {
+    if (!ctx || !ctx->ep) return fail(LUMEN_MOE_INVALID_ARG, "no expert-parallel window on this context");
+    lumen::ep_set_profile(ctx->ep, enable != 0);
+    return LUMEN_MOE_OK;
+}
+
+lumen_moe_status_t lumen_moe_ep_phase_ms(lumen_moe_ctx* ctx, float* out_ms6) {
+    if (!ctx || !ctx->ep || !out_ms6) return fail(LUMEN_MOE_INVALID_ARG, "bad argument");
+    return done(lumen::ep_phase_ms(ctx->ep, out_ms6));
+}
+
 lumen_moe_status_t lumen_moe_stack_prefill_ep(lumen_moe_ctx* ctx, const lumen_moe_layer* const* layers,
                                               const float* const* d_gammas, int32_t n_layers, float* d_x,
                                               float* d_normed, float eps, int32_t tokens, void* stream) {

@@ -321,6 +321,10 @@ struct EpState {
     RouteDev RX{};        // expert_bounds / uexp / n_uexp of MY experts (the other fields unused)
     unsigned int* done_counter = nullptr;
     uint32_t epoch = 0;
+    // optional phase timing of a call (lumen_moe_ep_profile): events between the launches
+    bool profile = false;
+    cudaEvent_t ev[7] = {};
+    bool ev_made = false, ev_valid = false;
 };
 
 #define CUDA_TRY(expr)                                                                              \
@@ -336,6 +340,8 @@ void ep_free(EpState* s) {
         if (s->opened[r] && s->peers.win[r]) cudaIpcCloseMemHandle(s->peers.win[r]);
     if (s->win) cudaFree(s->win);
     if (s->local) cudaFree(s->local);
+    if (s->ev_made)
+        for (cudaEvent_t e : s->ev) cudaEventDestroy(e);
     delete s;
 }
 
@@ -435,6 +441,14 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
 
     const unsigned long long limit_ns = sc->wait_limit_us ? (unsigned long long)sc->wait_limit_us * 1000ull : 2000000000ull;
     const uint32_t epoch = ++s->epoch;
+    if (s->profile && !s->ev_made) {
+        for (cudaEvent_t& e : s->ev) CUDA_TRY(cudaEventCreate(&e));
+        s->ev_made = true;
+    }
+    auto mark = [&](int i) {
+        if (s->profile) cudaEventRecord(s->ev[i], st);
+    };
+    mark(0);
     // 1. route my tokens over ALL experts and sort the pairs (no tile lists: the GEMMs run on received rows)
     PrefillArgs p{};
     p.L = layer.dev;
@@ -453,6 +467,7 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     p.status = sc->status;
     p.status_host = sc->status_host;
     CUDA_TRY(launch_route_large(p, st));
+    mark(1);
     const int C = batch * sc->K;
     // 2. counts to everyone
     count_launch(2);
@@ -481,6 +496,7 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     const int dgrid = C < sc->sms * 8 ? C : sc->sms * 8;
     if (act_dtype == 0) ep::ep_dispatch_kernel<float><<<dgrid, 256, 0, st>>>(d);
     else ep::ep_dispatch_kernel<__nv_bfloat16><<<dgrid, 256, 0, st>>>(d);
+    mark(2);
     // 4. what arrived for my experts
     count_launch(1);
     ep::ep_plan_kernel<<<1, 256, 0, st>>>(s->win, s->wl, sc->E, s->epr, s->world, s->rank, s->rows_cap, epoch, limit_ns,
@@ -488,6 +504,7 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     // expected rows per expert under balanced routing decide the gate/up tile width
     const int gu_cols = ((long long)C > 128ll * s->epr) ? 256 : 128;
     CUDA_TRY(launch_tile_plan(s->RX, s->epr, sc->H, sc->I, s->rows_cap, gu_cols, s->tiles, s->n_tiles, st));
+    mark(3);
     // 5. grouped products on my experts; outputs go back to the pairs' home ranks
     PrefillArgs q{};
     q.L = layer.dev;
@@ -510,13 +527,32 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     int grid = sc->sms;
     if (sc->tc_ctas > 0 && sc->tc_ctas < grid) grid = sc->tc_ctas;
     CUDA_TRY(launch_grouped_tc(q, s->win + s->wl.x16, grid, st, nullptr, &plan, &po));
+    mark(4);
     // 6. results are out; wait for everyone's; combine
     count_launch(2);
     ep::ep_signal_kernel<<<1, 32, 0, st>>>(s->peers, s->wl, s->world, s->rank, epoch);
     ep::ep_wait_kernel<<<1, 32, 0, st>>>(s->win, s->wl, s->world, epoch, limit_ns, sc->status, sc->status_host);
     CUDA_TRY(cudaGetLastError());
+    mark(5);
     CUDA_TRY(launch_scatter_accum(reinterpret_cast<const __half*>(s->win + s->wl.back), residual, sc->R, output, batch,
                                   sc->H, sc->K, st));
+    mark(6);
+    s->ev_valid = s->profile;
+    return Status::Ok();
+}
+
+void ep_set_profile(EpState* s, bool on) {
+    s->profile = on;
+    if (!on) s->ev_valid = false;
+}
+
+// ms of the last profiled call: route+sort | counts+dispatch (includes waiting for every rank's
+// counts) | wait for every rank's rows + tile plan | gate/up+SwiGLU+down | wait for every rank's
+// results | combine
+Status ep_phase_ms(EpState* s, float* out6) {
+    if (!s->ev_valid) return Status::Err(1, "no profiled call yet (lumen_moe_ep_profile)");
+    CUDA_TRY(cudaEventSynchronize(s->ev[6]));
+    for (int i = 0; i < 6; ++i) CUDA_TRY(cudaEventElapsedTime(&out6[i], s->ev[i], s->ev[i + 1]));
     return Status::Ok();
 }
 

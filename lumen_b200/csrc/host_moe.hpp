@@ -170,6 +170,8 @@ int ep_rank(const EpState* ep);
 int ep_world(const EpState* ep);
 int ep_experts_per_rank(const EpState* ep);
 size_t ep_window_bytes(const EpState* ep);
+void ep_set_profile(EpState* ep, bool on);
+Status ep_phase_ms(EpState* ep, float* out6);
 Status encode_moe_ffn_prefill_ep(CudaMoeScratch* scratch, EpState* ep, const MoeLayer& layer, const void* normed,
                                  int act_dtype, const float* residual, float* output, int batch, cudaStream_t st);
 

@@ -342,6 +342,16 @@ class MoeScratch:
                                               output.data_ptr(), T, act, _stream()))
         return output
 
+    EP_PHASES = ("route", "counts+dispatch", "wait_rows+plan", "experts", "wait_results", "combine")
+
+    def ep_profile(self, on: bool) -> None:
+        check(_lib.lib().lumen_moe_ep_profile(self._h, 1 if on else 0))
+
+    def ep_phase_ms(self) -> dict:
+        out = (ctypes.c_float * 6)()
+        check(_lib.lib().lumen_moe_ep_phase_ms(self._h, out))
+        return dict(zip(self.EP_PHASES, [float(v) for v in out]))
+
     def stack_prefill_ep(self, layers: Sequence[MoeLayer], gammas: Sequence[torch.Tensor], x: torch.Tensor,
                          eps: float, normed: Optional[torch.Tensor] = None) -> torch.Tensor:
         _need(x, torch.float32, "x")

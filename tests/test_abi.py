@@ -54,20 +54,21 @@ def test_build_moe_meta_returns_none_for_dense_layers():
     assert build_moe_meta(0, []) is None
 
 
-def test_integration_binding_matches_the_header():
-    """Every function of the Rust extern block shown in INTEGRATION.md is declared in the
-    header with the same number of parameters."""
+def test_rust_binding_matches_the_header():
+    """rust/lumen_moe_sys.rs (the extern block a lumen-runtime maintainer adds; it cannot be
+    compiled in this image) declares exactly the functions of the header, each with the same
+    number of parameters."""
     header = (ROOT / "include" / "lumen_moe.h").read_text()
-    doc = (ROOT / "INTEGRATION.md").read_text()
-    block = doc[doc.index('extern "C" {'):]
-    block = block[:block.index("```")]
-    rust = re.findall(r"pub fn (lumen_\w+)\s*\(([^)]*)\)", block, flags=re.S)
-    assert len(rust) >= 10
-    for name, params in rust:
-        m = re.search(r"\b" + name + r"\s*\(([^;]*?)\)\s*;", header, flags=re.S)
-        assert m, name
-        c_params = [p for p in m.group(1).split(",") if p.strip() and p.strip() != "void"]
-        r_params = [p for p in params.split(",") if p.strip()]
+    src = (ROOT / "rust" / "lumen_moe_sys.rs").read_text()
+    block = src[src.index('extern "C" {'):]
+    block = re.sub(r"/\*.*?\*/", "", block[:block.index("\n}\n")], flags=re.S)
+    block = re.sub(r"//[^\n]*", "", block)
+    rust = dict(re.findall(r"pub fn (lumen_\w+)\s*\(([^)]*)\)", block, flags=re.S))
+    c_decls = dict(re.findall(r"LUMEN_MOE_API\s+[\w\s\*]+?\b(lumen_\w+)\s*\(([^;]*?)\)\s*;", header, flags=re.S))
+    assert set(rust) == set(c_decls), set(rust) ^ set(c_decls)
+    for name, params in rust.items():
+        c_params = [q for q in c_decls[name].split(",") if q.strip() and q.strip() != "void"]
+        r_params = [q for q in params.split(",") if q.strip()]
         assert len(c_params) == len(r_params), (name, len(c_params), len(r_params))
 
 

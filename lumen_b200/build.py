@@ -17,7 +17,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 BUILD = PKG / "_build"
 LIB = PKG / "liblumen_moe_b200.so"
-SOURCES = ["decode.cu", "decode_small.cu", "decode_fused.cu", "static_scratch.cu", "misc.cu", "route_large.cu", "prefill_tc.cu", "ep_push.cu", "host_moe.cu", "lbc_index.cu", "api.cu"]
+SOURCES = ["decode.cu", "decode_small.cu", "decode_fused.cu", "static_scratch.cu", "misc.cu", "route_large.cu", "route_tc.cu", "prefill_tc.cu", "ep_push.cu", "host_moe.cu", "lbc_index.cu", "api.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",

@@ -105,6 +105,9 @@ lumen_moe_status_t lumen_moe_layer_prepare(lumen_moe_ctx* ctx, const void* d_lay
         {
             lumen::Status rs = lumen::aligned_router(d_layer_blob, router_off, sc.E, sc.H, st, &r->layer.repacked,
                                                      &r->layer.dev.router_w);
+            if (rs.ok())
+                rs = lumen::build_router_w16(r->layer.dev.router_w, sc.E, sc.H, st, &r->layer.repacked,
+                                             &r->layer.dev.router_w16);
             if (rs.ok() && cudaStreamSynchronize(st) != cudaSuccess) rs = lumen::Status::Err(LUMEN_MOE_CUDA_ERROR, "copy of the router weight failed");
             if (!rs.ok()) {
                 lumen::free_moe_layer(&r->layer);
@@ -165,7 +168,8 @@ void lumen_moe_layer_destroy(lumen_moe_layer* layer) {
 size_t lumen_moe_layer_bytes(const lumen_moe_layer* layer) {
     if (!layer) return 0;
     const size_t router_copy = layer->layer.repacked.router_copy ? (size_t)layer->layer.dev.E * layer->layer.dev.H * sizeof(float) : 0;
-    return layer->layer.repacked.q_bytes + layer->layer.repacked.s_bytes + router_copy +
+    const size_t router_w16 = layer->layer.repacked.router_w16 ? (size_t)2 * layer->layer.dev.E * layer->layer.dev.H * 2 : 0;
+    return layer->layer.repacked.q_bytes + layer->layer.repacked.s_bytes + router_copy + router_w16 +
            5 * sizeof(uint64_t) * layer->layer.dev.E;
 }
 
@@ -492,12 +496,16 @@ lumen_moe_status_t lumen_moe_ep_layer_prepare(lumen_moe_ctx* ctx, const void* d_
     if (s.ok())
         s = lumen::build_repacked(sc, d_layer_blob, blob_bytes, m, l->layer.offsets, sc.H, sc.I, epr, st,
                                   &l->layer.repacked, &l->layer.dev);
-    if (s.ok() && l->layer.repacked.router_copy) {
-        // the aligned copy made there covers this rank's experts only: the router needs all E rows
+    if (s.ok()) {
+        // what build_repacked made of the router covers this rank's experts only: the router needs all E rows
         cudaStreamSynchronize(st);
-        cudaFree(l->layer.repacked.router_copy);
+        if (l->layer.repacked.router_copy) cudaFree(l->layer.repacked.router_copy);
+        if (l->layer.repacked.router_w16) cudaFree(l->layer.repacked.router_w16);
         l->layer.repacked.router_copy = nullptr;
+        l->layer.repacked.router_w16 = nullptr;
         s = lumen::aligned_router(d_layer_blob, router_off, sc.E, sc.H, st, &l->layer.repacked, &l->layer.dev.router_w);
+        if (s.ok())
+            s = lumen::build_router_w16(l->layer.dev.router_w, sc.E, sc.H, st, &l->layer.repacked, &l->layer.dev.router_w16);
     }
     if (s.ok()) {
         cudaError_t e = cudaStreamSynchronize(st);

@@ -462,6 +462,11 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     p.logits_override = sc->logits_override;
     p.blk_hist = sc->blk_hist;
     p.w16 = sc->w16;
+    p.xr16 = sc->xr16;
+    p.rpart = sc->rpart;
+    p.any_lo = sc->any_lo;
+    p.sms = sc->sms;
+    p.wait_limit_us = sc->wait_limit_us;
     p.tiles = nullptr;
     p.n_tiles = sc->n_tiles;
     p.status = sc->status;

@@ -105,6 +105,7 @@ Status build_repacked(const CudaMoeScratch& sc, const void* layer_buf, size_t bl
     L.blob = static_cast<const uint8_t*>(layer_buf);
     {
         Status rs = aligned_router(layer_buf, meta.router_weight_off, E, H, st, out, &L.router_w);
+        if (rs.ok()) rs = build_router_w16(L.router_w, E, H, st, out, &L.router_w16);
         if (!rs.ok()) return rs;
     }
     L.quant = quant;
@@ -134,21 +135,23 @@ Status build_repacked(const CudaMoeScratch& sc, const void* layer_buf, size_t bl
 }
 
 static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
-    // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf, w16, xq
+    // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf, w16, xq, xr16, rpart
     const size_t C = (size_t)cap * s.K;
     const size_t nblk_h_pad = (size_t)((s.H / 32 + 3) / 4) * 4, nblk_i_pad = (size_t)((s.I / 32 + 3) / 4) * 4;
     const size_t max_ct = C / 128 + s.E, max_ct_dn = C / 128 + s.E;  // gate/up tiles of 128 or 256 columns (sized for 128), down tiles of 128
     const size_t n_tile_entries = max_ct * ((size_t)s.I / 128 + 1) + max_ct_dn * ((size_t)s.H / 256 + 1);
-    size_t sizes[15] = {
+    size_t sizes[17] = {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,
         (size_t)((cap + 31) / 32) * s.E * 4,
         n_tile_entries * sizeof(int4),
         C * s.I * 2, C * s.H * 2, C * s.H * 2,
         (size_t)cap * 2 * nblk_h_pad * 64, C * 2 * nblk_i_pad * 64,
         (size_t)s.E * s.H * 4,
-        (size_t)DECODE_MAX_TOKENS * (18 * nblk_h_pad + 16) * 4};  // xq_tok_words(nblk_h_pad) words per token
+        (size_t)DECODE_MAX_TOKENS * (18 * nblk_h_pad + 16) * 4,  // xq_tok_words(nblk_h_pad) words per token
+        (size_t)cap * s.H * 2 * 2,
+        (size_t)ROUTER_TC_MAX_KSPLIT * cap * s.E * 4};
     size_t off = 0;
-    for (int i = 0; i < 15; ++i) {
+    for (int i = 0; i < 17; ++i) {
         offs[i] = off;
         off += align_up(sizes[i], 256);
     }
@@ -156,7 +159,7 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
 }
 
 static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
-    size_t offs[15];
+    size_t offs[17];
     const size_t bytes = tok_arena_bytes(*s, cap, offs);
     void* p = nullptr;
     CUDA_TRY(cudaMalloc(&p, bytes));
@@ -182,6 +185,8 @@ static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
     s->sf = reinterpret_cast<uint4*>(b + offs[12]);
     s->w16 = reinterpret_cast<__half*>(b + offs[13]);
     s->xq = reinterpret_cast<unsigned*>(b + offs[14]);
+    s->xr16 = reinterpret_cast<__half*>(b + offs[15]);
+    s->rpart = reinterpret_cast<float*>(b + offs[16]);
     return Status::Ok();
 }
 
@@ -213,6 +218,7 @@ Status allocate_moe_scratch(int device, int H, int I, int E, int K, int gating, 
     s.R.ticket = reinterpret_cast<unsigned int*>(b + 256);
     s.n_tiles = reinterpret_cast<int32_t*>(b + 512);
     s.status = reinterpret_cast<int32_t*>(b + 768);
+    s.any_lo = reinterpret_cast<int32_t*>(b + 772);
     s.R.work = reinterpret_cast<int4*>(b + 1024);
     s.bar = reinterpret_cast<unsigned int*>(b + 1024 + (size_t)MAX_EXPERTS * 2 * sizeof(int4));  // 1024 per-CTA flags
     s.flags = flags;
@@ -285,8 +291,19 @@ Status aligned_router(const void* layer_buf, uint64_t router_off, int E, int H, 
     return Status::Ok();
 }
 
+// f16 high / low planes of the router weight, once per layer (the batched router multiplies on tcgen05)
+Status build_router_w16(const float* router_w, int E, int H, cudaStream_t st, CudaMoeRepacked* out, const __half** w16) {
+    *w16 = nullptr;
+    if (H % 64 != 0) return Status::Ok();  // the tcgen05 router does not take this shape
+    CUDA_TRY(cudaMalloc(&out->router_w16, (size_t)2 * E * H * sizeof(__half)));
+    CUDA_TRY(launch_split_router_w16(router_w, out->router_w16, E, H, st));
+    *w16 = out->router_w16;
+    return Status::Ok();
+}
+
 void free_moe_layer(MoeLayer* l) {
     if (l->repacked.router_copy) cudaFree(l->repacked.router_copy);
+    if (l->repacked.router_w16) cudaFree(l->repacked.router_w16);
     if (l->offsets.gate_up_offsets) cudaFree(l->offsets.gate_up_offsets);
     if (l->repacked.q) cudaFree(l->repacked.q);
     if (l->repacked.s) cudaFree(l->repacked.s);
@@ -414,7 +431,12 @@ Status encode_route_only(CudaMoeScratch* s, const MoeLayer* layer, const float* 
         p.gating = s->gating;
         p.logits_override = logits_in;
         p.blk_hist = s->blk_hist;
-    p.w16 = s->w16;
+        p.w16 = s->w16;
+        p.xr16 = s->xr16;
+        p.rpart = s->rpart;
+        p.any_lo = s->any_lo;
+        p.sms = s->sms;
+        p.wait_limit_us = s->wait_limit_us;
         p.tiles = nullptr;
         p.n_tiles = s->n_tiles;
         CUDA_TRY(launch_route_large(p, st));
@@ -458,6 +480,10 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     p.gating = s->gating;
     p.blk_hist = s->blk_hist;
     p.w16 = s->w16;
+    p.xr16 = s->xr16;
+    p.rpart = s->rpart;
+    p.any_lo = s->any_lo;
+    p.sms = s->sms;
     p.s16 = s->s16;
     p.d16 = s->d16;
     p.tiles = s->tiles;

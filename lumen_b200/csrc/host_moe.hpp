@@ -79,12 +79,14 @@ struct CudaMoeRepacked {
     // 16-byte-aligned copy of the router weight, made only when the blob holds it at an
     // address the vector loads cannot take (a file's layer blob aligns tensors to 4 bytes)
     float* router_copy = nullptr;
+    __half* router_w16 = nullptr;  // f16 high / low planes of the router weight for the batched tcgen05 router
 };
 
 // Router weight pointer for the kernels: in place when 16-byte aligned in device memory,
 // else a copy owned by `out` (enqueued on `st`).
 Status aligned_router(const void* layer_buf, uint64_t router_off, int E, int H, cudaStream_t st,
                       CudaMoeRepacked* out, const float** router_w);
+Status build_router_w16(const float* router_w, int E, int H, cudaStream_t st, CudaMoeRepacked* out, const __half** w16);
 
 // CudaMoeScratch + CudaMoePrefillGrouped, cuda/moe.rs:101-210.
 struct CudaMoeScratch {
@@ -102,6 +104,9 @@ struct CudaMoeScratch {
     __half* s16 = nullptr;
     __half* d16 = nullptr;
     __half* x16 = nullptr;  // permuted 16-bit activations for the tcgen05 path
+    __half* xr16 = nullptr; // f16 high / low planes of the batch for the tcgen05 router
+    float* rpart = nullptr; // partial logits of the tcgen05 router
+    int32_t* any_lo = nullptr;
     int4* tiles = nullptr;
     int32_t* n_tiles = nullptr;
     unsigned int* tile_counter = nullptr;

@@ -41,6 +41,7 @@ constexpr int DECODE_MAX_TOKENS = 16;
 struct LayerDev {
     const uint8_t* blob;
     const float* router_w;  // blob + router_off, [E,H] f32
+    const __half* router_w16;  // [2][E][H] f16 high / low parts of router_w (batched router on tcgen05), or null
     const uint4* q;         // all experts' quant planes
     const uint4* s;         // all experts' scale planes (unused for BF16)
     int quant, H, I, E;
@@ -139,7 +140,11 @@ struct PrefillArgs {
     int T, K, gating;
     // scratch
     int32_t* blk_hist;      // [nchunks, E]
-    __half* w16;            // [2, E, H] router weight split into f16 high and low planes (per call)
+    __half* w16;            // [2, E, H] router weight split into f16 high and low planes (per call, when the layer has none)
+    __half* xr16;           // [2, T, H] activations split into f16 high and low planes (tcgen05 router)
+    float* rpart;           // [ksplit, T, E] partial logits of the tcgen05 router
+    int32_t* any_lo;        // [1] some low part of the activations is non-zero
+    int sms;                // multiprocessors of the device
     __half* s16;            // [C, I] f16 SwiGLU output, row-major by compact column
     __half* d16;            // [C, H] f16 down output by compact column
     int4* tiles;            // tile list for the grouped GEMMs
@@ -155,6 +160,14 @@ struct PrefillArgs {
     const float* weights_in; // [T,K] or null (= 1)
 };
 cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st);
+// tcgen05 router (route_tc.cu)
+cudaError_t launch_split_router_w16(const float* w, __half* w16, int E, int H, cudaStream_t st);
+int router_tc_ksplit(int T, int E, int H, int sms);
+bool router_tc_applicable(int T, int E, int H, const void* x);
+cudaError_t launch_router_logits_tc(const void* x, int act_dtype, const __half* w16, int T, int E, int H, int ksplit,
+                                    __half* x16, int32_t* any_lo, float* part, int32_t* status, int32_t* status_host,
+                                    unsigned wait_limit_us, cudaStream_t st);
+constexpr int ROUTER_TC_MAX_KSPLIT = 4;
 
 // Expert-parallel form of the grouped products: the rows of the activation operand are not this
 // rank's T*K compact columns but whatever the peers pushed into its receive window, and the down

@@ -26,7 +26,7 @@
 // (permute_x16_kernel); the SwiGLU output is written in the same order so the
 // down product reads it back without any shuffle.
 #include "mma_frag.cuh"
-#include <cuda.h>
+#include "tc_common.cuh"
 #include <cstdlib>
 
 namespace lumen {
@@ -36,83 +36,6 @@ namespace tc {
 constexpr int EPI_WARPS = 8, A_WARPS = 8, B_WARPS = 1;  // B: one thread drives the TMA
 constexpr int A_WARP0 = EPI_WARPS, B_WARP0 = A_WARP0 + A_WARPS, MMA_WARP = B_WARP0 + B_WARPS;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
-constexpr int SUB_BYTES = 128 * 128;  // [128 rows x 64 k] f16, 128-byte rows, SWIZZLE_128B
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-// Bounded wait. Returns false when another role aborted or the limit expired
-// (in which case it raises the abort flag itself).
-struct AbortCtl {
-    volatile uint32_t* flag;  // CTA-wide abort flag in shared memory
-    uint64_t limit_ns;
-};
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortCtl& ac) {
-    if (mbar_try(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
-    for (uint32_t i = 0;; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if ((i & 63u) == 63u) {
-            if (*ac.flag) return false;
-            if (globaltimer_ns() - t0 > ac.limit_ns) {
-                *ac.flag = 1u;
-                return false;
-            }
-        }
-    }
-}
-
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-    // K-major, SWIZZLE_128B: 8-row groups 1024 B apart (SBO), LBO unused (1), descriptor version 1
-    return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
-}
-__device__ __forceinline__ uint32_t make_idesc(int n, bool bf16) {
-    const uint32_t fmt = bf16 ? 1u : 0u;
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     uint32_t r;
@@ -509,8 +432,7 @@ cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_
     return cudaGetLastError();
 }
 
-// [rows, cols] f16 row-major -> tensor map with a 64 x 128 box and the 128-byte swizzle
-static cudaError_t make_tmap(const void* base, uint64_t rows, uint64_t cols, CUtensorMap* out) {
+cudaError_t make_tmap_f16(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
     typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -525,7 +447,7 @@ static cudaError_t make_tmap(const void* base, uint64_t rows, uint64_t cols, CUt
     }
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t box[2] = {64, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -556,7 +478,7 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     const int max_ct = C / gu_cols + p.L.E;
     const int mt_gu = p.L.I / 128;
     tc::Args gu{};
-    cudaError_t te = make_tmap(x16, (uint64_t)C, (uint64_t)p.L.H, &gu.tmap);
+    cudaError_t te = make_tmap_f16(x16, (uint64_t)C, (uint64_t)p.L.H, 128, &gu.tmap);
     if (te != cudaSuccess) return te;
     gu.L = p.L;
     gu.col_src_tok = p.R.col_src_tok;
@@ -571,7 +493,7 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     gu.kdim = p.L.H;
     gu.out_ld = p.L.I;
     tc::Args dn = gu;
-    te = make_tmap(p.s16, (uint64_t)C, (uint64_t)p.L.I, &dn.tmap);
+    te = make_tmap_f16(p.s16, (uint64_t)C, (uint64_t)p.L.I, 128, &dn.tmap);
     if (te != cudaSuccess) return te;
     dn.col_src_tok = nullptr;
     dn.debug_extra_tx = 0;  // the hook applies to the first kernel of the pair

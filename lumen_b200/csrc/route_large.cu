@@ -250,16 +250,23 @@ router_logits_mma_kernel(const XT* __restrict__ x, const __half* __restrict__ w1
     }
 }
 
+// nparts > 0: the logits arrive as `nparts` partial sums [nparts][T][E] (k ranges of the tcgen05
+// router); they are added in a fixed order and the sum is left in logits_out.
 constexpr int TK_WARPS = 4;
 __global__ void __launch_bounds__(TK_WARPS * 32)
-topk_large_kernel(const float* __restrict__ logits, int T, int E, int K, int gating,
-                  uint32_t* __restrict__ ids, float* __restrict__ weights) {
+topk_large_kernel(const float* __restrict__ logits, int nparts, float* __restrict__ logits_out, int T, int E, int K,
+                  int gating, uint32_t* __restrict__ ids, float* __restrict__ weights) {
     __shared__ __align__(16) float p_s[TK_WARPS][MAX_EXPERTS];
     __shared__ __align__(16) float lg_s[TK_WARPS][MAX_EXPERTS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * TK_WARPS + warp;
     if (t >= T) return;
-    for (int i = lane; i < E; i += 32) lg_s[warp][i] = logits[(size_t)t * E + i];
+    for (int i = lane; i < E; i += 32) {
+        float v = logits[(size_t)t * E + i];
+        for (int q = 1; q < nparts; ++q) v += logits[((size_t)q * T + t) * E + i];
+        if (nparts > 0) logits_out[(size_t)t * E + i] = v;
+        lg_s[warp][i] = v;
+    }
     __syncwarp();
     warp_topk(lg_s[warp], E, K, gating, p_s[warp], nullptr, ids + (size_t)t * K, weights + (size_t)t * K);
 }
@@ -552,10 +559,19 @@ __global__ void set_routing_kernel(const uint32_t* __restrict__ ids_in, const fl
 cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const int T = a.T, E = a.L.E, H = a.L.H, K = a.K;
     const float* lg = a.logits_override;
+    int nparts = 0;
     if (a.ids_in != nullptr) {
         count_launch();
         set_routing_kernel<<<(T * K + 255) / 256, 256, 0, st>>>(a.ids_in, a.weights_in, T * K, E, a.R.ids, a.R.weights,
                                                                 a.status, a.status_host);
+    } else if (lg == nullptr && a.L.router_w16 != nullptr && a.xr16 != nullptr && a.rpart != nullptr &&
+               router_tc_applicable(T, E, H, a.x)) {
+        // tcgen05 router: partial logits per k range, summed by the top-k kernel
+        nparts = router_tc_ksplit(T, E, H, a.sms > 0 ? a.sms : 148);
+        cudaError_t e = launch_router_logits_tc(a.x, a.act_dtype, a.L.router_w16, T, E, H, nparts, a.xr16, a.any_lo,
+                                                a.rpart, a.status, a.status_host, a.wait_limit_us, st);
+        if (e != cudaSuccess) return e;
+        lg = a.rpart;
     } else if (lg == nullptr) {
         count_launch();
         if (H % 32 == 0 && a.w16 != nullptr && reinterpret_cast<uintptr_t>(a.x) % 16 == 0) {
@@ -589,8 +605,8 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     }
     count_launch(5);
     if (a.ids_in == nullptr)
-        topk_large_kernel<<<(T + TK_WARPS - 1) / TK_WARPS, TK_WARPS * 32, 0, st>>>(lg, T, E, K, a.gating, a.R.ids,
-                                                                                   a.R.weights);
+        topk_large_kernel<<<(T + TK_WARPS - 1) / TK_WARPS, TK_WARPS * 32, 0, st>>>(lg, nparts, a.R.logits, T, E, K,
+                                                                                   a.gating, a.R.ids, a.R.weights);
     const int nchunks = (T + SORT_TOK - 1) / SORT_TOK;
     sort_hist_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist);
     const int C = T * K;

@@ -208,12 +208,17 @@ cudaError_t launch_split_router_w16(const float* w, __half* w16, int E, int H, c
     return cudaGetLastError();
 }
 
-// ksplit for a batch: enough CTAs to cover the machine, k ranges of whole 64-input stages, at most 4
+// k ranges per tile: a function of the shape only, never of the batch size, so that a token's
+// logits (the order in which its partial sums are added) do not depend on how many tokens it is
+// routed with: an expert-parallel rank routing its shard must get the bits one GPU gets for the
+// whole batch. Four ranges of whole 64-input stages when H allows (a few thousand tokens then
+// fill the machine), else two, else one.
 int router_tc_ksplit(int T, int E, int H, int sms) {
-    const int tiles = ((T + rtc::BN - 1) / rtc::BN) * ((E + 127) / 128);
-    int ks = 1;
-    while (ks < 4 && tiles * ks < sms && (H / 64) % (ks * 2) == 0) ks *= 2;
-    return ks;
+    (void)T;
+    (void)E;
+    (void)sms;
+    const int stages = H / 64;
+    return (stages % 4 == 0) ? 4 : (stages % 2 == 0) ? 2 : 1;
 }
 
 bool router_tc_applicable(int T, int E, int H, const void* x) {

@@ -151,6 +151,21 @@ def test_router_logits_at_the_headline_shape(cuda_lib, T, act):
                 assert np.array_equal(r["ids"][t], o_ids[0])
 
 
+def test_batched_router_logits_do_not_depend_on_the_batch(cuda_lib):
+    """A token's logits must be the same bits whether it is routed alone in a shard or inside the
+    whole batch (an expert-parallel rank routes its shard and must pick what one GPU picks)."""
+    H, I, E, K = 1024, 128, 64, 4
+    lay = synth.LayerLayout(H, I, E, 1)
+    blob = synth.make_layer_blob(lay, 5)
+    sc = moe.allocate_moe_scratch(H, I, E, K, 3000)
+    layer = sc.prepare_router_only(blob, lay.meta().router_weight_off)
+    x = torch.randn((3000, H), generator=torch.Generator("cuda").manual_seed(2), device="cuda")
+    ids_all, w_all, lg_all = sc.route_only(layer, x, want_logits=True)
+    for lo, hi in ((0, 17), (1000, 1777), (2900, 3000)):
+        ids, w, lg = sc.route_only(layer, x[lo:hi].contiguous(), want_logits=True)
+        assert torch.equal(lg, lg_all[lo:hi]) and torch.equal(ids, ids_all[lo:hi]) and torch.equal(w, w_all[lo:hi])
+
+
 def test_quantizers_bit_exact(cuda_lib):
     g = torch.Generator("cuda").manual_seed(9)
     w = torch.randn(32 * 4096, generator=g, device="cuda") * 0.02

@@ -263,12 +263,12 @@ def sub_decode(torch, np, moe, synth, dev, quant_name, T, n_layers, layers=None,
     return rec
 
 
-def sub_prefill(torch, np, moe, synth, dev, quant_name, T, routing="zipf", steps=10, n_layers=2):
+def sub_prefill(torch, np, moe, synth, dev, quant_name, T, routing="zipf", steps=10, n_layers=2, flags=0):
     """One prefill call of T tokens (bf16 activations), Zipf(1.1)-skewed expert loads through the
     logits entry, rotating over n_layers layer blobs."""
     quant = QUANTS[quant_name]
     lay = synth.LayerLayout(H, I, E, quant)
-    sc = moe.allocate_moe_scratch(H, I, E, K, T, device=dev.index)
+    sc = moe.allocate_moe_scratch(H, I, E, K, T, device=dev.index, flags=flags)
     layers = [sc.prepare_layer(synth.make_layer_blob(lay, l, device=dev), lay.meta()) for l in range(n_layers)]
     g = torch.Generator(device=dev)
     g.manual_seed(1)
@@ -297,7 +297,11 @@ def sub_prefill(torch, np, moe, synth, dev, quant_name, T, routing="zipf", steps
     cpu = cpu_pair(quant, 64, blob0, 3.0)
     cpu["sample"] = "token subset: " + cpu["sample"]
     cpu["extrapolated_ms_for_this_call"] = 1e3 * T / cpu["value"]
-    rec = {"workload": f"moe_ffn_prefill_{quant_name}_T{T}_{routing}", "ms_per_call": ms, "tokens_per_s": T / (ms / 1e3),
+    weights_form = ("plain f16 matrices fed by TMA" if (quant == 2 or flags & 0x8) else
+                    "quantised planes dequantised in shared memory")
+    rec = {"workload": f"moe_ffn_prefill_{quant_name}_T{T}_{routing}" + ("_f16weights" if flags & 0x8 else ""),
+           "weight_operand": weights_form, "layer_device_bytes": layers[0].device_bytes,
+           "ms_per_call": ms, "tokens_per_s": T / (ms / 1e3),
            "tflops": tf, "flops_per_call": flops, "frac_of_burst_peak": tf / burst, "frac_of_sustained_peak": tf / sustained,
            "peak_source": src, "launches_per_call": launches,
            "expert_load": {"max": int(loads.max()), "median": float(np.median(loads)), "min": int(loads.min())},
@@ -695,6 +699,8 @@ def run_gpu(args):
                 subs["prefill"] = [sub_prefill(torch, np, moe, synth, dev, q, 4096) for q in ("q4_0", "q8_0", "bf16")]
                 # the same call with the layer's own router instead of supplied logits (router products included)
                 subs["prefill"].append(sub_prefill(torch, np, moe, synth, dev, "q4_0", 4096, routing="router"))
+                # memory traded for speed: the Q4_0 layer also kept as f16 matrices (LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS)
+                subs["prefill"].append(sub_prefill(torch, np, moe, synth, dev, "q4_0", 4096, flags=0x8))
                 subs["stack"] = sub_stack(torch, np, moe, synth, dev, layers, scratch)
             else:
                 from lumen_b200 import ep

@@ -80,10 +80,16 @@ typedef struct {
  *   cooperative kernel (for a process that cannot give the kernel every SM of the device).
  * PREFILL_MMA: grouped products on mma.sync instead of tcgen05 (values outside f16 range).
  * SHORT_WAITS: device-side bounded waits give up after 2 ms instead of 1-2 s (tests).
+ * PREFILL_F16_WEIGHTS: layers prepared on this context also keep their Q4_0 / Q8_0 expert weights
+ *   as plain f16 matrices (2 more bytes per weight per layer: 1.2 GB at H=2048, I=768, E=128),
+ *   and prefill feeds the tensor cores from them with TMA instead of dequantising in shared
+ *   memory: memory traded for prefill speed. BF16 layers always work that way (nothing to
+ *   dequantise). Decode is not affected.
  * TC_CTAS(n): cap of the persistent tcgen05 grid, n CTAs (one per SM), 0 = every SM. */
 #define LUMEN_MOE_FLAG_DECODE_SPLIT 0x1
 #define LUMEN_MOE_FLAG_PREFILL_MMA 0x2
 #define LUMEN_MOE_FLAG_SHORT_WAITS 0x4
+#define LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS 0x8
 #define LUMEN_MOE_FLAG_TC_CTAS(n) (((n) & 0xff) << 8)
 
 typedef struct lumen_moe_ctx lumen_moe_ctx;     /* ~ CudaMoeScratch, cuda/moe.rs:101-170 */

@@ -13,7 +13,7 @@ Q8_0, Q4_0, BF16 = 0, 1, 2
 SOFTMAX_RENORM, SIGMOID_RENORM, SIGMOID_GATE, UNIT_WEIGHT = 0, 1, 2, 3
 ACT_F32, ACT_BF16, ACT_F16 = 0, 1, 2
 # lumen_moe_config.flags
-FLAG_DECODE_SPLIT, FLAG_PREFILL_MMA, FLAG_SHORT_WAITS = 0x1, 0x2, 0x4
+FLAG_DECODE_SPLIT, FLAG_PREFILL_MMA, FLAG_SHORT_WAITS, FLAG_PREFILL_F16_WEIGHTS = 0x1, 0x2, 0x4, 0x8
 
 
 def flag_tc_ctas(n: int) -> int:

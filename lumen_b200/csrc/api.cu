@@ -52,7 +52,7 @@ lumen_moe_status_t lumen_moe_create(const lumen_moe_config* cfg, lumen_moe_ctx**
         return fail(LUMEN_MOE_UNSUPPORTED, "this build contains sm_100a code only (Blackwell B200 required)");
     lumen_moe_ctx* ctx = new (std::nothrow) lumen_moe_ctx();
     if (!ctx) return fail(LUMEN_MOE_CUDA_ERROR, "out of host memory");
-    if (cfg->flags & ~(0x7 | 0xff00)) {
+    if (cfg->flags & ~(0xf | 0xff00)) {
         delete ctx;
         return fail(LUMEN_MOE_INVALID_ARG, "unknown bits in lumen_moe_config.flags");
     }
@@ -169,7 +169,8 @@ size_t lumen_moe_layer_bytes(const lumen_moe_layer* layer) {
     if (!layer) return 0;
     const size_t router_copy = layer->layer.repacked.router_copy ? (size_t)layer->layer.dev.E * layer->layer.dev.H * sizeof(float) : 0;
     const size_t router_w16 = layer->layer.repacked.router_w16 ? (size_t)2 * layer->layer.dev.E * layer->layer.dev.H * 2 : 0;
-    return layer->layer.repacked.q_bytes + layer->layer.repacked.s_bytes + router_copy + router_w16 +
+    const size_t f16w = layer->layer.repacked.gu16 ? (size_t)layer->layer.dev.E * 3 * layer->layer.dev.I * layer->layer.dev.H * 2 : 0;
+    return layer->layer.repacked.q_bytes + layer->layer.repacked.s_bytes + router_copy + router_w16 + f16w +
            5 * sizeof(uint64_t) * layer->layer.dev.E;
 }
 

@@ -156,6 +156,7 @@ struct DispatchArgs {
     Peers peers;
     WindowLayout wl;
     int C, H, E, epr, world, me, rows_cap;
+    int natural;                   // rows in the natural input order (TMA-fed weights) instead of the dequantiser's order
     uint32_t epoch;
     unsigned long long limit_ns;
     int32_t* status;
@@ -222,16 +223,24 @@ ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
             uint8_t* w = a.peers.win[owner];
             uint16_t* dst = reinterpret_cast<uint16_t*>(w + a.wl.x16) + (size_t)drow * a.H;
             const XT* src = x + (size_t)tok * a.H;
-            // chunk t of a 32-block holds inputs (4t, 4t+2, 16+4t, 16+4t+2, 4t+1, 4t+3, 16+4t+1, 16+4t+3)
+            // chunk t of a 32-block holds inputs (4t, 4t+2, 16+4t, 16+4t+2, 4t+1, 4t+3, 16+4t+1, 16+4t+3),
+            // or, for TMA-fed weights, chunk ch holds inputs 8 ch .. 8 ch + 7 as they are
             for (int ch = tid; ch < a.H / 8; ch += 256) {
                 const int blk = ch >> 2, t = ch & 3;
-                const Run p = *reinterpret_cast<const Run*>(src + blk * 32 + 4 * t);
-                const Run q = *reinterpret_cast<const Run*>(src + blk * 32 + 16 + 4 * t);
+                const Run p = *reinterpret_cast<const Run*>(src + (a.natural ? ch * 8 : blk * 32 + 4 * t));
+                const Run q = *reinterpret_cast<const Run*>(src + (a.natural ? ch * 8 + 4 : blk * 32 + 16 + 4 * t));
                 uint4 o;
-                o.x = (uint32_t)to_f16_bits<XT>(p.v[0]) | ((uint32_t)to_f16_bits<XT>(p.v[2]) << 16);
-                o.y = (uint32_t)to_f16_bits<XT>(q.v[0]) | ((uint32_t)to_f16_bits<XT>(q.v[2]) << 16);
-                o.z = (uint32_t)to_f16_bits<XT>(p.v[1]) | ((uint32_t)to_f16_bits<XT>(p.v[3]) << 16);
-                o.w = (uint32_t)to_f16_bits<XT>(q.v[1]) | ((uint32_t)to_f16_bits<XT>(q.v[3]) << 16);
+                if (a.natural) {
+                    o.x = (uint32_t)to_f16_bits<XT>(p.v[0]) | ((uint32_t)to_f16_bits<XT>(p.v[1]) << 16);
+                    o.y = (uint32_t)to_f16_bits<XT>(p.v[2]) | ((uint32_t)to_f16_bits<XT>(p.v[3]) << 16);
+                    o.z = (uint32_t)to_f16_bits<XT>(q.v[0]) | ((uint32_t)to_f16_bits<XT>(q.v[1]) << 16);
+                    o.w = (uint32_t)to_f16_bits<XT>(q.v[2]) | ((uint32_t)to_f16_bits<XT>(q.v[3]) << 16);
+                } else {
+                    o.x = (uint32_t)to_f16_bits<XT>(p.v[0]) | ((uint32_t)to_f16_bits<XT>(p.v[2]) << 16);
+                    o.y = (uint32_t)to_f16_bits<XT>(q.v[0]) | ((uint32_t)to_f16_bits<XT>(q.v[2]) << 16);
+                    o.z = (uint32_t)to_f16_bits<XT>(p.v[1]) | ((uint32_t)to_f16_bits<XT>(p.v[3]) << 16);
+                    o.w = (uint32_t)to_f16_bits<XT>(q.v[1]) | ((uint32_t)to_f16_bits<XT>(q.v[3]) << 16);
+                }
                 *reinterpret_cast<uint4*>(dst + blk * 32 + t * 8) = o;
             }
             if (tid == 0) reinterpret_cast<int32_t*>(w + a.wl.ret_map)[drow] = (a.me << 24) | c;
@@ -493,6 +502,7 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     d.world = s->world;
     d.me = s->rank;
     d.rows_cap = s->rows_cap;
+    d.natural = layer.dev.gu16 != nullptr ? 1 : 0;
     d.epoch = epoch;
     d.limit_ns = limit_ns;
     d.status = sc->status;

@@ -15,7 +15,7 @@ cudaError_t launch_scatter_accum(const __half* d16, const float* residual, const
 cudaError_t launch_build_xf(const void* x, int act_dtype, int T, int H, int nblk_pad, bool bf16_mode,
                             uint4* xf, cudaStream_t st);
 cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_t* col_src_tok, int C, int H, void* out,
-                                      cudaStream_t st);
+                                      cudaStream_t st, bool natural);
 cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, cudaStream_t st, __half* out16_rows,
                               const TcPlan* plan = nullptr, const TcPeerOut* peer = nullptr);
 cudaError_t launch_rows_from_cols(const __half* d16, const int32_t* dst_to_col, __half* out16, int T, int H, cudaStream_t st);
@@ -85,7 +85,6 @@ Status build_batched_offsets(const CudaMoeMeta& meta, cudaStream_t st, CudaMoeBa
 Status build_repacked(const CudaMoeScratch& sc, const void* layer_buf, size_t blob_bytes, const CudaMoeMeta& meta,
                       const CudaMoeBatchedOffsets& offs, int H, int I, int E, cudaStream_t st,
                       CudaMoeRepacked* out, LayerDev* dev) {
-    (void)sc;
     const int quant = meta.expert_gate_quant;
     // cuda/moe.rs:1185-1191: only (Q8_0,Q8_0), (Q4_0,Q4_0), (Bf16,Bf16)
     if (quant != meta.expert_down_quant || quant < 0 || quant > 2)
@@ -130,6 +129,19 @@ Status build_repacked(const CudaMoeScratch& sc, const void* layer_buf, size_t bl
     L.q = out->q;
     L.s = out->s;
     CUDA_TRY(launch_repack(L.blob, offs.gate_offsets, offs.up_offsets, offs.down_offsets, L, out->q, out->s, st));
+    // Plain f16 copies of the expert matrices: always for BF16 weights (there is nothing to
+    // dequantise: TMA feeds the tensor cores directly, as it does the activations), and for
+    // Q4_0 / Q8_0 when the context asks to trade memory for prefill speed
+    // (LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS: 2 bytes per weight more per layer).
+    if ((quant == BF16 || (sc.flags & 0x8)) && H % 256 == 0 && I % 128 == 0) {
+        const size_t n = (size_t)E * 3 * I * H;
+        CUDA_TRY(cudaMalloc(&out->gu16, (size_t)E * 2 * I * H * sizeof(__half)));
+        CUDA_TRY(cudaMalloc(&out->dn16, (size_t)E * H * I * sizeof(__half)));
+        (void)n;
+        CUDA_TRY(launch_dequant_f16(L.blob, offs.gate_offsets, offs.up_offsets, offs.down_offsets, L, out->gu16, out->dn16, st));
+        L.gu16 = out->gu16;
+        L.dn16 = out->dn16;
+    }
     *dev = L;
     return Status::Ok();
 }
@@ -304,6 +316,8 @@ Status build_router_w16(const float* router_w, int E, int H, cudaStream_t st, Cu
 void free_moe_layer(MoeLayer* l) {
     if (l->repacked.router_copy) cudaFree(l->repacked.router_copy);
     if (l->repacked.router_w16) cudaFree(l->repacked.router_w16);
+    if (l->repacked.gu16) cudaFree(l->repacked.gu16);
+    if (l->repacked.dn16) cudaFree(l->repacked.dn16);
     if (l->offsets.gate_up_offsets) cudaFree(l->offsets.gate_up_offsets);
     if (l->repacked.q) cudaFree(l->repacked.q);
     if (l->repacked.s) cudaFree(l->repacked.s);
@@ -498,7 +512,8 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     CUDA_TRY(launch_route_large(p, st));
     const bool bf16_mode = (layer.dev.quant == BF16);
     if (p.impl == 0) {
-        CUDA_TRY(launch_gather_permute_x16(normed, act_dtype, s->R.col_src_tok, batch * s->K, s->H, s->x16, st));
+        CUDA_TRY(launch_gather_permute_x16(normed, act_dtype, s->R.col_src_tok, batch * s->K, s->H, s->x16, st,
+                                           layer.dev.gu16 != nullptr));
         // persistent grid, one CTA per SM; LUMEN_MOE_FLAG_TC_CTAS leaves some SMs to kernels that run beside it
         int sms = s->sms;
         if (s->tc_ctas > 0 && s->tc_ctas < sms) sms = s->tc_ctas;

@@ -80,6 +80,8 @@ struct CudaMoeRepacked {
     // address the vector loads cannot take (a file's layer blob aligns tensors to 4 bytes)
     float* router_copy = nullptr;
     __half* router_w16 = nullptr;  // f16 high / low planes of the router weight for the batched tcgen05 router
+    __half* gu16 = nullptr;        // plain f16 expert matrices for the TMA-fed prefill products (see LayerDev)
+    __half* dn16 = nullptr;
 };
 
 // Router weight pointer for the kernels: in place when 16-byte aligned in device memory,

@@ -140,6 +140,67 @@ static cudaError_t repack_t(const uint8_t* blob, const uint64_t* d_gate, const u
     return cudaGetLastError();
 }
 
+// Expert weights as plain f16 matrices (scale folded in, one rounding: the value the grouped
+// GEMM's in-smem dequantiser produces), row-major, for the TMA-fed form of the prefill
+// products: gu16 [E][2 I rows: gate then up][H], dn16 [E][H rows][I]. One thread per 32-block.
+template <int Q>
+__global__ void dequant_rows_f16_kernel(const uint8_t* __restrict__ blob, const uint64_t* __restrict__ offs, int rows,
+                                        int nblk, size_t exp_rows, size_t row_off, __half* __restrict__ out) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)rows * nblk) return;
+    const int e = blockIdx.y;
+    const int r = (int)(idx / nblk), b = (int)(idx % nblk);
+    const uint8_t* mat = blob + offs[e];
+    __align__(16) __half v[32];
+    if (Q == BF16) {
+        const uint8_t* p = mat + ((size_t)r * nblk + b) * 64;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const uint32_t bits = ((uint32_t)p[2 * i] | ((uint32_t)p[2 * i + 1] << 8)) << 16;
+            v[i] = __float2half_rn(__uint_as_float(bits));
+        }
+    } else {
+        const int bb = (Q == Q4_0) ? 18 : 34;
+        const uint8_t* p = mat + ((size_t)r * nblk + b) * bb;
+        const float sc = __half2float(__ushort_as_half((unsigned short)((uint32_t)p[0] | ((uint32_t)p[1] << 8))));
+        if (Q == Q4_0) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                v[i] = __float2half_rn((float)((int)(p[2 + i] & 0xF) - 8) * sc);
+                v[16 + i] = __float2half_rn((float)((int)(p[2 + i] >> 4) - 8) * sc);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float2half_rn((float)(int)(int8_t)p[2 + i] * sc);
+        }
+    }
+    uint4* dst = reinterpret_cast<uint4*>(out + (((size_t)e * exp_rows + row_off + r) * nblk + b) * 32);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] = reinterpret_cast<const uint4*>(v)[i];
+}
+
+template <int Q>
+static cudaError_t dequant_f16_t(const uint8_t* blob, const uint64_t* d_gate, const uint64_t* d_up, const uint64_t* d_down,
+                                 const LayerDev& L, __half* gu16, __half* dn16, cudaStream_t st) {
+    const int nblk_h = L.H / 32, nblk_i = L.I / 32;
+    const dim3 g_gu((unsigned)(((size_t)L.I * nblk_h + 255) / 256), L.E), g_dn((unsigned)(((size_t)L.H * nblk_i + 255) / 256), L.E);
+    count_launch(3);
+    dequant_rows_f16_kernel<Q><<<g_gu, 256, 0, st>>>(blob, d_gate, L.I, nblk_h, (size_t)2 * L.I, 0, gu16);
+    dequant_rows_f16_kernel<Q><<<g_gu, 256, 0, st>>>(blob, d_up, L.I, nblk_h, (size_t)2 * L.I, (size_t)L.I, gu16);
+    dequant_rows_f16_kernel<Q><<<g_dn, 256, 0, st>>>(blob, d_down, L.H, nblk_i, (size_t)L.H, 0, dn16);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_dequant_f16(const uint8_t* blob, const uint64_t* d_gate_offs, const uint64_t* d_up_offs,
+                               const uint64_t* d_down_offs, const LayerDev& L, __half* gu16, __half* dn16,
+                               cudaStream_t st) {
+    switch (L.quant) {
+        case Q4_0: return dequant_f16_t<Q4_0>(blob, d_gate_offs, d_up_offs, d_down_offs, L, gu16, dn16, st);
+        case Q8_0: return dequant_f16_t<Q8_0>(blob, d_gate_offs, d_up_offs, d_down_offs, L, gu16, dn16, st);
+        default: return dequant_f16_t<BF16>(blob, d_gate_offs, d_up_offs, d_down_offs, L, gu16, dn16, st);
+    }
+}
+
 cudaError_t launch_repack(const uint8_t* blob, const uint64_t* d_gate_offs, const uint64_t* d_up_offs,
                           const uint64_t* d_down_offs, const LayerDev& L, uint4* q, uint4* s,
                           cudaStream_t st) {

@@ -44,6 +44,10 @@ struct LayerDev {
     const __half* router_w16;  // [2][E][H] f16 high / low parts of router_w (batched router on tcgen05), or null
     const uint4* q;         // all experts' quant planes
     const uint4* s;         // all experts' scale planes (unused for BF16)
+    // optional plain f16 matrices of all experts (scale folded in) for the TMA-fed prefill products:
+    // gu16 [E][2 I rows: gate then up][H], dn16 [E][H rows][I]; null = dequantise in shared memory
+    const __half* gu16;
+    const __half* dn16;
     int quant, H, I, E;
     int kg_h, kg_i;  // 128-input groups along H (gate/up) and I (down)
     int rt_i, rt_h;  // 16-row tiles of gate/up (I rows) and down (H rows)
@@ -116,6 +120,9 @@ __device__ __forceinline__ void raise_status(int32_t* status, int32_t* status_ho
 cudaError_t launch_repack(const uint8_t* blob, const uint64_t* d_gate_offs, const uint64_t* d_up_offs,
                           const uint64_t* d_down_offs, const LayerDev& L, uint4* q, uint4* s,
                           cudaStream_t st);
+cudaError_t launch_dequant_f16(const uint8_t* blob, const uint64_t* d_gate_offs, const uint64_t* d_up_offs,
+                               const uint64_t* d_down_offs, const LayerDev& L, __half* gu16, __half* dn16,
+                               cudaStream_t st);
 cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t st);
 cudaError_t launch_ep_prepare(const void* x, int act_dtype, const RouteDev& R, int C, int H, int E, int epr, void* rows,
                               int32_t* local_ids, long long* send_counts, cudaStream_t st);

@@ -59,6 +59,9 @@ __host__ __device__ __forceinline__ int perm_pos(int e) {
 
 struct Args {
     CUtensorMap tmap;            // activation operand [rows, kdim] f16, box 64 x 128, SWIZZLE_128B (first: 64-byte aligned)
+    CUtensorMap tmap_a;          // ATMA form: the experts' plain f16 matrices as one 2-D array [E * a_rows_exp, kdim]
+    int a_rows_exp;              // rows per expert there: 2 I (gate rows then up rows) or H (down)
+    int a_row1;                  // second operand's rows relative to the first: I (up) or 128 (next row tile of down)
     LayerDev L;
     const int32_t* col_src_tok;  // unused by the GEMM (rows are pre-gathered); kept for diagnostics
     const int4* tiles;
@@ -136,7 +139,10 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
     }
 }
 
-template <int Q, int MODE, int BN>
+// ATMA: the weight operands are not dequantised here but copied by TMA from plain f16 matrices
+// (BF16 layers; Q4_0 / Q8_0 layers of a context created with LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS): the
+// producer warps have nothing to do and every operand is in the natural input order.
+template <int Q, int MODE, int BN, bool ATMA = false>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     // Two 128-row weight operands share every activation stage (gate and up rows of the
@@ -168,7 +174,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     if (tid == 0) {
         abort_s = 0u;
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), A_WARPS * 32 + 1);  // weight producers + the TMA thread's expect_tx arrive
+            mbar_init(smem_u32(&full_bar[s]), ATMA ? 1 : A_WARPS * 32 + 1);  // weight producers + the TMA thread's expect_tx arrive
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         for (int b = 0; b < NACC; ++b) {
@@ -212,8 +218,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ab * NA * BN;
             size_t off0, off1 = 0;
             if (MODE == 0) {
-                const int irow = tile.w * 128 + row;  // SwiGLU output is stored in the permuted order
-                off0 = (size_t)(irow & ~31) + perm_pos(irow & 31);
+                const int irow = tile.w * 128 + row;  // SwiGLU output is stored in the order the down product reads it
+                off0 = ATMA ? (size_t)irow : (size_t)(irow & ~31) + perm_pos(irow & 31);
             } else {
                 off0 = (size_t)(tile.w * 256 + row);
                 off1 = off0 + 128;
@@ -238,7 +244,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                         }
                         if (MODE == 0) {
                             const float gt = __uint_as_float(v0[j]);
-                            dst[off0] = __float2half_rn((gt / (1.0f + __expf(-gt))) * __uint_as_float(v1[j]));
+                            // SwiGLU (cuda/shaders/moe_expert.cu:47-50) with the fast exp and divide: their
+                            // error (~2^-21) is far below the f16 rounding of the result that follows
+                            dst[off0] = __float2half_rn(__fdividef(gt, 1.0f + __expf(-gt)) * __uint_as_float(v1[j]));
                         } else {
                             dst[off0] = __float2half_rn(__uint_as_float(v0[j]));
                             dst[off1] = __float2half_rn(__uint_as_float(v1[j]));
@@ -252,7 +260,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     } else if (warp < B_WARP0) {
         // --------------------------- weight producers --------------------------
         const int rtl = warp - A_WARP0;  // 16-row tile within the 128-row M tile
-        const int my_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const int my_tiles = (!ATMA && ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const int ngroups = my_tiles * kgs;
         WTile<Q> cur[NA], nxt[NA];
         auto issue = [&](const int4& tile, int kg, WTile<Q>(&dst)[NA]) {
@@ -312,7 +320,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             const int my_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
             const int nitems = my_tiles * khs;
             const uint64_t tmap_addr = reinterpret_cast<uint64_t>(&a.tmap);
-            int row0 = 0, nbox = 1;
+            const uint64_t tmap_a_addr = reinterpret_cast<uint64_t>(&a.tmap_a);
+            int row0 = 0, nbox = 1, arow0 = 0;
             bool ok = true;
             for (int n = 0; ok && n < nitems; ++n) {
                 const int kh = n % khs;
@@ -320,6 +329,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                     const int4 tile = a.tiles[blockIdx.x + (n / khs) * gridDim.x];
                     row0 = tile.y;
                     nbox = (BN > 128 && tile.z > 128) ? 2 : 1;
+                    arow0 = tile.x * a.a_rows_exp + tile.w * (MODE == 0 ? 128 : 256);
                 }
                 const int s = n % STAGES, ph = (n / STAGES) & 1;
                 ok = mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
@@ -328,8 +338,17 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 const uint32_t bbase = stage0 + s * STAGE_BYTES + NA * SUB_BYTES;
                 // (test hook: with debug_extra_tx the very first stage can never complete)
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
-                             "r"(nbox * SUB_BYTES + (n == 0 ? a.debug_extra_tx : 0))
+                             "r"((nbox + (ATMA ? NA : 0)) * SUB_BYTES + (n == 0 ? a.debug_extra_tx : 0))
                              : "memory");
+                if (ATMA) {
+#pragma unroll
+                    for (int op = 0; op < NA; ++op)
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+                            "[%0], [%1, {%2, %3}], [%4];" ::"r"(stage0 + s * STAGE_BYTES + op * SUB_BYTES),
+                            "l"(tmap_a_addr), "r"(kh * 64), "r"(arow0 + op * a.a_row1), "r"(bar)
+                            : "memory");
+                }
                 for (int q = 0; q < nbox; ++q)
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
@@ -391,7 +410,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 // activations -> f16, gathered into compact-column order (row c = token
 // col_src_tok[c]) and permuted within each 32-block: the grouped GEMM then reads
 // plain 2-D boxes of it with TMA
-template <typename XT, bool IS_F16 = false>
+template <typename XT, bool IS_F16 = false, bool NATURAL = false>
 __global__ void __launch_bounds__(256)
 gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ col_src_tok, int H,
                           uint16_t* __restrict__ out) {
@@ -409,10 +428,17 @@ gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ 
     struct __align__(4 * sizeof(XT)) Run { XT v[4]; };
     for (int ch = threadIdx.x; ch < H / 8; ch += 256) {
         const int blk = ch >> 2, t = ch & 3;
-        const Run a = *reinterpret_cast<const Run*>(src + blk * 32 + 4 * t);
-        const Run b = *reinterpret_cast<const Run*>(src + blk * 32 + 16 + 4 * t);
-        __align__(16) uint16_t o[8] = {to_h(a.v[0]), to_h(a.v[2]), to_h(b.v[0]), to_h(b.v[2]),
-                                       to_h(a.v[1]), to_h(a.v[3]), to_h(b.v[1]), to_h(b.v[3])};
+        // NATURAL (TMA-fed weights): chunk ch holds inputs 8 ch .. 8 ch + 7 as they are
+        const Run a = *reinterpret_cast<const Run*>(src + (NATURAL ? ch * 8 : blk * 32 + 4 * t));
+        const Run b = *reinterpret_cast<const Run*>(src + (NATURAL ? ch * 8 + 4 : blk * 32 + 16 + 4 * t));
+        __align__(16) uint16_t o[8];
+        if (NATURAL) {
+            o[0] = to_h(a.v[0]); o[1] = to_h(a.v[1]); o[2] = to_h(a.v[2]); o[3] = to_h(a.v[3]);
+            o[4] = to_h(b.v[0]); o[5] = to_h(b.v[1]); o[6] = to_h(b.v[2]); o[7] = to_h(b.v[3]);
+        } else {
+            o[0] = to_h(a.v[0]); o[1] = to_h(a.v[2]); o[2] = to_h(b.v[0]); o[3] = to_h(b.v[2]);
+            o[4] = to_h(a.v[1]); o[5] = to_h(a.v[3]); o[6] = to_h(b.v[1]); o[7] = to_h(b.v[3]);
+        }
         *reinterpret_cast<uint4*>(dst + blk * 32 + t * 8) = *reinterpret_cast<const uint4*>(o);
     }
 }
@@ -420,15 +446,21 @@ gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ 
 }  // namespace tc
 
 cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_t* col_src_tok, int C, int H, void* out,
-                                      cudaStream_t st) {
+                                      cudaStream_t st, bool natural) {
     count_launch();
-    if (act_dtype == 0)
-        tc::gather_permute_x16_kernel<float><<<C, 256, 0, st>>>((const float*)x, col_src_tok, H, (uint16_t*)out);
-    else if (act_dtype == 2)
-        tc::gather_permute_x16_kernel<__half, true><<<C, 256, 0, st>>>((const __half*)x, col_src_tok, H, (uint16_t*)out);
-    else
-        tc::gather_permute_x16_kernel<__nv_bfloat16><<<C, 256, 0, st>>>((const __nv_bfloat16*)x, col_src_tok, H,
-                                                                        (uint16_t*)out);
+#define LUMEN_GATHER(XT, F16, NAT) \
+    tc::gather_permute_x16_kernel<XT, F16, NAT><<<C, 256, 0, st>>>((const XT*)x, col_src_tok, H, (uint16_t*)out)
+    if (act_dtype == 0) {
+        if (natural) LUMEN_GATHER(float, false, true);
+        else LUMEN_GATHER(float, false, false);
+    } else if (act_dtype == 2) {
+        if (natural) LUMEN_GATHER(__half, true, true);
+        else LUMEN_GATHER(__half, true, false);
+    } else {
+        if (natural) LUMEN_GATHER(__nv_bfloat16, false, true);
+        else LUMEN_GATHER(__nv_bfloat16, false, false);
+    }
+#undef LUMEN_GATHER
     return cudaGetLastError();
 }
 
@@ -455,18 +487,18 @@ cudaError_t make_tmap_f16(const void* base, uint64_t rows, uint64_t cols, uint32
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int Q, int MODE, int BN>
+template <int Q, int MODE, int BN, bool ATMA = false>
 static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
     constexpr int NA = 2;
     constexpr int STAGES = (BN == 128) ? 4 : 3;
     const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024;
     static SmemOptIn optin;
     {
-        cudaError_t e = ensure_dyn_smem(tc::grouped_gemm_tc_kernel<Q, MODE, BN>, (size_t)smem, optin);
+        cudaError_t e = ensure_dyn_smem(tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA>, (size_t)smem, optin);
         if (e != cudaSuccess) return e;
     }
     count_launch();
-    tc::grouped_gemm_tc_kernel<Q, MODE, BN><<<grid, tc::THREADS, smem, st>>>(a);
+    tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA><<<grid, tc::THREADS, smem, st>>>(a);
     return cudaGetLastError();
 }
 
@@ -506,6 +538,20 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     dn.kdim = p.L.I;
     dn.out_ld = p.L.H;
     cudaError_t e;
+    if (p.L.gu16 != nullptr) {
+        // TMA-fed weights: the experts' plain f16 matrices as two 2-D arrays
+        te = make_tmap_f16(p.L.gu16, (uint64_t)p.L.E * 2 * p.L.I, (uint64_t)p.L.H, 128, &gu.tmap_a);
+        if (te != cudaSuccess) return te;
+        gu.a_rows_exp = 2 * p.L.I;
+        gu.a_row1 = p.L.I;
+        te = make_tmap_f16(p.L.dn16, (uint64_t)p.L.E * p.L.H, (uint64_t)p.L.I, 128, &dn.tmap_a);
+        if (te != cudaSuccess) return te;
+        dn.a_rows_exp = p.L.H;
+        dn.a_row1 = 128;
+        e = (gu_cols == 256) ? launch_tc_one<BF16, 0, 256, true>(gu, grid, st) : launch_tc_one<BF16, 0, 128, true>(gu, grid, st);
+        if (e != cudaSuccess) return e;
+        return launch_tc_one<BF16, 1, 128, true>(dn, grid, st);
+    }
     switch (p.L.quant) {
         case Q4_0:
             e = (gu_cols == 256) ? launch_tc_one<Q4_0, 0, 256>(gu, grid, st) : launch_tc_one<Q4_0, 0, 128>(gu, grid, st);

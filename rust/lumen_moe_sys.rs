@@ -47,6 +47,7 @@ pub const LUMEN_MOE_ACT_F16: i32 = 2;
 pub const LUMEN_MOE_FLAG_DECODE_SPLIT: i32 = 0x1;
 pub const LUMEN_MOE_FLAG_PREFILL_MMA: i32 = 0x2;
 pub const LUMEN_MOE_FLAG_SHORT_WAITS: i32 = 0x4;
+pub const LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS: i32 = 0x8;
 pub const fn lumen_moe_flag_tc_ctas(n: i32) -> i32 { (n & 0xff) << 8 }
 
 pub const LUMEN_MOE_EP_HANDLE_BYTES: usize = 64;

@@ -193,6 +193,37 @@ def test_prefill_full_shape_other_formats_against_oracle(cuda_lib, quant, T, rou
     assert rel_l2(out[sample].cpu().numpy(), o_out) < TOL_REL_L2
 
 
+@pytest.mark.parametrize("quant,T,act", [(1, 300, "bf16"), (0, 77, "f32"), (1, 2304, "bf16")])
+def test_prefill_from_plain_f16_weights_matches_in_smem_dequant(cuda_lib, quant, T, act):
+    """LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS: the same weights as f16 matrices fed by TMA. The operands
+    are the same values (scale folded in, one rounding), so the result must stay within the
+    tolerance of the CPU reference and next to the default path's."""
+    H, I, E, K = (512, 256, 16, 4) if T < 2000 else (2048, 768, 128, 8)
+    lay = synth.LayerLayout(H, I, E, quant)
+    blob = synth.make_layer_blob(lay, 3)
+    g = torch.Generator("cuda").manual_seed(8)
+    x32 = torch.randn((T, H), generator=g, device="cuda")
+    x = x32.to(torch.bfloat16) if act == "bf16" else x32
+    res = torch.randn((T, H), generator=g, device="cuda")
+    lg = synth.zipf_logits(T, E, 4)
+    outs = []
+    for flags in (0, _lib.FLAG_PREFILL_F16_WEIGHTS):
+        sc = moe.allocate_moe_scratch(H, I, E, K, T, flags=flags)
+        layer = sc.prepare_layer(blob, lay.meta())
+        sc.set_logits_override(lg)
+        outs.append(sc.prefill(layer, x, res).clone())
+        r = sc.get_routing(T)
+    assert rel_l2((outs[1] - res).cpu().numpy(), (outs[0] - res).cpu().numpy()) < 2e-4
+    sample = sorted(set([0, T // 2, T - 1]))
+    xs = x[sample].float().cpu().numpy()
+    meta = lay.meta()
+    o_out, _, _ = oracle.moe_layer(blob.cpu().numpy(), 0, meta.expert_gate_offs, meta.expert_up_offs, meta.expert_down_offs,
+                                   quant, H, I, E, K, xs, res[sample].cpu().numpy(), ids=r["ids"][sample],
+                                   weights=r["weights"][sample], threads=8)
+    rs = res[sample].cpu().numpy()
+    assert rel_l2(outs[1][sample].cpu().numpy() - rs, o_out - rs) < TOL_REL_L2
+
+
 @pytest.mark.parametrize("quant,T", [(1, 40), (0, 300)])
 def test_stack_prefill_matches_layer_by_layer(cuda_lib, quant, T):
     """x <- x + MoE_l(rmsnorm(x)) over 3 layers in one call, in place: bit-identical to the

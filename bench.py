@@ -393,6 +393,21 @@ def sub_ep(torch, np, dist, moe, synth, ep, dev, rank, world, layers, args):
         dist.barrier()
         return maxr(ev0.elapsed_time(ev1) / n)
 
+    def graphed(fn, collective=True):
+        """The launches of one call replayed from a CUDA graph, as the headline does (the reference's
+        backend enqueues from Rust; a Python loop would time the interpreter at 256 tokens)."""
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.synchronize()
+        if collective:
+            dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return g.replay
+
     records = []
     for T, steps in ((16384, 10), (256, 20)):
         Tl = T // world
@@ -412,7 +427,7 @@ def sub_ep(torch, np, dist, moe, synth, ep, dev, rank, world, layers, args):
             fwd = lambda: pe.forward(ep_layers[0], x, res, out)
             for _ in range(3):
                 fwd()
-            ms = timed_all(fwd, steps)
+            ms = timed_all(graphed(fwd), steps)
             pe.sc.ep_profile(True)
             fwd()
             ph = pe.sc.ep_phase_ms()
@@ -430,7 +445,7 @@ def sub_ep(torch, np, dist, moe, synth, ep, dev, rank, world, layers, args):
                 one = lambda: sc1.prefill(layers[0], x_all, res_all, ref)
                 for _ in range(3):
                     one()
-                ms1 = event_ms(torch, one, steps)
+                ms1 = event_ms(torch, graphed(one, collective=False), steps)
                 ids_ref.copy_(torch.from_numpy(sc1.get_routing(T)["ids"].astype(np.int32)))
             dist.barrier()
             dist.broadcast(ref, 0)
@@ -476,7 +491,7 @@ def sub_ep(torch, np, dist, moe, synth, ep, dev, rank, world, layers, args):
         work.copy_(mine0)
         pe.stack_forward(ep_layers, gammas, work, 1e-6, normed)
     sfwd()
-    ms = timed_all(sfwd, 3)
+    ms = timed_all(graphed(sfwd), 3)
     ref = torch.empty((T, H), device=dev)
     ms1 = 0.0
     if rank == 0:
@@ -487,7 +502,7 @@ def sub_ep(torch, np, dist, moe, synth, ep, dev, rank, world, layers, args):
             ref.copy_(x0)
             sc1.stack_prefill(layers, gammas, ref, 1e-6, n1)
         one()
-        ms1 = event_ms(torch, one, 2)
+        ms1 = event_ms(torch, graphed(one, collective=False), 2)
     dist.barrier()
     dist.broadcast(ref, 0)
     ms1 = maxr(ms1)
@@ -690,6 +705,19 @@ def run_gpu(args):
     # ---- sub-records (after the headline; nothing below changes the numbers above) ----
     dev = torch.device("cuda", local)
     subs = {}
+    # A sub-record must never cost the headline: if the section below is still running after ten
+    # minutes (a rank that died inside a collective of the comparison code, say), rank 0 prints the
+    # line it has and every rank leaves. The library's own cross-rank waits give up after 2 s each.
+    watchdog = None
+    if world > 1 and not args.no_sub:
+        def give_up():
+            if rank == 0:
+                line["error"] = "sub-records abandoned after 600 s"
+                print(json.dumps(line), flush=True)
+            os._exit(0)
+        watchdog = threading.Timer(600.0, give_up)
+        watchdog.daemon = True
+        watchdog.start()
     if not args.no_sub and quant == 1 and T == 1:
         try:
             if world == 1:
@@ -708,6 +736,8 @@ def run_gpu(args):
                 subs["ep_prefill"], subs["stack_prefill"] = recs, stack
         except Exception as exc:  # a failing sub-record must not cost the headline
             subs["error"] = repr(exc)
+    if watchdog is not None:
+        watchdog.cancel()
     if rank == 0:
         line.update(subs)
         print(json.dumps(line), flush=True)
@@ -725,7 +755,7 @@ def run_prefill(args):
     build.build()
     quant, T = QUANTS[args.quant], args.tokens
     lay = synth.LayerLayout(H, I, E, quant)
-    sc = moe.allocate_moe_scratch(H, I, E, K, T)
+    sc = moe.allocate_moe_scratch(H, I, E, K, T, flags=0x8 if args.f16_weights else 0)
     layers = [sc.prepare_layer(synth.make_layer_blob(lay, l), lay.meta()) for l in range(min(args.layers, 4))]
     g = torch.Generator(device="cuda")
     g.manual_seed(1)
@@ -923,6 +953,8 @@ def main():
     ap.add_argument("--ep-chunks", type=int, default=1,
                     help="expert-parallel workloads: parts whose dispatch / expert products / combine overlap (1 = off)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--f16-weights", action="store_true",
+                    help="--workload prefill: keep the layers as plain f16 matrices too (LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS)")
     ap.add_argument("--no-sub", action="store_true", help="headline only: skip the sub-records of the other configurations")
     args = ap.parse_args()
     if args.impl == "reference":

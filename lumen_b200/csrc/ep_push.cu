@@ -121,9 +121,19 @@ __device__ __forceinline__ bool wait_flags(const uint32_t* flags, int world, uin
 // ---------------------------------------------------------------------------
 // my counts -> every rank
 // ---------------------------------------------------------------------------
+// The number of the call that tags every flag lives in device memory and is advanced here, by the
+// first kernel of a call, so that a captured call can be replayed from a CUDA graph (a host-side
+// counter would be frozen into the graph).
 __global__ void __launch_bounds__(256)
 ep_counts_kernel(const int32_t* __restrict__ expert_bounds, int E, int world, int me, Peers peers, WindowLayout wl,
-                 uint32_t epoch) {
+                 uint32_t* epoch_dev) {
+    __shared__ uint32_t epoch_s;
+    if (threadIdx.x == 0) {
+        epoch_s = *epoch_dev + 1u;
+        *epoch_dev = epoch_s;
+    }
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
     for (int i = threadIdx.x; i < world * E; i += 256) {
         const int r = i / E, e = i - r * E;
         int32_t* cnt = reinterpret_cast<int32_t*>(peers.win[r] + wl.cnt) + (size_t)me * E;
@@ -157,7 +167,7 @@ struct DispatchArgs {
     WindowLayout wl;
     int C, H, E, epr, world, me, rows_cap;
     int natural;                   // rows in the natural input order (TMA-fed weights) instead of the dequantiser's order
-    uint32_t epoch;
+    const uint32_t* epoch_dev;     // number of this call (advanced by ep_counts_kernel)
     unsigned long long limit_ns;
     int32_t* status;
     int32_t* status_host;
@@ -173,8 +183,9 @@ ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
     __shared__ int fail_s;
     __shared__ int over_s;
     const int tid = threadIdx.x;
+    const uint32_t epoch = *a.epoch_dev;
     const uint32_t* flags = reinterpret_cast<const uint32_t*>(a.my_win + a.wl.flags);
-    const bool ok = wait_flags(flags + 0 * FLAG_STRIDE, a.world, a.epoch, a.limit_ns, a.status, a.status_host, &fail_s);
+    const bool ok = wait_flags(flags + 0 * FLAG_STRIDE, a.world, epoch, a.limit_ns, a.status, a.status_host, &fail_s);
     if (tid == 0) over_s = 0;
     const int32_t* cnt = reinterpret_cast<const int32_t*>(a.my_win + a.wl.cnt);
     const int cols_cap = a.rows_cap;  // no count can exceed the window
@@ -257,7 +268,7 @@ ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
     if (fail_s) {
         __threadfence_system();
         if (tid < a.world)
-            st_release_sys(reinterpret_cast<uint32_t*>(a.peers.win[tid] + a.wl.flags) + 1 * FLAG_STRIDE + a.me, a.epoch);
+            st_release_sys(reinterpret_cast<uint32_t*>(a.peers.win[tid] + a.wl.flags) + 1 * FLAG_STRIDE + a.me, epoch);
         if (tid == 0) *a.done_counter = 0u;
     }
 }
@@ -266,10 +277,12 @@ ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
 // receive side: column counts of my experts once every rank's rows are in
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-ep_plan_kernel(const uint8_t* my_win, WindowLayout wl, int E, int epr, int world, int me, int rows_cap, uint32_t epoch,
-               unsigned long long limit_ns, int32_t* status, int32_t* status_host, int32_t* counts_out) {
+ep_plan_kernel(const uint8_t* my_win, WindowLayout wl, int E, int epr, int world, int me, int rows_cap,
+               const uint32_t* epoch_dev, unsigned long long limit_ns, int32_t* status, int32_t* status_host,
+               int32_t* counts_out) {
     __shared__ int fail_s;
     __shared__ int tot_s[MAX_EXPERTS];
+    const uint32_t epoch = *epoch_dev;
     const uint32_t* flags = reinterpret_cast<const uint32_t*>(my_win + wl.flags);
     const bool ok = wait_flags(flags + 1 * FLAG_STRIDE, world, epoch, limit_ns, status, status_host, &fail_s);
     const int32_t* cnt = reinterpret_cast<const int32_t*>(my_win + wl.cnt);
@@ -294,15 +307,17 @@ ep_plan_kernel(const uint8_t* my_win, WindowLayout wl, int E, int epr, int world
     }
 }
 
-__global__ void ep_signal_kernel(Peers peers, WindowLayout wl, int world, int me, uint32_t epoch) {
+__global__ void ep_signal_kernel(Peers peers, WindowLayout wl, int world, int me, const uint32_t* epoch_dev) {
+    const uint32_t epoch = *epoch_dev;
     __threadfence_system();
     if ((int)threadIdx.x < world)
         st_release_sys(reinterpret_cast<uint32_t*>(peers.win[threadIdx.x] + wl.flags) + 2 * FLAG_STRIDE + me, epoch);
 }
 
-__global__ void ep_wait_kernel(const uint8_t* my_win, WindowLayout wl, int world, uint32_t epoch,
+__global__ void ep_wait_kernel(const uint8_t* my_win, WindowLayout wl, int world, const uint32_t* epoch_dev,
                                unsigned long long limit_ns, int32_t* status, int32_t* status_host) {
     __shared__ int fail_s;
+    const uint32_t epoch = *epoch_dev;
     const uint32_t* flags = reinterpret_cast<const uint32_t*>(my_win + wl.flags);
     wait_flags(flags + 2 * FLAG_STRIDE, world, epoch, limit_ns, status, status_host, &fail_s);
 }
@@ -329,7 +344,7 @@ struct EpState {
     int32_t* n_tiles = nullptr;
     RouteDev RX{};        // expert_bounds / uexp / n_uexp of MY experts (the other fields unused)
     unsigned int* done_counter = nullptr;
-    uint32_t epoch = 0;
+    uint32_t* epoch_dev = nullptr;  // number of the current call, in device memory
     // optional phase timing of a call (lumen_moe_ep_profile): events between the launches
     bool profile = false;
     cudaEvent_t ev[7] = {};
@@ -399,6 +414,7 @@ Status ep_create(CudaMoeScratch* sc, int rank, int world, int max_tokens, int re
     s->RX.n_uexp = misc + 528;
     s->n_tiles = misc + 536;               // [2]
     s->done_counter = reinterpret_cast<unsigned int*>(misc + 544);
+    s->epoch_dev = reinterpret_cast<uint32_t*>(misc + 552);
     s->peers.win[rank] = s->win;
     if (world == 1) s->attached = true;
     if (handle64) {
@@ -449,7 +465,6 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     if (!g.ok()) return g;
 
     const unsigned long long limit_ns = sc->wait_limit_us ? (unsigned long long)sc->wait_limit_us * 1000ull : 2000000000ull;
-    const uint32_t epoch = ++s->epoch;
     if (s->profile && !s->ev_made) {
         for (cudaEvent_t& e : s->ev) CUDA_TRY(cudaEventCreate(&e));
         s->ev_made = true;
@@ -485,7 +500,7 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     const int C = batch * sc->K;
     // 2. counts to everyone
     count_launch(2);
-    ep::ep_counts_kernel<<<1, 256, 0, st>>>(sc->R.expert_bounds, sc->E, s->world, s->rank, s->peers, s->wl, epoch);
+    ep::ep_counts_kernel<<<1, 256, 0, st>>>(sc->R.expert_bounds, sc->E, s->world, s->rank, s->peers, s->wl, s->epoch_dev);
     // 3. rows to their owners
     ep::DispatchArgs d{};
     d.x = normed;
@@ -503,7 +518,7 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     d.me = s->rank;
     d.rows_cap = s->rows_cap;
     d.natural = layer.dev.gu16 != nullptr ? 1 : 0;
-    d.epoch = epoch;
+    d.epoch_dev = s->epoch_dev;
     d.limit_ns = limit_ns;
     d.status = sc->status;
     d.status_host = sc->status_host;
@@ -514,8 +529,8 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     mark(2);
     // 4. what arrived for my experts
     count_launch(1);
-    ep::ep_plan_kernel<<<1, 256, 0, st>>>(s->win, s->wl, sc->E, s->epr, s->world, s->rank, s->rows_cap, epoch, limit_ns,
-                                          sc->status, sc->status_host, s->RX.expert_bounds);
+    ep::ep_plan_kernel<<<1, 256, 0, st>>>(s->win, s->wl, sc->E, s->epr, s->world, s->rank, s->rows_cap, s->epoch_dev,
+                                          limit_ns, sc->status, sc->status_host, s->RX.expert_bounds);
     // expected rows per expert under balanced routing decide the gate/up tile width
     const int gu_cols = ((long long)C > 128ll * s->epr) ? 256 : 128;
     CUDA_TRY(launch_tile_plan(s->RX, s->epr, sc->H, sc->I, s->rows_cap, gu_cols, s->tiles, s->n_tiles, st));
@@ -545,8 +560,8 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     mark(4);
     // 6. results are out; wait for everyone's; combine
     count_launch(2);
-    ep::ep_signal_kernel<<<1, 32, 0, st>>>(s->peers, s->wl, s->world, s->rank, epoch);
-    ep::ep_wait_kernel<<<1, 32, 0, st>>>(s->win, s->wl, s->world, epoch, limit_ns, sc->status, sc->status_host);
+    ep::ep_signal_kernel<<<1, 32, 0, st>>>(s->peers, s->wl, s->world, s->rank, s->epoch_dev);
+    ep::ep_wait_kernel<<<1, 32, 0, st>>>(s->win, s->wl, s->world, s->epoch_dev, limit_ns, sc->status, sc->status_host);
     CUDA_TRY(cudaGetLastError());
     mark(5);
     CUDA_TRY(launch_scatter_accum(reinterpret_cast<const __half*>(s->win + s->wl.back), residual, sc->R, output, batch,

@@ -52,6 +52,37 @@ def test_one_rank_window_equals_plain_prefill(cuda_lib, T, act, routing):
     assert np.linalg.norm(got - want) / np.linalg.norm(want) < 1e-3
 
 
+def test_expert_parallel_call_replayed_from_a_cuda_graph(cuda_lib):
+    # the call number that tags the flags lives in device memory: a captured call can be replayed
+    from lumen_b200 import ep, moe, synth
+    H, I, E, K, T = 512, 256, 32, 4, 200
+    lay = synth.LayerLayout(H, I, E, 1)
+    blob = synth.make_layer_blob(lay, 3)
+    g = torch.Generator("cuda").manual_seed(4)
+    x = torch.randn((T, H), generator=g, device="cuda")
+    res = torch.randn((T, H), generator=g, device="cuda")
+    sc = moe.allocate_moe_scratch(H, I, E, K, T)
+    ref = sc.prefill(sc.prepare_layer(blob, lay.meta()), x, res)
+    pe = ep.PushExpertParallel(H, I, E, K, T, 0, 1, 0)
+    layer = pe.prepare_layer(blob, lay.meta())
+    out = torch.empty_like(res)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        pe.forward(layer, x, res, out)   # first call outside the capture (one-time set-up inside the library)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        pe.forward(layer, x, res, out)
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert pe.sc.poll_status() == 0
+        assert torch.equal(out, ref)
+    # eager calls still work after the replays
+    assert torch.equal(pe.forward(layer, x, res), ref)
+
+
 def test_receive_window_overflow_is_an_error_code(cuda_lib):
     # a window smaller than what the routing sends: no row may land outside it; the context reports it
     from lumen_b200 import _lib, ep, synth

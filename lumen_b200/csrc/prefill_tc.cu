@@ -216,6 +216,50 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ab * NA * BN;
+            if (MODE == 1) {
+                // Down product: the tile's columns (tokens) are the TMEM lanes and the 256 output rows
+                // of the m-tile the TMEM columns, so a thread owns one token and reads 16 consecutive
+                // output rows per load: its stores are 16 bytes wide and each token's 512 bytes are
+                // contiguous (a whole NVLink packet when the row lives on another rank).
+                const int tcol = row;  // token column of the tile
+                bool live = tcol < ncols;
+                __half* dst = a.out16;
+                if (live) {
+                    int orow_idx = tile.y + tcol;
+                    if (a.out_row_map != nullptr) orow_idx = a.out_row_map[orow_idx];
+                    dst = a.out16 + (size_t)orow_idx * a.out_ld;
+                    if (a.peer.ret_map != nullptr) {
+                        // plain stores into the return buffer of the rank the row came from
+                        const int m = a.peer.ret_map[orow_idx];
+                        const int pr = (m >> 24) & 0xff, prow = m & 0xffffff;
+                        live = pr < a.peer.world && prow < a.peer.rows_cap;  // never leave the buffers
+                        if (live) dst = a.peer.base[pr] + (size_t)prow * a.out_ld;
+                    }
+                    dst += (size_t)tile.w * 256 + (warp >> 2) * 128;
+                }
+                const uint32_t tcolbase = taddr + (warp >> 2) * 128;
+                // (every lane takes part in the loads: tcgen05.ld is a warp-wide instruction)
+#pragma unroll 2
+                for (int n0 = 0; n0 < 128; n0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld16(tcolbase + n0, v);
+                    tmem_ld_wait();
+                    if (live) {
+                        uint32_t h[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const __half2 pr2 = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                            h[j] = *reinterpret_cast<const uint32_t*>(&pr2);
+                        }
+                        uint4* d4 = reinterpret_cast<uint4*>(dst + n0);
+                        d4[0] = make_uint4(h[0], h[1], h[2], h[3]);
+                        d4[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                    }
+                }
+                tc_fence_before();
+                mbar_arrive(smem_u32(&acc_empty_bar[ab]));
+                continue;
+            }
             size_t off0, off1 = 0;
             if (MODE == 0) {
                 const int irow = tile.w * 128 + row;  // SwiGLU output is stored in the order the down product reads it
@@ -366,7 +410,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
                 const int4 tile = a.tiles[ti];
                 const int n16 = (tile.z + 15) & ~15;
-                const uint32_t idesc = make_idesc(n16, bf16_mode);
+                // down: D[128 tokens, 256 output rows] = X[128, k] W[256, k]^T, the two adjacent 128-row
+                // weight operands of a stage forming one 256-row N operand
+                const uint32_t idesc = make_idesc(MODE == 1 ? 256 : n16, bf16_mode);
                 const int ab = tl % NACC, use = tl / NACC;
                 ok = mbar_wait(smem_u32(&acc_empty_bar[ab]), (use & 1) ^ 1, abort_flag);
                 if (!ok) break;
@@ -382,10 +428,14 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                     for (int j = 0; j < 4; ++j) {
                         const uint64_t bdesc = make_desc(bbase + j * 32);
                         const uint32_t acc = (kh > 0 || j > 0) ? 1u : 0u;
+                        if (MODE == 1) {
+                            umma(tmem_base + ab * NA * BN, bdesc, make_desc(sbase + j * 32), idesc, acc);
+                        } else {
 #pragma unroll
-                        for (int op = 0; op < NA; ++op) {
-                            const uint64_t adesc = make_desc(sbase + op * SUB_BYTES + j * 32);
-                            umma(tmem_base + ab * NA * BN + op * BN, adesc, bdesc, idesc, acc);
+                            for (int op = 0; op < NA; ++op) {
+                                const uint64_t adesc = make_desc(sbase + op * SUB_BYTES + j * 32);
+                                umma(tmem_base + ab * NA * BN + op * BN, adesc, bdesc, idesc, acc);
+                            }
                         }
                     }
                     umma_commit(smem_u32(&empty_bar[s]));

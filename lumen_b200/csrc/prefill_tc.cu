@@ -142,6 +142,24 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
 // ATMA: the weight operands are not dequantised here but copied by TMA from plain f16 matrices
 // (BF16 layers; Q4_0 / Q8_0 layers of a context created with LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS): the
 // producer warps have nothing to do and every operand is in the natural input order.
+// Operand stages and depth of the raw-tile ring. The dequantising producers prefetch the next
+// 128-input group of quantised tiles while they work on the current one. For Q4_0 (3 uint4 per
+// lane and tile) the prefetch lives in registers. For Q8_0 (5 uint4) two operands x two groups
+// do not fit the 96 registers a thread has here and used to spill: there every producer warp
+// keeps its raw tiles in flight with cp.async (16 bytes per lane, into a ring of its own in
+// shared memory: no other warp touches it) and reads a group back with 128-bit shared loads
+// when it has landed (0.75 -> 0.59 ms per 4096-token call). The ring's shared memory comes out
+// of the operand stages; for Q4_0 the same ring with one stage less was measured slower
+// (0.53 -> 0.58 ms) and is not used.
+template <int Q, bool ATMA>
+struct RingOf {
+    static constexpr int value = (!ATMA && Q == Q8_0) ? 2 : 0;
+};
+template <int Q, int BN, bool ATMA>
+struct StagesOf {
+    static constexpr int value = (RingOf<Q, ATMA>::value > 0) ? ((BN == 128) ? 3 : 2) : ((BN == 128) ? 4 : 3);
+};
+
 template <int Q, int MODE, int BN, bool ATMA = false>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
@@ -158,7 +176,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     constexpr int NA = 2;
     // BN: columns per tile
     constexpr int NACC = (BN == 128) ? 2 : 1;          // accumulator sets in TMEM
-    constexpr int STAGES = (BN == 128) ? 4 : 3;        // one stage = 64 inputs (one swizzle atom in K)
+    constexpr int STAGES = StagesOf<Q, BN, ATMA>::value;  // one stage = 64 inputs (one swizzle atom in K)
+    constexpr int RING = RingOf<Q, ATMA>::value;       // raw weight tiles in flight per producer warp (128-input groups)
+    constexpr int RAW_U4 = QTraits<Q>::NQ * 32 + 8;    // uint4 of one raw tile: lane-major quant words, then 8 scale words
     constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operands then B
     constexpr int TMEM_COLS = NA * BN * NACC;
 
@@ -306,52 +326,129 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         const int rtl = warp - A_WARP0;  // 16-row tile within the 128-row M tile
         const int my_tiles = (!ATMA && ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
         const int ngroups = my_tiles * kgs;
-        WTile<Q> cur[NA], nxt[NA];
-        auto issue = [&](const int4& tile, int kg, WTile<Q>(&dst)[NA]) {
-            const int e = tile.x;
-            if (MODE == 0) {
-                const int rt = tile.w * 8 + rtl;  // m-tile = 128 rows of I: operand 0 gate, operand 1 up
-                load_wtile<Q>(dst[0], a.L.gate_q(e), a.L.gate_s(e), rt * kgs + kg, lane);
-                load_wtile<Q>(dst[1], a.L.up_q(e), a.L.up_s(e), rt * kgs + kg, lane);
-            } else {
-                const int rt = tile.w * 16 + rtl;  // m-tile = 256 rows of H: two adjacent 128-row tiles
-                load_wtile<Q>(dst[0], a.L.down_q(e), a.L.down_s(e), rt * kgs + kg, lane);
-                load_wtile<Q>(dst[1], a.L.down_q(e), a.L.down_s(e), (rt + 8) * kgs + kg, lane);
-            }
-        };
-        // tile descriptors are fetched one tile ahead so that no weight load waits on one
-        int4 tile_c = (my_tiles > 0) ? a.tiles[blockIdx.x] : make_int4(0, 0, 0, 0);
-        int4 tile_n = tile_c;
-        if (ngroups > 0) issue(tile_c, 0, cur);
-        bool ok = true;
-        int it = 0, kg = 0, tl = 0;
-        for (int n = 0; ok && n < ngroups; ++n) {
-            if (kg == 0 && tl + 1 < my_tiles) tile_n = a.tiles[blockIdx.x + (tl + 1) * gridDim.x];
-            if (n + 1 < ngroups) {
-                if (kg + 1 < kgs) issue(tile_c, kg + 1, nxt);
-                else issue(tile_n, 0, nxt);
-            }
-#pragma unroll
-            for (int sub = 0; sub < 2; ++sub, ++it) {
-                const int s = it % STAGES, ph = (it / STAGES) & 1;
-                ok = ok && mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
-                if (ok) {
-                    const uint32_t sbase = stage0 + s * STAGE_BYTES;
-#pragma unroll
-                    for (int op = 0; op < NA; ++op)
-                        dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
-                    fence_proxy_async();
-                    mbar_arrive(smem_u32(&full_bar[s]));
+        if constexpr (RING > 0) {
+            // this warp's ring: [RING][NA][RAW_U4] uint4, behind the operand stages
+            uint4* ring = reinterpret_cast<uint4*>(smem_raw + (stage0 - smem_u32(smem_raw)) + STAGES * STAGE_BYTES) +
+                          (size_t)rtl * (RING > 0 ? RING : 1) * NA * RAW_U4;
+            // raw tiles of group m (m-th 128-input group of this CTA's tile sequence) into ring slot m % RING
+            auto request = [&](int m) {
+                const int tl_m = m / kgs, kg_m = m - tl_m * kgs;
+                const int4 tile = a.tiles[blockIdx.x + tl_m * gridDim.x];
+                const int e = tile.x;
+                uint4* slot = ring + (size_t)(m % (RING > 0 ? RING : 1)) * NA * RAW_U4;
+    #pragma unroll
+                for (int op = 0; op < NA; ++op) {
+                    const uint4* qb;
+                    const uint4* sb;
+                    int tidx;
+                    if (MODE == 0) {
+                        // m-tile = 128 rows of I: operand 0 gate, operand 1 up
+                        qb = op ? a.L.up_q(e) : a.L.gate_q(e);
+                        sb = op ? a.L.up_s(e) : a.L.gate_s(e);
+                        tidx = (tile.w * 8 + rtl) * kgs + kg_m;
+                    } else {
+                        // m-tile = 256 rows of H: two adjacent 128-row tiles
+                        qb = a.L.down_q(e);
+                        sb = a.L.down_s(e);
+                        tidx = (tile.w * 16 + rtl + op * 8) * kgs + kg_m;
+                    }
+                    uint4* dst = slot + op * RAW_U4;
+                    const uint4* qp = qb + ((size_t)tidx * QTraits<Q>::NQ) * 32 + lane;
+    #pragma unroll
+                    for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(smem_u32(dst + j * 32 + lane), qp + j * 32, 16);
+                    if (Q != BF16 && lane < 8) cp_async16(smem_u32(dst + QTraits<Q>::NQ * 32 + lane), sb + (size_t)tidx * 8 + lane, 16);
+                }
+            };
+            WTile<Q> cur[NA];
+            if (RING > 0) {
+    #pragma unroll 1
+                for (int m = 0; m < RING - 1; ++m) {
+                    if (m < ngroups) request(m);
+                    asm volatile("cp.async.commit_group;" ::: "memory");
                 }
             }
-            if (n + 1 < ngroups) {
-#pragma unroll
-                for (int op = 0; op < NA; ++op) cur[op] = nxt[op];
+            bool ok = true;
+            int it = 0;
+            for (int n = 0; ok && n < ngroups; ++n) {
+                if (RING > 0) {
+                    if (n + RING - 1 < ngroups) request(n + RING - 1);
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    // all but the RING - 1 youngest groups have landed: group n is in its slot
+                    if (RING == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
+                    else asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    __syncwarp();  // the scale words of a slot are copied by lanes 0..7 for the whole warp
+                    const uint4* slot = ring + (size_t)(n % (RING > 0 ? RING : 1)) * NA * RAW_U4;
+    #pragma unroll
+                    for (int op = 0; op < NA; ++op) {
+    #pragma unroll
+                        for (int j = 0; j < QTraits<Q>::NQ; ++j) cur[op].q[j] = slot[op * RAW_U4 + j * 32 + lane];
+                        if (Q != BF16) cur[op].s = slot[op * RAW_U4 + QTraits<Q>::NQ * 32 + (lane >> 2)];
+                    }
+                    __syncwarp();  // every lane has its words before the slot is requested again
+                }
+    #pragma unroll
+                for (int sub = 0; sub < 2; ++sub, ++it) {
+                    const int s = it % STAGES, ph = (it / STAGES) & 1;
+                    ok = ok && mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
+                    if (ok) {
+                        const uint32_t sbase = stage0 + s * STAGE_BYTES;
+    #pragma unroll
+                        for (int op = 0; op < NA; ++op)
+                            dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
+                        fence_proxy_async();
+                        mbar_arrive(smem_u32(&full_bar[s]));
+                    }
+                }
             }
-            if (++kg == kgs) {
-                kg = 0;
-                ++tl;
-                tile_c = tile_n;
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        } else {
+            WTile<Q> cur[NA], nxt[NA];
+            auto issue = [&](const int4& tile, int kg, WTile<Q>(&dst)[NA]) {
+                const int e = tile.x;
+                if (MODE == 0) {
+                    const int rt = tile.w * 8 + rtl;  // m-tile = 128 rows of I: operand 0 gate, operand 1 up
+                    load_wtile<Q>(dst[0], a.L.gate_q(e), a.L.gate_s(e), rt * kgs + kg, lane);
+                    load_wtile<Q>(dst[1], a.L.up_q(e), a.L.up_s(e), rt * kgs + kg, lane);
+                } else {
+                    const int rt = tile.w * 16 + rtl;  // m-tile = 256 rows of H: two adjacent 128-row tiles
+                    load_wtile<Q>(dst[0], a.L.down_q(e), a.L.down_s(e), rt * kgs + kg, lane);
+                    load_wtile<Q>(dst[1], a.L.down_q(e), a.L.down_s(e), (rt + 8) * kgs + kg, lane);
+                }
+            };
+            // tile descriptors are fetched one tile ahead so that no weight load waits on one
+            int4 tile_c = (my_tiles > 0) ? a.tiles[blockIdx.x] : make_int4(0, 0, 0, 0);
+            int4 tile_n = tile_c;
+            if (ngroups > 0) issue(tile_c, 0, cur);
+            bool ok = true;
+            int it = 0, kg = 0, tl = 0;
+            for (int n = 0; ok && n < ngroups; ++n) {
+                if (kg == 0 && tl + 1 < my_tiles) tile_n = a.tiles[blockIdx.x + (tl + 1) * gridDim.x];
+                if (n + 1 < ngroups) {
+                    if (kg + 1 < kgs) issue(tile_c, kg + 1, nxt);
+                    else issue(tile_n, 0, nxt);
+                }
+    #pragma unroll
+                for (int sub = 0; sub < 2; ++sub, ++it) {
+                    const int s = it % STAGES, ph = (it / STAGES) & 1;
+                    ok = ok && mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
+                    if (ok) {
+                        const uint32_t sbase = stage0 + s * STAGE_BYTES;
+    #pragma unroll
+                        for (int op = 0; op < NA; ++op)
+                            dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
+                        fence_proxy_async();
+                        mbar_arrive(smem_u32(&full_bar[s]));
+                    }
+                }
+                if (n + 1 < ngroups) {
+    #pragma unroll
+                    for (int op = 0; op < NA; ++op) cur[op] = nxt[op];
+                }
+                if (++kg == kgs) {
+                    kg = 0;
+                    ++tl;
+                    tile_c = tile_n;
+                }
             }
         }
     } else if (warp < MMA_WARP) {
@@ -540,8 +637,10 @@ cudaError_t make_tmap_f16(const void* base, uint64_t rows, uint64_t cols, uint32
 template <int Q, int MODE, int BN, bool ATMA = false>
 static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
     constexpr int NA = 2;
-    constexpr int STAGES = (BN == 128) ? 4 : 3;
-    const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024;
+    constexpr int STAGES = tc::StagesOf<Q, BN, ATMA>::value;
+    constexpr int RING = tc::RingOf<Q, ATMA>::value;
+    const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024 +
+                     tc::A_WARPS * RING * NA * (QTraits<Q>::NQ * 32 + 8) * 16;
     static SmemOptIn optin;
     {
         cudaError_t e = ensure_dyn_smem(tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA>, (size_t)smem, optin);
@@ -612,9 +711,8 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
             if (e != cudaSuccess) return e;
             return launch_tc_one<Q8_0, 1, 128>(dn, grid, st);
         default:
-            e = (gu_cols == 256) ? launch_tc_one<BF16, 0, 256>(gu, grid, st) : launch_tc_one<BF16, 0, 128>(gu, grid, st);
-            if (e != cudaSuccess) return e;
-            return launch_tc_one<BF16, 1, 128>(dn, grid, st);
+            // BF16 layers always carry their plain f16 matrices on this path (see above)
+            return cudaErrorInvalidValue;
     }
 }
 

@@ -13,9 +13,10 @@
 //            routing never makes a second trip through memory; CTA 0 publishes the tables.
 //            gate/up + SwiGLU work items (expert with work, 16 inter rows), dealt
 //            round-robin from the last CTA downwards; each warp owns one 128-input
-//            group, next item's weights are requested before the current one is used.
-//            The down-projection weights of this CTA's 16 output rows are prefetched
-//            into shared memory with cp.async as soon as the routing is known.
+//            group; an item's weight tiles arrive by bulk copies (cp.async.bulk on
+//            mbarriers) through a ring of up to three items, requested for the expert set
+//            predicted from the raw logits while the exact gating still runs. The
+//            down-projection weights of this CTA's 16 output rows are requested the same way.
 //            (cuda/shaders/moe_expert_q4_0.cu:58-108; moe_expert.cu:62-97)
 //   barrier 2
 //   phase C  down product for output rows 16*CTA.., all experts with work; weighted

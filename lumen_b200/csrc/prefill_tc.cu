@@ -4,27 +4,34 @@
 // cuda/shaders/moe_grouped.cu:1202-1510; the Q8_0 dp4a / mma.sync variants :566-1170,
 // :2183-2598; the BF16 variants :1523-1760).
 //
-// Formulation ("weights are the M operand"): for a tile of up to 128 compact
-// columns of one expert,  D[128 weight rows, N columns] += W[128, k] * X[N, k]^T,
-// one tcgen05.mma of shape M=128 x N(16..128) x K=16 per 16 inputs. N follows
-// the ragged per-expert column counts (Zipf-skewed loads) without padding M.
+// Formulation. Gate/up + SwiGLU ("weights are the M operand"): for a tile of up to 256
+// compact columns of one expert,  D_g[128 gate rows, N] += G[128, k] X[N, k]^T  and the
+// same for the up rows, two tcgen05.mma of shape M=128 x N(16..256) x K=16 per 16 inputs
+// sharing the activation operand; N follows the ragged per-expert column counts
+// (Zipf-skewed loads) without padding M. Down ("tokens are the M operand"): for up to 128
+// columns,  D[128 tokens, 256 output rows] += S[128, k] W[256, k]^T, one MMA per 16 inputs
+// whose N operand is the stage's two adjacent 128-row weight tiles, so that an epilogue
+// thread owns one token and stores 16 bytes at a time.
 //
-// One CTA per SM, persistent over a device-built tile list, warp-specialised:
-//   warps 0-3   epilogue: tcgen05.ld of the accumulators, SwiGLU (gate/up mode),
-//               f16 store by compact column
-//   warps 4-11  weight producers: 128-bit loads of the repacked quant tiles,
-//               dequantise to f16 (scale folded in) in registers, store into the
-//               128-byte-swizzled K-major operand tile in shared memory
-//   warps 12-15 activation producers: cp.async rows (gathered through
-//               col_src_tok) into the swizzled operand tile
-//   warp 16     one elected thread issues tcgen05.mma / tcgen05.commit
+// One CTA per SM, persistent over a device-built tile list, warp-specialised (18 warps):
+//   warps 0-7   epilogue: tcgen05.ld of the accumulators, SwiGLU (gate/up), f16 stores
+//               (into another rank's return buffer for an expert-parallel down product)
+//   warps 8-15  weight producers: 128-bit loads of the repacked quant tiles (Q4_0: the next
+//               128-input group prefetched in registers; Q8_0: raw tiles kept in flight by
+//               cp.async through a ring of the warp's own in shared memory), dequantise to
+//               f16 (scale folded in) in registers, store into the 128-byte-swizzled
+//               K-major operand tile in shared memory. Idle when the weights are plain f16
+//               matrices copied by TMA (BF16 layers; LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS)
+//   warp 16     one thread feeds the activation operand (and TMA-fed weights) with
+//               cp.async.bulk.tensor.2d boxes of 64 inputs x 128 rows
+//   warp 17     one elected thread issues tcgen05.mma / tcgen05.commit
 // Stages are handed over with mbarriers; every wait is bounded (on expiry the
 // kernel raises a status word, drains and frees its TMEM instead of hanging).
 //
-// Inputs are 16-bit: activations pre-converted to f16 (bf16 for BF16 weights)
+// Inputs are 16-bit: activations pre-converted to f16, gathered into compact-column order
 // and pre-permuted within each 32-block to the order the dequantiser emits
-// (permute_x16_kernel); the SwiGLU output is written in the same order so the
-// down product reads it back without any shuffle.
+// (gather_permute_x16_kernel; natural order for TMA-fed weights); the SwiGLU output is
+// written in the same order so the down product reads it back without any shuffle.
 #include "mma_frag.cuh"
 #include "tc_common.cuh"
 #include <cstdlib>

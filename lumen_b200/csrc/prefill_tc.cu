@@ -40,7 +40,7 @@ namespace lumen {
 
 namespace tc {
 
-constexpr int EPI_WARPS = 8, A_WARPS = 8, B_WARPS = 1;  // B: one thread drives the TMA
+constexpr int EPI_WARPS = 8, A_WARPS = 16, B_WARPS = 1;  // B: one thread drives the TMA
 constexpr int A_WARP0 = EPI_WARPS, B_WARP0 = A_WARP0 + A_WARPS, MMA_WARP = B_WARP0 + B_WARPS;
 constexpr int THREADS = (MMA_WARP + 1) * 32;
 
@@ -85,64 +85,62 @@ struct Args {
     TcPeerOut peer;              // down mode, expert parallel: output rows go to other ranks' buffers (ret_map null = off)
 };
 
-__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
-    const __half2 h = __floats2half2_rn(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
-
 // Dequantise one lane's share of half a weight tile (16 rows x 64 k: blocks
 // 2*sub and 2*sub+1) into the operand tile: 4 chunks of 16 bytes (rows g, g+8).
+//
+// Lanes with odd g handle the second block of the pair first: the eight lanes of a quarter
+// warp then hit eight different 16-byte chunk positions (rows are 128 bytes apart, i.e. a
+// whole bank cycle) and the 128-bit stores are conflict-free. The choice is made on the raw
+// words (two selects per block for Q4_0, four for Q8_0), not on the sixteen unpacked ones.
 template <int Q>
 __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32_t a_base, int rtl, int lane) {
+    if constexpr (Q == BF16) return;  // BF16 layers feed this path from plain f16 matrices (ATMA): no producers
     const int g = lane >> 2, t = lane & 3;
-    uint32_t d[2][2][4];  // [block of the pair][row g | row g+8][four f16x2 words of one 16-byte chunk]
-#pragma unroll
-    for (int bb = 0; bb < 2; ++bb) {
-        const int b = sub * 2 + bb;
-        uint32_t lo[4], hi[4];
-        unpack_block<Q>(w, b, lo, hi);
-        if (Q == BF16) {
-            // bf16 -> f16 is exact for 2^-14 <= |w| < 65504 (8 significand bits fit in 11);
-            // smaller magnitudes lose bits only below 2^-24 absolute. The host keeps layers
-            // with |w| >= 65504 off this path.
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                lo[i] = bf16x2_to_f16x2(lo[i]);
-                hi[i] = bf16x2_to_f16x2(hi[i]);
-            }
-        } else {
-            const uint32_t s_g = (b < 2) ? w.s.x : w.s.y;
-            const uint32_t s_g8 = (b < 2) ? w.s.z : w.s.w;
-            const uint32_t sg2 = prmt(s_g, s_g, (b & 1) ? 0x3232u : 0x1010u);
-            const uint32_t sg82 = prmt(s_g8, s_g8, (b & 1) ? 0x3232u : 0x1010u);
-            lo[0] = hmul2_u32(lo[0], sg2);
-            hi[0] = hmul2_u32(hi[0], sg2);
-            lo[2] = hmul2_u32(lo[2], sg2);
-            hi[2] = hmul2_u32(hi[2], sg2);
-            lo[1] = hmul2_u32(lo[1], sg82);
-            hi[1] = hmul2_u32(hi[1], sg82);
-            lo[3] = hmul2_u32(lo[3], sg82);
-            hi[3] = hmul2_u32(hi[3], sg82);
-        }
-        d[bb][0][0] = lo[0]; d[bb][0][1] = hi[0]; d[bb][0][2] = lo[2]; d[bb][0][3] = hi[2];
-        d[bb][1][0] = lo[1]; d[bb][1][1] = hi[1]; d[bb][1][2] = lo[3]; d[bb][1][3] = hi[3];
-    }
-    // Lanes with odd g store the second block first: the eight lanes of a quarter
-    // warp then hit eight different 16-byte chunk positions (rows are 128 bytes
-    // apart, i.e. a whole bank cycle) and the 128-bit stores are conflict-free.
     const bool odd = (g & 1) != 0;
     const int r0 = rtl * 16 + g, r1 = r0 + 8;
+    const uint32_t s_g = (sub == 0) ? w.s.x : w.s.y;   // f16 scales of blocks 2 sub, 2 sub + 1: row g
+    const uint32_t s_g8 = (sub == 0) ? w.s.z : w.s.w;  // row g + 8
 #pragma unroll
     for (int pass = 0; pass < 2; ++pass) {
-        const bool second = (pass == 1) != odd;  // which block of the pair this lane stores in this pass
-        uint32_t x[2][4];
-#pragma unroll
-        for (int rr = 0; rr < 2; ++rr)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) x[rr][i] = second ? d[1][rr][i] : d[0][rr][i];
+        const bool second = (pass == 1) != odd;  // which block of the pair this lane handles in this pass
+        uint32_t lo[4], hi[4];
+        if (Q == Q4_0) {
+            const uint4 v = w.q[sub];
+            const uint32_t wg = second ? v.z : v.x;   // row g
+            const uint32_t wg8 = second ? v.w : v.y;  // row g+8
+            const uint32_t sub_lo = 0x64086408u;      // 1032 = 1024 + 8
+            const uint32_t sub_hi = 0x54805480u;      // 72   = 64 + 8
+            lo[0] = hsub2_u32(lop_and_or(wg, 0x000F000Fu, 0x64006400u), sub_lo);
+            lo[1] = hsub2_u32(lop_and_or(wg8, 0x000F000Fu, 0x64006400u), sub_lo);
+            lo[2] = hsub2_u32(lop_and_or(wg >> 8, 0x000F000Fu, 0x64006400u), sub_lo);
+            lo[3] = hsub2_u32(lop_and_or(wg8 >> 8, 0x000F000Fu, 0x64006400u), sub_lo);
+            hi[0] = hsub2_u32(lop_and_or(wg, 0x00F000F0u, 0x54005400u), sub_hi);
+            hi[1] = hsub2_u32(lop_and_or(wg8, 0x00F000F0u, 0x54005400u), sub_hi);
+            hi[2] = hsub2_u32(lop_and_or(wg >> 8, 0x00F000F0u, 0x54005400u), sub_hi);
+            hi[3] = hsub2_u32(lop_and_or(wg8 >> 8, 0x00F000F0u, 0x54005400u), sub_hi);
+        } else {
+            const uint4 va = w.q[(2 * sub) % QTraits<Q>::NQ], vb = w.q[(2 * sub + 1) % QTraits<Q>::NQ];
+            // bytes biased by 128 -> unsigned; 0x64xx = 1024 + xx; subtract 1152.
+            const uint32_t sb = 0x64806480u;
+            const uint32_t x0 = (second ? vb.x : va.x) ^ 0x80808080u, x1 = (second ? vb.y : va.y) ^ 0x80808080u;
+            const uint32_t y0 = (second ? vb.z : va.z) ^ 0x80808080u, y1 = (second ? vb.w : va.w) ^ 0x80808080u;
+            lo[0] = hsub2_u32(prmt(x0, 0x64646464u, 0x4240u), sb);
+            lo[1] = hsub2_u32(prmt(y0, 0x64646464u, 0x4240u), sb);
+            lo[2] = hsub2_u32(prmt(x0, 0x64646464u, 0x4341u), sb);
+            lo[3] = hsub2_u32(prmt(y0, 0x64646464u, 0x4341u), sb);
+            hi[0] = hsub2_u32(prmt(x1, 0x64646464u, 0x4240u), sb);
+            hi[1] = hsub2_u32(prmt(y1, 0x64646464u, 0x4240u), sb);
+            hi[2] = hsub2_u32(prmt(x1, 0x64646464u, 0x4341u), sb);
+            hi[3] = hsub2_u32(prmt(y1, 0x64646464u, 0x4341u), sb);
+        }
+        const uint32_t bsel = second ? 0x3232u : 0x1010u;  // the block's scale, in both halves
+        const uint32_t sg2 = prmt(s_g, s_g, bsel);
+        const uint32_t sg82 = prmt(s_g8, s_g8, bsel);
         const int c = (second ? 4 : 0) + t;
-        sts128(a_base + r0 * 128 + ((c ^ (r0 & 7)) << 4), x[0][0], x[0][1], x[0][2], x[0][3]);
-        sts128(a_base + r1 * 128 + ((c ^ (r1 & 7)) << 4), x[1][0], x[1][1], x[1][2], x[1][3]);
+        sts128(a_base + r0 * 128 + ((c ^ (r0 & 7)) << 4), hmul2_u32(lo[0], sg2), hmul2_u32(hi[0], sg2),
+               hmul2_u32(lo[2], sg2), hmul2_u32(hi[2], sg2));
+        sts128(a_base + r1 * 128 + ((c ^ (r1 & 7)) << 4), hmul2_u32(lo[1], sg82), hmul2_u32(hi[1], sg82),
+               hmul2_u32(lo[3], sg82), hmul2_u32(hi[3], sg82));
     }
 }
 
@@ -183,6 +181,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     constexpr int NA = 2;
     // BN: columns per tile
     constexpr int NACC = (BN == 128) ? 2 : 1;          // accumulator sets in TMEM
+    // With one accumulator set the tensor pipe idles during a tile's epilogue. When the weights come
+    // by TMA the producer warps have nothing else to do and share the epilogue. (For dequantising
+    // producers the same was measured slower: they are the critical resource of those kernels.)
+    constexpr bool HELP = (NACC == 1) && ATMA;
     constexpr int STAGES = StagesOf<Q, BN, ATMA>::value;  // one stage = 64 inputs (one swizzle atom in K)
     constexpr int RING = RingOf<Q, ATMA>::value;       // raw weight tiles in flight per producer warp (128-input groups)
     constexpr int RAW_U4 = QTraits<Q>::NQ * 32 + 8;    // uint4 of one raw tile: lane-major quant words, then 8 scale words
@@ -206,7 +208,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         }
         for (int b = 0; b < NACC; ++b) {
             mbar_init(smem_u32(&acc_full_bar[b]), 1);
-            mbar_init(smem_u32(&acc_empty_bar[b]), EPI_WARPS * 32);
+            mbar_init(smem_u32(&acc_empty_bar[b]), (HELP ? EPI_WARPS + A_WARPS : EPI_WARPS) * 32);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -227,28 +229,21 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     // every operand is f16 here: BF16 weights are converted exactly (see dequant_store)
     const bool bf16_mode = false;
 
-    if (warp < EPI_WARPS) {
-        // ------------------------------ epilogue ------------------------------
-        // warp w reads TMEM lanes 32*(w%4).. (hardware rule); warps 0-3 take the first half
-        // of the tile's columns, warps 4-7 the second half
+    // Epilogue of one tile by one warp: the warp's TMEM lanes are 32 (warp % 4).. (hardware rule);
+    // of the tile's 16-column TMEM chunks it takes those with chunk % nparts == part.
+    auto epilogue_part = [&](const int4& tile, int ab, int part, int nparts) {
         const int row = (warp & 3) * 32 + lane;
-        const int chalf = (warp >> 2) * (BN / 2);
-        int tl = 0;
-        bool ok = true;
-        for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
-            const int4 tile = a.tiles[ti];
-            const int ncols = tile.z;
-            const int ab = tl % NACC, use = tl / NACC;  // accumulator set and how often it has been used
-            ok = mbar_wait(smem_u32(&acc_full_bar[ab]), use & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ab * NA * BN;
-            if (MODE == 1) {
-                // Down product: the tile's columns (tokens) are the TMEM lanes and the 256 output rows
-                // of the m-tile the TMEM columns, so a thread owns one token and reads 16 consecutive
-                // output rows per load: its stores are 16 bytes wide and each token's 512 bytes are
-                // contiguous (a whole NVLink packet when the row lives on another rank).
-                const int tcol = row;  // token column of the tile
+        const int ncols = tile.z;
+        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ab * NA * BN;
+        if (MODE == 1) {
+            // Down product: the tile's columns (tokens) are the TMEM lanes and the 256 output rows
+            // of the m-tile the TMEM columns, so a thread owns one token and reads 16 consecutive
+            // output rows per load: its stores are 16 bytes wide and each token's 512 bytes are
+            // contiguous (a whole NVLink packet when the row lives on another rank). A 256-column
+            // tile is two such token halves side by side in TMEM.
+#pragma unroll 1
+            for (int h = 0; h < BN / 128 && h * 128 < ncols; ++h) {
+                const int tcol = h * 128 + row;  // token column of the tile
                 bool live = tcol < ncols;
                 __half* dst = a.out16;
                 if (live) {
@@ -262,146 +257,134 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                         live = pr < a.peer.world && prow < a.peer.rows_cap;  // never leave the buffers
                         if (live) dst = a.peer.base[pr] + (size_t)prow * a.out_ld;
                     }
-                    dst += (size_t)tile.w * 256 + (warp >> 2) * 128;
+                    dst += (size_t)tile.w * 256;
                 }
-                const uint32_t tcolbase = taddr + (warp >> 2) * 128;
                 // (every lane takes part in the loads: tcgen05.ld is a warp-wide instruction)
 #pragma unroll 2
-                for (int n0 = 0; n0 < 128; n0 += 16) {
+                for (int n0 = part * 16; n0 < 256; n0 += nparts * 16) {
                     uint32_t v[16];
-                    tmem_ld16(tcolbase + n0, v);
+                    tmem_ld16(taddr + h * 256 + n0, v);
                     tmem_ld_wait();
                     if (live) {
-                        uint32_t h[8];
+                        uint32_t hh[8];
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const __half2 pr2 = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
-                            h[j] = *reinterpret_cast<const uint32_t*>(&pr2);
+                            hh[j] = *reinterpret_cast<const uint32_t*>(&pr2);
                         }
                         uint4* d4 = reinterpret_cast<uint4*>(dst + n0);
-                        d4[0] = make_uint4(h[0], h[1], h[2], h[3]);
-                        d4[1] = make_uint4(h[4], h[5], h[6], h[7]);
+                        d4[0] = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+                        d4[1] = make_uint4(hh[4], hh[5], hh[6], hh[7]);
                     }
                 }
-                tc_fence_before();
-                mbar_arrive(smem_u32(&acc_empty_bar[ab]));
-                continue;
             }
-            size_t off0, off1 = 0;
-            if (MODE == 0) {
-                const int irow = tile.w * 128 + row;  // SwiGLU output is stored in the order the down product reads it
-                off0 = ATMA ? (size_t)irow : (size_t)(irow & ~31) + perm_pos(irow & 31);
-            } else {
-                off0 = (size_t)(tile.w * 256 + row);
-                off1 = off0 + 128;
-            }
-            for (int n0 = chalf; n0 < ncols && n0 < chalf + BN / 2; n0 += 16) {
+        } else {
+            // Gate/up: a thread owns one row of I (its TMEM lane) and walks the token columns
+            const int irow = tile.w * 128 + row;  // SwiGLU output is stored in the order the down product reads it
+            const size_t off0 = ATMA ? (size_t)irow : (size_t)(irow & ~31) + perm_pos(irow & 31);
+            for (int n0 = part * 16; n0 < ncols; n0 += nparts * 16) {
                 uint32_t v0[16], v1[16];
                 tmem_ld16(taddr + n0, v0);
                 tmem_ld16(taddr + BN + n0, v1);
                 tmem_ld_wait();
+                __half* dst = a.out16 + (size_t)(tile.y + n0) * a.out_ld + off0;
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     if (n0 + j < ncols) {
-                        int orow_idx = tile.y + n0 + j;
-                        if (MODE == 1 && a.out_row_map != nullptr) orow_idx = a.out_row_map[orow_idx];
-                        __half* dst = a.out16 + (size_t)orow_idx * a.out_ld;
-                        if (MODE == 1 && a.peer.ret_map != nullptr) {
-                            // plain stores into the return buffer of the rank the row came from
-                            const int m = a.peer.ret_map[orow_idx];
-                            const int pr = (m >> 24) & 0xff, prow = m & 0xffffff;
-                            if (pr >= a.peer.world || prow >= a.peer.rows_cap) continue;  // never leave the buffers
-                            dst = a.peer.base[pr] + (size_t)prow * a.out_ld;
-                        }
-                        if (MODE == 0) {
-                            const float gt = __uint_as_float(v0[j]);
-                            // SwiGLU (cuda/shaders/moe_expert.cu:47-50) with the fast exp and divide: their
-                            // error (~2^-21) is far below the f16 rounding of the result that follows
-                            dst[off0] = __float2half_rn(__fdividef(gt, 1.0f + __expf(-gt)) * __uint_as_float(v1[j]));
-                        } else {
-                            dst[off0] = __float2half_rn(__uint_as_float(v0[j]));
-                            dst[off1] = __float2half_rn(__uint_as_float(v1[j]));
-                        }
+                        const float gt = __uint_as_float(v0[j]);
+                        // SwiGLU (cuda/shaders/moe_expert.cu:47-50) with the fast exp and divide: their
+                        // error (~2^-21) is far below the f16 rounding of the result that follows
+                        dst[(size_t)j * a.out_ld] =
+                            __float2half_rn(__fdividef(gt, 1.0f + __expf(-gt)) * __uint_as_float(v1[j]));
                     }
                 }
             }
+        }
+    };
+    constexpr int EPI_PARTS = EPI_WARPS / 4 + (HELP ? A_WARPS / 4 : 0);  // groups of four warps sharing a tile's epilogue
+
+    if (warp < EPI_WARPS) {
+        // ------------------------------ epilogue ------------------------------
+        int tl = 0;
+        bool ok = true;
+        for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
+            const int4 tile = a.tiles[ti];
+            const int ab = tl % NACC, use = tl / NACC;  // accumulator set and how often it has been used
+            ok = mbar_wait(smem_u32(&acc_full_bar[ab]), use & 1, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            epilogue_part(tile, ab, warp >> 2, EPI_PARTS);
             tc_fence_before();
             mbar_arrive(smem_u32(&acc_empty_bar[ab]));
         }
     } else if (warp < B_WARP0) {
         // --------------------------- weight producers --------------------------
-        const int rtl = warp - A_WARP0;  // 16-row tile within the 128-row M tile
-        const int my_tiles = (!ATMA && ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        // Sixteen warps, one 16-row weight tile each per 128-input group: warps 0-7 the eight row
+        // tiles of the stage's first operand, warps 8-15 those of the second.
+        const int pw = warp - A_WARP0;
+        const int op = pw >> 3, rtl = pw & 7;  // operand of the stage, 16-row tile within its 128 rows
+        const int all_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const int my_tiles = ATMA ? 0 : all_tiles;
         const int ngroups = my_tiles * kgs;
+        bool ok = true;
+        // quant words and scales of this warp's tile of 128-input group kg of a tile of the list
+        auto tile_ptrs = [&](const int4& tile, int kg, const uint4*& qp, const uint4*& sp) {
+            const int e = tile.x;
+            int tidx;
+            const uint4 *qb, *sb;
+            if (MODE == 0) {
+                // m-tile = 128 rows of I: operand 0 gate, operand 1 up
+                qb = op ? a.L.up_q(e) : a.L.gate_q(e);
+                sb = op ? a.L.up_s(e) : a.L.gate_s(e);
+                tidx = (tile.w * 8 + rtl) * kgs + kg;
+            } else {
+                // m-tile = 256 rows of H: two adjacent 128-row tiles
+                qb = a.L.down_q(e);
+                sb = a.L.down_s(e);
+                tidx = (tile.w * 16 + pw) * kgs + kg;
+            }
+            qp = qb + ((size_t)tidx * QTraits<Q>::NQ) * 32 + lane;
+            sp = sb + (size_t)tidx * 8;
+        };
         if constexpr (RING > 0) {
-            // this warp's ring: [RING][NA][RAW_U4] uint4, behind the operand stages
+            // this warp's ring: [RING][RAW_U4] uint4, behind the operand stages
             uint4* ring = reinterpret_cast<uint4*>(smem_raw + (stage0 - smem_u32(smem_raw)) + STAGES * STAGE_BYTES) +
-                          (size_t)rtl * (RING > 0 ? RING : 1) * NA * RAW_U4;
-            // raw tiles of group m (m-th 128-input group of this CTA's tile sequence) into ring slot m % RING
+                          (size_t)pw * RING * RAW_U4;
+            // raw tile of group m (m-th 128-input group of this CTA's tile sequence) into ring slot m % RING
             auto request = [&](int m) {
                 const int tl_m = m / kgs, kg_m = m - tl_m * kgs;
                 const int4 tile = a.tiles[blockIdx.x + tl_m * gridDim.x];
-                const int e = tile.x;
-                uint4* slot = ring + (size_t)(m % (RING > 0 ? RING : 1)) * NA * RAW_U4;
+                const uint4 *qp, *sp;
+                tile_ptrs(tile, kg_m, qp, sp);
+                uint4* dst = ring + (size_t)(m % RING) * RAW_U4;
     #pragma unroll
-                for (int op = 0; op < NA; ++op) {
-                    const uint4* qb;
-                    const uint4* sb;
-                    int tidx;
-                    if (MODE == 0) {
-                        // m-tile = 128 rows of I: operand 0 gate, operand 1 up
-                        qb = op ? a.L.up_q(e) : a.L.gate_q(e);
-                        sb = op ? a.L.up_s(e) : a.L.gate_s(e);
-                        tidx = (tile.w * 8 + rtl) * kgs + kg_m;
-                    } else {
-                        // m-tile = 256 rows of H: two adjacent 128-row tiles
-                        qb = a.L.down_q(e);
-                        sb = a.L.down_s(e);
-                        tidx = (tile.w * 16 + rtl + op * 8) * kgs + kg_m;
-                    }
-                    uint4* dst = slot + op * RAW_U4;
-                    const uint4* qp = qb + ((size_t)tidx * QTraits<Q>::NQ) * 32 + lane;
-    #pragma unroll
-                    for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(smem_u32(dst + j * 32 + lane), qp + j * 32, 16);
-                    if (Q != BF16 && lane < 8) cp_async16(smem_u32(dst + QTraits<Q>::NQ * 32 + lane), sb + (size_t)tidx * 8 + lane, 16);
-                }
+                for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(smem_u32(dst + j * 32 + lane), qp + j * 32, 16);
+                if (lane < 8) cp_async16(smem_u32(dst + QTraits<Q>::NQ * 32 + lane), sp + lane, 16);
             };
-            WTile<Q> cur[NA];
-            if (RING > 0) {
+            WTile<Q> cur;
     #pragma unroll 1
-                for (int m = 0; m < RING - 1; ++m) {
-                    if (m < ngroups) request(m);
-                    asm volatile("cp.async.commit_group;" ::: "memory");
-                }
+            for (int m = 0; m < RING - 1; ++m) {
+                if (m < ngroups) request(m);
+                asm volatile("cp.async.commit_group;" ::: "memory");
             }
-            bool ok = true;
             int it = 0;
             for (int n = 0; ok && n < ngroups; ++n) {
-                if (RING > 0) {
-                    if (n + RING - 1 < ngroups) request(n + RING - 1);
-                    asm volatile("cp.async.commit_group;" ::: "memory");
-                    // all but the RING - 1 youngest groups have landed: group n is in its slot
-                    if (RING == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
-                    else asm volatile("cp.async.wait_group 1;" ::: "memory");
-                    __syncwarp();  // the scale words of a slot are copied by lanes 0..7 for the whole warp
-                    const uint4* slot = ring + (size_t)(n % (RING > 0 ? RING : 1)) * NA * RAW_U4;
+                if (n + RING - 1 < ngroups) request(n + RING - 1);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                // all but the RING - 1 youngest groups have landed: group n is in its slot
+                asm volatile("cp.async.wait_group %0;" ::"n"(RING - 1) : "memory");
+                __syncwarp();  // the scale words of a slot are copied by lanes 0..7 for the whole warp
+                const uint4* slot = ring + (size_t)(n % RING) * RAW_U4;
     #pragma unroll
-                    for (int op = 0; op < NA; ++op) {
-    #pragma unroll
-                        for (int j = 0; j < QTraits<Q>::NQ; ++j) cur[op].q[j] = slot[op * RAW_U4 + j * 32 + lane];
-                        if (Q != BF16) cur[op].s = slot[op * RAW_U4 + QTraits<Q>::NQ * 32 + (lane >> 2)];
-                    }
-                    __syncwarp();  // every lane has its words before the slot is requested again
-                }
+                for (int j = 0; j < QTraits<Q>::NQ; ++j) cur.q[j] = slot[j * 32 + lane];
+                cur.s = slot[QTraits<Q>::NQ * 32 + (lane >> 2)];
+                __syncwarp();  // every lane has its words before the slot is requested again
     #pragma unroll
                 for (int sub = 0; sub < 2; ++sub, ++it) {
                     const int s = it % STAGES, ph = (it / STAGES) & 1;
                     ok = ok && mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
                     if (ok) {
-                        const uint32_t sbase = stage0 + s * STAGE_BYTES;
-    #pragma unroll
-                        for (int op = 0; op < NA; ++op)
-                            dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
+                        dequant_store<Q>(cur, sub, stage0 + s * STAGE_BYTES + op * SUB_BYTES, rtl, lane);
                         fence_proxy_async();
                         mbar_arrive(smem_u32(&full_bar[s]));
                     }
@@ -409,24 +392,18 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             }
             asm volatile("cp.async.wait_group 0;" ::: "memory");
         } else {
-            WTile<Q> cur[NA], nxt[NA];
-            auto issue = [&](const int4& tile, int kg, WTile<Q>(&dst)[NA]) {
-                const int e = tile.x;
-                if (MODE == 0) {
-                    const int rt = tile.w * 8 + rtl;  // m-tile = 128 rows of I: operand 0 gate, operand 1 up
-                    load_wtile<Q>(dst[0], a.L.gate_q(e), a.L.gate_s(e), rt * kgs + kg, lane);
-                    load_wtile<Q>(dst[1], a.L.up_q(e), a.L.up_s(e), rt * kgs + kg, lane);
-                } else {
-                    const int rt = tile.w * 16 + rtl;  // m-tile = 256 rows of H: two adjacent 128-row tiles
-                    load_wtile<Q>(dst[0], a.L.down_q(e), a.L.down_s(e), rt * kgs + kg, lane);
-                    load_wtile<Q>(dst[1], a.L.down_q(e), a.L.down_s(e), (rt + 8) * kgs + kg, lane);
-                }
+            WTile<Q> cur, nxt;
+            auto issue = [&](const int4& tile, int kg, WTile<Q>& dst) {
+                const uint4 *qp, *sp;
+                tile_ptrs(tile, kg, qp, sp);
+    #pragma unroll
+                for (int j = 0; j < QTraits<Q>::NQ; ++j) dst.q[j] = ldg_stream(qp + j * 32);
+                if (Q != BF16) dst.s = ldg_stream(sp + (lane >> 2));
             };
             // tile descriptors are fetched one tile ahead so that no weight load waits on one
             int4 tile_c = (my_tiles > 0) ? a.tiles[blockIdx.x] : make_int4(0, 0, 0, 0);
             int4 tile_n = tile_c;
             if (ngroups > 0) issue(tile_c, 0, cur);
-            bool ok = true;
             int it = 0, kg = 0, tl = 0;
             for (int n = 0; ok && n < ngroups; ++n) {
                 if (kg == 0 && tl + 1 < my_tiles) tile_n = a.tiles[blockIdx.x + (tl + 1) * gridDim.x];
@@ -439,23 +416,29 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                     const int s = it % STAGES, ph = (it / STAGES) & 1;
                     ok = ok && mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
                     if (ok) {
-                        const uint32_t sbase = stage0 + s * STAGE_BYTES;
-    #pragma unroll
-                        for (int op = 0; op < NA; ++op)
-                            dequant_store<Q>(cur[op], sub, sbase + op * SUB_BYTES, rtl, lane);
+                        dequant_store<Q>(cur, sub, stage0 + s * STAGE_BYTES + op * SUB_BYTES, rtl, lane);
                         fence_proxy_async();
                         mbar_arrive(smem_u32(&full_bar[s]));
                     }
                 }
-                if (n + 1 < ngroups) {
-    #pragma unroll
-                    for (int op = 0; op < NA; ++op) cur[op] = nxt[op];
-                }
+                if (n + 1 < ngroups) cur = nxt;
                 if (++kg == kgs) {
                     kg = 0;
                     ++tl;
                     tile_c = tile_n;
                 }
+            }
+        }
+        if constexpr (HELP) {
+            // TMA-fed weights: nothing to dequantise, this warp shares every tile's epilogue instead
+            for (int tl = 0; ok && tl < all_tiles; ++tl) {
+                const int4 tile = a.tiles[blockIdx.x + tl * gridDim.x];
+                ok = mbar_wait(smem_u32(&acc_full_bar[0]), tl & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                epilogue_part(tile, 0, EPI_WARPS / 4 + (pw >> 2), EPI_PARTS);
+                tc_fence_before();
+                mbar_arrive(smem_u32(&acc_empty_bar[0]));
             }
         }
     } else if (warp < MMA_WARP) {
@@ -647,7 +630,7 @@ static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
     constexpr int STAGES = tc::StagesOf<Q, BN, ATMA>::value;
     constexpr int RING = tc::RingOf<Q, ATMA>::value;
     const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024 +
-                     tc::A_WARPS * RING * NA * (QTraits<Q>::NQ * 32 + 8) * 16;
+                     tc::A_WARPS * RING * (QTraits<Q>::NQ * 32 + 8) * 16;
     static SmemOptIn optin;
     {
         cudaError_t e = ensure_dyn_smem(tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA>, (size_t)smem, optin);

@@ -490,62 +490,81 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
     uint4* my_ring = dc_ring + (size_t)warp * DcRing<Q>::value * TU4;
     const int n_exp_w = (U > warp) ? (U - warp + DC_WARPS - 1) / DC_WARPS : 0;
     const int nitems = n_exp_w * kg_i;
-    auto issue = [&](int n) {
-        if (n < nitems) {
-            const int uu = warp + DC_WARPS * (n / kg_i), kg = n % kg_i;
-            const int ee = exp_s[uu];
-            const int tile = rt * kg_i + kg;
-            uint4* slot = my_ring + (size_t)(n % DcRing<Q>::value) * TU4;
+    // (expert slot, k-group) of the next item to request / to prefetch activations for / to multiply:
+    // three cursors stepped by one item, no division in the loop
+    int is_u = warp, is_kg = 0, is_slot = 0;
+    auto issue = [&]() {
+        if (is_u < U) {
+            const int ee = exp_s[is_u];
+            const int tile = rt * kg_i + is_kg;
+            uint4* slot = my_ring + (size_t)is_slot * TU4;
             const uint4* qp = a.L.down_q(ee) + (size_t)tile * NQ32 + lane;
 #pragma unroll
             for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16_dc(slot + j * 32 + lane, qp + j * 32);
             if (Q != BF16 && lane < 8) cp_async16_dc(slot + NQ32 + lane, a.L.down_s(ee) + (size_t)tile * 8 + lane);
+            if (++is_kg == kg_i) {
+                is_kg = 0;
+                is_u += DC_WARPS;
+            }
         }
+        if (++is_slot == DcRing<Q>::value) is_slot = 0;
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
 #pragma unroll 1
-    for (int i = 0; i < DcRing<Q>::value; ++i) issue(i);
+    for (int i = 0; i < DcRing<Q>::value; ++i) issue();
     float acc[4][4];
     const uint4* bbase[4] = {nullptr, nullptr, nullptr, nullptr};
     int c0 = 0, ncol = 0, ng = 0;
     // activation fragments of the first column group (an expert rarely has more than four columns
     // here) are fetched one item ahead, so that their L2 latency is not paid tile by tile
-    auto b0_ptr = [&](int n) -> const uint4* {
-        const int uu = warp + DC_WARPS * (n / kg_i), kg = n % kg_i;
-        const int colr = gq >> 1;
-        if (n >= nitems || colr >= nc_s[uu]) return nullptr;
-        return a.sf + ((size_t)((c0_s[uu] + colr) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4 + (size_t)kg * 16;
+    int pb_u = warp, pb_kg = 0;
+    auto b0_next = [&]() -> const uint4* {
+        const uint4* p = nullptr;
+        if (pb_u < U) {
+            const int colr = gq >> 1;
+            if (colr < nc_s[pb_u])
+                p = a.sf + ((size_t)((c0_s[pb_u] + colr) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4 + (size_t)pb_kg * 16;
+            if (++pb_kg == kg_i) {
+                pb_kg = 0;
+                pb_u += DC_WARPS;
+            }
+        }
+        return p;
     };
     uint4 bnx[4];
     {
-        const uint4* p0 = b0_ptr(0);
+        const uint4* p0 = b0_next();
 #pragma unroll
         for (int b = 0; b < 4; ++b) bnx[b] = p0 ? ldg_cached(p0 + b * 4) : make_uint4(0u, 0u, 0u, 0u);
     }
+    int uu = warp - DC_WARPS, kg = kg_i - 1, rslot = 0;
 #pragma unroll 1
     for (int n = 0; n < nitems; ++n) {
         asm volatile("cp.async.wait_group %0;" ::"n"(DcRing<Q>::value - 1) : "memory");
         __syncwarp();
         WTile<Q> cur;
         {
-            const uint4* slot = my_ring + (size_t)(n % DcRing<Q>::value) * TU4;
+            const uint4* slot = my_ring + (size_t)rslot * TU4;
 #pragma unroll
             for (int j = 0; j < QTraits<Q>::NQ; ++j) cur.q[j] = slot[j * 32 + lane];
             if (Q != BF16) cur.s = slot[NQ32 + (lane >> 2)];
+            if (++rslot == DcRing<Q>::value) rslot = 0;
         }
         __syncwarp();
-        issue(n + DcRing<Q>::value);  // refill the slot just read
+        issue();  // refill the slot just read
         uint4 bcur[4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) bcur[b] = bnx[b];
         {
-            const uint4* p1 = b0_ptr(n + 1);
+            const uint4* p1 = b0_next();
 #pragma unroll
             for (int b = 0; b < 4; ++b) bnx[b] = p1 ? ldg_cached(p1 + b * 4) : make_uint4(0u, 0u, 0u, 0u);
         }
-        const int kg = n % kg_i;
+        if (++kg == kg_i) {
+            kg = 0;
+            uu += DC_WARPS;
+        }
         if (kg == 0) {
-            const int uu = warp + DC_WARPS * (n / kg_i);
             c0 = c0_s[uu];
             ncol = nc_s[uu];
             ng = (ncol + 3) >> 2;

@@ -269,6 +269,136 @@ down_small_kernel(const __grid_constant__ DecodeArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// gate/up + SwiGLU for decode batches of 5..16 tokens, Q4_0 with int8 activations: streaming form.
+//
+// gate_up_small_kernel above is one CTA per (16 rows of I, expert): descriptor, weights,
+// products, a reduction across its warps, SwiGLU, a chain of a few microseconds per CTA and 13
+// waves of them at 16 tokens. Here a WARP owns a whole item (16 rows of I of one expert with
+// work, every input group): it streams the item's gate and up tiles through a ring of its own
+// in shared memory (cp.async, GS_RING tile pairs in flight), multiplies them with the int8
+// activations of the expert's tokens (the whole batch's, 16 x 4.7 KB, is staged in shared memory
+// once per CTA) and finishes the 16 rows itself: no reduction between warps. One CTA of 16 warps per SM;
+// items are dealt so that every SM gets the same number of them (+-1).
+// (cuda/shaders/moe_expert_q4_0.cu:58-108; SwiGLU cuda/shaders/moe_expert.cu:47-50)
+// ---------------------------------------------------------------------------
+constexpr int GS_WARPS = 16, GS_RING = 3;
+constexpr int GS_TU4 = QTraits<Q4_0>::NQ * 32 + 8;  // uint4 of one raw tile: quant words, then 8 scale words
+
+__global__ void __launch_bounds__(GS_WARPS * 32, 1)
+gate_up_stream_kernel(const __grid_constant__ DecodeArgs a) {
+    extern __shared__ uint4 gs_ring[];  // [GS_WARPS][GS_RING][gate | up][GS_TU4]
+    pdl_wait();
+    pdl_trigger();
+    constexpr int NQ32 = QTraits<Q4_0>::NQ * 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int gq = lane >> 2, t4 = lane & 3;
+    const int kg_h = a.L.kg_h, rt_i = a.L.rt_i, I = a.L.I;
+    const int nblk_pad = kg_h * 4, nblk_i_pad = a.L.kg_i * 4;
+    const int xq_term = xq_term_words(nblk_pad), xq_tok = xq_tok_words(nblk_pad);  // 32-bit words
+    const int nitems = *a.R.n_uexp * rt_i;
+    uint4* ring = gs_ring + (size_t)warp * GS_RING * 2 * GS_TU4;
+    // the batch's int8 activations, staged once (16-byte copies: xq_tok is a multiple of four words)
+    unsigned* xq_s = reinterpret_cast<unsigned*>(gs_ring + (size_t)GS_WARPS * GS_RING * 2 * GS_TU4);
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(a.xq);
+        uint4* dst = reinterpret_cast<uint4*>(xq_s);
+        const int n16 = a.T * xq_tok / 4;
+        for (int i = tid; i < n16; i += GS_WARPS * 32) cp_async16(dst + i, src + i);
+        cp_async_wait_all();
+        __syncthreads();
+    }
+    // warp-major numbering over the grid: consecutive items go to different SMs
+    for (int item = warp * gridDim.x + blockIdx.x; item < nitems; item += GS_WARPS * gridDim.x) {
+        const int u = item / rt_i, rt = item - u * rt_i;
+        const int4 wd = a.R.work[2 * u];      // {expert, first column, columns}
+        const int4 wt = a.R.work[2 * u + 1];  // source tokens of the first four columns
+        const int e = wd.x, c0 = wd.y;
+        if (e < 0) continue;
+        const uint4* gqb = a.L.gate_q(e) + (size_t)rt * kg_h * NQ32 + lane;
+        const uint4* uqb = a.L.up_q(e) + (size_t)rt * kg_h * NQ32 + lane;
+        const uint4* gsb = a.L.gate_s(e) + (size_t)rt * kg_h * 8;
+        const uint4* usb = a.L.up_s(e) + (size_t)rt * kg_h * 8;
+        // the expert's columns four at a time (one MMA column group; rarely more than one round)
+        for (int cb = 0; cb < wd.z; cb += 4) {
+            const int ncol = min(4, wd.z - cb);
+            auto tok_of = [&](int j) -> int {
+                return (cb == 0) ? (j == 0 ? wt.x : j == 1 ? wt.y : j == 2 ? wt.z : wt.w) : a.R.col_src_tok[c0 + cb + j];
+            };
+            const int jcol = gq >> 1;          // column of this lane's B fragment (n index = 2 * column + term)
+            const bool bvalid = jcol < ncol;
+            const int tok_b = tok_of(bvalid ? jcol : 0);
+            const int tok_s = tok_of(t4 < ncol ? t4 : 0);  // column of this lane's accumulators
+            const unsigned* bq0 = xq_s + (size_t)tok_b * xq_tok + (gq & 1) * xq_term + t4 * 2;
+            const float2* sc0 = reinterpret_cast<const float2*>(xq_s + (size_t)tok_s * xq_tok + 2 * xq_term);
+            auto issue = [&](int kg) {
+                if (kg < kg_h) {
+                    uint4* slot = ring + (size_t)(kg % GS_RING) * 2 * GS_TU4;
+                    cp_async16(slot + lane, gqb + (size_t)kg * NQ32);
+                    cp_async16(slot + 32 + lane, gqb + (size_t)kg * NQ32 + 32);
+                    cp_async16(slot + GS_TU4 + lane, uqb + (size_t)kg * NQ32);
+                    cp_async16(slot + GS_TU4 + 32 + lane, uqb + (size_t)kg * NQ32 + 32);
+                    if (lane < 8) cp_async16(slot + NQ32 + lane, gsb + (size_t)kg * 8 + lane);
+                    else if (lane < 16) cp_async16(slot + GS_TU4 + NQ32 + lane - 8, usb + (size_t)kg * 8 + lane - 8);
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            };
+#pragma unroll 1
+            for (int i = 0; i < GS_RING; ++i) issue(i);
+            float acc_g0 = 0.f, acc_g8 = 0.f, acc_u0 = 0.f, acc_u8 = 0.f;  // rows gq, gq + 8 of column t4
+#pragma unroll 1
+            for (int kg = 0; kg < kg_h; ++kg) {
+                asm volatile("cp.async.wait_group %0;" ::"n"(GS_RING - 1) : "memory");
+                __syncwarp();  // the scale words of a slot are copied by lanes 0..15 for the whole warp
+                const uint4* slot = ring + (size_t)(kg % GS_RING) * 2 * GS_TU4;
+                WTile<Q4_0> wg, wu;
+                wg.q[0] = slot[lane];
+                wg.q[1] = slot[32 + lane];
+                wg.s = slot[NQ32 + (lane >> 2)];
+                wu.q[0] = slot[GS_TU4 + lane];
+                wu.q[1] = slot[GS_TU4 + 32 + lane];
+                wu.s = slot[GS_TU4 + NQ32 + (lane >> 2)];
+                __syncwarp();  // every lane has its words before the slot is requested again
+                issue(kg + GS_RING);
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    // raw nibbles (u8) times the two int8 terms of the activations
+                    const uint4 qg = wg.q[b >> 1], qu = wu.q[b >> 1];
+                    const unsigned g0 = (b & 1) ? qg.z : qg.x, g8 = (b & 1) ? qg.w : qg.y;
+                    const unsigned u0 = (b & 1) ? qu.z : qu.x, u8 = (b & 1) ? qu.w : qu.y;
+                    int cg[4] = {0, 0, 0, 0}, cu[4] = {0, 0, 0, 0};
+                    uint2 bb = make_uint2(0u, 0u);
+                    if (bvalid) bb = *reinterpret_cast<const uint2*>(bq0 + (size_t)(kg * 4 + b) * 8);
+                    mma_u8s8(cg, g0 & 0x0F0F0F0Fu, g8 & 0x0F0F0F0Fu, (g0 >> 4) & 0x0F0F0F0Fu, (g8 >> 4) & 0x0F0F0F0Fu,
+                             bb.x, bb.y);
+                    mma_u8s8(cu, u0 & 0x0F0F0F0Fu, u8 & 0x0F0F0F0Fu, (u0 >> 4) & 0x0F0F0F0Fu, (u8 >> 4) & 0x0F0F0F0Fu,
+                             bb.x, bb.y);
+                    const float2 sxo = sc0[kg * 4 + b];  // {sx, 8 * sx * sum(q)}
+                    const float2 sg = block_scales<Q4_0>(wg, b), su = block_scales<Q4_0>(wu, b);
+                    const float k1 = 1.0f / 254.0f;
+                    acc_g0 = fmaf(sg.x, fmaf(sxo.x, fmaf((float)cg[1], k1, (float)cg[0]), -sxo.y), acc_g0);
+                    acc_g8 = fmaf(sg.y, fmaf(sxo.x, fmaf((float)cg[3], k1, (float)cg[2]), -sxo.y), acc_g8);
+                    acc_u0 = fmaf(su.x, fmaf(sxo.x, fmaf((float)cu[1], k1, (float)cu[0]), -sxo.y), acc_u0);
+                    acc_u8 = fmaf(su.y, fmaf(sxo.x, fmaf((float)cu[3], k1, (float)cu[2]), -sxo.y), acc_u8);
+                }
+            }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            if (t4 < ncol) {
+                const int col = c0 + cb + t4;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const float gate = h ? acc_g8 : acc_g0, up = h ? acc_u8 : acc_u0;
+                    const float sv = (gate / (1.0f + expf(-gate))) * up;
+                    const int irow = rt * 16 + gq + 8 * h;
+                    if (a.s_f32 != nullptr) a.s_f32[(size_t)col * I + irow] = sv;
+                    store_swiglu_frag<Q4_0>(a.sf, col, irow, nblk_i_pad, sv);
+                }
+            }
+            __syncwarp();
+        }
+    }
+}
+
 template <typename Kern>
 static cudaError_t launch_pdl_smem(Kern kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                                    const DecodeArgs& a) {
@@ -305,6 +435,17 @@ template <int Q>
 static cudaError_t launch_small_t(const DecodeArgs& a, int phase, cudaStream_t st) {
     const int C = a.T * a.K;
     const int nu = C < a.L.E ? C : a.L.E;
+    const size_t gs_smem = (size_t)GS_WARPS * GS_RING * 2 * GS_TU4 * 16 + (size_t)a.T * xq_tok_words(a.L.kg_h * 4) * 4;
+    if (phase == 1 && Q == Q4_0 && a.xq != nullptr && a.T > 4 && gs_smem <= 220 * 1024) {
+        const size_t smem = gs_smem;
+        static SmemOptIn optin_gs;
+        cudaError_t e = ensure_dyn_smem(gate_up_stream_kernel, smem, optin_gs);
+        if (e != cudaSuccess) return e;
+        int device = 0, sms = 0;
+        if ((e = cudaGetDevice(&device)) != cudaSuccess) return e;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return e;
+        return launch_pdl_smem(gate_up_stream_kernel, dim3(sms), dim3(GS_WARPS * 32), smem, st, a);
+    }
     if (phase == 1) {
         const size_t smem = (size_t)min(a.T, 4) * 2 * a.L.kg_h * 4 * 4 * 16;
         static SmemOptIn optin_gu;

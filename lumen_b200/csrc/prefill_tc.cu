@@ -165,6 +165,17 @@ struct StagesOf {
     static constexpr int value = (RingOf<Q, ATMA>::value > 0) ? ((BN == 128) ? 3 : 2) : ((BN == 128) ? 4 : 3);
 };
 
+// Debug aid (compile with -DLUMEN_TC_TRACE): per CTA, the cycles the MMA thread and the first
+// producer warp spend in their waits, read back with lumen_debug_tc_trace.
+#ifdef LUMEN_TC_TRACE
+__device__ unsigned long long g_tc_trace[2][160][8];
+#define TRACE_WAIT(acc, expr) ([&] { const long long t0_ = clock64(); const bool r_ = (expr); (acc) += clock64() - t0_; return r_; }())
+#define TRACE_PUT(slot, v) g_tc_trace[MODE][blockIdx.x][slot] = (unsigned long long)(v)
+#else
+#define TRACE_WAIT(acc, expr) (expr)
+#define TRACE_PUT(slot, v)
+#endif
+
 template <int Q, int MODE, int BN, bool ATMA = false>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
@@ -182,8 +193,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     // BN: columns per tile
     constexpr int NACC = (BN == 128) ? 2 : 1;          // accumulator sets in TMEM
     // With one accumulator set the tensor pipe idles during a tile's epilogue. When the weights come
-    // by TMA the producer warps have nothing else to do and share the epilogue. (For dequantising
-    // producers the same was measured slower: they are the critical resource of those kernels.)
+    // by TMA the producer warps have nothing else to do and share the epilogue. (Dequantising
+    // producers doing the same was measured slower, 0.52 -> 0.60 ms per 4096-token Q4_0 call: their
+    // own work is what those kernels wait for.)
     constexpr bool HELP = (NACC == 1) && ATMA;
     constexpr int STAGES = StagesOf<Q, BN, ATMA>::value;  // one stage = 64 inputs (one swizzle atom in K)
     constexpr int RING = RingOf<Q, ATMA>::value;       // raw weight tiles in flight per producer warp (128-input groups)
@@ -346,6 +358,31 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             qp = qb + ((size_t)tidx * QTraits<Q>::NQ) * 32 + lane;
             sp = sb + (size_t)tidx * 8;
         };
+        // With one accumulator set (HELP) this warp also does a share of every tile's epilogue. Before
+        // it fills global stage number `it` it must have done so for every tile before the one stage
+        // it - STAGES belongs to: that stage is only consumed, and its slot freed, after those epilogues.
+        int helped = 0;
+        auto help_until = [&](int upto) {
+            if constexpr (HELP) {
+                while (ok && helped < upto) {
+                    const int4 tile = a.tiles[blockIdx.x + helped * gridDim.x];
+                    ok = mbar_wait(smem_u32(&acc_full_bar[0]), helped & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    epilogue_part(tile, 0, EPI_WARPS / 4 + (pw >> 2), EPI_PARTS);
+                    tc_fence_before();
+                    mbar_arrive(smem_u32(&acc_empty_bar[0]));
+                    ++helped;
+                }
+            }
+        };
+        auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool { return mbar_wait(bar, parity, abort_flag); };
+        auto warp_arrive = [&](uint32_t bar) {
+#ifndef LUMEN_TC_NOFENCE
+            fence_proxy_async();
+#endif
+            mbar_arrive(bar);
+        };
         if constexpr (RING > 0) {
             // this warp's ring: [RING][RAW_U4] uint4, behind the operand stages
             uint4* ring = reinterpret_cast<uint4*>(smem_raw + (stage0 - smem_u32(smem_raw)) + STAGES * STAGE_BYTES) +
@@ -382,11 +419,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     #pragma unroll
                 for (int sub = 0; sub < 2; ++sub, ++it) {
                     const int s = it % STAGES, ph = (it / STAGES) & 1;
-                    ok = ok && mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
+                    if (HELP && it >= STAGES) help_until((it - STAGES) / khs);
+                    ok = ok && warp_wait(smem_u32(&empty_bar[s]), ph ^ 1);
                     if (ok) {
                         dequant_store<Q>(cur, sub, stage0 + s * STAGE_BYTES + op * SUB_BYTES, rtl, lane);
-                        fence_proxy_async();
-                        mbar_arrive(smem_u32(&full_bar[s]));
+                        warp_arrive(smem_u32(&full_bar[s]));
                     }
                 }
             }
@@ -405,6 +442,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             int4 tile_n = tile_c;
             if (ngroups > 0) issue(tile_c, 0, cur);
             int it = 0, kg = 0, tl = 0;
+            long long tr_w = 0;
+            const long long tr_t0 = clock64();
             for (int n = 0; ok && n < ngroups; ++n) {
                 if (kg == 0 && tl + 1 < my_tiles) tile_n = a.tiles[blockIdx.x + (tl + 1) * gridDim.x];
                 if (n + 1 < ngroups) {
@@ -414,11 +453,11 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     #pragma unroll
                 for (int sub = 0; sub < 2; ++sub, ++it) {
                     const int s = it % STAGES, ph = (it / STAGES) & 1;
-                    ok = ok && mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abort_flag);
+                    if (HELP && it >= STAGES) help_until((it - STAGES) / khs);
+                    ok = ok && TRACE_WAIT(tr_w, warp_wait(smem_u32(&empty_bar[s]), ph ^ 1));
                     if (ok) {
                         dequant_store<Q>(cur, sub, stage0 + s * STAGE_BYTES + op * SUB_BYTES, rtl, lane);
-                        fence_proxy_async();
-                        mbar_arrive(smem_u32(&full_bar[s]));
+                        warp_arrive(smem_u32(&full_bar[s]));
                     }
                 }
                 if (n + 1 < ngroups) cur = nxt;
@@ -428,19 +467,14 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                     tile_c = tile_n;
                 }
             }
-        }
-        if constexpr (HELP) {
-            // TMA-fed weights: nothing to dequantise, this warp shares every tile's epilogue instead
-            for (int tl = 0; ok && tl < all_tiles; ++tl) {
-                const int4 tile = a.tiles[blockIdx.x + tl * gridDim.x];
-                ok = mbar_wait(smem_u32(&acc_full_bar[0]), tl & 1, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                epilogue_part(tile, 0, EPI_WARPS / 4 + (pw >> 2), EPI_PARTS);
-                tc_fence_before();
-                mbar_arrive(smem_u32(&acc_empty_bar[0]));
+            if (pw == 0 && lane == 0) {
+                TRACE_PUT(0, tr_w);
+                TRACE_PUT(1, clock64() - tr_t0);
             }
+            (void)tr_w;
+            (void)tr_t0;
         }
+        help_until(all_tiles);  // (TMA-fed weights: nothing was dequantised, every tile is still to do)
     } else if (warp < MMA_WARP) {
         // ------------------------- activation producers ------------------------
         // One thread feeds the activation operand with TMA: per 64-input stage one or two
@@ -494,6 +528,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         if (lane == 0) {
             int it = 0, tl = 0;
             bool ok = true;
+            long long tr_wf = 0, tr_wa = 0;
+            const long long tr_t0 = clock64();
             for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
                 const int4 tile = a.tiles[ti];
                 const int n16 = (tile.z + 15) & ~15;
@@ -501,12 +537,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 // weight operands of a stage forming one 256-row N operand
                 const uint32_t idesc = make_idesc(MODE == 1 ? 256 : n16, bf16_mode);
                 const int ab = tl % NACC, use = tl / NACC;
-                ok = mbar_wait(smem_u32(&acc_empty_bar[ab]), (use & 1) ^ 1, abort_flag);
+                ok = TRACE_WAIT(tr_wa, mbar_wait(smem_u32(&acc_empty_bar[ab]), (use & 1) ^ 1, abort_flag));
                 if (!ok) break;
                 tc_fence_after();
                 for (int kh = 0; kh < khs; ++kh, ++it) {
                     const int s = it % STAGES, ph = (it / STAGES) & 1;
-                    ok = mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag);
+                    ok = TRACE_WAIT(tr_wf, mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t sbase = stage0 + s * STAGE_BYTES;
@@ -530,6 +566,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 if (!ok) break;
                 umma_commit(smem_u32(&acc_full_bar[ab]));
             }
+            TRACE_PUT(2, tr_wf);
+            TRACE_PUT(3, tr_wa);
+            TRACE_PUT(4, clock64() - tr_t0);
+            TRACE_PUT(5, tl);
+            (void)tr_wf;
+            (void)tr_wa;
+            (void)tr_t0;
         }
         __syncwarp();
     }
@@ -707,3 +750,9 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
 }
 
 }  // namespace lumen
+
+#ifdef LUMEN_TC_TRACE
+extern "C" __attribute__((visibility("default"))) int lumen_debug_tc_trace(unsigned long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, lumen::tc::g_tc_trace, sizeof(unsigned long long) * 2 * 160 * 8);
+}
+#endif

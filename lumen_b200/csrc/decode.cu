@@ -20,6 +20,7 @@
 // streaming loads, every load of a warp's share is in flight before the first
 // use, and the arithmetic runs on the tensor cores (mma_frag.cuh).
 #include "decode_common.cuh"
+#include <type_traits>
 #include "router.cuh"
 
 namespace lumen {
@@ -338,8 +339,9 @@ template <int Q>
 __global__ void __launch_bounds__(GU_THREADS)
 gate_up_kernel(const __grid_constant__ DecodeArgs a) {
     __shared__ float red[GU_WARPS][4][16][4][2];  // [warp][group][row][token in group][gate,up]
-    pdl_trigger();
+    // wait first, then release the down kernel: it reads the router's tables before its own wait
     pdl_wait();
+    pdl_trigger();
     const int u = blockIdx.y;
     if (u >= *a.R.n_uexp) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -458,13 +460,18 @@ __device__ __forceinline__ void cp_async16_dc(void* smem_dst, const void* gsrc) 
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
 }
 
-template <int Q>
+// I8 (Q4_0 only): the SwiGLU outputs arrive as two-term int8 blocks (a.sq, written by
+// gate_up_stream_kernel) and the products run on the integer tensor cores, raw nibbles against
+// int8, as in the gate/up kernels: ~20 instead of ~33 instructions per 32-input block.
+template <int Q, bool I8 = false>
 __global__ void __launch_bounds__(DC_THREADS)
 down_combine_kernel(const __grid_constant__ DecodeArgs a) {
     __shared__ float dsm[DC_MAX_COLS][16];
     __shared__ int exp_s[MAX_EXPERTS], c0_s[MAX_EXPERTS], nc_s[MAX_EXPERTS];
+    // The routing tables come from the router kernel, which had completed before the gate/up kernel
+    // (the immediate predecessor) released this launch: they are read, and the first weight tiles
+    // they determine requested, before waiting for gate/up.
     pdl_trigger();
-    pdl_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, t4 = lane & 3;
     const int rt = blockIdx.x;
@@ -493,15 +500,20 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
     // (expert slot, k-group) of the next item to request / to prefetch activations for / to multiply:
     // three cursors stepped by one item, no division in the loop
     int is_u = warp, is_kg = 0, is_slot = 0;
+    const uint4 *is_q = nullptr, *is_s = nullptr;  // this lane's source words of the next item
     auto issue = [&]() {
         if (is_u < U) {
-            const int ee = exp_s[is_u];
-            const int tile = rt * kg_i + is_kg;
+            if (is_kg == 0) {
+                const int ee = exp_s[is_u];
+                is_q = a.L.down_q(ee) + (size_t)rt * kg_i * NQ32 + lane;
+                is_s = a.L.down_s(ee) + (size_t)rt * kg_i * 8 + lane;
+            }
             uint4* slot = my_ring + (size_t)is_slot * TU4;
-            const uint4* qp = a.L.down_q(ee) + (size_t)tile * NQ32 + lane;
 #pragma unroll
-            for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16_dc(slot + j * 32 + lane, qp + j * 32);
-            if (Q != BF16 && lane < 8) cp_async16_dc(slot + NQ32 + lane, a.L.down_s(ee) + (size_t)tile * 8 + lane);
+            for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16_dc(slot + j * 32 + lane, is_q + j * 32);
+            if (Q != BF16 && lane < 8) cp_async16_dc(slot + NQ32 + lane, is_s);
+            is_q += NQ32;
+            is_s += 8;
             if (++is_kg == kg_i) {
                 is_kg = 0;
                 is_u += DC_WARPS;
@@ -512,31 +524,72 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
     };
 #pragma unroll 1
     for (int i = 0; i < DcRing<Q>::value; ++i) issue();
+    pdl_wait();  // the SwiGLU outputs are final from here on
     float acc[4][4];
-    const uint4* bbase[4] = {nullptr, nullptr, nullptr, nullptr};
     int c0 = 0, ncol = 0, ng = 0;
     // activation fragments of the first column group (an expert rarely has more than four columns
     // here) are fetched one item ahead, so that their L2 latency is not paid tile by tile
+    const int sq_term = dcommon::xq_term_words(nblk_i_pad), sq_tok = dcommon::xq_tok_words(nblk_i_pad);
+    // B operand of block b of item (expert slot u_slot, k-group kgx), column group g. f16 form: the
+    // lane's fragment of the hi / lo plane of its column. Int8 form: {word pair of the lane's
+    // column and term, {sx, 8 sx sum q} of the column of the lane's accumulators}.
+    auto load_b = [&](int u_slot, int kgx, int g, int b) -> uint4 {
+        const int ncu = nc_s[u_slot], c0u = c0_s[u_slot];
+        const int colr = 4 * g + (gq >> 1);
+        if (I8) {
+            const int cols = 4 * g + t4;
+            uint2 w = make_uint2(0u, 0u);
+            if (colr < ncu)
+                w = __ldg(reinterpret_cast<const uint2*>(a.sq + (size_t)(c0u + colr) * sq_tok + (gq & 1) * sq_term +
+                                                         (size_t)(kgx * 4 + b) * 8 + t4 * 2));
+            const float2 sc = __ldg(reinterpret_cast<const float2*>(a.sq + (size_t)(c0u + (cols < ncu ? cols : 0)) * sq_tok +
+                                                                    2 * sq_term) + kgx * 4 + b);
+            return make_uint4(w.x, w.y, __float_as_uint(sc.x), __float_as_uint(sc.y));
+        }
+        if (colr >= ncu) return make_uint4(0u, 0u, 0u, 0u);
+        return ldg_cached(a.sf + ((size_t)((c0u + colr) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4 + (size_t)kgx * 16 + b * 4);
+    };
+    // group 0 of the next item: running pointers, recomputed when the expert changes (null = no column)
     int pb_u = warp, pb_kg = 0;
-    auto b0_next = [&]() -> const uint4* {
-        const uint4* p = nullptr;
+    const unsigned* pb_w = nullptr;  // int8 form: word pairs of the lane's column and term | f16 form: fragments
+    const float2* pb_s = nullptr;    // int8 form: scales of the column of the lane's accumulators
+    uint4 bnx[4];
+    auto b0_next = [&]() {
         if (pb_u < U) {
-            const int colr = gq >> 1;
-            if (colr < nc_s[pb_u])
-                p = a.sf + ((size_t)((c0_s[pb_u] + colr) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4 + (size_t)pb_kg * 16;
+            if (pb_kg == 0) {
+                const int ncu = nc_s[pb_u], c0u = c0_s[pb_u];
+                const int colr = gq >> 1;
+                if (I8) {
+                    pb_w = (colr < ncu) ? a.sq + (size_t)(c0u + colr) * sq_tok + (gq & 1) * sq_term + t4 * 2 : nullptr;
+                    pb_s = reinterpret_cast<const float2*>(a.sq + (size_t)(c0u + (t4 < ncu ? t4 : 0)) * sq_tok + 2 * sq_term);
+                } else {
+                    pb_w = (colr < ncu) ? reinterpret_cast<const unsigned*>(
+                                              a.sf + ((size_t)((c0u + colr) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4)
+                                        : nullptr;
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                if (I8) {
+                    const uint2 w = pb_w ? __ldg(reinterpret_cast<const uint2*>(pb_w) + b * 4) : make_uint2(0u, 0u);
+                    const float2 sc = __ldg(pb_s + b);
+                    bnx[b] = make_uint4(w.x, w.y, __float_as_uint(sc.x), __float_as_uint(sc.y));
+                } else {
+                    bnx[b] = pb_w ? ldg_cached(reinterpret_cast<const uint4*>(pb_w) + b * 4) : make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            if (pb_w) pb_w += I8 ? 32 : 64;  // one k-group on: 4 blocks x 8 words | 16 uint4
+            pb_s += 4;
             if (++pb_kg == kg_i) {
                 pb_kg = 0;
                 pb_u += DC_WARPS;
             }
-        }
-        return p;
-    };
-    uint4 bnx[4];
-    {
-        const uint4* p0 = b0_next();
+        } else {
 #pragma unroll
-        for (int b = 0; b < 4; ++b) bnx[b] = p0 ? ldg_cached(p0 + b * 4) : make_uint4(0u, 0u, 0u, 0u);
-    }
+            for (int b = 0; b < 4; ++b) bnx[b] = make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    b0_next();
     int uu = warp - DC_WARPS, kg = kg_i - 1, rslot = 0;
 #pragma unroll 1
     for (int n = 0; n < nitems; ++n) {
@@ -555,11 +608,7 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
         uint4 bcur[4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) bcur[b] = bnx[b];
-        {
-            const uint4* p1 = b0_next();
-#pragma unroll
-            for (int b = 0; b < 4; ++b) bnx[b] = p1 ? ldg_cached(p1 + b * 4) : make_uint4(0u, 0u, 0u, 0u);
-        }
+        b0_next();
         if (++kg == kg_i) {
             kg = 0;
             uu += DC_WARPS;
@@ -569,41 +618,62 @@ down_combine_kernel(const __grid_constant__ DecodeArgs a) {
             ncol = nc_s[uu];
             ng = (ncol + 3) >> 2;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                const int colr = 4 * g + (gq >> 1);
-                bbase[g] = (colr < ncol)
-                               ? a.sf + ((size_t)((c0 + colr) * 2 + (gq & 1)) * nblk_i_pad) * 4 + t4
-                               : nullptr;
+            for (int g = 0; g < 4; ++g)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[g][i] = 0.0f;
-            }
         }
-        // group 0 from the prefetched registers, further groups (rare) through their pointers
+        // Group 0 from the prefetched registers, further groups fetched in place. An expert with more
+        // than four columns is rare in a decode batch, so the one-group case gets code of its own:
+        // in the four-group form the compiler predicates the other groups' bodies instead of
+        // branching around them, and a tile then costs ~400 issued instructions instead of ~150.
+        auto tile_blocks = [&](auto ng_tag) {
+            constexpr int NG = decltype(ng_tag)::value;
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            uint32_t a_lo[4], a_hi[4];
-            unpack_block<Q>(cur, b, a_lo, a_hi);
-            const float2 sc = block_scales<Q>(cur, b);
+            for (int b = 0; b < 4; ++b) {
+                const float2 sc = block_scales<Q>(cur, b);
+                if (I8) {
+                    const uint4 qv = cur.q[(b >> 1) % QTraits<Q>::NQ];
+                    const unsigned w0 = (b & 1) ? qv.z : qv.x, w8 = (b & 1) ? qv.w : qv.y;
+                    const unsigned a0 = w0 & 0x0F0F0F0Fu, a1 = w8 & 0x0F0F0F0Fu;
+                    const unsigned a2 = (w0 >> 4) & 0x0F0F0F0Fu, a3 = (w8 >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-                if (g < ng) {
-                    uint4 bf = bcur[b];
-                    if (g > 0) bf = bbase[g] ? ldg_cached(bbase[g] + (size_t)kg * 16 + b * 4) : make_uint4(0u, 0u, 0u, 0u);
-                    float c[4] = {0.f, 0.f, 0.f, 0.f};
-                    if (Q == BF16) {
-                        mma_bf16(c, a_lo, bf.x, bf.y);
-                        mma_bf16(c, a_hi, bf.z, bf.w);
-                    } else {
-                        mma_f16(c, a_lo, bf.x, bf.y);
-                        mma_f16(c, a_hi, bf.z, bf.w);
+                    for (int g = 0; g < NG; ++g) {
+                        if (g == 0 || g < ng) {
+                            const uint4 bf = (g == 0) ? bcur[b] : load_b(uu, kg, g, b);
+                            int c[4] = {0, 0, 0, 0};
+                            dcommon::mma_u8s8(c, a0, a1, a2, a3, bf.x, bf.y);
+                            const float sx = __uint_as_float(bf.z), off = __uint_as_float(bf.w);
+                            const float k1 = 1.0f / 254.0f;
+                            acc[g][0] = fmaf(sc.x, fmaf(sx, fmaf((float)c[1], k1, (float)c[0]), -off), acc[g][0]);
+                            acc[g][2] = fmaf(sc.y, fmaf(sx, fmaf((float)c[3], k1, (float)c[2]), -off), acc[g][2]);
+                        }
                     }
-                    acc[g][0] = fmaf(sc.x, c[0], acc[g][0]);
-                    acc[g][1] = fmaf(sc.x, c[1], acc[g][1]);
-                    acc[g][2] = fmaf(sc.y, c[2], acc[g][2]);
-                    acc[g][3] = fmaf(sc.y, c[3], acc[g][3]);
+                } else {
+                    uint32_t a_lo[4], a_hi[4];
+                    unpack_block<Q>(cur, b, a_lo, a_hi);
+#pragma unroll
+                    for (int g = 0; g < NG; ++g) {
+                        if (g == 0 || g < ng) {
+                            const uint4 bf = (g == 0) ? bcur[b] : load_b(uu, kg, g, b);
+                            float c[4] = {0.f, 0.f, 0.f, 0.f};
+                            if (Q == BF16) {
+                                mma_bf16(c, a_lo, bf.x, bf.y);
+                                mma_bf16(c, a_hi, bf.z, bf.w);
+                            } else {
+                                mma_f16(c, a_lo, bf.x, bf.y);
+                                mma_f16(c, a_hi, bf.z, bf.w);
+                            }
+                            acc[g][0] = fmaf(sc.x, c[0], acc[g][0]);
+                            acc[g][1] = fmaf(sc.x, c[1], acc[g][1]);
+                            acc[g][2] = fmaf(sc.y, c[2], acc[g][2]);
+                            acc[g][3] = fmaf(sc.y, c[3], acc[g][3]);
+                        }
+                    }
                 }
             }
-        }
+        };
+        if (ng <= 1) tile_blocks(std::integral_constant<int, 1>{});
+        else tile_blocks(std::integral_constant<int, 4>{});
         if (kg == kg_i - 1) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -732,12 +802,12 @@ static cudaError_t launch_pdl(Kern kern, dim3 grid, dim3 block, cudaStream_t st,
     return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
-template <int Q>
+template <int Q, bool I8 = false>
 static cudaError_t launch_down_combine(const DecodeArgs& a, dim3 grid, cudaStream_t st) {
     const size_t smem = (size_t)DC_WARPS * DcRing<Q>::value * (QTraits<Q>::NQ * 32 + 8) * 16;
     static SmemOptIn optin;
     {
-        cudaError_t e = ensure_dyn_smem(down_combine_kernel<Q>, smem, optin);
+        cudaError_t e = ensure_dyn_smem(down_combine_kernel<Q, I8>, smem, optin);
         if (e != cudaSuccess) return e;
     }
     cudaLaunchConfig_t cfg = {};
@@ -751,7 +821,7 @@ static cudaError_t launch_down_combine(const DecodeArgs& a, dim3 grid, cudaStrea
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     count_launch();
-    return cudaLaunchKernelEx(&cfg, down_combine_kernel<Q>, a);
+    return cudaLaunchKernelEx(&cfg, down_combine_kernel<Q, I8>, a);
 }
 
 cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st) {
@@ -759,12 +829,16 @@ cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st) {
 }
 
 bool decode_small_applicable(const DecodeArgs& a, int phase);
+bool decode_stream_applicable(const DecodeArgs& a);
 cudaError_t launch_decode_small_phase(const DecodeArgs& a, int phase, cudaStream_t st);
 
 cudaError_t launch_decode_phase(const DecodeArgs& a_in, int phase, cudaStream_t st) {
     // the int8 activation form belongs to the Q4_0 gate/up kernel that walks columns four at a time
     DecodeArgs a = a_in;
     if (!(a.xq != nullptr && a.xf != nullptr && a.L.quant == Q4_0 && decode_small_applicable(a, 1))) a.xq = nullptr;
+    // 5..16 tokens, Q4_0: streaming gate/up that hands the down product int8 activations
+    const bool stream = decode_stream_applicable(a);
+    if (!stream) a.sq = nullptr;
     if (phase == 0) return launch_route_small(a, st);
     if (decode_small_applicable(a, phase)) return launch_decode_small_phase(a, phase, st);
     const int C = a.T * a.K;
@@ -778,7 +852,7 @@ cudaError_t launch_decode_phase(const DecodeArgs& a_in, int phase, cudaStream_t 
         }
     }
     switch (a.L.quant) {
-        case Q4_0: return launch_down_combine<Q4_0>(a, g_dc, st);
+        case Q4_0: return stream ? launch_down_combine<Q4_0, true>(a, g_dc, st) : launch_down_combine<Q4_0>(a, g_dc, st);
         case Q8_0: return launch_down_combine<Q8_0>(a, g_dc, st);
         default: return launch_down_combine<BF16>(a, g_dc, st);
     }

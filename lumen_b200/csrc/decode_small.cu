@@ -288,6 +288,7 @@ constexpr int GS_TU4 = QTraits<Q4_0>::NQ * 32 + 8;  // uint4 of one raw tile: qu
 __global__ void __launch_bounds__(GS_WARPS * 32, 1)
 gate_up_stream_kernel(const __grid_constant__ DecodeArgs a) {
     extern __shared__ uint4 gs_ring[];  // [GS_WARPS][GS_RING][gate | up][GS_TU4]
+    __shared__ float pair_s[GS_WARPS][4][2];  // [warp][column][absmax | sum] for the partner warp
     pdl_wait();
     pdl_trigger();
     constexpr int NQ32 = QTraits<Q4_0>::NQ * 32;
@@ -308,9 +309,14 @@ gate_up_stream_kernel(const __grid_constant__ DecodeArgs a) {
         cp_async_wait_all();
         __syncthreads();
     }
-    // warp-major numbering over the grid: consecutive items go to different SMs
-    for (int item = warp * gridDim.x + blockIdx.x; item < nitems; item += GS_WARPS * gridDim.x) {
-        const int u = item / rt_i, rt = item - u * rt_i;
+    // Warps 2p and 2p+1 of a CTA take the two 16-row halves of the same 32-row block of I, so that
+    // together they hold the block an int8 activation scale belongs to (see the epilogue).
+    // Pair-major numbering over the grid: consecutive blocks go to different SMs.
+    const int sq_term = xq_term_words(nblk_i_pad), sq_tok = xq_tok_words(nblk_i_pad);
+    const int half = warp & 1, pair_bar = 1 + (warp >> 1);
+    for (int pitem = (warp >> 1) * gridDim.x + blockIdx.x; pitem < nitems / 2; pitem += (GS_WARPS / 2) * gridDim.x) {
+        const int u = pitem / (rt_i / 2), blk_i = pitem - u * (rt_i / 2);
+        const int rt = blk_i * 2 + half;
         const int4 wd = a.R.work[2 * u];      // {expert, first column, columns}
         const int4 wt = a.R.work[2 * u + 1];  // source tokens of the first four columns
         const int e = wd.x, c0 = wd.y;
@@ -383,15 +389,46 @@ gate_up_stream_kernel(const __grid_constant__ DecodeArgs a) {
                 }
             }
             asm volatile("cp.async.wait_group 0;" ::: "memory");
-            if (t4 < ncol) {
-                const int col = c0 + cb + t4;
+            // SwiGLU of rows gq, gq + 8 of column t4, then the block's two-term int8 form for the down
+            // product (x ~ sx (q0 + q1 / 254), sx = absmax / 127 over the 32 rows of the block): the
+            // absmax and the sum of the quantised values need the partner warp's half, exchanged
+            // through shared memory behind a named barrier of the pair.
+            const bool cvalid = t4 < ncol;
+            const float sv0 = cvalid ? (acc_g0 / (1.0f + expf(-acc_g0))) * acc_u0 : 0.0f;
+            const float sv8 = cvalid ? (acc_g8 / (1.0f + expf(-acc_g8))) * acc_u8 : 0.0f;
+            const int col = c0 + cb + (cvalid ? t4 : 0);
+            if (cvalid && a.s_f32 != nullptr) {
+                a.s_f32[(size_t)col * I + rt * 16 + gq] = sv0;
+                a.s_f32[(size_t)col * I + rt * 16 + gq + 8] = sv8;
+            }
+            float am = fmaxf(fabsf(sv0), fabsf(sv8));
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const float gate = h ? acc_g8 : acc_g0, up = h ? acc_u8 : acc_u0;
-                    const float sv = (gate / (1.0f + expf(-gate))) * up;
-                    const int irow = rt * 16 + gq + 8 * h;
-                    if (a.s_f32 != nullptr) a.s_f32[(size_t)col * I + irow] = sv;
-                    store_swiglu_frag<Q4_0>(a.sf, col, irow, nblk_i_pad, sv);
+            for (int o = 4; o < 32; o <<= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+            if (gq == 0) pair_s[warp][t4][0] = am;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            am = fmaxf(am, pair_s[warp ^ 1][t4][0]);
+            const float inv = (am > 0.0f) ? 127.0f / am : 0.0f;
+            const float sx = am * (1.0f / 127.0f);
+            const float r0 = sv0 * inv, r8 = sv8 * inv;
+            const float q00 = rintf(r0), q08 = rintf(r8);
+            const float q10 = rintf((r0 - q00) * 254.0f), q18 = rintf((r8 - q08) * 254.0f);
+            float sum = (q00 + q08) + (q10 + q18) * (1.0f / 254.0f);
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            if (gq == 0) pair_s[warp][t4][1] = sum;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            if (cvalid) {
+                // input i of the block (0..31) is byte i % 4 of word (i % 16) / 4 * 2 + i / 16
+                unsigned* sqc = a.sq + (size_t)col * sq_tok;
+                signed char* w0 = reinterpret_cast<signed char*>(sqc + blk_i * 8 + (gq >> 2) * 2 + half) + (gq & 3);
+                signed char* w8 = reinterpret_cast<signed char*>(sqc + blk_i * 8 + (2 + (gq >> 2)) * 2 + half) + (gq & 3);
+                w0[0] = (signed char)(int)q00;
+                w8[0] = (signed char)(int)q08;
+                w0[(size_t)sq_term * 4] = (signed char)(int)q10;
+                w8[(size_t)sq_term * 4] = (signed char)(int)q18;
+                if (half == 0 && gq == 0) {
+                    const float total = sum + pair_s[warp ^ 1][t4][1];  // first half + second half
+                    reinterpret_cast<float2*>(sqc + 2 * sq_term)[blk_i] = make_float2(sx, 8.0f * sx * total);
                 }
             }
             __syncwarp();
@@ -431,13 +468,23 @@ bool decode_small_applicable(const DecodeArgs& a, int phase) {
     return (phase == 1) ? gu_smem <= 160 * 1024 : dn_smem <= 200 * 1024;
 }
 
+static size_t gate_up_stream_smem(const DecodeArgs& a) {
+    return (size_t)GS_WARPS * GS_RING * 2 * GS_TU4 * 16 + (size_t)a.T * xq_tok_words(a.L.kg_h * 4) * 4;
+}
+
+// The streaming gate/up kernel and the int8 down product that consumes its output: Q4_0 layers,
+// 5..16 tokens, batch activations + rings within shared memory.
+bool decode_stream_applicable(const DecodeArgs& a) {
+    return a.L.quant == Q4_0 && a.xq != nullptr && a.sq != nullptr && a.T > 4 && a.T <= DECODE_MAX_TOKENS &&
+           a.L.kg_h <= 16 && (a.L.rt_i & 1) == 0 && gate_up_stream_smem(a) <= 220 * 1024;
+}
+
 template <int Q>
 static cudaError_t launch_small_t(const DecodeArgs& a, int phase, cudaStream_t st) {
     const int C = a.T * a.K;
     const int nu = C < a.L.E ? C : a.L.E;
-    const size_t gs_smem = (size_t)GS_WARPS * GS_RING * 2 * GS_TU4 * 16 + (size_t)a.T * xq_tok_words(a.L.kg_h * 4) * 4;
-    if (phase == 1 && Q == Q4_0 && a.xq != nullptr && a.T > 4 && gs_smem <= 220 * 1024) {
-        const size_t smem = gs_smem;
+    if (phase == 1 && decode_stream_applicable(a)) {
+        const size_t smem = gate_up_stream_smem(a);
         static SmemOptIn optin_gs;
         cudaError_t e = ensure_dyn_smem(gate_up_stream_kernel, smem, optin_gs);
         if (e != cudaSuccess) return e;

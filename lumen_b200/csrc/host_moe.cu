@@ -147,12 +147,12 @@ Status build_repacked(const CudaMoeScratch& sc, const void* layer_buf, size_t bl
 }
 
 static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
-    // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf, w16, xq, xr16, rpart
+    // order: logits, ids, weights, col_expert, col_src_tok, dst_to_col, blk_hist, tiles, s16, d16, x16, xf, sf, w16, xq, xr16, rpart, sq
     const size_t C = (size_t)cap * s.K;
     const size_t nblk_h_pad = (size_t)((s.H / 32 + 3) / 4) * 4, nblk_i_pad = (size_t)((s.I / 32 + 3) / 4) * 4;
     const size_t max_ct = C / 128 + s.E, max_ct_dn = C / 128 + s.E;  // gate/up tiles of 128 or 256 columns (sized for 128), down tiles of 128
     const size_t n_tile_entries = max_ct * ((size_t)s.I / 128 + 1) + max_ct_dn * ((size_t)s.H / 256 + 1);
-    size_t sizes[17] = {
+    size_t sizes[18] = {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,
         (size_t)((cap + 31) / 32) * s.E * 4,
         n_tile_entries * sizeof(int4),
@@ -161,9 +161,10 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
         (size_t)s.E * s.H * 4,
         (size_t)DECODE_MAX_TOKENS * (18 * nblk_h_pad + 16) * 4,  // xq_tok_words(nblk_h_pad) words per token
         (size_t)cap * s.H * 2 * 2,
-        (size_t)ROUTER_TC_MAX_KSPLIT * cap * s.E * 4};
+        (size_t)ROUTER_TC_MAX_KSPLIT * cap * s.E * 4,
+        (size_t)DECODE_MAX_TOKENS * s.K * (18 * nblk_i_pad + 16) * 4};  // xq_tok_words(nblk_i_pad) words per decode column
     size_t off = 0;
-    for (int i = 0; i < 17; ++i) {
+    for (int i = 0; i < 18; ++i) {
         offs[i] = off;
         off += align_up(sizes[i], 256);
     }
@@ -171,7 +172,7 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
 }
 
 static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
-    size_t offs[17];
+    size_t offs[18];
     const size_t bytes = tok_arena_bytes(*s, cap, offs);
     void* p = nullptr;
     CUDA_TRY(cudaMalloc(&p, bytes));
@@ -199,6 +200,7 @@ static Status alloc_tok_arena(CudaMoeScratch* s, int cap) {
     s->xq = reinterpret_cast<unsigned*>(b + offs[14]);
     s->xr16 = reinterpret_cast<__half*>(b + offs[15]);
     s->rpart = reinterpret_cast<float*>(b + offs[16]);
+    s->sq = reinterpret_cast<unsigned*>(b + offs[17]);
     return Status::Ok();
 }
 
@@ -348,6 +350,7 @@ static DecodeArgs make_decode_args(CudaMoeScratch* s, const MoeLayer& layer, int
     a.R = s->R;
     a.xf = s->xf;
     a.xq = s->xq;
+    a.sq = s->sq;
     a.sf = s->sf;
     a.s_f32 = nullptr;
     a.T = tokens;
@@ -428,6 +431,7 @@ Status encode_route_only(CudaMoeScratch* s, const MoeLayer* layer, const float* 
         a.logits_override = logits_in;
         a.xf = nullptr;
         a.xq = nullptr;
+        a.sq = nullptr;
         CUDA_TRY(launch_route_small(a, st));
     } else {
         PrefillArgs p{};

@@ -98,6 +98,7 @@ struct CudaMoeScratch {
     RouteDev R{};
     uint4* xf = nullptr;    // decode activation fragments
     unsigned* xq = nullptr; // decode activations as two-term int8 blocks (Q4_0 gate/up of the three-kernel chain)
+    unsigned* sq = nullptr; // SwiGLU outputs of a 5..16-token Q4_0 decode in the same form, per compact column
     uint4* sf = nullptr;    // decode SwiGLU fragments
     float* s_f32 = nullptr; // optional debug copy
     // prefill (grow-only)

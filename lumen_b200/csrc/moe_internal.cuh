@@ -95,6 +95,7 @@ struct DecodeArgs {
     const float* logits_override;  // [T,E] or null
     uint4* xf;              // activation fragments [T][2][kg_h*4][4]
     unsigned* xq;           // two-term int8 activations [T][xq_tok_words] of the three-kernel chain's Q4_0 gate/up (null = f16 fragments in xf)
+    unsigned* sq;           // two-term int8 SwiGLU outputs [C][xq_tok_words(kg_i*4)]: down operand of the 5..16-token Q4_0 chain (null = f16 fragments in sf)
     uint4* sf;              // SwiGLU fragments     [C][2][kg_i*4][4]
     float* s_f32;           // optional [C,I] f32 copy of the SwiGLU output (null = skip)
     int T, K, gating;

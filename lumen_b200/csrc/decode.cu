@@ -287,7 +287,9 @@ router_small_kernel(const __grid_constant__ DecodeArgs a) {
 constexpr int GU_THREADS = 256;
 constexpr int GU_WARPS = GU_THREADS / 32;
 
-template <int Q>
+// NG: column groups the code covers (1 or 4). The groups' bodies are predicated, not branched
+// around, so a caller that knows there is one group uses NG = 1 and issues a quarter of the code.
+template <int Q, int NG = 4>
 __device__ __forceinline__ void tile_mma_pair(const WTile<Q>& wg, const WTile<Q>& wu,
                                               const uint4* (&bptr)[4], int ngroups,
                                               float (&acc_g)[4][4], float (&acc_u)[4][4]) {
@@ -299,7 +301,7 @@ __device__ __forceinline__ void tile_mma_pair(const WTile<Q>& wg, const WTile<Q>
         const float2 sg = block_scales<Q>(wg, b);
         const float2 su = block_scales<Q>(wu, b);
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
+        for (int g = 0; g < NG; ++g) {
             if (g < ngroups) {
                 uint4 bf = make_uint4(0u, 0u, 0u, 0u);
                 if (bptr[g] != nullptr) bf = ldg_cached(bptr[g] + b * 4);
@@ -390,7 +392,8 @@ gate_up_kernel(const __grid_constant__ DecodeArgs a) {
             const uint4* bp[4];
 #pragma unroll
             for (int g = 0; g < 4; ++g) bp[g] = bbase[g] ? bbase[g] + (size_t)kg * 16 : nullptr;
-            tile_mma_pair<Q>(wg, wu, bp, ng, acc_g, acc_u);
+            if (ng <= 1) tile_mma_pair<Q, 1>(wg, wu, bp, ng, acc_g, acc_u);
+            else tile_mma_pair<Q, 4>(wg, wu, bp, ng, acc_g, acc_u);
             if (more) {
                 wg = ng_t;
                 wu = nu_t;

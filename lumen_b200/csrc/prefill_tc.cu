@@ -191,7 +191,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     // epilogue of tile i runs under the MMAs of tile i+1.
     constexpr int NA = 2;
     // BN: columns per tile
-    constexpr int NACC = (BN == 128) ? 2 : 1;          // accumulator sets in TMEM
+    // Accumulator sets in TMEM (512 columns). Gate/up: a set is the gate and the up accumulator of BN
+    // columns each, so 128-column tiles have two sets and 256-column tiles one. Down: a set is 256
+    // columns (the output rows of an m-tile) for 128 tokens, always two of them; a 256-token tile of
+    // the BN = 256 form takes both at once (its two token halves, one weight stage serving both),
+    // a tile of up to 128 tokens takes one, and the epilogue works through the halves one by one.
+    constexpr int NACC = (MODE == 1 || BN == 128) ? 2 : 1;
+    constexpr int ACC_COLS = (MODE == 1) ? 256 : NA * BN;  // TMEM columns of one set
     // With one accumulator set the tensor pipe idles during a tile's epilogue. When the weights come
     // by TMA the producer warps have nothing else to do and share the epilogue. (Dequantising
     // producers doing the same was measured slower, 0.52 -> 0.60 ms per 4096-token Q4_0 call: their
@@ -201,7 +207,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     constexpr int RING = RingOf<Q, ATMA>::value;       // raw weight tiles in flight per producer warp (128-input groups)
     constexpr int RAW_U4 = QTraits<Q>::NQ * 32 + 8;    // uint4 of one raw tile: lane-major quant words, then 8 scale words
     constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operands then B
-    constexpr int TMEM_COLS = NA * BN * NACC;
+    constexpr int TMEM_COLS = ACC_COLS * NACC;
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[NACC], acc_empty_bar[NACC];
@@ -243,19 +249,17 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 
     // Epilogue of one tile by one warp: the warp's TMEM lanes are 32 (warp % 4).. (hardware rule);
     // of the tile's 16-column TMEM chunks it takes those with chunk % nparts == part.
-    auto epilogue_part = [&](const int4& tile, int ab, int part, int nparts) {
+    auto epilogue_part = [&](const int4& tile, int ab, int h, int part, int nparts) {
         const int row = (warp & 3) * 32 + lane;
         const int ncols = tile.z;
-        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ab * NA * BN;
+        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ab * ACC_COLS;
         if (MODE == 1) {
             // Down product: the tile's columns (tokens) are the TMEM lanes and the 256 output rows
             // of the m-tile the TMEM columns, so a thread owns one token and reads 16 consecutive
             // output rows per load: its stores are 16 bytes wide and each token's 512 bytes are
-            // contiguous (a whole NVLink packet when the row lives on another rank). A 256-column
-            // tile is two such token halves side by side in TMEM.
-#pragma unroll 1
-            for (int h = 0; h < BN / 128 && h * 128 < ncols; ++h) {
-                const int tcol = h * 128 + row;  // token column of the tile
+            // contiguous (a whole NVLink packet when the row lives on another rank).
+            {
+                const int tcol = h * 128 + row;  // token column of the tile (h: its half of a 256-token tile)
                 bool live = tcol < ncols;
                 __half* dst = a.out16;
                 if (live) {
@@ -275,7 +279,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 #pragma unroll 2
                 for (int n0 = part * 16; n0 < 256; n0 += nparts * 16) {
                     uint32_t v[16];
-                    tmem_ld16(taddr + h * 256 + n0, v);
+                    tmem_ld16(taddr + n0, v);
                     tmem_ld_wait();
                     if (live) {
                         uint32_t hh[8];
@@ -294,22 +298,49 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             // Gate/up: a thread owns one row of I (its TMEM lane) and walks the token columns
             const int irow = tile.w * 128 + row;  // SwiGLU output is stored in the order the down product reads it
             const size_t off0 = ATMA ? (size_t)irow : (size_t)(irow & ~31) + perm_pos(irow & 31);
-            for (int n0 = part * 16; n0 < ncols; n0 += nparts * 16) {
-                uint32_t v0[16], v1[16];
-                tmem_ld16(taddr + n0, v0);
-                tmem_ld16(taddr + BN + n0, v1);
-                tmem_ld_wait();
-                __half* dst = a.out16 + (size_t)(tile.y + n0) * a.out_ld + off0;
+            // 8-column pieces of this warp's 16-column chunks, the TMEM loads of the next piece issued
+            // before the current one is worked on
+            auto piece_col = [&](int p) { return part * 16 + (p >> 1) * nparts * 16 + (p & 1) * 8; };
+            auto work = [&](int col, const uint32_t (&g)[8], const uint32_t (&u)[8]) {
+                __half* dst = a.out16 + (size_t)(tile.y + col) * a.out_ld + off0;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (n0 + j < ncols) {
-                        const float gt = __uint_as_float(v0[j]);
+                for (int j = 0; j < 8; ++j) {
+                    if (col + j < ncols) {
+                        const float gt = __uint_as_float(g[j]);
                         // SwiGLU (cuda/shaders/moe_expert.cu:47-50) with the fast exp and divide: their
                         // error (~2^-21) is far below the f16 rounding of the result that follows
                         dst[(size_t)j * a.out_ld] =
-                            __float2half_rn(__fdividef(gt, 1.0f + __expf(-gt)) * __uint_as_float(v1[j]));
+                            __float2half_rn(__fdividef(gt, 1.0f + __expf(-gt)) * __uint_as_float(u[j]));
                     }
                 }
+            };
+            uint32_t g0[8], u0[8], g1[8], u1[8];
+            int p = 0;
+            if (piece_col(0) < ncols) {
+                tmem_ld8(taddr + piece_col(0), g0);
+                tmem_ld8(taddr + BN + piece_col(0), u0);
+            }
+            while (piece_col(p) < ncols) {
+                // (the loop condition is uniform over the warp: tcgen05.ld is a warp-wide instruction)
+                tmem_ld_wait();
+                tmem_ld_fence8(g0);
+                tmem_ld_fence8(u0);
+                const bool more1 = piece_col(p + 1) < ncols;
+                if (more1) {
+                    tmem_ld8(taddr + piece_col(p + 1), g1);
+                    tmem_ld8(taddr + BN + piece_col(p + 1), u1);
+                }
+                work(piece_col(p), g0, u0);
+                if (!more1) break;
+                tmem_ld_wait();
+                tmem_ld_fence8(g1);
+                tmem_ld_fence8(u1);
+                if (piece_col(p + 2) < ncols) {
+                    tmem_ld8(taddr + piece_col(p + 2), g0);
+                    tmem_ld8(taddr + BN + piece_col(p + 2), u0);
+                }
+                work(piece_col(p + 1), g1, u1);
+                p += 2;
             }
         }
     };
@@ -317,17 +348,20 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 
     if (warp < EPI_WARPS) {
         // ------------------------------ epilogue ------------------------------
-        int tl = 0;
+        int v = 0;  // accumulator sets handed over so far: set v % NACC, used v / NACC times before
         bool ok = true;
-        for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
+        for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x) {
             const int4 tile = a.tiles[ti];
-            const int ab = tl % NACC, use = tl / NACC;  // accumulator set and how often it has been used
-            ok = mbar_wait(smem_u32(&acc_full_bar[ab]), use & 1, abort_flag);
-            if (!ok) break;
-            tc_fence_after();
-            epilogue_part(tile, ab, warp >> 2, EPI_PARTS);
-            tc_fence_before();
-            mbar_arrive(smem_u32(&acc_empty_bar[ab]));
+            const int nh = (MODE == 1 && tile.z > 128) ? 2 : 1;
+            for (int h = 0; ok && h < nh; ++h, ++v) {
+                const int ab = v % NACC, use = v / NACC;
+                ok = mbar_wait(smem_u32(&acc_full_bar[ab]), use & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                epilogue_part(tile, ab, h, warp >> 2, EPI_PARTS);
+                tc_fence_before();
+                mbar_arrive(smem_u32(&acc_empty_bar[ab]));
+            }
         }
     } else if (warp < B_WARP0) {
         // --------------------------- weight producers --------------------------
@@ -369,7 +403,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                     ok = mbar_wait(smem_u32(&acc_full_bar[0]), helped & 1, abort_flag);
                     if (!ok) break;
                     tc_fence_after();
-                    epilogue_part(tile, 0, EPI_WARPS / 4 + (pw >> 2), EPI_PARTS);
+                    epilogue_part(tile, 0, 0, EPI_WARPS / 4 + (pw >> 2), EPI_PARTS);
                     tc_fence_before();
                     mbar_arrive(smem_u32(&acc_empty_bar[0]));
                     ++helped;
@@ -530,16 +564,22 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             bool ok = true;
             long long tr_wf = 0, tr_wa = 0;
             const long long tr_t0 = clock64();
+            int v = 0;  // accumulator sets taken so far (see the epilogue)
             for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
                 const int4 tile = a.tiles[ti];
                 const int n16 = (tile.z + 15) & ~15;
                 // down: D[128 tokens, 256 output rows] = X[128, k] W[256, k]^T, the two adjacent 128-row
-                // weight operands of a stage forming one 256-row N operand
+                // weight operands of a stage forming one 256-row N operand; a tile of more than 128
+                // tokens is two such products per 16 inputs, into two accumulator sets
                 const uint32_t idesc = make_idesc(MODE == 1 ? 256 : n16, bf16_mode);
-                const int ab = tl % NACC, use = tl / NACC;
-                ok = TRACE_WAIT(tr_wa, mbar_wait(smem_u32(&acc_empty_bar[ab]), (use & 1) ^ 1, abort_flag));
+                const int nh = (MODE == 1 && tile.z > 128) ? 2 : 1;
+                for (int h = 0; ok && h < nh; ++h) {
+                    const int ab = (v + h) % NACC, use = (v + h) / NACC;
+                    ok = TRACE_WAIT(tr_wa, mbar_wait(smem_u32(&acc_empty_bar[ab]), (use & 1) ^ 1, abort_flag));
+                }
                 if (!ok) break;
                 tc_fence_after();
+                const uint32_t acc0 = tmem_base + (v % NACC) * ACC_COLS, acc1 = tmem_base + ((v + 1) % NACC) * ACC_COLS;
                 for (int kh = 0; kh < khs; ++kh, ++it) {
                     const int s = it % STAGES, ph = (it / STAGES) & 1;
                     ok = TRACE_WAIT(tr_wf, mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag));
@@ -552,19 +592,22 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                         const uint64_t bdesc = make_desc(bbase + j * 32);
                         const uint32_t acc = (kh > 0 || j > 0) ? 1u : 0u;
                         if (MODE == 1) {
-                            umma(tmem_base + ab * NA * BN, bdesc, make_desc(sbase + j * 32), idesc, acc);
+                            const uint64_t wdesc = make_desc(sbase + j * 32);
+                            umma(acc0, bdesc, wdesc, idesc, acc);
+                            if (nh == 2) umma(acc1, make_desc(bbase + SUB_BYTES + j * 32), wdesc, idesc, acc);
                         } else {
 #pragma unroll
                             for (int op = 0; op < NA; ++op) {
                                 const uint64_t adesc = make_desc(sbase + op * SUB_BYTES + j * 32);
-                                umma(tmem_base + ab * NA * BN + op * BN, adesc, bdesc, idesc, acc);
+                                umma(acc0 + op * BN, adesc, bdesc, idesc, acc);
                             }
                         }
                     }
                     umma_commit(smem_u32(&empty_bar[s]));
                 }
                 if (!ok) break;
-                umma_commit(smem_u32(&acc_full_bar[ab]));
+                for (int h = 0; h < nh; ++h) umma_commit(smem_u32(&acc_full_bar[(v + h) % NACC]));
+                v += nh;
             }
             TRACE_PUT(2, tr_wf);
             TRACE_PUT(3, tr_wa);
@@ -592,34 +635,49 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 // plain 2-D boxes of it with TMA
 template <typename XT, bool IS_F16 = false, bool NATURAL = false>
 __global__ void __launch_bounds__(256)
-gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ col_src_tok, int H,
+gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ col_src_tok, int C, int H,
                           uint16_t* __restrict__ out) {
-    const int c = blockIdx.x;
-    const int tok = col_src_tok[c];
-    const XT* src = x + (size_t)tok * H;
-    uint16_t* dst = out + (size_t)c * H;
     // one thread per output chunk of 8 values (16 bytes): chunk t of a 32-block holds inputs
-    // (4t, 4t+2, 16+4t, 16+4t+2, 4t+1, 4t+3, 16+4t+1, 16+4t+3), i.e. perm_pos of two runs of four
+    // (4t, 4t+2, 16+4t, 16+4t+2, 4t+1, 4t+3, 16+4t+1, 16+4t+3), i.e. perm_pos of two runs of four.
+    // Four rows per step: their source rows are known first, then all eight loads of a thread are
+    // in flight together (one row per CTA was a chain of dependent latencies: 43 us for 134 MB).
     auto to_h = [](XT v) -> uint16_t {
         if (sizeof(XT) == 4) return __half_as_ushort(__float2half_rn(*reinterpret_cast<const float*>(&v)));
         if (IS_F16) return *reinterpret_cast<const uint16_t*>(&v);
         return __half_as_ushort(__float2half_rn(__bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(&v))));
     };
     struct __align__(4 * sizeof(XT)) Run { XT v[4]; };
-    for (int ch = threadIdx.x; ch < H / 8; ch += 256) {
-        const int blk = ch >> 2, t = ch & 3;
-        // NATURAL (TMA-fed weights): chunk ch holds inputs 8 ch .. 8 ch + 7 as they are
-        const Run a = *reinterpret_cast<const Run*>(src + (NATURAL ? ch * 8 : blk * 32 + 4 * t));
-        const Run b = *reinterpret_cast<const Run*>(src + (NATURAL ? ch * 8 + 4 : blk * 32 + 16 + 4 * t));
-        __align__(16) uint16_t o[8];
-        if (NATURAL) {
-            o[0] = to_h(a.v[0]); o[1] = to_h(a.v[1]); o[2] = to_h(a.v[2]); o[3] = to_h(a.v[3]);
-            o[4] = to_h(b.v[0]); o[5] = to_h(b.v[1]); o[6] = to_h(b.v[2]); o[7] = to_h(b.v[3]);
-        } else {
-            o[0] = to_h(a.v[0]); o[1] = to_h(a.v[2]); o[2] = to_h(b.v[0]); o[3] = to_h(b.v[2]);
-            o[4] = to_h(a.v[1]); o[5] = to_h(a.v[3]); o[6] = to_h(b.v[1]); o[7] = to_h(b.v[3]);
+    constexpr int R = 4;
+    for (int c0 = blockIdx.x * R; c0 < C; c0 += gridDim.x * R) {
+        int tok[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) tok[r] = col_src_tok[min(c0 + r, C - 1)];
+        for (int ch = threadIdx.x; ch < H / 8; ch += 256) {
+            const int blk = ch >> 2, t = ch & 3;
+            // NATURAL (TMA-fed weights): chunk ch holds inputs 8 ch .. 8 ch + 7 as they are
+            const int oa = NATURAL ? ch * 8 : blk * 32 + 4 * t, ob = NATURAL ? ch * 8 + 4 : blk * 32 + 16 + 4 * t;
+            Run a[R], b[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const XT* src = x + (size_t)tok[r] * H;
+                a[r] = *reinterpret_cast<const Run*>(src + oa);
+                b[r] = *reinterpret_cast<const Run*>(src + ob);
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                if (c0 + r < C) {
+                    __align__(16) uint16_t o[8];
+                    if (NATURAL) {
+                        o[0] = to_h(a[r].v[0]); o[1] = to_h(a[r].v[1]); o[2] = to_h(a[r].v[2]); o[3] = to_h(a[r].v[3]);
+                        o[4] = to_h(b[r].v[0]); o[5] = to_h(b[r].v[1]); o[6] = to_h(b[r].v[2]); o[7] = to_h(b[r].v[3]);
+                    } else {
+                        o[0] = to_h(a[r].v[0]); o[1] = to_h(a[r].v[2]); o[2] = to_h(b[r].v[0]); o[3] = to_h(b[r].v[2]);
+                        o[4] = to_h(a[r].v[1]); o[5] = to_h(a[r].v[3]); o[6] = to_h(b[r].v[1]); o[7] = to_h(b[r].v[3]);
+                    }
+                    *reinterpret_cast<uint4*>(out + (size_t)(c0 + r) * H + blk * 32 + t * 8) = *reinterpret_cast<const uint4*>(o);
+                }
+            }
         }
-        *reinterpret_cast<uint4*>(dst + blk * 32 + t * 8) = *reinterpret_cast<const uint4*>(o);
     }
 }
 
@@ -628,8 +686,10 @@ gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ 
 cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_t* col_src_tok, int C, int H, void* out,
                                       cudaStream_t st, bool natural) {
     count_launch();
+    if (C <= 0) return cudaSuccess;
+    const int ggrid = (C + 3) / 4;  // four rows per CTA step; every CTA takes one step at these sizes
 #define LUMEN_GATHER(XT, F16, NAT) \
-    tc::gather_permute_x16_kernel<XT, F16, NAT><<<C, 256, 0, st>>>((const XT*)x, col_src_tok, H, (uint16_t*)out)
+    tc::gather_permute_x16_kernel<XT, F16, NAT><<<ggrid, 256, 0, st>>>((const XT*)x, col_src_tok, C, H, (uint16_t*)out)
     if (act_dtype == 0) {
         if (natural) LUMEN_GATHER(float, false, true);
         else LUMEN_GATHER(float, false, false);
@@ -732,17 +792,17 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
         dn.a_row1 = 128;
         e = (gu_cols == 256) ? launch_tc_one<BF16, 0, 256, true>(gu, grid, st) : launch_tc_one<BF16, 0, 128, true>(gu, grid, st);
         if (e != cudaSuccess) return e;
-        return launch_tc_one<BF16, 1, 128, true>(dn, grid, st);
+        return (gu_cols == 256) ? launch_tc_one<BF16, 1, 256, true>(dn, grid, st) : launch_tc_one<BF16, 1, 128, true>(dn, grid, st);
     }
     switch (p.L.quant) {
         case Q4_0:
             e = (gu_cols == 256) ? launch_tc_one<Q4_0, 0, 256>(gu, grid, st) : launch_tc_one<Q4_0, 0, 128>(gu, grid, st);
             if (e != cudaSuccess) return e;
-            return launch_tc_one<Q4_0, 1, 128>(dn, grid, st);
+            return (gu_cols == 256) ? launch_tc_one<Q4_0, 1, 256>(dn, grid, st) : launch_tc_one<Q4_0, 1, 128>(dn, grid, st);
         case Q8_0:
             e = (gu_cols == 256) ? launch_tc_one<Q8_0, 0, 256>(gu, grid, st) : launch_tc_one<Q8_0, 0, 128>(gu, grid, st);
             if (e != cudaSuccess) return e;
-            return launch_tc_one<Q8_0, 1, 128>(dn, grid, st);
+            return (gu_cols == 256) ? launch_tc_one<Q8_0, 1, 256>(dn, grid, st) : launch_tc_one<Q8_0, 1, 128>(dn, grid, st);
         default:
             // BF16 layers always carry their plain f16 matrices on this path (see above)
             return cudaErrorInvalidValue;

@@ -473,29 +473,54 @@ build_xf_kernel(const XT* __restrict__ x, int T, int H, int nblk_pad, bool bf16_
 // ---------------------------------------------------------------------------
 // scatter-accumulate
 // ---------------------------------------------------------------------------
+// One thread per 8 consecutive outputs (16-byte loads of the f16 rows); the slots are taken four
+// at a time so that their rows are in flight together, and added in slot order.
 __global__ void __launch_bounds__(256)
 scatter_accum_kernel(const __half* __restrict__ d16, const float* residual,
                      const float* __restrict__ weights, const int32_t* __restrict__ dst_to_col,
                      float* out, int T, int H, int K) {  // residual may be out (in-place layer stacks)
     const int t = blockIdx.x;  // tokens on grid.x: the y dimension is limited to 65535
-    const int h2 = blockIdx.y * 256 + threadIdx.x;  // pair index
-    if (h2 * 2 >= H) return;
-    const size_t o = (size_t)t * H + h2 * 2;
-    float2 acc = *reinterpret_cast<const float2*>(residual + o);
-    for (int slot = 0; slot < K; ++slot) {
-        const int col = dst_to_col[(size_t)t * K + slot];
-        const float w = weights[(size_t)t * K + slot];
-        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(d16 + (size_t)col * H + h2 * 2));
-        acc.x = __fadd_rn(acc.x, __fmul_rn(w, d.x));
-        acc.y = __fadd_rn(acc.y, __fmul_rn(w, d.y));
+    const int h8 = blockIdx.y * 256 + threadIdx.x;  // group of 8 outputs
+    if (h8 * 8 >= H) return;
+    const size_t o = (size_t)t * H + h8 * 8;
+    float acc[8];
+    {
+        const float4 r0 = *reinterpret_cast<const float4*>(residual + o);
+        const float4 r1 = *reinterpret_cast<const float4*>(residual + o + 4);
+        acc[0] = r0.x; acc[1] = r0.y; acc[2] = r0.z; acc[3] = r0.w;
+        acc[4] = r1.x; acc[5] = r1.y; acc[6] = r1.z; acc[7] = r1.w;
     }
-    *reinterpret_cast<float2*>(out + o) = acc;
+    for (int s0 = 0; s0 < K; s0 += 4) {
+        uint4 d[4];
+        float w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int slot = min(s0 + j, K - 1);
+            const int col = dst_to_col[(size_t)t * K + slot];
+            w[j] = weights[(size_t)t * K + slot];
+            d[j] = *reinterpret_cast<const uint4*>(d16 + (size_t)col * H + h8 * 8);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (s0 + j < K) {
+                const __half2* hp = reinterpret_cast<const __half2*>(&d[j]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(hp[i]);
+                    acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(w[j], f.x));
+                    acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(w[j], f.y));
+                }
+            }
+        }
+    }
+    *reinterpret_cast<float4*>(out + o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(out + o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
 cudaError_t launch_scatter_accum(const __half* d16, const float* residual, const RouteDev& R, float* out,
                                  int T, int H, int K, cudaStream_t st) {
     count_launch();
-    scatter_accum_kernel<<<dim3(T, (H / 2 + 255) / 256), 256, 0, st>>>(d16, residual, R.weights, R.dst_to_col,
+    scatter_accum_kernel<<<dim3(T, (H / 8 + 255) / 256), 256, 0, st>>>(d16, residual, R.weights, R.dst_to_col,
                                                                        out, T, H, K);
     return cudaGetLastError();
 }
@@ -610,8 +635,8 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const int nchunks = (T + SORT_TOK - 1) / SORT_TOK;
     sort_hist_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist);
     const int C = T * K;
-    // columns per grouped-GEMM tile: 128 or 256 for gate/up, 128 for down
-    const int tile_cols = tc_gu_tile_cols(C, E), tile_cols_dn = 128;
+    // columns per grouped-GEMM tile: 128 or 256, the same for gate/up and down
+    const int tile_cols = tc_gu_tile_cols(C, E), tile_cols_dn = tile_cols;
     const int max_ct = C / tile_cols + E, max_ct_dn = C / tile_cols_dn + E;
     const int mt_gu = a.L.I / 128, mt_dn = a.L.H / 256;  // m-tiles: 128 gate + 128 up rows | 256 down rows
     int4* tiles_gu = a.tiles;
@@ -628,7 +653,7 @@ cudaError_t launch_tile_plan(const RouteDev& R, int E, int H, int I, int rows_ca
     const int max_ct = rows_cap / gu_cols + E, max_ct_dn = rows_cap / 128 + E;
     const int mt_gu = I / 128, mt_dn = H / 256;
     count_launch();
-    sort_scan_kernel<<<1, 256, 0, st>>>(0, E, R, gu_cols, 128, mt_gu, mt_dn, tiles,
+    sort_scan_kernel<<<1, 256, 0, st>>>(0, E, R, gu_cols, gu_cols, mt_gu, mt_dn, tiles,
                                         tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1), n_tiles, max_ct * mt_gu,
                                         max_ct_dn * mt_dn);
     return cudaGetLastError();

@@ -222,39 +222,60 @@ ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
         const int start = mine_s[((a.me + 1) % a.world) * a.epr];
         const XT* x = static_cast<const XT*>(a.x);
         struct __align__(4 * sizeof(XT)) Run { XT v[4]; };
-        for (int ci = blockIdx.x; ci < a.C; ci += gridDim.x) {
-            int c = ci + start;
-            if (c >= a.C) c -= a.C;
-            const int e = a.col_expert[c];
-            const int tok = a.col_src_tok[c];
-            if ((unsigned)e >= (unsigned)a.E) continue;
-            const int owner = e / a.epr;
-            const int drow = base_s[e] + (c - mine_s[e]);
-            if (drow >= a.rows_cap) continue;
-            uint8_t* w = a.peers.win[owner];
-            uint16_t* dst = reinterpret_cast<uint16_t*>(w + a.wl.x16) + (size_t)drow * a.H;
-            const XT* src = x + (size_t)tok * a.H;
+        // Four rows per step: where they go is worked out first, then all of a thread's loads are in
+        // flight together before the peer stores (one row per step was a chain of dependent latencies).
+        constexpr int R = 4;
+        for (int ci0 = blockIdx.x * R; ci0 < a.C; ci0 += gridDim.x * R) {
+            uint16_t* dstrow[R];
+            const XT* srcrow[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                dstrow[r] = nullptr;
+                srcrow[r] = x;
+                const int ci = ci0 + r;
+                if (ci >= a.C) continue;
+                int c = ci + start;
+                if (c >= a.C) c -= a.C;
+                const int e = a.col_expert[c];
+                const int tok = a.col_src_tok[c];
+                if ((unsigned)e >= (unsigned)a.E) continue;
+                const int owner = e / a.epr;
+                const int drow = base_s[e] + (c - mine_s[e]);
+                if (drow >= a.rows_cap) continue;
+                uint8_t* w = a.peers.win[owner];
+                dstrow[r] = reinterpret_cast<uint16_t*>(w + a.wl.x16) + (size_t)drow * a.H;
+                srcrow[r] = x + (size_t)tok * a.H;
+                if (tid == 0) reinterpret_cast<int32_t*>(w + a.wl.ret_map)[drow] = (a.me << 24) | c;
+            }
             // chunk t of a 32-block holds inputs (4t, 4t+2, 16+4t, 16+4t+2, 4t+1, 4t+3, 16+4t+1, 16+4t+3),
             // or, for TMA-fed weights, chunk ch holds inputs 8 ch .. 8 ch + 7 as they are
             for (int ch = tid; ch < a.H / 8; ch += 256) {
                 const int blk = ch >> 2, t = ch & 3;
-                const Run p = *reinterpret_cast<const Run*>(src + (a.natural ? ch * 8 : blk * 32 + 4 * t));
-                const Run q = *reinterpret_cast<const Run*>(src + (a.natural ? ch * 8 + 4 : blk * 32 + 16 + 4 * t));
-                uint4 o;
-                if (a.natural) {
-                    o.x = (uint32_t)to_f16_bits<XT>(p.v[0]) | ((uint32_t)to_f16_bits<XT>(p.v[1]) << 16);
-                    o.y = (uint32_t)to_f16_bits<XT>(p.v[2]) | ((uint32_t)to_f16_bits<XT>(p.v[3]) << 16);
-                    o.z = (uint32_t)to_f16_bits<XT>(q.v[0]) | ((uint32_t)to_f16_bits<XT>(q.v[1]) << 16);
-                    o.w = (uint32_t)to_f16_bits<XT>(q.v[2]) | ((uint32_t)to_f16_bits<XT>(q.v[3]) << 16);
-                } else {
-                    o.x = (uint32_t)to_f16_bits<XT>(p.v[0]) | ((uint32_t)to_f16_bits<XT>(p.v[2]) << 16);
-                    o.y = (uint32_t)to_f16_bits<XT>(q.v[0]) | ((uint32_t)to_f16_bits<XT>(q.v[2]) << 16);
-                    o.z = (uint32_t)to_f16_bits<XT>(p.v[1]) | ((uint32_t)to_f16_bits<XT>(p.v[3]) << 16);
-                    o.w = (uint32_t)to_f16_bits<XT>(q.v[1]) | ((uint32_t)to_f16_bits<XT>(q.v[3]) << 16);
+                const int oa = a.natural ? ch * 8 : blk * 32 + 4 * t, ob = a.natural ? ch * 8 + 4 : blk * 32 + 16 + 4 * t;
+                Run p[R], q[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    p[r] = *reinterpret_cast<const Run*>(srcrow[r] + oa);
+                    q[r] = *reinterpret_cast<const Run*>(srcrow[r] + ob);
                 }
-                *reinterpret_cast<uint4*>(dst + blk * 32 + t * 8) = o;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    if (dstrow[r] == nullptr) continue;
+                    uint4 o;
+                    if (a.natural) {
+                        o.x = (uint32_t)to_f16_bits<XT>(p[r].v[0]) | ((uint32_t)to_f16_bits<XT>(p[r].v[1]) << 16);
+                        o.y = (uint32_t)to_f16_bits<XT>(p[r].v[2]) | ((uint32_t)to_f16_bits<XT>(p[r].v[3]) << 16);
+                        o.z = (uint32_t)to_f16_bits<XT>(q[r].v[0]) | ((uint32_t)to_f16_bits<XT>(q[r].v[1]) << 16);
+                        o.w = (uint32_t)to_f16_bits<XT>(q[r].v[2]) | ((uint32_t)to_f16_bits<XT>(q[r].v[3]) << 16);
+                    } else {
+                        o.x = (uint32_t)to_f16_bits<XT>(p[r].v[0]) | ((uint32_t)to_f16_bits<XT>(p[r].v[2]) << 16);
+                        o.y = (uint32_t)to_f16_bits<XT>(q[r].v[0]) | ((uint32_t)to_f16_bits<XT>(q[r].v[2]) << 16);
+                        o.z = (uint32_t)to_f16_bits<XT>(p[r].v[1]) | ((uint32_t)to_f16_bits<XT>(p[r].v[3]) << 16);
+                        o.w = (uint32_t)to_f16_bits<XT>(q[r].v[1]) | ((uint32_t)to_f16_bits<XT>(q[r].v[3]) << 16);
+                    }
+                    *reinterpret_cast<uint4*>(dstrow[r] + blk * 32 + t * 8) = o;
+                }
             }
-            if (tid == 0) reinterpret_cast<int32_t*>(w + a.wl.ret_map)[drow] = (a.me << 24) | c;
         }
     }
     // my rows are out once every CTA's stores are: the last CTA to get here tells every rank
@@ -523,7 +544,7 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     d.status = sc->status;
     d.status_host = sc->status_host;
     d.done_counter = s->done_counter;
-    const int dgrid = C < sc->sms * 8 ? C : sc->sms * 8;
+    const int dgrid = (C + 3) / 4 < sc->sms * 8 ? (C + 3) / 4 : sc->sms * 8;  // four rows per CTA step
     if (act_dtype == 0) ep::ep_dispatch_kernel<float><<<dgrid, 256, 0, st>>>(d);
     else ep::ep_dispatch_kernel<__nv_bfloat16><<<dgrid, 256, 0, st>>>(d);
     mark(2);

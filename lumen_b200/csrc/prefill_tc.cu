@@ -277,7 +277,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 }
                 // (every lane takes part in the loads: tcgen05.ld is a warp-wide instruction)
 #pragma unroll 2
-                for (int n0 = part * 16; n0 < 256; n0 += nparts * 16) {
+                // a contiguous share of the 256 output rows per warp group: a thread's stores then fill
+                // whole 128-byte lines of its token's row (with 16-column shares dealt round-robin the
+                // lines were written in 32-byte pieces by two warps, and the expert-parallel return path,
+                // where these stores cross NVLink, took twice as long)
+                const int ow = 256 / nparts;
+                for (int n0 = part * ow; n0 < (part + 1) * ow; n0 += 16) {
                     uint32_t v[16];
                     tmem_ld16(taddr + n0, v);
                     tmem_ld_wait();
@@ -750,6 +755,11 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     const int C = plan ? plan->rows : p.T * p.K;
     const int gu_cols = plan ? plan->gu_cols : tc_gu_tile_cols(C, p.L.E);  // as the tile lists were built
     const int max_ct = C / gu_cols + p.L.E;
+    // Down tiles: up to 256 tokens (two accumulator sets at once, no epilogue overlap between such
+    // tiles) when the gate/up tiles are 256 wide, except with a tile plan of an expert-parallel call,
+    // whose lists are built for 128: its epilogue stores into other GPUs' memory and needs the overlap
+    // (measured: 0.43 -> 0.96 ms of expert time per call on 4 GPUs with the wide form).
+    const bool dn256 = (gu_cols == 256) && plan == nullptr;
     const int mt_gu = p.L.I / 128;
     tc::Args gu{};
     cudaError_t te = make_tmap_f16(x16, (uint64_t)C, (uint64_t)p.L.H, 128, &gu.tmap);
@@ -792,17 +802,17 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
         dn.a_row1 = 128;
         e = (gu_cols == 256) ? launch_tc_one<BF16, 0, 256, true>(gu, grid, st) : launch_tc_one<BF16, 0, 128, true>(gu, grid, st);
         if (e != cudaSuccess) return e;
-        return (gu_cols == 256) ? launch_tc_one<BF16, 1, 256, true>(dn, grid, st) : launch_tc_one<BF16, 1, 128, true>(dn, grid, st);
+        return dn256 ? launch_tc_one<BF16, 1, 256, true>(dn, grid, st) : launch_tc_one<BF16, 1, 128, true>(dn, grid, st);
     }
     switch (p.L.quant) {
         case Q4_0:
             e = (gu_cols == 256) ? launch_tc_one<Q4_0, 0, 256>(gu, grid, st) : launch_tc_one<Q4_0, 0, 128>(gu, grid, st);
             if (e != cudaSuccess) return e;
-            return (gu_cols == 256) ? launch_tc_one<Q4_0, 1, 256>(dn, grid, st) : launch_tc_one<Q4_0, 1, 128>(dn, grid, st);
+            return dn256 ? launch_tc_one<Q4_0, 1, 256>(dn, grid, st) : launch_tc_one<Q4_0, 1, 128>(dn, grid, st);
         case Q8_0:
             e = (gu_cols == 256) ? launch_tc_one<Q8_0, 0, 256>(gu, grid, st) : launch_tc_one<Q8_0, 0, 128>(gu, grid, st);
             if (e != cudaSuccess) return e;
-            return (gu_cols == 256) ? launch_tc_one<Q8_0, 1, 256>(dn, grid, st) : launch_tc_one<Q8_0, 1, 128>(dn, grid, st);
+            return dn256 ? launch_tc_one<Q8_0, 1, 256>(dn, grid, st) : launch_tc_one<Q8_0, 1, 128>(dn, grid, st);
         default:
             // BF16 layers always carry their plain f16 matrices on this path (see above)
             return cudaErrorInvalidValue;

@@ -653,7 +653,9 @@ cudaError_t launch_tile_plan(const RouteDev& R, int E, int H, int I, int rows_ca
     const int max_ct = rows_cap / gu_cols + E, max_ct_dn = rows_cap / 128 + E;
     const int mt_gu = I / 128, mt_dn = H / 256;
     count_launch();
-    sort_scan_kernel<<<1, 256, 0, st>>>(0, E, R, gu_cols, gu_cols, mt_gu, mt_dn, tiles,
+    // (down tiles of 128 tokens here: an expert-parallel down product stores its rows into other GPUs'
+    // memory, which only the always-overlapped epilogue of the 128-token form hides)
+    sort_scan_kernel<<<1, 256, 0, st>>>(0, E, R, gu_cols, 128, mt_gu, mt_dn, tiles,
                                         tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1), n_tiles, max_ct * mt_gu,
                                         max_ct_dn * mt_dn);
     return cudaGetLastError();

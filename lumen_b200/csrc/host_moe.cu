@@ -511,7 +511,9 @@ Status encode_moe_ffn_prefill_grouped(CudaMoeScratch* s, const MoeLayer& layer, 
     p.wait_limit_us = s->wait_limit_us;
     p.tc_ctas = s->tc_ctas;
     // the tcgen05 path reads activation rows with 16-byte loads (8-byte for 16-bit rows)
-    const bool tc_ok = (s->H % 256 == 0) && (s->I % 128 == 0) && (reinterpret_cast<uintptr_t>(normed) % 16 == 0);
+    // and stores f16 output rows 32 bytes at a time
+    const bool tc_ok = (s->H % 256 == 0) && (s->I % 128 == 0) && (reinterpret_cast<uintptr_t>(normed) % 16 == 0) &&
+                       (reinterpret_cast<uintptr_t>(out16_rows) % 32 == 0);
     p.impl = (s->prefill_impl == 1 || !tc_ok) ? 1 : 0;
     CUDA_TRY(launch_route_large(p, st));
     const bool bf16_mode = (layer.dev.quant == BF16);

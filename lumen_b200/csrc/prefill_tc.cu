@@ -256,7 +256,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         if (MODE == 1) {
             // Down product: the tile's columns (tokens) are the TMEM lanes and the 256 output rows
             // of the m-tile the TMEM columns, so a thread owns one token and reads 16 consecutive
-            // output rows per load: its stores are 16 bytes wide and each token's 512 bytes are
+            // output rows per load: its stores are 32 bytes wide and each token's 512 bytes are
             // contiguous (a whole NVLink packet when the row lives on another rank).
             {
                 const int tcol = h * 128 + row;  // token column of the tile (h: its half of a 256-token tile)
@@ -293,9 +293,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                             const __half2 pr2 = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
                             hh[j] = *reinterpret_cast<const uint32_t*>(&pr2);
                         }
-                        uint4* d4 = reinterpret_cast<uint4*>(dst + n0);
-                        d4[0] = make_uint4(hh[0], hh[1], hh[2], hh[3]);
-                        d4[1] = make_uint4(hh[4], hh[5], hh[6], hh[7]);
+                        st_global_v8(dst + n0, hh);  // 16 outputs = one 32-byte sector of the token's row
                     }
                 }
             }

@@ -473,9 +473,10 @@ static size_t gate_up_stream_smem(const DecodeArgs& a) {
 }
 
 // The streaming gate/up kernel and the int8 down product that consumes its output: Q4_0 layers,
-// 5..16 tokens, batch activations + rings within shared memory.
+// 2..16 tokens (whenever the three-kernel chain runs; from four tokens on it is also faster than the
+// fused kernel), batch activations + rings within shared memory.
 bool decode_stream_applicable(const DecodeArgs& a) {
-    return a.L.quant == Q4_0 && a.xq != nullptr && a.sq != nullptr && a.T > 4 && a.T <= DECODE_MAX_TOKENS &&
+    return a.L.quant == Q4_0 && a.xq != nullptr && a.sq != nullptr && a.T >= 2 && a.T <= DECODE_MAX_TOKENS &&
            a.L.kg_h <= 16 && (a.L.rt_i & 1) == 0 && gate_up_stream_smem(a) <= 220 * 1024;
 }
 

@@ -380,7 +380,7 @@ Status encode_moe_ffn_decode(CudaMoeScratch* s, const MoeLayer& layer, const flo
     a.out = output_x;
     s->last_decode = a;
     s->has_last_decode = true;
-    if (s->expire_next[0] && decode_fused_applicable(a)) {
+    if (s->expire_next[0] && decode_uses_fused(a)) {
         a.debug_extra_arrivals = 1;
         s->expire_next[0] = 0;
     }

@@ -129,6 +129,7 @@ cudaError_t launch_ep_prepare(const void* x, int act_dtype, const RouteDev& R, i
                               int32_t* local_ids, long long* send_counts, cudaStream_t st);
 cudaError_t launch_route_small(const DecodeArgs& a, cudaStream_t st);  // router + tables only (T <= 16)
 bool decode_fused_applicable(const DecodeArgs& a);
+bool decode_uses_fused(const DecodeArgs& a);  // whether launch_decode takes the fused kernel for this call
 cudaError_t launch_decode_fused(const DecodeArgs& a, cudaStream_t st);
 cudaError_t launch_decode_phase(const DecodeArgs& a, int phase, cudaStream_t st);  // one kernel of the three-kernel chain: 0 router, 1 gate/up, 2 down
 cudaError_t launch_quantize(const float* src, int64_t n, int quant, void* dst, cudaStream_t st);

@@ -154,7 +154,7 @@ static size_t tok_arena_bytes(const CudaMoeScratch& s, int cap, size_t* offs) {
     const size_t n_tile_entries = max_ct * ((size_t)s.I / 128 + 1) + max_ct_dn * ((size_t)s.H / 256 + 1);
     size_t sizes[18] = {
         (size_t)cap * s.E * 4, C * 4, C * 4, C * 4, C * 4, C * 4,
-        (size_t)((cap + 31) / 32) * s.E * 4,
+        (size_t)((cap + 7) / 8) * s.E * 4,  // one histogram per chunk of 8 tokens (SORT_TOK in route_large.cu)
         n_tile_entries * sizeof(int4),
         C * s.I * 2, C * s.H * 2, C * s.H * 2,
         (size_t)cap * 2 * nblk_h_pad * 64, C * 2 * nblk_i_pad * 64,

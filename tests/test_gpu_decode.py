@@ -196,3 +196,65 @@ def test_fused_decode_shape_sweep_real_router(cuda_lib, shape, quant, gating):
             gap = lg[t][order[K - 1]] - lg[t][order[K]]
             if gap > 1e-4:
                 assert set(order[:K].tolist()) == set(ids[t].tolist())
+
+
+# ---------------------------------------------------------------------------
+# Q4_0 chain with the streaming gate/up kernel and the int8 down product (2..16 tokens when the
+# context is created with LUMEN_MOE_FLAG_DECODE_SPLIT, 4..16 tokens otherwise)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("T", [2, 3, 4, 5, 8, 13, 16])
+def test_streaming_chain_every_batch_size(cuda_lib, T):
+    """Same logits on both sides: ids, weights and sort tables exact, output within the tolerance;
+    and the chain agrees with the fused kernel where both apply."""
+    from lumen_b200 import _lib
+    H, I, E, K = 2048, 768, 128, 8
+    lay = synth.LayerLayout(H, I, E, 1)
+    blob = synth.make_layer_blob(lay, 11)
+    torch.cuda.synchronize()
+    blob_np = blob.cpu().numpy()
+    meta = lay.meta()
+    g = torch.Generator("cuda").manual_seed(20 + T)
+    x = torch.randn((T, H), generator=g, device="cuda")
+    res = torch.randn((T, H), generator=g, device="cuda")
+    lg = synth.uniform_logits(T, E, 30 + T, tau=0.5)
+    outs = {}
+    for flags in (0, _lib.FLAG_DECODE_SPLIT):
+        sc = moe.allocate_moe_scratch(H, I, E, K, 16, flags=flags)
+        layer = sc.prepare_layer(blob, meta)
+        sc.set_logits_override(lg)
+        outs[flags] = sc.decode(layer, x, res).clone()
+        r = sc.get_routing(T)
+        o_out, o_ids, o_w = oracle_layer(blob_np, meta, lay, K, x.cpu().numpy(), res.cpu().numpy(), logits=lg.cpu().numpy())
+        assert np.array_equal(r["ids"], o_ids)
+        assert np.array_equal(r["weights"].view(np.uint32), o_w.view(np.uint32))
+        _, _, d2c, bounds = oracle.counting_sort(o_ids, E)
+        assert np.array_equal(r["dst_to_col"], d2c) and np.array_equal(r["expert_bounds"], bounds)
+        assert rel_l2(outs[flags].cpu().numpy() - res.cpu().numpy(), o_out - res.cpu().numpy()) < TOL_REL_L2
+        layer.close()
+        sc.close()
+    a, b = outs[0] - res, outs[_lib.FLAG_DECODE_SPLIT] - res
+    assert ((a - b).norm() / a.norm()).item() < 1e-4  # two-term int8 against hi+lo f16 activations in the down product
+
+
+@pytest.mark.parametrize("K", [8, 16])
+def test_streaming_chain_experts_with_many_columns(cuda_lib, K):
+    """Every token selects the same K experts: each of them has 16 columns (four column groups in
+    both expert kernels), all the others none."""
+    H, I, E, T = 512, 256, 32, 16
+    lay, meta, blob_np, sc, layer = make_layer(H, I, E, K, 1, seed=9)
+    g = torch.Generator("cuda").manual_seed(2)
+    x = torch.randn((T, H), generator=g, device="cuda")
+    res = torch.randn((T, H), generator=g, device="cuda")
+    lg = torch.full((T, E), -4.0, device="cuda")
+    lg[:, 3:3 + K] = torch.linspace(1.0, 2.0, K, device="cuda")[None, :]
+    sc.set_logits_override(lg)
+    out = sc.decode(layer, x, res)
+    r = sc.get_routing(T)
+    assert all(set(row.tolist()) == set(range(3, 3 + K)) for row in r["ids"])
+    assert np.diff(r["expert_bounds"]).max() == T
+    o_out, o_ids, _ = oracle_layer(blob_np, meta, lay, K, x.cpu().numpy(), res.cpu().numpy(), logits=lg.cpu().numpy())
+    assert np.array_equal(r["ids"], o_ids)
+    assert rel_l2(out.cpu().numpy() - res.cpu().numpy(), o_out - res.cpu().numpy()) < TOL_REL_L2
+    # determinism
+    out2 = sc.decode(layer, x, res)
+    assert torch.equal(out, out2)

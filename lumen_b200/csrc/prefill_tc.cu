@@ -52,9 +52,6 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
 
 // Position of element e (0..31) of a block in the permuted 16-bit layout:
 // chunk t = (e mod 16) / 4, slot order (4t, 4t+2, 16+4t, 16+4t+2, 4t+1, 4t+3, 16+4t+1, 16+4t+3).
@@ -146,23 +143,17 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
 
 // ATMA: the weight operands are not dequantised here but copied by TMA from plain f16 matrices
 // (BF16 layers; Q4_0 / Q8_0 layers of a context created with LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS): the
-// producer warps have nothing to do and every operand is in the natural input order.
-// Operand stages and depth of the raw-tile ring. The dequantising producers prefetch the next
-// 128-input group of quantised tiles while they work on the current one. For Q4_0 (3 uint4 per
-// lane and tile) the prefetch lives in registers. For Q8_0 (5 uint4) two operands x two groups
-// do not fit the 96 registers a thread has here and used to spill: there every producer warp
-// keeps its raw tiles in flight with cp.async (16 bytes per lane, into a ring of its own in
-// shared memory: no other warp touches it) and reads a group back with 128-bit shared loads
-// when it has landed (0.75 -> 0.59 ms per 4096-token call). The ring's shared memory comes out
-// of the operand stages; for Q4_0 the same ring with one stage less was measured slower
-// (0.53 -> 0.58 ms) and is not used.
-template <int Q, bool ATMA>
-struct RingOf {
-    static constexpr int value = (!ATMA && Q == Q8_0) ? 2 : 0;
-};
+// producer warps have nothing to dequantise and every operand is in the natural input order.
+//
+// Operand stages. The dequantising producers prefetch the next 128-input group of quantised tiles
+// into registers while they work on the current one: with sixteen producer warps of one tile
+// each that is 3 (Q4_0) or 5 (Q8_0) uint4 per lane in flight, inside the 72 registers a thread has.
+// (With eight warps of two tiles the Q8_0 prefetch spilled and a cp.async ring in shared memory
+// replaced it, at the price of an operand stage; the ring is gone again: 0.540 -> 0.50 ms per
+// 4096-token Q8_0 call.)
 template <int Q, int BN, bool ATMA>
 struct StagesOf {
-    static constexpr int value = (RingOf<Q, ATMA>::value > 0) ? ((BN == 128) ? 3 : 2) : ((BN == 128) ? 4 : 3);
+    static constexpr int value = (BN == 128) ? 4 : 3;
 };
 
 // Debug aid (compile with -DLUMEN_TC_TRACE): per CTA, the cycles the MMA thread and the first
@@ -205,8 +196,6 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     // epilogue between two such tiles is exposed too: Q4_0 0.463 -> 0.498 ms, Q8_0 and BF16 unchanged.)
     constexpr bool HELP = (NACC == 1) && ATMA;
     constexpr int STAGES = StagesOf<Q, BN, ATMA>::value;  // one stage = 64 inputs (one swizzle atom in K)
-    constexpr int RING = RingOf<Q, ATMA>::value;       // raw weight tiles in flight per producer warp (128-input groups)
-    constexpr int RAW_U4 = QTraits<Q>::NQ * 32 + 8;    // uint4 of one raw tile: lane-major quant words, then 8 scale words
     constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operands then B
     constexpr int TMEM_COLS = ACC_COLS * NACC;
 
@@ -413,57 +402,10 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         };
         auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool { return mbar_wait(bar, parity, abort_flag); };
         auto warp_arrive = [&](uint32_t bar) {
-#ifndef LUMEN_TC_NOFENCE
             fence_proxy_async();
-#endif
             mbar_arrive(bar);
         };
-        if constexpr (RING > 0) {
-            // this warp's ring: [RING][RAW_U4] uint4, behind the operand stages
-            uint4* ring = reinterpret_cast<uint4*>(smem_raw + (stage0 - smem_u32(smem_raw)) + STAGES * STAGE_BYTES) +
-                          (size_t)pw * RING * RAW_U4;
-            // raw tile of group m (m-th 128-input group of this CTA's tile sequence) into ring slot m % RING
-            auto request = [&](int m) {
-                const int tl_m = m / kgs, kg_m = m - tl_m * kgs;
-                const int4 tile = a.tiles[blockIdx.x + tl_m * gridDim.x];
-                const uint4 *qp, *sp;
-                tile_ptrs(tile, kg_m, qp, sp);
-                uint4* dst = ring + (size_t)(m % RING) * RAW_U4;
-    #pragma unroll
-                for (int j = 0; j < QTraits<Q>::NQ; ++j) cp_async16(smem_u32(dst + j * 32 + lane), qp + j * 32, 16);
-                if (lane < 8) cp_async16(smem_u32(dst + QTraits<Q>::NQ * 32 + lane), sp + lane, 16);
-            };
-            WTile<Q> cur;
-    #pragma unroll 1
-            for (int m = 0; m < RING - 1; ++m) {
-                if (m < ngroups) request(m);
-                asm volatile("cp.async.commit_group;" ::: "memory");
-            }
-            int it = 0;
-            for (int n = 0; ok && n < ngroups; ++n) {
-                if (n + RING - 1 < ngroups) request(n + RING - 1);
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                // all but the RING - 1 youngest groups have landed: group n is in its slot
-                asm volatile("cp.async.wait_group %0;" ::"n"(RING - 1) : "memory");
-                __syncwarp();  // the scale words of a slot are copied by lanes 0..7 for the whole warp
-                const uint4* slot = ring + (size_t)(n % RING) * RAW_U4;
-    #pragma unroll
-                for (int j = 0; j < QTraits<Q>::NQ; ++j) cur.q[j] = slot[j * 32 + lane];
-                cur.s = slot[QTraits<Q>::NQ * 32 + (lane >> 2)];
-                __syncwarp();  // every lane has its words before the slot is requested again
-    #pragma unroll
-                for (int sub = 0; sub < 2; ++sub, ++it) {
-                    const int s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (HELP && it >= STAGES) help_until((it - STAGES) / khs);
-                    ok = ok && warp_wait(smem_u32(&empty_bar[s]), ph ^ 1);
-                    if (ok) {
-                        dequant_store<Q>(cur, sub, stage0 + s * STAGE_BYTES + op * SUB_BYTES, rtl, lane);
-                        warp_arrive(smem_u32(&full_bar[s]));
-                    }
-                }
-            }
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        } else {
+        {
             WTile<Q> cur, nxt;
             auto issue = [&](const int4& tile, int kg, WTile<Q>& dst) {
                 const uint4 *qp, *sp;
@@ -732,9 +674,7 @@ template <int Q, int MODE, int BN, bool ATMA = false>
 static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
     constexpr int NA = 2;
     constexpr int STAGES = tc::StagesOf<Q, BN, ATMA>::value;
-    constexpr int RING = tc::RingOf<Q, ATMA>::value;
-    const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024 +
-                     tc::A_WARPS * RING * (QTraits<Q>::NQ * 32 + 8) * 16;
+    const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024;
     static SmemOptIn optin;
     {
         cudaError_t e = ensure_dyn_smem(tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA>, (size_t)smem, optin);
@@ -753,8 +693,8 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     const int max_ct = C / gu_cols + p.L.E;
     // Down tiles: up to 256 tokens (two accumulator sets at once, no epilogue overlap between such
     // tiles) when the gate/up tiles are 256 wide, except with a tile plan of an expert-parallel call,
-    // whose lists are built for 128: its epilogue stores into other GPUs' memory and needs the overlap
-    // (measured: 0.43 -> 0.96 ms of expert time per call on 4 GPUs with the wide form).
+    // whose lists are built for 128: its epilogue stores into other GPUs' memory, and with two
+    // independent accumulator sets those stores always run under the next tile's MMAs.
     const bool dn256 = (gu_cols == 256) && plan == nullptr;
     const int mt_gu = p.L.I / 128;
     tc::Args gu{};

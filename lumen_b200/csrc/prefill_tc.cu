@@ -11,20 +11,21 @@
 // (Zipf-skewed loads) without padding M. Down ("tokens are the M operand"): for up to 128
 // columns,  D[128 tokens, 256 output rows] += S[128, k] W[256, k]^T, one MMA per 16 inputs
 // whose N operand is the stage's two adjacent 128-row weight tiles, so that an epilogue
-// thread owns one token and stores 16 bytes at a time.
+// thread owns one token and stores 32 bytes at a time; a tile of up to 256 columns is two
+// such products against the same weight stage, into the two accumulator sets.
 //
-// One CTA per SM, persistent over a device-built tile list, warp-specialised (18 warps):
+// One CTA per SM, persistent over a device-built tile list, warp-specialised (26 warps):
 //   warps 0-7   epilogue: tcgen05.ld of the accumulators, SwiGLU (gate/up), f16 stores
 //               (into another rank's return buffer for an expert-parallel down product)
-//   warps 8-15  weight producers: 128-bit loads of the repacked quant tiles (Q4_0: the next
-//               128-input group prefetched in registers; Q8_0: raw tiles kept in flight by
-//               cp.async through a ring of the warp's own in shared memory), dequantise to
-//               f16 (scale folded in) in registers, store into the 128-byte-swizzled
-//               K-major operand tile in shared memory. Idle when the weights are plain f16
-//               matrices copied by TMA (BF16 layers; LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS)
-//   warp 16     one thread feeds the activation operand (and TMA-fed weights) with
+//   warps 8-23  weight producers, one 16-row tile each per 128-input group: 128-bit loads of
+//               the repacked quant tiles (the next group prefetched in registers), dequantise
+//               to f16 (scale folded in) in registers, store into the 128-byte-swizzled
+//               K-major operand tile in shared memory. When the weights are plain f16
+//               matrices copied by TMA (BF16 layers; LUMEN_MOE_FLAG_PREFILL_F16_WEIGHTS) they
+//               share the gate/up epilogue instead
+//   warp 24     one thread feeds the activation operand (and TMA-fed weights) with
 //               cp.async.bulk.tensor.2d boxes of 64 inputs x 128 rows
-//   warp 17     one elected thread issues tcgen05.mma / tcgen05.commit
+//   warp 25     one elected thread issues tcgen05.mma / tcgen05.commit
 // Stages are handed over with mbarriers; every wait is bounded (on expiry the
 // kernel raises a status word, drains and frees its TMEM instead of hanging).
 //

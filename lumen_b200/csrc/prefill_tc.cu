@@ -152,10 +152,14 @@ __device__ __forceinline__ void dequant_store(const WTile<Q>& w, int sub, uint32
 // (With eight warps of two tiles the Q8_0 prefetch spilled and a cp.async ring in shared memory
 // replaced it, at the price of an operand stage; the ring is gone again: 0.540 -> 0.50 ms per
 // 4096-token Q8_0 call.)
-template <int Q, int BN, bool ATMA>
+// STG (expert-parallel down product): an operand stage is given up for a staging tile from which
+// the output rows leave as 256-byte bulk copies (see the epilogue).
+template <int Q, int BN, bool ATMA, bool STG = false>
 struct StagesOf {
-    static constexpr int value = (BN == 128) ? 4 : 3;
+    static constexpr int value = ((BN == 128) ? 4 : 3) - (STG ? 1 : 0);
 };
+constexpr int STG_ROW_BYTES = 256 + 16;                 // 128 f16 outputs of one token + padding (bank spread)
+constexpr int STG_BYTES = 2 * 128 * STG_ROW_BYTES;      // two warp groups x 128 tokens
 
 // Debug aid (compile with -DLUMEN_TC_TRACE): per CTA, the cycles the MMA thread and the first
 // producer warp spend in their waits, read back with lumen_debug_tc_trace.
@@ -168,9 +172,10 @@ __device__ unsigned long long g_tc_trace[2][160][8];
 #define TRACE_PUT(slot, v)
 #endif
 
-template <int Q, int MODE, int BN, bool ATMA = false>
+template <int Q, int MODE, int BN, bool ATMA = false, bool STG = false>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
+    static_assert(!STG || (MODE == 1 && BN == 128), "the staged epilogue belongs to the 128-token down product");
     // Two 128-row weight operands share every activation stage (gate and up rows of the
     // same I range; two adjacent row tiles of the down matrix): the activation operand,
     // which comes from L2 at 2 bytes per element, is then read at half the rate.
@@ -196,7 +201,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     // own work is what those kernels wait for; the same again for the 256-token down tiles, whose
     // epilogue between two such tiles is exposed too: Q4_0 0.463 -> 0.498 ms, Q8_0 and BF16 unchanged.)
     constexpr bool HELP = (NACC == 1) && ATMA;
-    constexpr int STAGES = StagesOf<Q, BN, ATMA>::value;  // one stage = 64 inputs (one swizzle atom in K)
+    constexpr int STAGES = StagesOf<Q, BN, ATMA, STG>::value;  // one stage = 64 inputs (one swizzle atom in K)
     constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operands then B
     constexpr int TMEM_COLS = ACC_COLS * NACC;
 
@@ -269,6 +274,38 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 // (every lane takes part in the loads: tcgen05.ld is a warp-wide instruction)
                 // a contiguous share of the 256 output rows per warp group
                 const int ow = 256 / nparts;
+                if constexpr (STG) {
+                    // Rows that leave for another GPU: a lane's direct stores are 32-byte pieces of 32
+                    // different rows per warp instruction, which cross NVLink as small packets. Here the
+                    // lane collects its token's 128 outputs (256 bytes) in shared memory and sends them
+                    // as ONE asynchronous bulk copy. Row pitch 272 bytes: the eight lanes of a quarter
+                    // warp hit eight different 16-byte bank groups.
+                    const uint32_t srow = stage0 + STAGES * STAGE_BYTES + (uint32_t)(part * 128 + row) * STG_ROW_BYTES;
+                    // the previous tile's copy of this row must have read its bytes before they are overwritten
+                    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+#pragma unroll 2
+                    for (int n0 = 0; n0 < 128; n0 += 16) {
+                        uint32_t v[16];
+                        tmem_ld16(taddr + part * 128 + n0, v);
+                        tmem_ld_wait();
+                        uint32_t hh[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const __half2 pr2 = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                            hh[j] = *reinterpret_cast<const uint32_t*>(&pr2);
+                        }
+                        sts128(srow + n0 * 2, hh[0], hh[1], hh[2], hh[3]);
+                        sts128(srow + n0 * 2 + 16, hh[4], hh[5], hh[6], hh[7]);
+                    }
+                    fence_proxy_async();  // the lane's own writes, before the async proxy reads them
+                    if (live)
+                        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 256;" ::"l"(
+                                         __cvta_generic_to_global(dst + part * 128)),
+                                     "r"(srow)
+                                     : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                if constexpr (!STG) {
 #pragma unroll 2
                 for (int n0 = part * ow; n0 < (part + 1) * ow; n0 += 16) {
                     uint32_t v[16];
@@ -283,6 +320,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                         }
                         st_global_v8(dst + n0, hh);  // 16 outputs = one 32-byte sector of the token's row
                     }
+                }
                 }
             }
         } else {
@@ -354,6 +392,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 mbar_arrive(smem_u32(&acc_empty_bar[ab]));
             }
         }
+        if constexpr (STG) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every row has been written
     } else if (warp < B_WARP0) {
         // --------------------------- weight producers --------------------------
         // Sixteen warps, one 16-row weight tile each per 128-input group: warps 0-7 the eight row
@@ -671,18 +710,18 @@ cudaError_t make_tmap_f16(const void* base, uint64_t rows, uint64_t cols, uint32
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int Q, int MODE, int BN, bool ATMA = false>
+template <int Q, int MODE, int BN, bool ATMA = false, bool STG = false>
 static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
     constexpr int NA = 2;
-    constexpr int STAGES = tc::StagesOf<Q, BN, ATMA>::value;
-    const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024;
+    constexpr int STAGES = tc::StagesOf<Q, BN, ATMA, STG>::value;
+    const int smem = STAGES * (NA * tc::SUB_BYTES + BN * 128) + 1024 + (STG ? tc::STG_BYTES : 0);
     static SmemOptIn optin;
     {
-        cudaError_t e = ensure_dyn_smem(tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA>, (size_t)smem, optin);
+        cudaError_t e = ensure_dyn_smem(tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA, STG>, (size_t)smem, optin);
         if (e != cudaSuccess) return e;
     }
     count_launch();
-    tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA><<<grid, tc::THREADS, smem, st>>>(a);
+    tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA, STG><<<grid, tc::THREADS, smem, st>>>(a);
     return cudaGetLastError();
 }
 
@@ -697,6 +736,8 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
     // whose lists are built for 128: its epilogue stores into other GPUs' memory, and with two
     // independent accumulator sets those stores always run under the next tile's MMAs.
     const bool dn256 = (gu_cols == 256) && plan == nullptr;
+    // rows that go to other ranks' return buffers leave through the staged epilogue (bulk copies)
+    const bool stg = (peer != nullptr) && !dn256;
     const int mt_gu = p.L.I / 128;
     tc::Args gu{};
     cudaError_t te = make_tmap_f16(x16, (uint64_t)C, (uint64_t)p.L.H, 128, &gu.tmap);
@@ -739,16 +780,19 @@ cudaError_t launch_grouped_tc(const PrefillArgs& p, const void* x16, int grid, c
         dn.a_row1 = 128;
         e = (gu_cols == 256) ? launch_tc_one<BF16, 0, 256, true>(gu, grid, st) : launch_tc_one<BF16, 0, 128, true>(gu, grid, st);
         if (e != cudaSuccess) return e;
+        if (stg) return launch_tc_one<BF16, 1, 128, true, true>(dn, grid, st);
         return dn256 ? launch_tc_one<BF16, 1, 256, true>(dn, grid, st) : launch_tc_one<BF16, 1, 128, true>(dn, grid, st);
     }
     switch (p.L.quant) {
         case Q4_0:
             e = (gu_cols == 256) ? launch_tc_one<Q4_0, 0, 256>(gu, grid, st) : launch_tc_one<Q4_0, 0, 128>(gu, grid, st);
             if (e != cudaSuccess) return e;
+            if (stg) return launch_tc_one<Q4_0, 1, 128, false, true>(dn, grid, st);
             return dn256 ? launch_tc_one<Q4_0, 1, 256>(dn, grid, st) : launch_tc_one<Q4_0, 1, 128>(dn, grid, st);
         case Q8_0:
             e = (gu_cols == 256) ? launch_tc_one<Q8_0, 0, 256>(gu, grid, st) : launch_tc_one<Q8_0, 0, 128>(gu, grid, st);
             if (e != cudaSuccess) return e;
+            if (stg) return launch_tc_one<Q8_0, 1, 128, false, true>(dn, grid, st);
             return dn256 ? launch_tc_one<Q8_0, 1, 256>(dn, grid, st) : launch_tc_one<Q8_0, 1, 128>(dn, grid, st);
         default:
             // BF16 layers always carry their plain f16 matrices on this path (see above)

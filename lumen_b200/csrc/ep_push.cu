@@ -27,8 +27,9 @@
 //                         sets my row flag on every rank
 //   ep_plan_kernel        wait for all row flags; per-expert column counts of MY experts
 //   tile plan + grouped gate/up + SwiGLU + down on tcgen05 (prefill_tc.cu): operands in this
-//                         GPU's own memory; the down epilogue stores each output row into the
-//                         `back` buffer of the rank the row came from
+//                         GPU's own memory; the down epilogue sends each token's outputs, 256
+//                         bytes per m-tile as one cp.async.bulk copy from a staging tile in
+//                         shared memory, into the `back` buffer of the rank the row came from
 //   ep_signal_kernel      my result flag on every rank
 //   ep_wait_kernel        wait for all result flags
 //   scatter_accum_kernel  out[t] = residual[t] + sum_slot w * back[dst_to_col[t, slot]]

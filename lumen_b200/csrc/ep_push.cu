@@ -18,8 +18,8 @@
 // raises the context's status word and the remaining kernels only keep every index in range):
 //
 //   route + stable counting sort of my tokens         (route_large.cu, unchanged)
-//   ep_counts_kernel      my per-expert counts -> every rank's cnt[me][*], then their count flag
-//   ep_dispatch_kernel    wait for all count flags; from the count matrix every rank derives the
+//   ep_dispatch_kernel    CTA 0: my per-expert counts -> every rank's cnt[me][*], then their count
+//                         flag. All CTAs: wait for all count flags; from the count matrix every rank derives the
 //                         same layout of every receive window (rows grouped by expert, inside an
 //                         expert by source rank, inside a source in its compact-column order, i.e.
 //                         the stable order of cuda/moe.rs:2115-2147 applied globally); push my
@@ -30,8 +30,7 @@
 //                         GPU's own memory; the down epilogue sends each token's outputs, 256
 //                         bytes per m-tile as one cp.async.bulk copy from a staging tile in
 //                         shared memory, into the `back` buffer of the rank the row came from
-//   ep_signal_kernel      my result flag on every rank
-//   ep_wait_kernel        wait for all result flags
+//   ep_signal_wait_kernel my result flag on every rank, then wait for all result flags
 //   scatter_accum_kernel  out[t] = residual[t] + sum_slot w * back[dst_to_col[t, slot]]
 //
 // Reuse of the single-buffered window is safe in stream order: a rank leaves call n only after
@@ -122,30 +121,6 @@ __device__ __forceinline__ bool wait_flags(const uint32_t* flags, int world, uin
 // ---------------------------------------------------------------------------
 // my counts -> every rank
 // ---------------------------------------------------------------------------
-// The number of the call that tags every flag lives in device memory and is advanced here, by the
-// first kernel of a call, so that a captured call can be replayed from a CUDA graph (a host-side
-// counter would be frozen into the graph).
-__global__ void __launch_bounds__(256)
-ep_counts_kernel(const int32_t* __restrict__ expert_bounds, int E, int world, int me, Peers peers, WindowLayout wl,
-                 uint32_t* epoch_dev) {
-    __shared__ uint32_t epoch_s;
-    if (threadIdx.x == 0) {
-        epoch_s = *epoch_dev + 1u;
-        *epoch_dev = epoch_s;
-    }
-    __syncthreads();
-    const uint32_t epoch = epoch_s;
-    for (int i = threadIdx.x; i < world * E; i += 256) {
-        const int r = i / E, e = i - r * E;
-        int32_t* cnt = reinterpret_cast<int32_t*>(peers.win[r] + wl.cnt) + (size_t)me * E;
-        cnt[e] = expert_bounds[e + 1] - expert_bounds[e];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if ((int)threadIdx.x < world)
-        st_release_sys(reinterpret_cast<uint32_t*>(peers.win[threadIdx.x] + wl.flags) + 0 * FLAG_STRIDE + me, epoch);
-}
-
 // ---------------------------------------------------------------------------
 // push my rows to their final place in the owners' windows
 // ---------------------------------------------------------------------------
@@ -168,7 +143,7 @@ struct DispatchArgs {
     WindowLayout wl;
     int C, H, E, epr, world, me, rows_cap;
     int natural;                   // rows in the natural input order (TMA-fed weights) instead of the dequantiser's order
-    const uint32_t* epoch_dev;     // number of this call (advanced by ep_counts_kernel)
+    uint32_t* epoch_dev;           // number of the previous call; this kernel's last CTA advances it
     unsigned long long limit_ns;
     int32_t* status;
     int32_t* status_host;
@@ -184,7 +159,22 @@ ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
     __shared__ int fail_s;
     __shared__ int over_s;
     const int tid = threadIdx.x;
-    const uint32_t epoch = *a.epoch_dev;
+    // The number of the call that tags every flag lives in device memory, so that a captured call
+    // can be replayed from a CUDA graph (a host-side counter would be frozen into the graph). Every
+    // CTA reads the previous call's number here; the last CTA to finish stores this call's.
+    const uint32_t epoch = *a.epoch_dev + 1u;
+    if (blockIdx.x == 0) {
+        // my per-expert pair counts into every rank's count matrix, then my count flag there
+        for (int i = tid; i < a.world * a.E; i += 256) {
+            const int r = i / a.E, e = i - r * a.E;
+            int32_t* cnt = reinterpret_cast<int32_t*>(a.peers.win[r] + a.wl.cnt) + (size_t)a.me * a.E;
+            cnt[e] = a.expert_bounds[e + 1] - a.expert_bounds[e];
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (tid < a.world)
+            st_release_sys(reinterpret_cast<uint32_t*>(a.peers.win[tid] + a.wl.flags) + 0 * FLAG_STRIDE + a.me, epoch);
+    }
     const uint32_t* flags = reinterpret_cast<const uint32_t*>(a.my_win + a.wl.flags);
     const bool ok = wait_flags(flags + 0 * FLAG_STRIDE, a.world, epoch, a.limit_ns, a.status, a.status_host, &fail_s);
     if (tid == 0) over_s = 0;
@@ -291,7 +281,10 @@ ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
         __threadfence_system();
         if (tid < a.world)
             st_release_sys(reinterpret_cast<uint32_t*>(a.peers.win[tid] + a.wl.flags) + 1 * FLAG_STRIDE + a.me, epoch);
-        if (tid == 0) *a.done_counter = 0u;
+        if (tid == 0) {
+            *a.done_counter = 0u;
+            *a.epoch_dev = epoch;
+        }
     }
 }
 
@@ -329,17 +322,15 @@ ep_plan_kernel(const uint8_t* my_win, WindowLayout wl, int E, int epr, int world
     }
 }
 
-__global__ void ep_signal_kernel(Peers peers, WindowLayout wl, int world, int me, const uint32_t* epoch_dev) {
+// my result flag on every rank (the grouped GEMMs of this stream have completed), then wait for everyone's
+__global__ void ep_signal_wait_kernel(Peers peers, const uint8_t* my_win, WindowLayout wl, int world, int me,
+                                      const uint32_t* epoch_dev, unsigned long long limit_ns, int32_t* status,
+                                      int32_t* status_host) {
+    __shared__ int fail_s;
     const uint32_t epoch = *epoch_dev;
     __threadfence_system();
     if ((int)threadIdx.x < world)
         st_release_sys(reinterpret_cast<uint32_t*>(peers.win[threadIdx.x] + wl.flags) + 2 * FLAG_STRIDE + me, epoch);
-}
-
-__global__ void ep_wait_kernel(const uint8_t* my_win, WindowLayout wl, int world, const uint32_t* epoch_dev,
-                               unsigned long long limit_ns, int32_t* status, int32_t* status_host) {
-    __shared__ int fail_s;
-    const uint32_t epoch = *epoch_dev;
     const uint32_t* flags = reinterpret_cast<const uint32_t*>(my_win + wl.flags);
     wait_flags(flags + 2 * FLAG_STRIDE, world, epoch, limit_ns, status, status_host, &fail_s);
 }
@@ -520,10 +511,8 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     CUDA_TRY(launch_route_large(p, st));
     mark(1);
     const int C = batch * sc->K;
-    // 2. counts to everyone
-    count_launch(2);
-    ep::ep_counts_kernel<<<1, 256, 0, st>>>(sc->R.expert_bounds, sc->E, s->world, s->rank, s->peers, s->wl, s->epoch_dev);
-    // 3. rows to their owners
+    // 2. counts to everyone, 3. rows to their owners (one kernel)
+    count_launch(1);
     ep::DispatchArgs d{};
     d.x = normed;
     d.col_expert = sc->R.col_expert;
@@ -581,9 +570,9 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     CUDA_TRY(launch_grouped_tc(q, s->win + s->wl.x16, grid, st, nullptr, &plan, &po));
     mark(4);
     // 6. results are out; wait for everyone's; combine
-    count_launch(2);
-    ep::ep_signal_kernel<<<1, 32, 0, st>>>(s->peers, s->wl, s->world, s->rank, s->epoch_dev);
-    ep::ep_wait_kernel<<<1, 32, 0, st>>>(s->win, s->wl, s->world, s->epoch_dev, limit_ns, sc->status, sc->status_host);
+    count_launch(1);
+    ep::ep_signal_wait_kernel<<<1, 32, 0, st>>>(s->peers, s->win, s->wl, s->world, s->rank, s->epoch_dev, limit_ns,
+                                                sc->status, sc->status_host);
     CUDA_TRY(cudaGetLastError());
     mark(5);
     CUDA_TRY(launch_scatter_accum(reinterpret_cast<const __half*>(s->win + s->wl.back), residual, sc->R, output, batch,

@@ -13,13 +13,14 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("T,act,routing", [(600, torch.bfloat16, "router"), (77, torch.float32, "zipf"),
-                                           (1, torch.float32, "router")])
-def test_one_rank_window_equals_plain_prefill(cuda_lib, T, act, routing):
+@pytest.mark.parametrize("T,act,routing,quant", [(600, torch.bfloat16, "router", 1), (77, torch.float32, "zipf", 1),
+                                                 (1, torch.float32, "router", 1), (300, torch.bfloat16, "zipf", 0),
+                                                 (300, torch.float32, "router", 2), (1200, torch.bfloat16, "router", 1)])
+def test_one_rank_window_equals_plain_prefill(cuda_lib, T, act, routing, quant):
     from lumen_b200 import ep, moe, synth
     from oracle import oracle
     H, I, E, K = 512, 256, 32, 4
-    lay = synth.LayerLayout(H, I, E, 1)
+    lay = synth.LayerLayout(H, I, E, quant)
     blob = synth.make_layer_blob(lay, 3)
     g = torch.Generator("cuda").manual_seed(4)
     x = torch.randn((T, H), generator=g, device="cuda").to(act)
@@ -30,7 +31,7 @@ def test_one_rank_window_equals_plain_prefill(cuda_lib, T, act, routing):
     sc.set_logits_override(lg)
     ref = sc.prefill(full, x, res)
     r_ref = sc.get_routing(T)
-    pe = ep.PushExpertParallel(H, I, E, K, 700, 0, 1, 0)
+    pe = ep.PushExpertParallel(H, I, E, K, max(700, T), 0, 1, 0)
     layer = pe.prepare_layer(blob, lay.meta())
     pe.sc.set_logits_override(lg)
     outs = [pe.forward(layer, x, res).clone() for _ in range(3)]  # the window is reused call after call
@@ -45,7 +46,7 @@ def test_one_rank_window_equals_plain_prefill(cuda_lib, T, act, routing):
     xs = x[sample].float().cpu().numpy()
     meta = lay.meta()
     o_out, _, _ = oracle.moe_layer(blob.cpu().numpy(), 0, meta.expert_gate_offs, meta.expert_up_offs,
-                                   meta.expert_down_offs, 1, H, I, E, K, xs, res[sample].cpu().numpy(),
+                                   meta.expert_down_offs, quant, H, I, E, K, xs, res[sample].cpu().numpy(),
                                    ids=r["ids"][sample], weights=r["weights"][sample], threads=8)
     got = outs[0][sample].cpu().numpy() - res[sample].cpu().numpy()
     want = o_out - res[sample].cpu().numpy()

@@ -153,6 +153,7 @@ struct DispatchArgs {
 template <typename XT>
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const __grid_constant__ DispatchArgs a) {
+    grid_dep_sync();
     __shared__ int base_s[MAX_EXPERTS];   // first row, in the owner's window, of MY pairs of expert e
     __shared__ int tot_s[MAX_EXPERTS];    // pairs of expert e over all ranks
     __shared__ int mine_s[MAX_EXPERTS + 1];
@@ -295,6 +296,7 @@ __global__ void __launch_bounds__(256)
 ep_plan_kernel(const uint8_t* my_win, WindowLayout wl, int E, int epr, int world, int me, int rows_cap,
                const uint32_t* epoch_dev, unsigned long long limit_ns, int32_t* status, int32_t* status_host,
                int32_t* counts_out) {
+    grid_dep_sync();
     __shared__ int fail_s;
     __shared__ int tot_s[MAX_EXPERTS];
     const uint32_t epoch = *epoch_dev;
@@ -326,6 +328,7 @@ ep_plan_kernel(const uint8_t* my_win, WindowLayout wl, int E, int epr, int world
 __global__ void ep_signal_wait_kernel(Peers peers, const uint8_t* my_win, WindowLayout wl, int world, int me,
                                       const uint32_t* epoch_dev, unsigned long long limit_ns, int32_t* status,
                                       int32_t* status_host) {
+    grid_dep_sync();
     __shared__ int fail_s;
     const uint32_t epoch = *epoch_dev;
     __threadfence_system();
@@ -535,13 +538,14 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     d.status_host = sc->status_host;
     d.done_counter = s->done_counter;
     const int dgrid = (C + 3) / 4 < sc->sms * 8 ? (C + 3) / 4 : sc->sms * 8;  // four rows per CTA step
-    if (act_dtype == 0) ep::ep_dispatch_kernel<float><<<dgrid, 256, 0, st>>>(d);
-    else ep::ep_dispatch_kernel<__nv_bfloat16><<<dgrid, 256, 0, st>>>(d);
+    CUDA_TRY(act_dtype == 0 ? launch_dep(ep::ep_dispatch_kernel<float>, dim3(dgrid), dim3(256), 0, st, d)
+                            : launch_dep(ep::ep_dispatch_kernel<__nv_bfloat16>, dim3(dgrid), dim3(256), 0, st, d));
     mark(2);
     // 4. what arrived for my experts
     count_launch(1);
-    ep::ep_plan_kernel<<<1, 256, 0, st>>>(s->win, s->wl, sc->E, s->epr, s->world, s->rank, s->rows_cap, s->epoch_dev,
-                                          limit_ns, sc->status, sc->status_host, s->RX.expert_bounds);
+    CUDA_TRY(launch_dep(ep::ep_plan_kernel, dim3(1), dim3(256), 0, st, (const uint8_t*)s->win, s->wl, sc->E, s->epr, s->world,
+                        s->rank, s->rows_cap, (const uint32_t*)s->epoch_dev, limit_ns, sc->status, sc->status_host,
+                        s->RX.expert_bounds));
     // expected rows per expert under balanced routing decide the gate/up tile width
     const int gu_cols = ((long long)C > 128ll * s->epr) ? 256 : 128;
     CUDA_TRY(launch_tile_plan(s->RX, s->epr, sc->H, sc->I, s->rows_cap, gu_cols, s->tiles, s->n_tiles, st));
@@ -571,8 +575,8 @@ Status encode_moe_ffn_prefill_ep(CudaMoeScratch* sc, EpState* s, const MoeLayer&
     mark(4);
     // 6. results are out; wait for everyone's; combine
     count_launch(1);
-    ep::ep_signal_wait_kernel<<<1, 32, 0, st>>>(s->peers, s->win, s->wl, s->world, s->rank, s->epoch_dev, limit_ns,
-                                                sc->status, sc->status_host);
+    CUDA_TRY(launch_dep(ep::ep_signal_wait_kernel, dim3(1), dim3(32), 0, st, s->peers, (const uint8_t*)s->win, s->wl, s->world,
+                        s->rank, (const uint32_t*)s->epoch_dev, limit_ns, sc->status, sc->status_host));
     CUDA_TRY(cudaGetLastError());
     mark(5);
     CUDA_TRY(launch_scatter_accum(reinterpret_cast<const __half*>(s->win + s->wl.back), residual, sc->R, output, batch,

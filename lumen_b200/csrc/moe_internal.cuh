@@ -115,6 +115,33 @@ __device__ __forceinline__ void raise_status(int32_t* status, int32_t* status_ho
         __threadfence_system();
     }
 }
+
+// Programmatic dependent launch for the chains of small kernels around the grouped products. A
+// kernel launched with launch_dep() may be scheduled while the kernel before it in the stream
+// is still running; it calls grid_dep_sync() as its first statement (every thread, before any
+// early return, before touching anything an earlier kernel wrote): that returns once the
+// preceding kernel has completed and its writes are visible, so the order of the stream is
+// kept, and because every kernel of a chain does so, completion of one implies completion of
+// all before it. What overlaps is the launch itself and whatever the kernel does before the call.
+__device__ __forceinline__ void grid_dep_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dep(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 #endif
 
 // launchers (kernels.cu files)

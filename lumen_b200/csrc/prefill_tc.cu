@@ -237,6 +237,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
+    // (barriers and TMEM are set up above while the kernel before this one may still be running;
+    // everything it wrote, the tile list first of all, is read from here on)
+    grid_dep_sync();
     const int ntiles = a.n_tiles[MODE];
     const int kgs = a.kdim >> 7;   // 128-input groups (weight tile granularity)
     const int khs = kgs * 2;       // 64-input pipeline stages per tile
@@ -620,6 +623,7 @@ template <typename XT, bool IS_F16 = false, bool NATURAL = false>
 __global__ void __launch_bounds__(256)
 gather_permute_x16_kernel(const XT* __restrict__ x, const int32_t* __restrict__ col_src_tok, int C, int H,
                           uint16_t* __restrict__ out) {
+    grid_dep_sync();
     // one thread per output chunk of 8 values (16 bytes): chunk t of a 32-block holds inputs
     // (4t, 4t+2, 16+4t, 16+4t+2, 4t+1, 4t+3, 16+4t+1, 16+4t+3), i.e. perm_pos of two runs of four.
     // Four rows per step: their source rows are known first, then all eight loads of a thread are
@@ -671,8 +675,10 @@ cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_
     count_launch();
     if (C <= 0) return cudaSuccess;
     const int ggrid = (C + 3) / 4;  // four rows per CTA step; every CTA takes one step at these sizes
+    cudaError_t lerr = cudaSuccess;
 #define LUMEN_GATHER(XT, F16, NAT) \
-    tc::gather_permute_x16_kernel<XT, F16, NAT><<<ggrid, 256, 0, st>>>((const XT*)x, col_src_tok, C, H, (uint16_t*)out)
+    lerr = launch_dep(tc::gather_permute_x16_kernel<XT, F16, NAT>, dim3(ggrid), dim3(256), 0, st, (const XT*)x, col_src_tok, C, \
+                      H, (uint16_t*)out)
     if (act_dtype == 0) {
         if (natural) LUMEN_GATHER(float, false, true);
         else LUMEN_GATHER(float, false, false);
@@ -684,7 +690,7 @@ cudaError_t launch_gather_permute_x16(const void* x, int act_dtype, const int32_
         else LUMEN_GATHER(__nv_bfloat16, false, false);
     }
 #undef LUMEN_GATHER
-    return cudaGetLastError();
+    return lerr;
 }
 
 cudaError_t make_tmap_f16(const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out) {
@@ -721,8 +727,7 @@ static cudaError_t launch_tc_one(const tc::Args& a, int grid, cudaStream_t st) {
         if (e != cudaSuccess) return e;
     }
     count_launch();
-    tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA, STG><<<grid, tc::THREADS, smem, st>>>(a);
-    return cudaGetLastError();
+    return launch_dep(tc::grouped_gemm_tc_kernel<Q, MODE, BN, ATMA, STG>, dim3(grid), dim3(tc::THREADS), (size_t)smem, st, a);
 }
 
 // gate/up + SwiGLU then down, both on tcgen05. x16: permuted 16-bit activations [T,H].

@@ -20,6 +20,12 @@
 #include "router.cuh"
 #include "mma_frag.cuh"
 
+#define CUDA_RET(expr)                         \
+    do {                                       \
+        const cudaError_t e_ = (expr);         \
+        if (e_ != cudaSuccess) return e_;      \
+    } while (0)
+
 namespace lumen {
 
 // ---------------------------------------------------------------------------
@@ -259,6 +265,7 @@ constexpr int TK_WARPS = 8;
 __global__ void __launch_bounds__(TK_WARPS * 32)
 topk_large_kernel(const float* __restrict__ logits, int nparts, float* __restrict__ logits_out, int T, int E, int K,
                   int gating, uint32_t* __restrict__ ids, float* __restrict__ weights, int32_t* __restrict__ blk_hist) {
+    grid_dep_sync();
     __shared__ __align__(16) float p_s[TK_WARPS][MAX_EXPERTS];
     __shared__ __align__(16) float lg_s[TK_WARPS][MAX_EXPERTS];
     __shared__ int h[MAX_EXPERTS];
@@ -291,6 +298,7 @@ constexpr int SORT_TOK = TK_WARPS;  // tokens per chunk: one block of the top-k 
 
 __global__ void __launch_bounds__(256)
 sort_hist_kernel(const uint32_t* __restrict__ ids, int T, int K, int E, int32_t* __restrict__ blk_hist) {
+    grid_dep_sync();
     __shared__ int h[MAX_EXPERTS];
     const int tid = threadIdx.x;
     for (int e = tid; e < E; e += 256) h[e] = 0;
@@ -307,6 +315,7 @@ sort_hist_kernel(const uint32_t* __restrict__ ids, int T, int K, int E, int32_t*
 // the row total goes to expert_bounds[e] for sort_scan_kernel.
 __global__ void __launch_bounds__(32)
 sort_rowscan_kernel(int32_t* __restrict__ blk_hist, int nchunks, RouteDev R) {
+    grid_dep_sync();
     const int e = blockIdx.x, lane = threadIdx.x;
     int32_t* rowp = blk_hist + (size_t)e * nchunks;
     int run = 0;
@@ -339,6 +348,7 @@ __global__ void __launch_bounds__(256)
 sort_scan_kernel(int nchunks, int E, RouteDev R, int tile_cols, int tile_cols_dn,
                  int mt_gu, int mt_dn, int4* __restrict__ tiles_gu, int4* __restrict__ tiles_dn,
                  int32_t* __restrict__ n_tiles, int max_tiles_gu, int max_tiles_dn) {
+    grid_dep_sync();
     __shared__ int cnt_s[MAX_EXPERTS];
     __shared__ int bounds_s[MAX_EXPERTS + 1];
     __shared__ int tile_off_s[MAX_EXPERTS + 1];
@@ -433,6 +443,7 @@ sort_scan_kernel(int nchunks, int E, RouteDev R, int tile_cols, int tile_cols_dn
 __global__ void __launch_bounds__(256)
 sort_place_kernel(const uint32_t* __restrict__ ids, int T, int K, int E, const int32_t* __restrict__ blk_hist,
                   int nchunks, RouteDev R) {
+    grid_dep_sync();
     __shared__ int cursor[8][MAX_EXPERTS];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int chunk = blockIdx.x * 8 + warp;
@@ -494,6 +505,7 @@ __global__ void __launch_bounds__(256)
 scatter_accum_kernel(const __half* __restrict__ d16, const float* residual,
                      const float* __restrict__ weights, const int32_t* __restrict__ dst_to_col,
                      float* out, int T, int H, int K) {  // residual may be out (in-place layer stacks)
+    grid_dep_sync();
     const int t = blockIdx.x;  // tokens on grid.x: the y dimension is limited to 65535
     const int h8 = blockIdx.y * 256 + threadIdx.x;  // group of 8 outputs
     if (h8 * 8 >= H) return;
@@ -535,9 +547,8 @@ scatter_accum_kernel(const __half* __restrict__ d16, const float* residual,
 cudaError_t launch_scatter_accum(const __half* d16, const float* residual, const RouteDev& R, float* out,
                                  int T, int H, int K, cudaStream_t st) {
     count_launch();
-    scatter_accum_kernel<<<dim3(T, (H / 8 + 255) / 256), 256, 0, st>>>(d16, residual, R.weights, R.dst_to_col,
-                                                                       out, T, H, K);
-    return cudaGetLastError();
+    return launch_dep(scatter_accum_kernel, dim3(T, (H / 8 + 255) / 256), dim3(256), 0, st, d16, residual, R.weights,
+                      R.dst_to_col, out, T, H, K);
 }
 
 __global__ void __launch_bounds__(256)
@@ -646,10 +657,10 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     count_launch(4);
     const int nchunks = (T + SORT_TOK - 1) / SORT_TOK;
     if (a.ids_in == nullptr)
-        topk_large_kernel<<<nchunks, TK_WARPS * 32, 0, st>>>(lg, nparts, a.R.logits, T, E, K, a.gating, a.R.ids,
-                                                             a.R.weights, a.blk_hist);
+        CUDA_RET(launch_dep(topk_large_kernel, dim3(nchunks), dim3(TK_WARPS * 32), 0, st, lg, nparts, a.R.logits, T, E, K,
+                            a.gating, a.R.ids, a.R.weights, a.blk_hist));
     else
-        sort_hist_kernel<<<nchunks, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist);
+        CUDA_RET(launch_dep(sort_hist_kernel, dim3(nchunks), dim3(256), 0, st, a.R.ids, T, K, E, a.blk_hist));
     const int C = T * K;
     // columns per grouped-GEMM tile: 128 or 256, the same for gate/up and down
     const int tile_cols = tc_gu_tile_cols(C, E), tile_cols_dn = tile_cols;
@@ -657,11 +668,11 @@ cudaError_t launch_route_large(const PrefillArgs& a, cudaStream_t st) {
     const int mt_gu = a.L.I / 128, mt_dn = a.L.H / 256;  // m-tiles: 128 gate + 128 up rows | 256 down rows
     int4* tiles_gu = a.tiles;
     int4* tiles_dn = a.tiles ? a.tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1) : nullptr;
-    sort_rowscan_kernel<<<E, 32, 0, st>>>(a.blk_hist, nchunks, a.R);
-    sort_scan_kernel<<<1, 256, 0, st>>>(nchunks, E, a.R, tile_cols, tile_cols_dn, mt_gu, mt_dn, tiles_gu, tiles_dn,
-                                        a.n_tiles, max_ct * mt_gu, max_ct_dn * mt_dn);
-    sort_place_kernel<<<(nchunks + 7) / 8, 256, 0, st>>>(a.R.ids, T, K, E, a.blk_hist, nchunks, a.R);
-    return cudaGetLastError();
+    CUDA_RET(launch_dep(sort_rowscan_kernel, dim3(E), dim3(32), 0, st, a.blk_hist, nchunks, a.R));
+    CUDA_RET(launch_dep(sort_scan_kernel, dim3(1), dim3(256), 0, st, nchunks, E, a.R, tile_cols, tile_cols_dn, mt_gu, mt_dn,
+                        tiles_gu, tiles_dn, a.n_tiles, max_ct * mt_gu, max_ct_dn * mt_dn));
+    return launch_dep(sort_place_kernel, dim3((nchunks + 7) / 8), dim3(256), 0, st, a.R.ids, T, K, E, a.blk_hist, nchunks,
+                      a.R);
 }
 
 cudaError_t launch_tile_plan(const RouteDev& R, int E, int H, int I, int rows_cap, int gu_cols, int4* tiles,
@@ -671,10 +682,8 @@ cudaError_t launch_tile_plan(const RouteDev& R, int E, int H, int I, int rows_ca
     count_launch();
     // (down tiles of 128 tokens here: an expert-parallel down product stores its rows into other GPUs'
     // memory, which only the always-overlapped epilogue of the 128-token form hides)
-    sort_scan_kernel<<<1, 256, 0, st>>>(0, E, R, gu_cols, 128, mt_gu, mt_dn, tiles,
-                                        tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1), n_tiles, max_ct * mt_gu,
-                                        max_ct_dn * mt_dn);
-    return cudaGetLastError();
+    return launch_dep(sort_scan_kernel, dim3(1), dim3(256), 0, st, 0, E, R, gu_cols, 128, mt_gu, mt_dn, tiles,
+                      tiles + (size_t)max_ct * (mt_gu > 0 ? mt_gu : 1), n_tiles, max_ct * mt_gu, max_ct_dn * mt_dn);
 }
 
 // ---------------------------------------------------------------------------

@@ -62,6 +62,7 @@ router_logits_tc_kernel(const __grid_constant__ Args a) {
     const int t0 = tt * BN, e0 = mt * 128;
     const int kh_per = (a.H / 64) / a.ksplit;  // 64-input stages of this CTA's k range
     const int kh0 = ks * kh_per;
+    grid_dep_sync();  // (the planes of x and the flag come from the split kernel before this one)
     const bool use_lo = (*a.any_lo != 0);
 
     if (tid == 0) {
@@ -159,6 +160,7 @@ router_logits_tc_kernel(const __grid_constant__ Args a) {
 template <typename XT>
 __global__ void __launch_bounds__(256)
 split_x16_kernel(const XT* __restrict__ x, size_t n8, size_t plane, __half* __restrict__ out, int32_t* any_lo) {
+    grid_dep_sync();
     const size_t i = (size_t)blockIdx.x * 256 + threadIdx.x;
     unsigned nz = 0u;
     if (i < n8) {
@@ -233,11 +235,12 @@ cudaError_t launch_router_logits_tc(const void* x, int act_dtype, const __half* 
     cudaError_t e = cudaMemsetAsync(any_lo, 0, sizeof(int32_t), st);
     if (e != cudaSuccess) return e;
     count_launch(2);
-    if (act_dtype == 0)
-        rtc::split_x16_kernel<float><<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>((const float*)x, n8, plane, x16, any_lo);
-    else
-        rtc::split_x16_kernel<__nv_bfloat16><<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, n8, plane,
-                                                                                          x16, any_lo);
+    const dim3 sgrid((unsigned)((n8 + 255) / 256));
+    e = (act_dtype == 0)
+            ? launch_dep(rtc::split_x16_kernel<float>, sgrid, dim3(256), 0, st, (const float*)x, n8, plane, x16, any_lo)
+            : launch_dep(rtc::split_x16_kernel<__nv_bfloat16>, sgrid, dim3(256), 0, st, (const __nv_bfloat16*)x, n8, plane, x16,
+                         any_lo);
+    if (e != cudaSuccess) return e;
     rtc::Args a{};
     e = make_tmap_f16(w16, (uint64_t)2 * E, (uint64_t)H, 128, &a.tmap_w);
     if (e != cudaSuccess) return e;
@@ -258,8 +261,7 @@ cudaError_t launch_router_logits_tc(const void* x, int act_dtype, const __half* 
     e = ensure_dyn_smem(rtc::router_logits_tc_kernel, (size_t)smem, optin);
     if (e != cudaSuccess) return e;
     const int grid = ((T + rtc::BN - 1) / rtc::BN) * a.m_tiles * ksplit;
-    rtc::router_logits_tc_kernel<<<grid, rtc::THREADS, smem, st>>>(a);
-    return cudaGetLastError();
+    return launch_dep(rtc::router_logits_tc_kernel, dim3(grid), dim3(rtc::THREADS), (size_t)smem, st, a);
 }
 
 }  // namespace lumen

@@ -11,8 +11,11 @@
 //   gate_up_kernel        per (distinct expert, 16 rows of I): gate and up rows
 //                         times the tokens routed to the expert, SwiGLU
 //                         (cuda/shaders/moe_expert_q4_0.cu:58-108, moe_expert.cu:62-97).
+//                         The general form; Q4_0 layers take gate_up_stream_kernel and the
+//                         other small-batch forms of decode_small.cu.
 //   down_combine_kernel   per 16 rows of H: down rows of every selected expert
-//                         (moe_expert_q4_0.cu:118-151) and the weighted combine
+//                         (moe_expert_q4_0.cu:118-151; integer tensor cores on int8 SwiGLU
+//                         values after gate_up_stream_kernel) and the weighted combine
 //                         out = residual + sum_k w_k d_k in slot order
 //                         (cuda/shaders/moe_accum.cu:22-46, cuda/moe.rs:6508-6524).
 //

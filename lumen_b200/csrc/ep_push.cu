@@ -428,7 +428,7 @@ Status ep_create(CudaMoeScratch* sc, int rank, int world, int max_tokens, int re
     s->RX.expert_bounds = misc;            // [epr + 1] <= 257
     s->RX.uexp = misc + 264;               // [epr]
     s->RX.n_uexp = misc + 528;
-    s->n_tiles = misc + 536;               // [2]
+    s->n_tiles = misc + 536;               // [4]: tile counts and the tile counters of the two products
     s->done_counter = reinterpret_cast<unsigned int*>(misc + 544);
     s->epoch_dev = reinterpret_cast<uint32_t*>(misc + 552);
     s->peers.win[rank] = s->win;

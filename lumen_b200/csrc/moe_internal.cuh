@@ -184,7 +184,7 @@ struct PrefillArgs {
     __half* s16;            // [C, I] f16 SwiGLU output, row-major by compact column
     __half* d16;            // [C, H] f16 down output by compact column
     int4* tiles;            // tile list for the grouped GEMMs
-    int32_t* n_tiles;       // [2]: gate/up tiles, down tiles
+    int32_t* n_tiles;       // [4]: gate/up tiles, down tiles, and the two kernels' tile counters
     unsigned int* tile_counter;  // [2] dynamic tile scheduler counters
     int32_t* status;        // [1] device-side error flag (bounded waits, invalid caller-supplied ids)
     int32_t* status_host;   // the same code in mapped pinned host memory (null = none)

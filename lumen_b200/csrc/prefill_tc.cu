@@ -14,7 +14,7 @@
 // thread owns one token and stores 32 bytes at a time; a tile of up to 256 columns is two
 // such products against the same weight stage, into the two accumulator sets.
 //
-// One CTA per SM, persistent over a device-built tile list, warp-specialised (26 warps):
+// One CTA per SM, persistent over a device-built tile list, warp-specialised (27 warps):
 //   warps 0-7   epilogue: tcgen05.ld of the accumulators, SwiGLU (gate/up), f16 stores
 //               (into another rank's return buffer for an expert-parallel down product)
 //   warps 8-23  weight producers, one 16-row tile each per 128-input group: 128-bit loads of
@@ -26,6 +26,9 @@
 //   warp 24     one thread feeds the activation operand (and TMA-fed weights) with
 //               cp.async.bulk.tensor.2d boxes of 64 inputs x 128 rows
 //   warp 25     one elected thread issues tcgen05.mma / tcgen05.commit
+//   warp 26     one thread hands out the tiles: the CTA's first tile is its index, every further
+//               one is claimed from a device-wide counter while the tile before it is being
+//               multiplied, and reaches the roles through a small ring of descriptors
 // Stages are handed over with mbarriers; every wait is bounded (on expiry the
 // kernel raises a status word, drains and frees its TMEM instead of hanging).
 //
@@ -43,7 +46,9 @@ namespace tc {
 
 constexpr int EPI_WARPS = 8, A_WARPS = 16, B_WARPS = 1;  // B: one thread drives the TMA
 constexpr int A_WARP0 = EPI_WARPS, B_WARP0 = A_WARP0 + A_WARPS, MMA_WARP = B_WARP0 + B_WARPS;
-constexpr int THREADS = (MMA_WARP + 1) * 32;
+constexpr int SCHED_WARP = MMA_WARP + 1;  // one thread hands out the tiles
+constexpr int THREADS = (SCHED_WARP + 1) * 32;
+constexpr int SCHED_RING = 4;             // tile descriptors in flight between the scheduler and the roles
 
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
     uint32_t r;
@@ -70,7 +75,7 @@ struct Args {
     LayerDev L;
     const int32_t* col_src_tok;  // unused by the GEMM (rows are pre-gathered); kept for diagnostics
     const int4* tiles;
-    const int32_t* n_tiles;
+    int32_t* n_tiles;            // [0..1] tiles of the gate/up and the down list, [2..3] the kernels' tile counters (zero at launch)
     const void* b_src;      // 16-bit activations [rows, kdim], permuted order
     __half* out16;          // gate/up: S16 [C, I] permuted order; down: D16 [C, H] natural order
     int32_t* status;
@@ -209,6 +214,13 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[NACC], acc_empty_bar[NACC];
     __shared__ uint32_t tmem_base_s;
     __shared__ uint32_t abort_s;
+    // Tiles are handed out dynamically: the CTA's first tile is blockIdx.x, every further one the next
+    // of the list not yet taken by any CTA (a device-wide counter). One thread claims a tile while the
+    // MMA thread is still inside the tile before it, and passes the descriptor to the roles through
+    // this ring. (With tiles dealt round-robin the slowest CTA of a Zipf-loaded 4096-token call ran
+    // 11 % longer than the average one in gate/up and 8 % in down.)
+    __shared__ int4 sched_tile_s[SCHED_RING];
+    __shared__ uint64_t sched_full_bar[SCHED_RING], sched_empty_bar[SCHED_RING], sched_go_bar;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -224,6 +236,14 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             mbar_init(smem_u32(&acc_full_bar[b]), 1);
             mbar_init(smem_u32(&acc_empty_bar[b]), (HELP ? EPI_WARPS + A_WARPS : EPI_WARPS) * 32);
         }
+        // readers of a descriptor: epilogue warps, the producer warps when they dequantise or share the
+        // epilogue, the TMA thread and the MMA thread
+        constexpr int SCHED_READERS = EPI_WARPS * 32 + ((!ATMA || HELP) ? A_WARPS * 32 : 0) + 2;
+        for (int s = 0; s < SCHED_RING; ++s) {
+            mbar_init(smem_u32(&sched_full_bar[s]), 1);
+            mbar_init(smem_u32(&sched_empty_bar[s]), SCHED_READERS);
+        }
+        mbar_init(smem_u32(&sched_go_bar), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == MMA_WARP) {
@@ -245,6 +265,22 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     const int khs = kgs * 2;       // 64-input pipeline stages per tile
     // every operand is f16 here: BF16 weights are converted exactly (see dequant_store)
     const bool bf16_mode = false;
+    // The n-th tile of this CTA (n counted by the calling thread): false when the list is exhausted
+    // or the kernel gives up. The descriptor is copied and its ring slot released at once.
+    auto next_tile = [&](int& n, int4& tile) -> bool {
+        const int slot = n % SCHED_RING;
+        if (!mbar_wait(smem_u32(&sched_full_bar[slot]), (n / SCHED_RING) & 1, abort_flag)) return false;
+        tile = sched_tile_s[slot];
+        mbar_arrive(smem_u32(&sched_empty_bar[slot]));
+        ++n;
+        return tile.z >= 0;
+    };
+    // stage of a tile at which the MMA thread lets the scheduler claim the CTA's next tile: late, so
+    // that the last tiles of the list go to the CTAs that are free first, but early enough for the
+    // claim (an atomic and a load, ~2 us) to be back when the producers reach the tile's last group
+    // (the producers take the next descriptor before they fill the last two stages of a tile, so the
+    // signal has to come before the MMA thread needs those: go_kh <= khs - 2)
+    const int go_kh = (khs >= 24) ? khs / 2 - 4 : (khs >= 4 ? 1 : 0);
 
     // Epilogue of one tile by one warp: the warp's TMEM lanes are 32 (warp % 4).. (hardware rule);
     // of the tile's 16-column TMEM chunks it takes those with chunk % nparts == part.
@@ -382,8 +418,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         // ------------------------------ epilogue ------------------------------
         int v = 0;  // accumulator sets handed over so far: set v % NACC, used v / NACC times before
         bool ok = true;
-        for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x) {
-            const int4 tile = a.tiles[ti];
+        int tn = 0;
+        int4 tile;
+        while (ok && next_tile(tn, tile)) {
             const int nh = (MODE == 1 && tile.z > 128) ? 2 : 1;
             for (int h = 0; ok && h < nh; ++h, ++v) {
                 const int ab = v % NACC, use = v / NACC;
@@ -402,10 +439,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         // tiles of the stage's first operand, warps 8-15 those of the second.
         const int pw = warp - A_WARP0;
         const int op = pw >> 3, rtl = pw & 7;  // operand of the stage, 16-row tile within its 128 rows
-        const int all_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-        const int my_tiles = ATMA ? 0 : all_tiles;
-        const int ngroups = my_tiles * kgs;
         bool ok = true;
+        int tn = 0;
         // quant words and scales of this warp's tile of 128-input group kg of a tile of the list
         auto tile_ptrs = [&](const int4& tile, int kg, const uint4*& qp, const uint4*& sp) {
             const int e = tile.x;
@@ -425,30 +460,12 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             qp = qb + ((size_t)tidx * QTraits<Q>::NQ) * 32 + lane;
             sp = sb + (size_t)tidx * 8;
         };
-        // With one accumulator set (HELP) this warp also does a share of every tile's epilogue. Before
-        // it fills global stage number `it` it must have done so for every tile before the one stage
-        // it - STAGES belongs to: that stage is only consumed, and its slot freed, after those epilogues.
-        int helped = 0;
-        auto help_until = [&](int upto) {
-            if constexpr (HELP) {
-                while (ok && helped < upto) {
-                    const int4 tile = a.tiles[blockIdx.x + helped * gridDim.x];
-                    ok = mbar_wait(smem_u32(&acc_full_bar[0]), helped & 1, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
-                    epilogue_part(tile, 0, 0, EPI_WARPS / 4 + (pw >> 2), EPI_PARTS);
-                    tc_fence_before();
-                    mbar_arrive(smem_u32(&acc_empty_bar[0]));
-                    ++helped;
-                }
-            }
-        };
         auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool { return mbar_wait(bar, parity, abort_flag); };
         auto warp_arrive = [&](uint32_t bar) {
             fence_proxy_async();
             mbar_arrive(bar);
         };
-        {
+        if constexpr (!ATMA) {
             WTile<Q> cur, nxt;
             auto issue = [&](const int4& tile, int kg, WTile<Q>& dst) {
                 const uint4 *qp, *sp;
@@ -457,34 +474,38 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 for (int j = 0; j < QTraits<Q>::NQ; ++j) dst.q[j] = ldg_stream(qp + j * 32);
                 if (Q != BF16) dst.s = ldg_stream(sp + (lane >> 2));
             };
-            // tile descriptors are fetched one tile ahead so that no weight load waits on one
-            int4 tile_c = (my_tiles > 0) ? a.tiles[blockIdx.x] : make_int4(0, 0, 0, 0);
-            int4 tile_n = tile_c;
-            if (ngroups > 0) issue(tile_c, 0, cur);
-            int it = 0, kg = 0, tl = 0;
+            // The next tile's descriptor is taken before the last group of the current tile, so that
+            // the first group of the next tile is in flight while the last one is dequantised.
+            int4 tile_c, tile_n = make_int4(0, 0, -1, 0);
+            bool have_c = next_tile(tn, tile_c), have_n = false;
+            if (have_c) issue(tile_c, 0, cur);
+            int it = 0, kg = 0;
             long long tr_w = 0;
             const long long tr_t0 = clock64();
-            for (int n = 0; ok && n < ngroups; ++n) {
-                if (kg == 0 && tl + 1 < my_tiles) tile_n = a.tiles[blockIdx.x + (tl + 1) * gridDim.x];
-                if (n + 1 < ngroups) {
-                    if (kg + 1 < kgs) issue(tile_c, kg + 1, nxt);
-                    else issue(tile_n, 0, nxt);
+            while (ok && have_c) {
+                bool more = true;  // a group follows this one
+                if (kg + 1 < kgs) {
+                    issue(tile_c, kg + 1, nxt);
+                } else {
+                    have_n = next_tile(tn, tile_n);
+                    if (have_n) issue(tile_n, 0, nxt);
+                    more = have_n;
                 }
     #pragma unroll
                 for (int sub = 0; sub < 2; ++sub, ++it) {
                     const int s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (HELP && it >= STAGES) help_until((it - STAGES) / khs);
                     ok = ok && TRACE_WAIT(tr_w, warp_wait(smem_u32(&empty_bar[s]), ph ^ 1));
                     if (ok) {
                         dequant_store<Q>(cur, sub, stage0 + s * STAGE_BYTES + op * SUB_BYTES, rtl, lane);
                         warp_arrive(smem_u32(&full_bar[s]));
                     }
                 }
-                if (n + 1 < ngroups) cur = nxt;
+                if (more) cur = nxt;
                 if (++kg == kgs) {
                     kg = 0;
-                    ++tl;
                     tile_c = tile_n;
+                    have_c = have_n;
+                    have_n = false;
                 }
             }
             if (pw == 0 && lane == 0) {
@@ -494,7 +515,22 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             (void)tr_w;
             (void)tr_t0;
         }
-        help_until(all_tiles);  // (TMA-fed weights: nothing was dequantised, every tile is still to do)
+        if constexpr (HELP) {
+            // TMA-fed weights, one accumulator set: nothing to dequantise, the warp takes a share of
+            // every tile's epilogue instead
+            int4 tile;
+            for (int helped = 0; ok && next_tile(tn, tile); ++helped) {
+                ok = mbar_wait(smem_u32(&acc_full_bar[0]), helped & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                epilogue_part(tile, 0, 0, EPI_WARPS / 4 + (pw >> 2), EPI_PARTS);
+                tc_fence_before();
+                mbar_arrive(smem_u32(&acc_empty_bar[0]));
+            }
+        }
+        (void)warp_wait;
+        (void)warp_arrive;
+        (void)tile_ptrs;
     } else if (warp < MMA_WARP) {
         // ------------------------- activation producers ------------------------
         // One thread feeds the activation operand with TMA: per 64-input stage one or two
@@ -502,16 +538,16 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         // in the SWIZZLE_128B layout the MMA descriptor expects; completion is counted in
         // bytes on the stage's full barrier.
         if (lane == 0) {
-            const int my_tiles = (ntiles > (int)blockIdx.x) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-            const int nitems = my_tiles * khs;
             const uint64_t tmap_addr = reinterpret_cast<uint64_t>(&a.tmap);
             const uint64_t tmap_a_addr = reinterpret_cast<uint64_t>(&a.tmap_a);
             int row0 = 0, nbox = 1, arow0 = 0;
             bool ok = true;
-            for (int n = 0; ok && n < nitems; ++n) {
+            int tn = 0;
+            for (int n = 0; ok; ++n) {
                 const int kh = n % khs;
                 if (kh == 0) {
-                    const int4 tile = a.tiles[blockIdx.x + (n / khs) * gridDim.x];
+                    int4 tile;
+                    if (!next_tile(tn, tile)) break;
                     row0 = tile.y;
                     nbox = (BN > 128 && tile.z > 128) ? 2 : 1;
                     arow0 = tile.x * a.a_rows_exp + tile.w * (MODE == 0 ? 128 : 256);
@@ -543,7 +579,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp == MMA_WARP) {
         // -------------------------------- MMA ---------------------------------
         if (lane == 0) {
             int it = 0, tl = 0;
@@ -551,8 +587,9 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             long long tr_wf = 0, tr_wa = 0;
             const long long tr_t0 = clock64();
             int v = 0;  // accumulator sets taken so far (see the epilogue)
-            for (int ti = blockIdx.x; ok && ti < ntiles; ti += gridDim.x, ++tl) {
-                const int4 tile = a.tiles[ti];
+            int tn = 0;
+            int4 tile;
+            for (; ok && next_tile(tn, tile); ++tl) {
                 const int n16 = (tile.z + 15) & ~15;
                 // down: D[128 tokens, 256 output rows] = X[128, k] W[256, k]^T, the two adjacent 128-row
                 // weight operands of a stage forming one 256-row N operand; a tile of more than 128
@@ -568,6 +605,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 const uint32_t acc0 = tmem_base + (v % NACC) * ACC_COLS, acc1 = tmem_base + ((v + 1) % NACC) * ACC_COLS;
                 for (int kh = 0; kh < khs; ++kh, ++it) {
                     const int s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (kh == go_kh) mbar_arrive(smem_u32(&sched_go_bar));  // the CTA's next tile may be claimed now
                     ok = TRACE_WAIT(tr_wf, mbar_wait(smem_u32(&full_bar[s]), ph, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
@@ -602,6 +640,22 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             (void)tr_wf;
             (void)tr_wa;
             (void)tr_t0;
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------ scheduler ------------------------------
+        if (lane == 0) {
+            for (int n = 0;; ++n) {
+                const int slot = n % SCHED_RING;
+                // tile n >= 1 is claimed once the MMA thread is far enough into tile n - 1 (the thread
+                // cannot get two tiles ahead of this wait: tile n is not handed out before it)
+                if (n > 0 && !mbar_wait(smem_u32(&sched_go_bar), (n - 1) & 1, abort_flag)) break;
+                if (!mbar_wait(smem_u32(&sched_empty_bar[slot]), ((n / SCHED_RING) & 1) ^ 1, abort_flag)) break;
+                const int t = (n == 0) ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(a.n_tiles + 2 + MODE, 1);
+                sched_tile_s[slot] = (t < ntiles) ? a.tiles[t] : make_int4(0, 0, -1, 0);  // columns < 0: no more tiles
+                mbar_arrive(smem_u32(&sched_full_bar[slot]));
+                if (t >= ntiles) break;
+            }
         }
         __syncwarp();
     }

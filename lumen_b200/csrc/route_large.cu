@@ -406,6 +406,8 @@ sort_scan_kernel(int nchunks, int E, RouteDev R, int tile_cols, int tile_cols_dn
             *R.n_uexp = inz;
             n_tiles[0] = min(itl * mt_gu, max_tiles_gu);
             n_tiles[1] = min(itd * mt_dn, max_tiles_dn);
+            n_tiles[2] = 0;  // tile counters of the two grouped products (tiles are claimed dynamically)
+            n_tiles[3] = 0;
         }
     }
     __syncthreads();

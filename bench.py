@@ -538,7 +538,12 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    build.build()
+    # one rank brings the library up to date (a no-op when it is newer than its sources); the
+    # others must not load a file that is being rewritten
+    if rank == 0:
+        build.build()
+    if world > 1:
+        dist.barrier()
     quant, T, L = QUANTS[args.quant], args.tokens, args.layers
     lay = synth.LayerLayout(H, I, E, quant)
     scratch = moe.allocate_moe_scratch(H, I, E, K, 16, device=local)

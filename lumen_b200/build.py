@@ -54,9 +54,17 @@ def build(verbose: bool = False, force: bool = False) -> Path:
             jobs.append(cmd)
 
     def run(cmd):
-        r = subprocess.run(cmd, capture_output=True, text=True)
+        # Outputs are written under a private name and renamed into place: a process that loads
+        # the library (or another build running at the same time) never sees a half-written file.
+        out = Path(cmd[cmd.index("-o") + 1])
+        tmp = out.with_name(f".{out.name}.{os.getpid()}.tmp")
+        real = list(cmd)
+        real[real.index("-o") + 1] = str(tmp)
+        r = subprocess.run(real, capture_output=True, text=True)
         if r.returncode != 0:
+            tmp.unlink(missing_ok=True)
             raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+        os.replace(tmp, out)
         return r.stderr
 
     if jobs:

@@ -12,7 +12,7 @@ namespace lumen {
 enum Quant : int { Q8_0 = 0, Q4_0 = 1, BF16 = 2 };
 
 constexpr int MAX_EXPERTS = 256;  // cuda/shaders/moe_router.cu:33
-// Columns per tile of the tcgen05 gate/up product (the down product always uses 128): 256 once the
+// Columns per tile of the tcgen05 gate/up product (the down tiles of a one-GPU call follow it): 256 once the
 // experts average more than 128 columns (each dequantised weight tile then serves twice the
 // columns), else 128 (fewer empty columns in ragged tiles, epilogue overlapped).
 inline int tc_gu_tile_cols(int columns, int experts) { return (columns > 128 * experts) ? 256 : 128; }

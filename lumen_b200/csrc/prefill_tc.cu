@@ -218,7 +218,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     // of the list not yet taken by any CTA (a device-wide counter). One thread claims a tile while the
     // MMA thread is still inside the tile before it, and passes the descriptor to the roles through
     // this ring. (With tiles dealt round-robin the slowest CTA of a Zipf-loaded 4096-token call ran
-    // 11 % longer than the average one in gate/up and 8 % in down.)
+    // 11 % longer than the median one in gate/up and 13 % in down.)
     __shared__ int4 sched_tile_s[SCHED_RING];
     __shared__ uint64_t sched_full_bar[SCHED_RING], sched_empty_bar[SCHED_RING], sched_go_bar;
 

@@ -184,31 +184,36 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
     // Two 128-row weight operands share every activation stage (gate and up rows of the
     // same I range; two adjacent row tiles of the down matrix): the activation operand,
     // which comes from L2 at 2 bytes per element, is then read at half the rate.
-    // 256-column tiles (gate/up once the experts average more than 128 columns): the two
-    // 256-column f32 accumulators fill TMEM (512 columns), one accumulator set, the epilogue
-    // of a tile is not overlapped with the next tile's MMAs (its producers do run ahead);
-    // each dequantised weight tile serves 256 columns, and with K = H the main loop is long.
+    // 256-column tiles (gate/up once the experts average more than 128 columns): each dequantised
+    // weight tile serves 256 columns, and with K = H the main loop is long; the two 256-column f32
+    // accumulators of a full tile fill TMEM (512 columns), so its epilogue is not overlapped with
+    // the next tile's MMAs (its producers do run ahead).
     // 128-column tiles (down: K = I is short, 12 stages at I = 768, so the epilogue weighs
     // more; gate/up of small batches: fewer empty columns): TWO accumulator sets, the
     // epilogue of tile i runs under the MMAs of tile i+1.
     constexpr int NA = 2;
     // BN: columns per tile
-    // Accumulator sets in TMEM (512 columns). Gate/up: a set is the gate and the up accumulator of BN
-    // columns each, so 128-column tiles have two sets and 256-column tiles one. Down: a set is 256
-    // columns (the output rows of an m-tile) for 128 tokens, always two of them; a 256-token tile of
+    // Accumulator sets in TMEM (512 columns), always two.
+    // Down: a set is 256 columns (the output rows of an m-tile) for 128 tokens; a 256-token tile of
     // the BN = 256 form takes both at once (its two token halves, one weight stage serving both),
     // a tile of up to 128 tokens takes one, and the epilogue works through the halves one by one.
-    constexpr int NACC = (MODE == 1 || BN == 128) ? 2 : 1;
-    constexpr int ACC_COLS = (MODE == 1) ? 256 : NA * BN;  // TMEM columns of one set
-    // With one accumulator set the tensor pipe idles during a tile's epilogue. When the weights come
+    // Gate/up, BN = 128: a set is the gate and the up accumulator side by side (2 x 128 columns).
+    // Gate/up, BN = 256: the gate accumulator lives in TMEM columns 0..255 and the up accumulator in
+    // 256..511; a tile of up to 128 columns (the last chunk of most experts under skewed loads) takes
+    // one HALF of each (set s: columns 128 s.. of both), so two such tiles are in flight and the
+    // epilogue of one runs under the MMAs of the next; a wider tile takes both sets at once.
+    constexpr int NACC = 2;
+    constexpr bool WIDE_GU = (MODE == 0 && BN == 256);
+    constexpr int ACC_COLS = WIDE_GU ? 128 : 256;  // TMEM columns from one set to the next
+    // While a wide gate/up tile holds both sets the tensor pipe idles during its epilogue. When the weights come
     // by TMA the producer warps have nothing else to do and share the epilogue. (Dequantising
     // producers doing the same was measured slower, 0.52 -> 0.60 ms per 4096-token Q4_0 call: their
     // own work is what those kernels wait for; the same again for the 256-token down tiles, whose
     // epilogue between two such tiles is exposed too: Q4_0 0.463 -> 0.498 ms, Q8_0 and BF16 unchanged.)
-    constexpr bool HELP = (NACC == 1) && ATMA;
+    constexpr bool HELP = WIDE_GU && ATMA;
     constexpr int STAGES = StagesOf<Q, BN, ATMA, STG>::value;  // one stage = 64 inputs (one swizzle atom in K)
     constexpr int STAGE_BYTES = NA * SUB_BYTES + BN * 128;  // A operands then B
-    constexpr int TMEM_COLS = ACC_COLS * NACC;
+    constexpr int TMEM_COLS = 512;
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full_bar[NACC], acc_empty_bar[NACC];
@@ -413,6 +418,23 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         }
     };
     constexpr int EPI_PARTS = EPI_WARPS / 4 + (HELP ? A_WARPS / 4 : 0);  // groups of four warps sharing a tile's epilogue
+    // A warp's share of one tile's epilogue. v: accumulator sets handed over so far (set v % NACC, used
+    // v / NACC times before). A tile of more than 128 columns holds both sets: the down product works
+    // through them one after the other (its two token halves), gate/up reads them as one tile.
+    auto epilogue_tile = [&](const int4& tile, int& v, int part) -> bool {
+        const int nsets = (tile.z > 128) ? 2 : 1;
+        const int passes = (MODE == 1) ? nsets : 1, per_pass = (MODE == 1) ? 1 : nsets;
+        for (int h = 0; h < passes; ++h) {
+            for (int j = 0; j < per_pass; ++j)
+                if (!mbar_wait(smem_u32(&acc_full_bar[(v + j) % NACC]), ((v + j) / NACC) & 1, abort_flag)) return false;
+            tc_fence_after();
+            epilogue_part(tile, per_pass == 2 ? 0 : v % NACC, h, part, EPI_PARTS);
+            tc_fence_before();
+            for (int j = 0; j < per_pass; ++j) mbar_arrive(smem_u32(&acc_empty_bar[(v + j) % NACC]));
+            v += per_pass;
+        }
+        return true;
+    };
 
     if (warp < EPI_WARPS) {
         // ------------------------------ epilogue ------------------------------
@@ -420,18 +442,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
         bool ok = true;
         int tn = 0;
         int4 tile;
-        while (ok && next_tile(tn, tile)) {
-            const int nh = (MODE == 1 && tile.z > 128) ? 2 : 1;
-            for (int h = 0; ok && h < nh; ++h, ++v) {
-                const int ab = v % NACC, use = v / NACC;
-                ok = mbar_wait(smem_u32(&acc_full_bar[ab]), use & 1, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                epilogue_part(tile, ab, h, warp >> 2, EPI_PARTS);
-                tc_fence_before();
-                mbar_arrive(smem_u32(&acc_empty_bar[ab]));
-            }
-        }
+        while (ok && next_tile(tn, tile)) ok = epilogue_tile(tile, v, warp >> 2);
         if constexpr (STG) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // every row has been written
     } else if (warp < B_WARP0) {
         // --------------------------- weight producers --------------------------
@@ -519,14 +530,8 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
             // TMA-fed weights, one accumulator set: nothing to dequantise, the warp takes a share of
             // every tile's epilogue instead
             int4 tile;
-            for (int helped = 0; ok && next_tile(tn, tile); ++helped) {
-                ok = mbar_wait(smem_u32(&acc_full_bar[0]), helped & 1, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                epilogue_part(tile, 0, 0, EPI_WARPS / 4 + (pw >> 2), EPI_PARTS);
-                tc_fence_before();
-                mbar_arrive(smem_u32(&acc_empty_bar[0]));
-            }
+            int v = 0;
+            while (ok && next_tile(tn, tile)) ok = epilogue_tile(tile, v, EPI_WARPS / 4 + (pw >> 2));
         }
         (void)warp_wait;
         (void)warp_arrive;
@@ -595,7 +600,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
                 // weight operands of a stage forming one 256-row N operand; a tile of more than 128
                 // tokens is two such products per 16 inputs, into two accumulator sets
                 const uint32_t idesc = make_idesc(MODE == 1 ? 256 : n16, bf16_mode);
-                const int nh = (MODE == 1 && tile.z > 128) ? 2 : 1;
+                const int nh = (tile.z > 128) ? 2 : 1;  // accumulator sets of the tile
                 for (int h = 0; ok && h < nh; ++h) {
                     const int ab = (v + h) % NACC, use = (v + h) / NACC;
                     ok = TRACE_WAIT(tr_wa, mbar_wait(smem_u32(&acc_empty_bar[ab]), (use & 1) ^ 1, abort_flag));
@@ -623,7 +628,7 @@ grouped_gemm_tc_kernel(const __grid_constant__ Args a) {
 #pragma unroll
                             for (int op = 0; op < NA; ++op) {
                                 const uint64_t adesc = make_desc(sbase + op * SUB_BYTES + j * 32);
-                                umma(acc0 + op * BN, adesc, bdesc, idesc, acc);
+                                umma((nh == 2 ? tmem_base : acc0) + op * BN, adesc, bdesc, idesc, acc);
                             }
                         }
                     }
